@@ -1,0 +1,192 @@
+/*
+ * lspk_sm100.h -- C ABI of the sm_100a (B200) ternary-matmul library.
+ *
+ * Two groups of entry points:
+ *
+ *  (1) HOST-POINTER DROP-INS.  Same names, argument order and meaning as the symbols the
+ *      reference's ctypes loader binds (litespark_inference/torchless/kernel.py:227-322),
+ *      with the architecture tag `sm100` in place of `avx512` / `avx2` / `neon`.  Every
+ *      pointer is a host pointer; the call copies inputs to the GPU, runs the CUDA kernel,
+ *      copies the result back and returns when the result is in host memory.  Like the
+ *      reference they return void / a value; a failure is recorded and can be read with
+ *      lspk_last_error() / lspk_error_count().
+ *
+ *  (2) DEVICE-RESIDENT API.  Weights, activations and the KV cache live in GPU memory;
+ *      pointers are device pointers obtained from lspk_malloc (or any CUDA allocation of the
+ *      same context).  Every function returns an int status (0 = LSPK_OK).
+ *
+ * There is no CPU fallback: every entry point fails with LSPK_ERR_NO_DEVICE when no sm_100
+ * GPU is usable.
+ */
+#ifndef LSPK_SM100_H_
+#define LSPK_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    LSPK_OK = 0,
+    LSPK_ERR_ARG = 1,        /* bad shape / null pointer / unsupported size */
+    LSPK_ERR_CUDA = 2,       /* a CUDA runtime call failed; message has the detail */
+    LSPK_ERR_NO_DEVICE = 3,  /* no usable GPU */
+    LSPK_ERR_STATE = 4,      /* KV cache exhausted, model not finalised, ... */
+    LSPK_ERR_NCCL = 5,
+    LSPK_ERR_DEVICE_WAIT = 6 /* a bounded device-side wait ran out */
+};
+
+/* ------------------------------------------------------------------------------------ */
+/* Library state                                                                         */
+/* ------------------------------------------------------------------------------------ */
+int lspk_init(int device);              /* select the GPU for this process; idempotent   */
+int lspk_device_count(void);
+int lspk_sm_count(void);
+const char* lspk_last_error(void);      /* last recorded message ("" if none)            */
+int lspk_error_count(void);             /* number of failures recorded so far            */
+void lspk_clear_error(void);
+int lspk_set_pdl(int enabled);          /* programmatic dependent launch between kernels */
+int lspk_sync(void);                    /* wait for everything queued on the stream      */
+
+void* lspk_malloc(size_t bytes);        /* device memory; NULL on failure                */
+int lspk_free(void* dev);
+void* lspk_host_alloc(size_t bytes);    /* pinned host memory                            */
+int lspk_host_free(void* host);
+int lspk_h2d(void* dev, const void* host, size_t bytes);   /* stream-ordered, then waits */
+int lspk_d2h(void* host, const void* dev, size_t bytes);
+int lspk_h2d_async(void* dev, const void* host, size_t bytes);
+int lspk_d2h_async(void* host, const void* dev, size_t bytes);
+int lspk_memset(void* dev, int value, size_t bytes);
+int lspk_flush_l2(void);                /* overwrite a buffer larger than L2             */
+
+/* CUDA-event timer on the library's stream: start, enqueue work, stop -> milliseconds.   */
+int lspk_timer_start(void);
+int lspk_timer_stop(float* ms_out);
+
+/* ------------------------------------------------------------------------------------ */
+/* (a) Packed-weight upload: reference layout <-> device layout                          */
+/*     Reference layout: uint8 [N, K/4], byte = (w0+1)|(w1+1)<<2|(w2+1)<<4|(w3+1)<<6       */
+/*     (litespark_inference/torchless/pack.py:16-45; model.py:26-49 PackedProjection).    */
+/*     Plays the role the reference gives transpose_packed_to_amx_vnni                    */
+/*     (matmul_lut_avx512_extern_c.cpp:942-961): a load-time re-tiling for the hardware.  */
+/* ------------------------------------------------------------------------------------ */
+typedef struct lspk_weight_s* lspk_weight_t;
+lspk_weight_t lspk_upload_packed(const uint8_t* packed_host, int N, int K, float w_scale);
+int lspk_download_packed(lspk_weight_t w, uint8_t* packed_host_out);   /* exact inverse   */
+int lspk_weight_free(lspk_weight_t w);
+int lspk_weight_shape(lspk_weight_t w, int* N, int* K, float* scale, size_t* device_bytes);
+
+/* ------------------------------------------------------------------------------------ */
+/* (b)(c) Ternary GEMV / small-batch GEMM on device-resident data                         */
+/* ------------------------------------------------------------------------------------ */
+/* Prologue: what the kernel does to its input before the integer dot products.           */
+enum { LSPK_PRO_INT8 = 0,        /* x is int8 [M,K] with per-row fp32 scales (a5/a6 contract) */
+       LSPK_PRO_QUANT = 1,       /* x is fp32: per-token absmax int8 quantiser fused (a4)     */
+       LSPK_PRO_RMSNORM_QUANT = 2 /* x is fp32: RMSNorm(gamma, eps) then quantiser (a10)       */ };
+/* Epilogue: what happens to y = float(acc) * (x_scale * w_scale).                         */
+enum { LSPK_EPI_STORE = 0,       /* out = y                                               */
+       LSPK_EPI_ADD = 1,         /* out += y            (residual add, a12)                */
+       LSPK_EPI_RELU2_MUL = 2    /* two matrices (gate, up): out = max(g,0)^2 * u  (a11)   */ };
+
+typedef struct {
+    /* up to three matrices that share the input (q/k/v, or gate/up); rows are independent */
+    lspk_weight_t w[3];
+    float* out[3];               /* fp32 [M, N_i] row-major (RELU2_MUL: only out[0], [M,N])  */
+    int n_mats;
+    int M;                       /* token rows, 1..LSPK_MAX_GEMV_M for lspk_gemv           */
+    int prologue, epilogue;
+    const float* x_f32;          /* [M,K] for QUANT / RMSNORM_QUANT                         */
+    const int8_t* x_i8;          /* [M,K] for INT8                                          */
+    const float* x_scales;       /* [M] device array for INT8                               */
+    const void* gamma;           /* [K] bf16 bits (uint16) or fp32 for RMSNORM_QUANT        */
+    int gamma_is_bf16;
+    float eps;
+    /* optional taps for parity tests (may be NULL) */
+    int32_t* acc_out[3];         /* int32 [M, N_i]: the exact integer accumulators          */
+    int8_t* xq_out;              /* int8 [M,K]: the quantised activations the kernel used   */
+    float* xscale_out;           /* fp32 [M]                                                */
+} lspk_linear_args;
+
+#define LSPK_MAX_GEMV_M 8
+/* Replaces matmul_lut_{tag}_m1 / _mT (matmul_lut_avx512_extern_c.cpp:150-236, 258-339) plus
+ * the helpers fused around them.  Any M >= 1: rows are processed in tiles of up to
+ * LSPK_MAX_GEMV_M tokens by the CUDA-core kernel; lspk_linear picks the tcgen05 tensor-core
+ * GEMM instead when M is large enough and the shape allows it. */
+int lspk_linear(const lspk_linear_args* a);
+int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tcgen05 only */
+
+/* ------------------------------------------------------------------------------------ */
+/* Element-wise helpers on device-resident rows (batched over T rows)                     */
+/* ------------------------------------------------------------------------------------ */
+int lspk_quantize_rows(const float* x, int8_t* out, float* scales, int T, int K);           /* a4  */
+int lspk_rmsnorm_rows(const float* x, const void* gamma, int gamma_is_bf16, float* out,
+                      int T, int K, float eps);                                              /* a9  */
+int lspk_rmsnorm_quantize_rows(const float* x, const void* gamma, int gamma_is_bf16,
+                               int8_t* out, float* scales, int T, int K, float eps);         /* a10 */
+int lspk_relu2_mul_rows(const float* gate, const float* up, float* out, int T, int K);      /* a11 */
+int lspk_add_rows(float* a, const float* b, size_t n);                                       /* a12 */
+
+/* LM head GEMV on device-resident rows; kind: 0 bf16, 1 int8 (+scale), 2 int4 (+scale). a13 */
+int lspk_lm_head(int kind, const void* emb, const float* emb_scale, const float* x,
+                 float* logits, int T, int V, int H);
+
+/* ------------------------------------------------------------------------------------ */
+/* Host-pointer drop-ins (tag sm100).  kernel.py line of the binding each one replaces:   */
+/* ------------------------------------------------------------------------------------ */
+/* kernel.py:234-236  matmul_lut_{T}_m1 */
+void matmul_lut_sm100_m1(const int8_t* x, const uint8_t* packed_w, float w_scale, float x_scale,
+                         float* y, int N, int K);
+/* kernel.py:247-251  matmul_lut_{T}_mT (x86 argument order).  Any T >= 1: the reference's
+ * x86 kernel silently does nothing for T > 64 (matmul_lut_avx512_extern_c.cpp:266); this one
+ * computes every row. */
+void matmul_lut_sm100_mT(const int8_t* x, const float* x_scales, const uint8_t* packed_w,
+                         float w_scale, float* y, int T, int N, int K);
+/* kernel.py:252-256  matmul_lut_{T}_prefill (arm argument order) */
+void matmul_lut_sm100_prefill(const int8_t* x, const uint8_t* packed_w, float w_scale,
+                              const float* x_scale, float* y, int M, int N, int K);
+/* kernel.py:295-297, 289-291 */
+float quantize_activation_sm100(const float* x, int8_t* out, int K);
+void quantize_activation_batched_sm100(const float* x, int8_t* out, float* scales, int T, int K);
+/* kernel.py:307-312, 283-288 */
+void rmsnorm_bf16gamma_fp32_sm100(const float* x, const uint16_t* gamma, float* out, int K, float eps);
+void rmsnorm_fp32gamma_fp32_sm100(const float* x, const float* gamma, float* out, int K, float eps);
+void rmsnorm_bf16gamma_fp32_batched_sm100(const float* x, const uint16_t* gamma, float* out,
+                                          int T, int K, float eps);
+void rmsnorm_fp32gamma_fp32_batched_sm100(const float* x, const float* gamma, float* out,
+                                          int T, int K, float eps);
+/* kernel.py:273-279.  `tmp` (caller scratch in the reference) is accepted and left untouched. */
+float rmsnorm_quantize_bf16gamma_sm100(const float* x, const uint16_t* gamma, int8_t* out_i8,
+                                       float* tmp, int K, float eps);
+void rmsnorm_quantize_bf16gamma_batched_sm100(const float* x, const uint16_t* gamma, int8_t* out_i8,
+                                              float* scales, float* tmp, int T, int K, float eps);
+/* kernel.py:313-315, 292-294 */
+void relu2_mul_fp32_sm100(const float* gate, const float* up, float* out, int K);
+void relu2_mul_fp32_batched_sm100(const float* gate, const float* up, float* out, int T, int K);
+/* kernel.py:316-318 */
+void add_inplace_fp32_sm100(float* a, const float* b, int K);
+/* kernel.py:298-306 */
+void lm_head_bf16_fp32_sm100(const uint16_t* emb, const float* x, float* logits, int V, int H);
+void lm_head_int8_fp32_sm100(const int8_t* emb, const float* emb_scale, const float* x,
+                             float* logits, int V, int H);
+void lm_head_int4_fp32_sm100(const uint8_t* emb, const float* emb_scale, const float* x,
+                             float* logits, int V, int H);
+/* kernel.py:319-320.  has_omp reports 0 (no OpenMP anywhere); max_threads reports the SM count. */
+int matmul_lut_sm100_has_omp(void);
+int matmul_lut_sm100_max_threads(void);
+
+/* Weight residency for the drop-ins.  By default a drop-in uploads the packed matrix (or the
+ * embedding) on every call.  Registering a host buffer keeps a device copy keyed by its
+ * address: later drop-in calls given the same pointer and shape skip the upload.  The caller
+ * promises not to modify a registered buffer.  (No counterpart in the reference, whose
+ * kernels read host memory directly.) */
+int lspk_register_packed(const uint8_t* packed_host, int N, int K);
+int lspk_register_embedding(int kind, const void* emb_host, const float* emb_scale_host, int V, int H);
+int lspk_unregister(const void* host_ptr);
+int lspk_unregister_all(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LSPK_SM100_H_ */

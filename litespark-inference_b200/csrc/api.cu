@@ -1,0 +1,192 @@
+// Library state: device selection, stream, sticky error record, memory and timing helpers.
+#include <stdarg.h>
+#include <string.h>
+#include <stdlib.h>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lspk {
+
+static std::mutex g_mu;
+static char g_err[1024] = "";
+static int g_err_count = 0;
+static int g_device = -1;
+static int g_sm_count = 0;
+static cudaStream_t g_stream = nullptr;
+static bool g_pdl = true;
+static cudaEvent_t g_ev0 = nullptr, g_ev1 = nullptr;
+static void* g_flush_buf = nullptr;
+static const size_t kFlushBytes = 256u << 20;   // twice the 126 MB L2
+
+void set_error(const char* fmt, ...) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    ++g_err_count;
+}
+
+int fail(int code, const char* fmt, ...) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    ++g_err_count;
+    return code;
+}
+
+cudaStream_t stream() { return g_stream; }
+bool pdl_enabled() { return g_pdl; }
+int sm_count() { return g_sm_count; }
+
+// Lazily bind to a device the first time any entry point needs one.
+int ensure_init() {
+    if (g_device >= 0) return LSPK_OK;
+    const char* env = getenv("LITESPARK_DEVICE");
+    return lspk_init(env ? atoi(env) : 0);
+}
+
+}  // namespace lspk
+
+using namespace lspk;
+
+extern "C" {
+
+int lspk_init(int device) {
+    if (g_device == device && g_stream) return LSPK_OK;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        return fail(LSPK_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (device < 0 || device >= n) return fail(LSPK_ERR_ARG, "device %d out of range (have %d)", device, n);
+    cudaDeviceProp prop;
+    LSPK_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(LSPK_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
+                    device, prop.major, prop.minor);
+    LSPK_CUDA(cudaSetDevice(device));
+    if (g_stream && g_device != device) {
+        return fail(LSPK_ERR_STATE, "library already bound to device %d", g_device);
+    }
+    LSPK_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
+    LSPK_CUDA(cudaEventCreate(&g_ev0));
+    LSPK_CUDA(cudaEventCreate(&g_ev1));
+    g_sm_count = prop.multiProcessorCount;
+    g_device = device;
+    const char* p = getenv("LITESPARK_PDL");
+    if (p) g_pdl = atoi(p) != 0;
+    return LSPK_OK;
+}
+
+int lspk_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+    return n;
+}
+
+int lspk_sm_count(void) { return ensure_init() == LSPK_OK ? g_sm_count : 0; }
+
+const char* lspk_last_error(void) { return g_err; }
+int lspk_error_count(void) { return g_err_count; }
+void lspk_clear_error(void) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_err[0] = 0;
+    g_err_count = 0;
+}
+
+int lspk_set_pdl(int enabled) {
+    g_pdl = enabled != 0;
+    return LSPK_OK;
+}
+
+int lspk_sync(void) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_CUDA(cudaStreamSynchronize(g_stream));
+    return LSPK_OK;
+}
+
+void* lspk_malloc(size_t bytes) {
+    if (ensure_init()) return nullptr;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+    if (e != cudaSuccess) {
+        fail(LSPK_ERR_CUDA, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+        return nullptr;
+    }
+    return p;
+}
+
+int lspk_free(void* dev) {
+    if (!dev) return LSPK_OK;
+    LSPK_CUDA(cudaFree(dev));
+    return LSPK_OK;
+}
+
+void* lspk_host_alloc(size_t bytes) {
+    if (ensure_init()) return nullptr;
+    void* p = nullptr;
+    cudaError_t e = cudaMallocHost(&p, bytes ? bytes : 16);
+    if (e != cudaSuccess) {
+        fail(LSPK_ERR_CUDA, "cudaMallocHost(%zu) failed: %s", bytes, cudaGetErrorString(e));
+        return nullptr;
+    }
+    return p;
+}
+
+int lspk_host_free(void* host) {
+    if (!host) return LSPK_OK;
+    LSPK_CUDA(cudaFreeHost(host));
+    return LSPK_OK;
+}
+
+int lspk_h2d_async(void* dev, const void* host, size_t bytes) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, g_stream));
+    return LSPK_OK;
+}
+int lspk_d2h_async(void* host, const void* dev, size_t bytes) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, g_stream));
+    return LSPK_OK;
+}
+int lspk_h2d(void* dev, const void* host, size_t bytes) {
+    if (int rc = lspk_h2d_async(dev, host, bytes)) return rc;
+    LSPK_CUDA(cudaStreamSynchronize(g_stream));
+    return LSPK_OK;
+}
+int lspk_d2h(void* host, const void* dev, size_t bytes) {
+    if (int rc = lspk_d2h_async(host, dev, bytes)) return rc;
+    LSPK_CUDA(cudaStreamSynchronize(g_stream));
+    return LSPK_OK;
+}
+int lspk_memset(void* dev, int value, size_t bytes) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_CUDA(cudaMemsetAsync(dev, value, bytes, g_stream));
+    return LSPK_OK;
+}
+
+int lspk_flush_l2(void) {
+    if (int rc = ensure_init()) return rc;
+    if (!g_flush_buf) LSPK_CUDA(cudaMalloc(&g_flush_buf, kFlushBytes));
+    static int v = 0;
+    LSPK_CUDA(cudaMemsetAsync(g_flush_buf, ++v & 0xff, kFlushBytes, g_stream));
+    return LSPK_OK;
+}
+
+int lspk_timer_start(void) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_CUDA(cudaEventRecord(g_ev0, g_stream));
+    return LSPK_OK;
+}
+int lspk_timer_stop(float* ms_out) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_CUDA(cudaEventRecord(g_ev1, g_stream));
+    LSPK_CUDA(cudaEventSynchronize(g_ev1));
+    LSPK_CUDA(cudaEventElapsedTime(ms_out, g_ev0, g_ev1));
+    return LSPK_OK;
+}
+
+}  // extern "C"

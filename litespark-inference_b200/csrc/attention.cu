@@ -1,0 +1,216 @@
+// RoPE + KV-cache write + causal grouped-query attention on device-resident rows.
+//
+// Replaces the numpy section of the reference's forward pass: apply_rope / rope tables
+// (litespark_inference/torchless/ops.py:40-67), the cache write and the
+// scores -> softmax -> weighted sum of runtime.py:224-245 (decode) and :381-407 (prefill).
+// Arithmetic order follows the reference: split-half rotation with separately rounded
+// products, scores scaled by 1/sqrt(D) after the dot product, max-subtracted softmax,
+// probabilities normalised before the V product.  Query head h reads KV head h / (Q / KV).
+//
+// Cache layout is the reference's: [layer][position][kv_head][D], in fp32 or fp16.
+#include "internal.cuh"
+
+namespace lspk {
+
+constexpr int kAttnThreads = 256;
+constexpr int kAttnWarps = kAttnThreads / 32;
+
+template <typename KVT> __device__ __forceinline__ float kv_load(const KVT* p);
+template <> __device__ __forceinline__ float kv_load<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float kv_load<__half>(const __half* p) { return __half2float(*p); }
+template <typename KVT> __device__ __forceinline__ KVT kv_make(float v);
+template <> __device__ __forceinline__ float kv_make<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half kv_make<__half>(float v) { return __float2half_rn(v); }
+template <typename KVT> __device__ __forceinline__ float kv_round(float v);
+template <> __device__ __forceinline__ float kv_round<float>(float v) { return v; }
+template <> __device__ __forceinline__ float kv_round<__half>(float v) { return __half2float(__float2half_rn(v)); }
+
+__device__ __forceinline__ float rope_elem(const float* row, int d, int half, const float* cos_row,
+                                           const float* sin_row) {
+    const int i = d < half ? d : d - half;
+    const float x1 = row[i], x2 = row[half + i];
+    const float c = cos_row[i], s = sin_row[i];
+    return d < half ? __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s))
+                    : __fadd_rn(__fmul_rn(x1, s), __fmul_rn(x2, c));
+}
+
+
+// Rotate q in place and write rotated k and raw v into the cache, for T rows.
+template <typename KVT>
+__global__ void __launch_bounds__(kAttnThreads) rope_store_kernel(const AttnParams p) {
+    grid_dependency_launch();
+    grid_dependency_wait();
+    extern __shared__ __align__(16) float rs_smem[];     // (Q + KV) * D raw q and k of this row
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int pos = p.pos_per_row ? p.pos_ptr[t] : p.pos_ptr[0] + t;
+    const int D = p.D, half = D / 2;
+    const int qd = p.Q * D, kd = p.KV * D;
+    float* qrow = p.q + (size_t)t * qd;
+    const float* krow = p.k_cur + (size_t)t * kd;
+    const float* vrow = p.v_cur + (size_t)t * kd;
+    for (int i = tid; i < qd; i += kAttnThreads) rs_smem[i] = qrow[i];
+    for (int i = tid; i < kd; i += kAttnThreads) rs_smem[qd + i] = krow[i];
+    __syncthreads();
+    const float* cr = p.rope_cos + (size_t)pos * half;
+    const float* sr = p.rope_sin + (size_t)pos * half;
+    for (int i = tid; i < qd; i += kAttnThreads) {
+        const int hd = i / D, d = i % D;
+        qrow[i] = rope_elem(rs_smem + hd * D, d, half, cr, sr);
+    }
+    KVT* ck = reinterpret_cast<KVT*>(p.cache_k) + (size_t)t * p.cache_seq_stride + (size_t)pos * kd;
+    KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride + (size_t)pos * kd;
+    for (int i = tid; i < kd; i += kAttnThreads) {
+        const int hd = i / D, d = i % D;
+        ck[i] = kv_make<KVT>(rope_elem(rs_smem + qd + hd * D, d, half, cr, sr));
+        cv[i] = kv_make<KVT>(vrow[i]);
+    }
+}
+
+// One CTA per (query head, row).  EPL = D / 32 elements of the head dimension per lane.
+template <typename KVT, int EPL>
+__global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
+    constexpr int D = EPL * 32;
+    extern __shared__ __align__(16) float at_smem[];
+    float* qs = at_smem;                  // [D] rotated query
+    float* ks = qs + D;                   // [D] rotated current key (fused mode)
+    float* vs = ks + D;                   // [D] current value (fused mode)
+    float* raw = vs + D;                  // [2*D] raw q and k before rotation (fused mode)
+    float* acc_w = raw + 2 * D;           // [warps][D]
+    float* sc = acc_w + kAttnWarps * D;   // [n] scores / probabilities
+    __shared__ float red[32];
+
+    grid_dependency_launch();
+    grid_dependency_wait();
+
+    const int h = blockIdx.x, t = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.Q / p.KV, kvh = h / G;
+    const int pos = p.pos_per_row ? p.pos_ptr[t] : p.pos_ptr[0] + t;
+    const int n = pos + 1;
+    const int half = D / 2;
+    const int kd = p.KV * D;
+    KVT* ck = reinterpret_cast<KVT*>(p.cache_k) + (size_t)t * p.cache_seq_stride;
+    KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride;
+    const float* qrow = p.q + (size_t)t * p.Q * D + (size_t)h * D;
+
+    if (p.fused) {
+        const float* krow = p.k_cur + (size_t)t * kd + (size_t)kvh * D;
+        const float* vrow = p.v_cur + (size_t)t * kd + (size_t)kvh * D;
+        if (tid < D) {
+            raw[tid] = qrow[tid];
+            raw[D + tid] = krow[tid];
+        }
+        __syncthreads();
+        if (tid < D) {
+            const float* cr = p.rope_cos + (size_t)pos * half;
+            const float* sr = p.rope_sin + (size_t)pos * half;
+            qs[tid] = rope_elem(raw, tid, half, cr, sr);
+            const float kr = rope_elem(raw + D, tid, half, cr, sr);
+            const float vr = vrow[tid];
+            ks[tid] = kv_round<KVT>(kr);
+            vs[tid] = kv_round<KVT>(vr);
+            if (h % G == 0) {
+                ck[(size_t)pos * kd + (size_t)kvh * D + tid] = kv_make<KVT>(kr);
+                cv[(size_t)pos * kd + (size_t)kvh * D + tid] = kv_make<KVT>(vr);
+            }
+        }
+    } else {
+        if (tid < D) qs[tid] = qrow[tid];
+    }
+    __syncthreads();
+
+    float qreg[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qreg[e] = qs[lane * EPL + e];
+    const float inv_sqrt_d = 1.0f / sqrtf((float)D);
+
+    // scores
+    for (int i = warp; i < n; i += kAttnWarps) {
+        float dot = 0.0f;
+        if (p.fused && i == pos) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) dot = fmaf(qreg[e], ks[lane * EPL + e], dot);
+        } else {
+            const KVT* kp = ck + (size_t)i * kd + (size_t)kvh * D + lane * EPL;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) dot = fmaf(qreg[e], kv_load<KVT>(kp + e), dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) sc[i] = __fmul_rn(dot, inv_sqrt_d);
+    }
+    __syncthreads();
+
+    // softmax over sc[0..n)
+    float mx = -INFINITY;
+    for (int i = tid; i < n; i += kAttnThreads) mx = fmaxf(mx, sc[i]);
+    mx = block_max(mx, red);
+    float sum = 0.0f;
+    for (int i = tid; i < n; i += kAttnThreads) {
+        const float e = expf(sc[i] - mx);
+        sc[i] = e;
+        sum += e;
+    }
+    sum = block_sum(sum, red);
+    for (int i = tid; i < n; i += kAttnThreads) sc[i] = __fdiv_rn(sc[i], sum);
+    __syncthreads();
+
+    // weighted sum of values
+    float o[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) o[e] = 0.0f;
+    for (int i = warp; i < n; i += kAttnWarps) {
+        const float pi = sc[i];
+        if (p.fused && i == pos) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) o[e] = fmaf(pi, vs[lane * EPL + e], o[e]);
+        } else {
+            const KVT* vp = cv + (size_t)i * kd + (size_t)kvh * D + lane * EPL;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) o[e] = fmaf(pi, kv_load<KVT>(vp + e), o[e]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc_w[warp * D + lane * EPL + e] = o[e];
+    __syncthreads();
+    if (tid < D) {
+        float r = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kAttnWarps; ++w) r += acc_w[w * D + tid];
+        p.out[(size_t)t * p.Q * D + (size_t)h * D + tid] = r;
+    }
+}
+
+template <typename KVT>
+static int attention_launch_t(const AttnParams& p) {
+    const int D = p.D;
+    const size_t smem = (size_t)(5 * D + kAttnWarps * D + p.t_max) * sizeof(float);
+    LSPK_REQUIRE(smem <= 200 * 1024, "attention: t_max=%d too large for the shared score buffer", p.t_max);
+    static bool attr_set = false;
+    if (!attr_set) {
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(rope_store_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_set = true;
+    }
+    if (!p.fused) {
+        const size_t rs = (size_t)(p.Q + p.KV) * D * sizeof(float);
+        LSPK_CUDA(launch(rope_store_kernel<KVT>, dim3(p.T), dim3(kAttnThreads), rs, true, p));
+    }
+    const dim3 grid(p.Q, p.T);
+    cudaError_t e;
+    if (D == 64) e = launch(attention_kernel<KVT, 2>, grid, dim3(kAttnThreads), smem, true, p);
+    else if (D == 128) e = launch(attention_kernel<KVT, 4>, grid, dim3(kAttnThreads), smem, true, p);
+    else e = launch(attention_kernel<KVT, 8>, grid, dim3(kAttnThreads), smem, true, p);
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
+    return LSPK_OK;
+}
+
+int attention_launch(const AttnParams& p, int kv_is_fp16) {
+    LSPK_REQUIRE(p.D == 64 || p.D == 128 || p.D == 256, "attention: head_dim must be 64, 128 or 256 (got %d)", p.D);
+    LSPK_REQUIRE(p.Q % p.KV == 0, "attention: num_heads must be a multiple of num_kv_heads");
+    LSPK_REQUIRE(!p.fused || p.T == 1 || p.pos_per_row, "attention: the fused form needs rows that do not attend to each other");
+    return kv_is_fp16 ? attention_launch_t<__half>(p) : attention_launch_t<float>(p);
+}
+
+}  // namespace lspk

@@ -1,0 +1,167 @@
+// Shared device/host helpers for the sm_100a ternary-matmul library.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/lspk_sm100.h"
+
+namespace lspk {
+
+// ---- sticky error state (host) -------------------------------------------------
+void set_error(const char* fmt, ...);
+int  fail(int code, const char* fmt, ...);          // records the message, returns code
+cudaStream_t stream();                              // the library's launch stream
+bool pdl_enabled();                                 // programmatic dependent launch on/off
+int  sm_count();
+int  ensure_init();                                 // bind to a GPU on first use
+
+#define LSPK_CUDA(expr)                                                              \
+    do {                                                                             \
+        cudaError_t _e = (expr);                                                     \
+        if (_e != cudaSuccess)                                                       \
+            return ::lspk::fail(LSPK_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,       \
+                                cudaGetErrorString(_e), __FILE__, __LINE__);         \
+    } while (0)
+
+#define LSPK_REQUIRE(cond, ...)                                                      \
+    do {                                                                             \
+        if (!(cond)) return ::lspk::fail(LSPK_ERR_ARG, __VA_ARGS__);                 \
+    } while (0)
+
+// ---- device layout of one ternary matrix ---------------------------------------
+// The reference stores uint8 [N, K/4], weight k of row n at bits 2*(k%4) of byte k/4.
+// On the device the same bytes are regrouped (no bit is changed) into 16-byte chunks
+// (64 weights) ordered [row-group of 16][chunk index along K][row within group], so that
+// 32 lanes reading "16 rows x 2 consecutive chunks" touch one contiguous 512-byte span.
+// Rows are padded to a multiple of 16 and K to a multiple of 64 with code 1 (weight 0).
+constexpr int kRowsPerGroup = 16;
+constexpr int kWeightsPerChunk = 64;
+
+struct Weight {
+    uint4* dev;        // [groups][chunks][16] chunks of 16 bytes
+    int N, K;          // logical shape
+    int groups;        // ceil(N / 16)
+    int chunks;        // ceil(K / 64)
+    float scale;       // per-tensor weight scale
+    size_t bytes;      // groups * chunks * 16 * 16
+};
+
+// ---- launch helper: optional programmatic dependent launch ----------------------
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          bool allow_pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    if (allow_pdl && pdl_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#ifdef __CUDACC__
+// ---- device helpers --------------------------------------------------------------
+
+// Wait until the kernels this launch depends on have completed and their writes are
+// visible.  A no-op when the launch carries no programmatic dependency.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Allow the next kernel in the stream to start launching (it still waits, in its own
+// grid_dependency_wait, for this grid to finish before touching what this grid writes).
+__device__ __forceinline__ void grid_dependency_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// 4-way byte dot product, unsigned a (weight codes) x signed b (activations), s32 accumulate.
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {
+    return __uint_as_float(((uint32_t)b) << 16);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide reductions.  `red` is a shared array of at least 32 elements; every thread
+// of the block must call; the result is returned to every thread.  Two barriers each, so
+// the same `red` can be reused by consecutive calls.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : 0.0f;
+    r = warp_sum(r);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ int block_sum(int v, int* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    int r = (lane < nw) ? red[lane] : 0;
+    r = warp_sum(r);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : -INFINITY;
+    r = warp_max(r);
+    __syncthreads();
+    return r;
+}
+
+// Per-token absmax int8 quantiser, the arithmetic of the reference's vector path
+// (quantize_activation_avx512, matmul_lut_avx512_extern_c.cpp:443-456): every step is a
+// single correctly rounded fp32 operation, round-half-even conversion, saturation to
+// [-128, 127].
+__device__ __forceinline__ float quant_scale_from_absmax(float absmax) {
+    if (absmax < 1e-5f) absmax = 1e-5f;
+    return __fdiv_rn(absmax, 127.0f);
+}
+__device__ __forceinline__ int quant_one(float v, float inv_scale) {
+    int q = __float2int_rn(__fmul_rn(v, inv_scale));
+    return max(-128, min(127, q));
+}
+
+// Position of activation k inside the permuted int8 row kept in shared memory.  Within each
+// 16-element block the 4x4 index grid is transposed, so that the 32-bit word (16*blk + 4*j)
+// holds activations 16*blk + {j, 4+j, 8+j, 12+j}: exactly the four activations that multiply
+// the four 2-bit fields at bit offset 2*j of the four bytes of a packed weight word.
+__device__ __forceinline__ int perm_index(int k) {
+    return (k & ~15) | ((k & 3) << 2) | ((k >> 2) & 3);
+}
+#endif  // __CUDACC__
+
+}  // namespace lspk

@@ -1,0 +1,429 @@
+// Ternary linear layer on CUDA cores: y[m, n] = float(sum_k w[n,k] * xq[m,k]) * (xscale[m] * wscale)
+// for M = 1 .. 8 token rows per CTA, with the activation quantiser (and optionally the RMSNorm
+// in front of it) fused in as a prologue and the residual add / ReLU^2 gate fused as epilogue.
+//
+// Replaces matmul_lut_avx512_m1 / _mT (matmul_lut_avx512_extern_c.cpp:150-236, 258-339) and,
+// through the prologue / epilogue switches, quantize_activation (:425-466),
+// rmsnorm_quantize_bf16gamma (:975-1048), relu2_mul_fp32 (:653-670) and add_inplace_fp32
+// (:1127-1137).
+//
+// Work split: one CTA owns one group of 16 output rows (for the ReLU^2 pairing: row group g of
+// the gate matrix and of the up matrix).  Lanes 0-15 / 16-31 of a warp hold the 16 rows for an
+// even / odd 64-weight chunk, so every warp-wide 16-byte load is one contiguous 512-byte span
+// of the device layout.  The 8 warps stride over the chunks of the row group.  A lane decodes
+// a packed word with four masks (no shifts): the four 2-bit fields stay at their bit offset
+// and are accumulated in four separate int32 sums that are scaled back by exact shifts at the
+// end.  Like the reference the codes stay unsigned {0,1,2}; sum(x) is subtracted once per row.
+#include "internal.cuh"
+
+namespace lspk {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+
+struct LinearSeg {
+    const uint4* w;
+    float* out;
+    int32_t* acc_out;
+    int N;
+    int groups;
+    float w_scale;
+};
+
+struct LinearParams {
+    LinearSeg seg[3];
+    int n_seg;
+    int K, chunks;
+    int M;
+    int prologue, epilogue;
+    const float* x_f32;
+    const int8_t* x_i8;
+    const float* x_scales;
+    const void* gamma;
+    int gamma_is_bf16;
+    float eps;
+    int8_t* xq_out;
+    float* xscale_out;
+};
+
+__device__ __forceinline__ void transpose4x4_bytes(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                   uint32_t& o0, uint32_t& o1, uint32_t& o2, uint32_t& o3) {
+    const uint32_t t0 = __byte_perm(a0, a1, 0x5140), t1 = __byte_perm(a2, a3, 0x5140);
+    const uint32_t t2 = __byte_perm(a0, a1, 0x7362), t3 = __byte_perm(a2, a3, 0x7362);
+    o0 = __byte_perm(t0, t1, 0x5410);
+    o1 = __byte_perm(t0, t1, 0x7632);
+    o2 = __byte_perm(t2, t3, 0x5410);
+    o3 = __byte_perm(t2, t3, 0x7632);
+}
+
+// Accumulate one 16-byte weight chunk (64 weights) against the matching 64 permuted activations.
+__device__ __forceinline__ void chunk_dot(const uint4& wv, const int4* __restrict__ xp, int acc[4]) {
+    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        const int4 xv = xp[m];
+        acc[0] = dp4a_us(w[m] & 0x03030303u, xv.x, acc[0]);
+        acc[1] = dp4a_us(w[m] & 0x0C0C0C0Cu, xv.y, acc[1]);
+        acc[2] = dp4a_us(w[m] & 0x30303030u, xv.z, acc[2]);
+        acc[3] = dp4a_us(w[m] & 0xC0C0C0C0u, xv.w, acc[3]);
+    }
+}
+
+template <int MT, int NI, bool PAIR>
+__global__ void __launch_bounds__(kThreads)
+ternary_linear_kernel(const __grid_constant__ LinearParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int Kp = p.chunks * kWeightsPerChunk;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = lane & 15, h = lane >> 4;
+
+    float* xs = reinterpret_cast<float*>(smem_raw);
+    const size_t xs_bytes = (p.prologue == LSPK_PRO_INT8) ? 0 : (size_t)Kp * sizeof(float);
+    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw + xs_bytes);
+    int* part = reinterpret_cast<int*>(xq + (size_t)MT * Kp);
+    constexpr int kPartInts = kWarps * MT * 16 * (PAIR ? 2 : 1);
+    float* redf = reinterpret_cast<float*>(part + kPartInts);
+    float* s_scale = redf + 32;
+    int* s_sumx = reinterpret_cast<int*>(s_scale + MT);
+
+    // ---- which row group ------------------------------------------------------------
+    int g = blockIdx.x, s = 0;
+    if (!PAIR) {
+        while (s < p.n_seg - 1 && g >= p.seg[s].groups) {
+            g -= p.seg[s].groups;
+            ++s;
+        }
+    }
+    const LinearSeg& sg = p.seg[s];
+    const uint4* wa_base = sg.w + (size_t)g * p.chunks * kRowsPerGroup + r;
+    const uint4* wb_base = PAIR ? (p.seg[1].w + (size_t)g * p.chunks * kRowsPerGroup + r) : nullptr;
+
+    // ---- issue the first batch of weight loads before anything that depends on the
+    //      previous kernel: weights are never written by a kernel of the forward pass ---------
+    uint4 wa[NI], wb[PAIR ? NI : 1];
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+        const int j = 2 * (warp + kWarps * i) + h;
+        if (j < p.chunks) {
+            wa[i] = __ldg(wa_base + (size_t)j * kRowsPerGroup);
+            if (PAIR) wb[i] = __ldg(wb_base + (size_t)j * kRowsPerGroup);
+        }
+    }
+    grid_dependency_launch();
+    grid_dependency_wait();
+
+    // ---- prologue: bring this tile's activations into shared memory as permuted int8 ----
+    const int m0 = blockIdx.y * MT;
+    const int mt = min(MT, p.M - m0);
+    const int tail_start = p.K & ~15;      // the reference's scalar-tail rule applies from here
+    for (int m = 0; m < mt; ++m) {
+        int8_t* xq_row = xq + (size_t)m * Kp;
+        int sumx = 0;
+        float scale = 1.0f;
+        if (p.prologue == LSPK_PRO_INT8) {
+            const int8_t* src = p.x_i8 + (size_t)(m0 + m) * p.K;
+            for (int b = tid; b < Kp / 16; b += kThreads) {
+                uint32_t a[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int k = b * 16 + q * 4;
+                    a[q] = (k < p.K) ? *reinterpret_cast<const uint32_t*>(src + k) : 0u;
+                    sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                }
+                uint32_t o0, o1, o2, o3;
+                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
+            }
+            scale = p.x_scales[m0 + m];
+        } else {
+            const float* src = p.x_f32 + (size_t)(m0 + m) * p.K;
+            float ssq = 0.0f;
+            for (int k4 = tid; k4 < Kp / 4; k4 += kThreads) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k4 * 4 < p.K) v = *reinterpret_cast<const float4*>(src + k4 * 4);
+                reinterpret_cast<float4*>(xs)[k4] = v;
+                ssq = fmaf(v.x, v.x, ssq);
+                ssq = fmaf(v.y, v.y, ssq);
+                ssq = fmaf(v.z, v.z, ssq);
+                ssq = fmaf(v.w, v.w, ssq);
+            }
+            float amax = 0.0f;
+            if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
+                ssq = block_sum(ssq, redf);
+                const float rrms =
+                    __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
+                for (int k4 = tid; k4 < Kp / 4; k4 += kThreads) {
+                    float4 v = reinterpret_cast<float4*>(xs)[k4];
+                    float4 gm = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (k4 * 4 < p.K) {
+                        if (p.gamma_is_bf16) {
+                            const uint2 gb = *reinterpret_cast<const uint2*>(
+                                reinterpret_cast<const uint16_t*>(p.gamma) + k4 * 4);
+                            gm.x = __uint_as_float(gb.x << 16);
+                            gm.y = __uint_as_float(gb.x & 0xffff0000u);
+                            gm.z = __uint_as_float(gb.y << 16);
+                            gm.w = __uint_as_float(gb.y & 0xffff0000u);
+                        } else {
+                            gm = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.gamma) + k4 * 4);
+                        }
+                    }
+                    v.x = __fmul_rn(__fmul_rn(v.x, rrms), gm.x);
+                    v.y = __fmul_rn(__fmul_rn(v.y, rrms), gm.y);
+                    v.z = __fmul_rn(__fmul_rn(v.z, rrms), gm.z);
+                    v.w = __fmul_rn(__fmul_rn(v.w, rrms), gm.w);
+                    reinterpret_cast<float4*>(xs)[k4] = v;
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
+            } else {
+                for (int k4 = tid; k4 < Kp / 4; k4 += kThreads) {
+                    const float4 v = reinterpret_cast<float4*>(xs)[k4];
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
+            }
+            amax = block_max(amax, redf);          // also orders the xs writes before the reads below
+            scale = quant_scale_from_absmax(amax);
+            const float inv = __fdiv_rn(1.0f, scale);
+            const bool tap = (p.xq_out != nullptr) && blockIdx.x == 0;
+            for (int b = tid; b < Kp / 16; b += kThreads) {
+                uint32_t a[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v = reinterpret_cast<float4*>(xs)[b * 4 + q];
+                    const float f[4] = {v.x, v.y, v.z, v.w};
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int k = b * 16 + q * 4 + e;
+                        int qv;
+                        if (k < tail_start) {
+                            qv = quant_one(f[e], inv);
+                        } else if (k < p.K) {
+                            qv = (int)roundf(__fmul_rn(f[e], inv));
+                            qv = max(-127, min(127, qv));
+                        } else {
+                            qv = 0;
+                        }
+                        word |= ((uint32_t)qv & 0xffu) << (8 * e);
+                    }
+                    a[q] = word;
+                    sumx = __dp4a((int)word, 0x01010101, sumx);
+                    if (tap && b * 16 + q * 4 < p.K)
+                        *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)(m0 + m) * p.K + b * 16 + q * 4) = word;
+                }
+                uint32_t o0, o1, o2, o3;
+                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
+            }
+        }
+        sumx = block_sum(sumx, reinterpret_cast<int*>(redf));   // barriers: xs may be reused next m
+        if (tid == 0) {
+            s_scale[m] = scale;
+            s_sumx[m] = sumx;
+            if (p.xscale_out && blockIdx.x == 0) p.xscale_out[m0 + m] = scale;
+        }
+    }
+    __syncthreads();
+
+    // ---- integer dot products ----------------------------------------------------------
+    int acc_a[MT][4], acc_b[PAIR ? MT : 1][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            acc_a[m][c] = 0;
+            if (PAIR) acc_b[m][c] = 0;
+        }
+
+    const int pairs = (p.chunks + 1) / 2;
+    for (int base = 0;; ) {
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int j = 2 * (warp + kWarps * (base + i)) + h;
+            if (j < p.chunks) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    if (m < mt) {
+                        const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)m * Kp + (size_t)j * 64);
+                        chunk_dot(wa[i], xp, acc_a[m]);
+                        if (PAIR) chunk_dot(wb[i], xp, acc_b[m]);
+                    }
+                }
+            }
+        }
+        base += NI;
+        if (kWarps * base >= pairs) break;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int j = 2 * (warp + kWarps * (base + i)) + h;
+            if (j < p.chunks) {
+                wa[i] = __ldg(wa_base + (size_t)j * kRowsPerGroup);
+                if (PAIR) wb[i] = __ldg(wb_base + (size_t)j * kRowsPerGroup);
+            }
+        }
+    }
+
+    // ---- reduce: fields -> one int, odd/even chunk halves by shuffle, warps through smem ----
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        int v = acc_a[m][0] + (acc_a[m][1] >> 2) + (acc_a[m][2] >> 4) + (acc_a[m][3] >> 6);
+        v += __shfl_down_sync(0xffffffffu, v, 16);
+        if (h == 0) part[(warp * MT + m) * 16 + r] = v;
+        if (PAIR) {
+            int u = acc_b[m][0] + (acc_b[m][1] >> 2) + (acc_b[m][2] >> 4) + (acc_b[m][3] >> 6);
+            u += __shfl_down_sync(0xffffffffu, u, 16);
+            if (h == 0) part[kWarps * MT * 16 + (warp * MT + m) * 16 + r] = u;
+        }
+    }
+    __syncthreads();
+
+    if (tid < MT * 16) {
+        const int m = tid >> 4, rr = tid & 15;
+        const int n = g * kRowsPerGroup + rr;
+        if (m < mt && n < sg.N) {
+            int va = 0, vb = 0;
+#pragma unroll
+            for (int w = 0; w < kWarps; ++w) {
+                va += part[(w * MT + m) * 16 + rr];
+                if (PAIR) vb += part[kWarps * MT * 16 + (w * MT + m) * 16 + rr];
+            }
+            va -= s_sumx[m];
+            const size_t o = (size_t)(m0 + m) * sg.N + n;
+            if (sg.acc_out) sg.acc_out[o] = va;
+            const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[m], sg.w_scale));
+            if (PAIR) {
+                vb -= s_sumx[m];
+                if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
+                const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[m], p.seg[1].w_scale));
+                const float gpos = fmaxf(ya, 0.0f);
+                sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+            } else if (p.epilogue == LSPK_EPI_ADD) {
+                sg.out[o] = __fadd_rn(sg.out[o], ya);
+            } else {
+                sg.out[o] = ya;
+            }
+        }
+    }
+}
+
+static size_t linear_smem_bytes(int MT, int Kp, int prologue, bool pair) {
+    size_t b = (prologue == LSPK_PRO_INT8) ? 0 : (size_t)Kp * 4;
+    b += (size_t)MT * Kp;
+    b += (size_t)kWarps * MT * 16 * (pair ? 2 : 1) * 4;
+    b += 32 * 4 + MT * 8;
+    return b;
+}
+
+template <int MT, int NI, bool PAIR>
+static cudaError_t launch_linear(const LinearParams& p, int grid_x, size_t smem) {
+    static bool attr_set = false;
+    auto kern = ternary_linear_kernel<MT, NI, PAIR>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const dim3 grid(grid_x, (p.M + MT - 1) / MT);
+    return launch(kern, grid, dim3(kThreads), smem, true, p);
+}
+
+template <int MT>
+static cudaError_t launch_linear_mt(const LinearParams& p, int grid_x, bool pair, size_t smem) {
+    const bool big = p.chunks > 64;
+    if (pair) return big ? launch_linear<MT, 8, true>(p, grid_x, smem) : launch_linear<MT, 4, true>(p, grid_x, smem);
+    return big ? launch_linear<MT, 8, false>(p, grid_x, smem) : launch_linear<MT, 4, false>(p, grid_x, smem);
+}
+
+// Host-side validation + launch of the CUDA-core kernel.  Used by lspk_linear and by the
+// forward pass.
+int linear_cuda_core(const lspk_linear_args* a) {
+    LSPK_REQUIRE(a, "linear: null args");
+    LSPK_REQUIRE(a->n_mats >= 1 && a->n_mats <= 3, "linear: n_mats must be 1..3 (got %d)", a->n_mats);
+    LSPK_REQUIRE(a->M >= 1, "linear: M must be >= 1 (got %d)", a->M);
+    const bool pair = a->epilogue == LSPK_EPI_RELU2_MUL;
+    LSPK_REQUIRE(!pair || a->n_mats == 2, "linear: the ReLU^2 epilogue takes exactly two matrices (gate, up)");
+    LinearParams p = {};
+    const Weight* w0 = reinterpret_cast<const Weight*>(a->w[0]);
+    LSPK_REQUIRE(w0, "linear: null weight");
+    p.K = w0->K;
+    p.chunks = w0->chunks;
+    p.n_seg = a->n_mats;
+    int groups = 0;
+    for (int i = 0; i < a->n_mats; ++i) {
+        const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
+        LSPK_REQUIRE(w && w->K == p.K, "linear: matrices must share K");
+        LSPK_REQUIRE(pair ? (i == 1 || a->out[i] != nullptr) : a->out[i] != nullptr, "linear: null output");
+        LSPK_REQUIRE(!pair || w->N == w0->N, "linear: gate and up must have the same N");
+        p.seg[i] = LinearSeg{w->dev, a->out[i], a->acc_out[i], w->N, w->groups, w->scale};
+        groups += w->groups;
+    }
+    if (pair) groups = w0->groups;
+    p.M = a->M;
+    p.prologue = a->prologue;
+    p.epilogue = a->epilogue;
+    p.x_f32 = a->x_f32;
+    p.x_i8 = a->x_i8;
+    p.x_scales = a->x_scales;
+    p.gamma = a->gamma;
+    p.gamma_is_bf16 = a->gamma_is_bf16;
+    p.eps = a->eps;
+    p.xq_out = a->xq_out;
+    p.xscale_out = a->xscale_out;
+    switch (a->prologue) {
+        case LSPK_PRO_INT8:
+            LSPK_REQUIRE(a->x_i8 && a->x_scales, "linear: INT8 prologue needs x_i8 and x_scales");
+            break;
+        case LSPK_PRO_RMSNORM_QUANT:
+            LSPK_REQUIRE(a->gamma, "linear: RMSNORM_QUANT prologue needs gamma");
+            /* fallthrough */
+        case LSPK_PRO_QUANT:
+            LSPK_REQUIRE(a->x_f32, "linear: fp32 prologue needs x_f32");
+            break;
+        default:
+            return fail(LSPK_ERR_ARG, "linear: unknown prologue %d", a->prologue);
+    }
+    LSPK_REQUIRE(a->epilogue >= 0 && a->epilogue <= 2, "linear: unknown epilogue %d", a->epilogue);
+    const int MT = a->M == 1 ? 1 : a->M == 2 ? 2 : a->M <= 4 ? 4 : 8;
+    const int Kp = p.chunks * kWeightsPerChunk;
+    const size_t smem = linear_smem_bytes(MT, Kp, p.prologue, pair);
+    LSPK_REQUIRE(smem <= 200 * 1024, "linear: K=%d too large for the shared-memory activation tile", p.K);
+    cudaError_t e;
+    switch (MT) {
+        case 1: e = launch_linear_mt<1>(p, groups, pair, smem); break;
+        case 2: e = launch_linear_mt<2>(p, groups, pair, smem); break;
+        case 4: e = launch_linear_mt<4>(p, groups, pair, smem); break;
+        default: e = launch_linear_mt<8>(p, groups, pair, smem); break;
+    }
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear launch failed: %s", cudaGetErrorString(e));
+    return LSPK_OK;
+}
+
+}  // namespace lspk
+
+using namespace lspk;
+
+static int g_force_path = 0;   // 0 auto, 1 CUDA-core only, 2 tensor-core only
+
+extern "C" int lspk_linear_force_path(int path) {
+    LSPK_REQUIRE(path >= 0 && path <= 2, "lspk_linear_force_path: path must be 0, 1 or 2");
+    g_force_path = path;
+    return LSPK_OK;
+}
+
+extern "C" int lspk_linear(const lspk_linear_args* a) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_REQUIRE(a, "lspk_linear: null args");
+    if (a->prologue != LSPK_PRO_INT8) {
+        LSPK_REQUIRE(((uintptr_t)a->x_f32 & 15) == 0, "lspk_linear: x_f32 must be 16-byte aligned");
+        LSPK_REQUIRE(a->prologue != LSPK_PRO_RMSNORM_QUANT || ((uintptr_t)a->gamma & (a->gamma_is_bf16 ? 7 : 15)) == 0,
+                     "lspk_linear: gamma must be 8-byte (bf16) / 16-byte (fp32) aligned");
+    } else {
+        LSPK_REQUIRE(((uintptr_t)a->x_i8 & 3) == 0, "lspk_linear: x_i8 must be 4-byte aligned");
+    }
+    if (g_force_path != 1) {
+        int handled = 0;
+        if (int rc = linear_tensor_core(a, &handled)) return rc;
+        if (handled) return LSPK_OK;
+        if (g_force_path == 2) return fail(LSPK_ERR_ARG, "lspk_linear: shape not supported by the tensor-core path");
+    }
+    return linear_cuda_core(a);
+}

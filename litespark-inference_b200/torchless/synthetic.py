@@ -1,0 +1,63 @@
+"""Seeded synthetic models and inputs with the reference benchmark's shapes and value
+distributions (ternary weights uniform over {-1,0,+1}, per-tensor scale ~U(0.5,1.5), norm
+weights 1, bf16 embedding ~N(0,1), uniform random token ids).  They stand in for the real
+checkpoint and prompt, which need network access."""
+from __future__ import annotations
+
+import numpy as np
+
+from .model import BitNetConfig, PackedBitNetModel, PackedLayer, PackedProjection
+from .pack import pack_ternary_4_per_byte
+from .quantize import fp32_to_bf16_u16
+
+BITNET_2B = dict(hidden_size=2560, num_layers=30, num_heads=20, num_kv_heads=5, intermediate_size=6912,
+                 vocab_size=128256, max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=500000.0)
+
+# (N, K) of the BitNet-2B projections
+BITNET_2B_SHAPES = {"q": (2560, 2560), "k": (640, 2560), "v": (640, 2560), "o": (2560, 2560),
+                    "gate": (6912, 2560), "up": (6912, 2560), "down": (2560, 6912)}
+
+
+def random_projection(rng: np.random.Generator, N: int, K: int) -> PackedProjection:
+    w = rng.integers(-1, 2, size=(N, K), dtype=np.int8)
+    scale = float(np.float32(rng.uniform(0.5, 1.5)))
+    return PackedProjection(w_packed=pack_ternary_4_per_byte(w), w_sum=None, scale=scale,
+                            in_features=K, out_features=N)
+
+
+def random_model(cfg: BitNetConfig, seed: int = 0, norm_jitter: float = 0.0) -> PackedBitNetModel:
+    """Random-init model of the given shape.  norm_jitter > 0 perturbs the norm weights away
+    from 1 (tests use it so that the gamma multiply is actually exercised)."""
+    rng = np.random.default_rng(seed)
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    D = H // cfg.num_heads
+    kv = cfg.num_kv_heads * D
+
+    def gamma(n):
+        g = np.ones(n, dtype=np.float32)
+        if norm_jitter:
+            g += rng.uniform(-norm_jitter, norm_jitter, n).astype(np.float32)
+        return fp32_to_bf16_u16(g)
+
+    layers = []
+    for _ in range(cfg.num_layers):
+        layers.append(PackedLayer(
+            q_proj=random_projection(rng, H, H), k_proj=random_projection(rng, kv, H),
+            v_proj=random_projection(rng, kv, H), o_proj=random_projection(rng, H, H),
+            gate_proj=random_projection(rng, I, H), up_proj=random_projection(rng, I, H),
+            down_proj=random_projection(rng, H, I),
+            input_norm=gamma(H), post_attn_norm=gamma(H), attn_sub_norm=gamma(H), ffn_sub_norm=gamma(I)))
+    emb = fp32_to_bf16_u16(rng.standard_normal((cfg.vocab_size, H), dtype=np.float32))
+    return PackedBitNetModel(config=cfg, embed_tokens=emb, final_norm=gamma(H), layers=layers)
+
+
+def bitnet_2b_config(**over) -> BitNetConfig:
+    d = dict(BITNET_2B)
+    d.update(over)
+    return BitNetConfig(**d)
+
+
+def toy_config(hidden=256, layers=2, heads=4, kv_heads=2, inter=512, vocab=1024) -> BitNetConfig:
+    return BitNetConfig(hidden_size=hidden, num_layers=layers, num_heads=heads, num_kv_heads=kv_heads,
+                        intermediate_size=inter, vocab_size=vocab, max_position_embeddings=4096,
+                        rms_norm_eps=1e-5, rope_theta=500000.0)
