@@ -1,0 +1,384 @@
+"""Benchmark of the ternary-matmul hot path: tg128 decode throughput of a BitNet-2B-shaped model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the headline metric is quoted on): 30-layer BitNet-b1.58-2B-shaped
+decoder with random-init ternary weights and a bf16 tied embedding, a 128-token uniform-random
+prompt, then 128 greedy decode steps at batch 1 with an fp16 KV cache.  One "step" of this
+benchmark is one tg128 pass: the position is rolled back to 128 and 128 tokens are decoded.
+Each decoded token streams ~1.18 GB of weights (ternary projections + LM head), far more than
+the 126 MB L2, so no explicit L2 flush is needed between iterations.
+
+Prints ONE JSON line.  `value` is timed on the device (CUDA events around the 128 chained
+graph launches, token fed back on the GPU).  `e2e` is the same loop driven from the host
+through the public Python API: every step sends the input token from host memory and reads the
+greedy token back.  `roofline` is for the dominant kernel (the ternary linear kernel), timed
+live here by replaying the 120 linear launches of a token over the model's 521 MB of packed
+weights.  `cpu_baseline` times the reference's own compiled CPU kernels (oracle/_ref) on the
+host cores for a bounded sample of the same workload.
+
+With --gpus N > 1 (one process per GPU under torchrun) every rank decodes its own sequence on
+its own replica -- no data-path collective; torch.distributed is used only for the barrier and
+the max-over-ranks of the device time.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+PROMPT_LEN = 128
+GEN_LEN = 128
+METRIC = "tg128 decode tok/s at BitNet-2B shape; ternary GEMV GB/s vs B200 HBM peak"
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Sample SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        return False
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_model(seed: int = 0):
+    entry.load_package()
+    from litespark_inference_b200.torchless import synthetic
+    cfg = synthetic.bitnet_2b_config()
+    return cfg, synthetic.random_model(cfg, seed=seed, fast=True)
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_reference_tok_s(model, prompt, n_prompt: int, n_decode: int):
+    """Decode tok/s of the reference's CPU kernels on this host: the compiled reference objects
+    under oracle/_ref when this CPU can run them, else the C restatement.  The host loop is the
+    oracle's numpy restatement of the reference's forward_one."""
+    orc = entry.load_oracle()
+    tier = orc.ref_tier()
+    if tier is not None:
+        kern, kind, what = orc.Kernels("ref", tier), "reference", f"oracle/_ref {tier} build"
+    else:
+        kern, kind, what = orc.Kernels("port"), "port", "oracle C restatement (no usable reference object)"
+    st = orc.State(model.config, n_prompt + n_decode + 1, np.float16)
+    logits = orc.forward_prefill(kern, model, st, prompt[:n_prompt])
+    tok = int(np.argmax(logits))
+    t0 = time.perf_counter()
+    for _ in range(n_decode):
+        logits = orc.forward_one(kern, model, st, tok)
+        tok = int(np.argmax(logits))
+    dt = time.perf_counter() - t0
+    return n_decode / dt, kind, what, kern.max_threads()
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg, model = build_model()
+    prompt = [int(t) for t in np.random.default_rng(1).integers(0, cfg.vocab_size, PROMPT_LEN)]
+    n_prompt, n_decode = 16, 16
+    vals = []
+    for i in range(args.warmup + args.steps):
+        v, kind, what, threads = cpu_reference_tok_s(model, prompt, n_prompt, n_decode)
+        if i >= args.warmup:
+            vals.append(v)
+    value = statistics.mean(vals)
+    sample = (f"{what}; {n_decode} greedy decode steps after a {n_prompt}-token prompt per step "
+              f"(bounded sample of pp128+tg128), fp16 KV, OMP threads={threads}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * n_decode / value,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32",
+        "data": "synthetic",
+        "config": {"workload": "BitNet-2B-shaped decoder, pp128+tg128 batch 1 (bounded CPU sample)",
+                   "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    global PROMPT_LEN, GEN_LEN
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seqs-per-gpu", type=int, default=8, help="batch of the extra data-parallel measurement")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompt for profiler captures")
+    ap.add_argument("--gen-len", type=int, default=GEN_LEN, help="fewer decode steps for profiler captures")
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="only the device-timed loop and the roofline replay (profiler captures)")
+    args = ap.parse_args()
+    PROMPT_LEN, GEN_LEN = args.prompt_len, args.gen_len
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ["LITESPARK_DEVICE"] = str(local)
+
+    cfg, model = build_model(seed=0)
+    from litespark_inference_b200.torchless import kernel as K
+    from litespark_inference_b200.torchless import runtime as rt
+    lib = K.load_library(True)
+    dm = rt.to_device(model)
+    rng = np.random.default_rng(100 + rank)
+    prompt = [int(t) for t in rng.integers(0, cfg.vocab_size, PROMPT_LEN)]
+    t_max = PROMPT_LEN + GEN_LEN
+    state = rt.init_state(dm, t_max, kv_dtype="fp16")
+    first = np.empty(1, np.int32)
+    ids = np.ascontiguousarray(prompt, dtype=np.int32)
+    K.check(lib.lspk_forward_prefill(state.handle, 0, ids.ctypes.data, PROMPT_LEN, None, None, first.ctypes.data))
+    toks = np.empty(GEN_LEN, np.int32)
+    ms = ctypes.c_float(0.0)
+
+    def tg128_device():
+        state.pos = PROMPT_LEN
+        K.check(lib.lspk_timer_start())
+        K.check(lib.lspk_decode_greedy(state.handle, first.ctypes.data, GEN_LEN, toks.ctypes.data))
+        K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
+        return float(ms.value)
+
+    def barrier():
+        K.check(lib.lspk_sync())
+        if dist is not None:
+            dist.barrier()
+
+    for _ in range(args.warmup):
+        tg128_device()
+    with ClockSampler(local) as clocks:
+        barrier()
+        per_step = [tg128_device() for _ in range(args.steps)]
+        barrier()
+    total_ms = sum(per_step)
+    if dist is not None:
+        import torch
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    value = world * args.steps * GEN_LEN / (total_ms / 1000.0)
+    step_kernels = state.step_kernel_count
+
+    # ---- end to end through the public API: host feeds each token, reads each greedy token ----
+    def tg128_host():
+        state.pos = PROMPT_LEN
+        tok = np.array([int(first[0])], dtype=np.int32)
+        t0 = time.perf_counter()
+        for _ in range(GEN_LEN):
+            tok = rt.forward_step(state, tok)
+        return time.perf_counter() - t0
+
+    if args.skip_extras:
+        args.no_cpu_baseline = True
+    tg128_host()
+    barrier()
+    e2e_s = max(tg128_host() for _ in range(1 if args.skip_extras else max(1, min(args.steps, 3))))
+    if dist is not None:
+        import torch
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * GEN_LEN / e2e_s
+
+    # the reference API's own loop: logits [V] fp32 to the host every step, argmax on the host
+    def tg128_host_logits():
+        state.pos = PROMPT_LEN
+        tok = int(first[0])
+        t0 = time.perf_counter()
+        for _ in range(GEN_LEN):
+            tok = int(np.argmax(rt.forward_one(dm, state, tok)))
+        return time.perf_counter() - t0
+
+    tg128_host_logits()
+    e2e_logits_value = GEN_LEN / tg128_host_logits()
+
+    if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel: the ternary linear kernel, timed live --------------------
+    peak, peak_kind = load_peaks()
+    n_launch, lin_bytes, lm_bytes = ctypes.c_int(0), ctypes.c_double(0.0), ctypes.c_double(0.0)
+    reps = 2 if args.skip_extras else 50
+    K.check(lib.lspk_bench_linears(state.handle, reps, ctypes.byref(ms), ctypes.byref(n_launch), ctypes.byref(lin_bytes)))
+    lin_ms = float(ms.value) / reps
+    bytes_per_launch = lin_bytes.value / n_launch.value
+    us_per_launch = 1000.0 * lin_ms / n_launch.value
+    lin_gbs = lin_bytes.value / (lin_ms * 1e-3) / 1e9
+    K.check(lib.lspk_bench_lm_head(state.handle, 20, ctypes.byref(ms), ctypes.byref(lm_bytes)))
+    lm_ms = float(ms.value) / 20
+    lm_gbs = lm_bytes.value / (lm_ms * 1e-3) / 1e9
+    token_ms = total_ms / (args.steps * GEN_LEN)
+    kv_bytes = 2 * cfg.num_layers * (PROMPT_LEN + GEN_LEN / 2) * cfg.num_kv_heads * 128 * 2
+    token_bytes = lin_bytes.value + lm_bytes.value + kv_bytes
+    token_gbs = token_bytes / (token_ms * 1e-3) / 1e9
+
+    # ---- extra: 8 independent sequences per GPU in lock step (small-batch GEMV rows) -----------------
+    extra = {}
+    try:
+        if args.skip_extras:
+            raise RuntimeError("skipped (--skip-extras)")
+        B = args.seqs_per_gpu
+        bstate = rt.init_state(dm, t_max, batch=B, kv_dtype="fp16")
+        firsts = np.empty(B, np.int32)
+        one = np.empty(1, np.int32)
+        for b in range(B):
+            pb = np.ascontiguousarray(np.random.default_rng(500 + b).integers(0, cfg.vocab_size, PROMPT_LEN), dtype=np.int32)
+            K.check(lib.lspk_forward_prefill(bstate.handle, b, pb.ctypes.data, PROMPT_LEN, None, None, one.ctypes.data))
+            firsts[b] = one[0]
+        btoks = np.empty((GEN_LEN, B), np.int32)
+
+        def tg128_batch():
+            for b in range(B):
+                bstate.set_pos(b, PROMPT_LEN)
+            K.check(lib.lspk_timer_start())
+            K.check(lib.lspk_decode_greedy(bstate.handle, firsts.ctypes.data, GEN_LEN, btoks.ctypes.data))
+            K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
+            return float(ms.value)
+
+        tg128_batch()
+        bms = min(tg128_batch() for _ in range(3))
+        extra["batch8_tok_s_per_gpu"] = B * GEN_LEN / (bms / 1000.0)
+        extra["batch8_step_kernels"] = bstate.step_kernel_count
+        bstate.close()
+    except Exception as ex:  # the headline line must still be printed
+        extra["batch8_error"] = str(ex)[:200]
+
+    # ---- CPU baseline: the reference's kernels on this host's cores, bounded sample ------------------
+    cpu = None
+    if not args.no_cpu_baseline:
+        v, kind, what, threads = cpu_reference_tok_s(model, prompt, 16, 24)
+        cpu = {"value": v, "unit": "tok/s", "cores": threads, "kind": kind,
+               "sample": f"{what}; 24 greedy decode steps after a 16-token prompt of the same model, fp16 KV"}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary(2-bit) -> int32, fp32 rescale",
+        "data": "synthetic",
+        "config": {"workload": "BitNet-2B-shaped decoder (30 layers, H=2560, I=6912, 20/5 heads, V=128256, "
+                               f"bf16 tied embedding), {PROMPT_LEN}-token random prompt + {GEN_LEN} greedy steps, "
+                               "batch 1 per GPU, fp16 KV",
+                   "parallelism": f"dp{world} (independent sequence per GPU, no collective)",
+                   "l2": "inputs larger than L2 (1.18 GB of weights streamed per token)",
+                   "step": "one tg128 pass = 128 chained decode steps"},
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * GEN_LEN,
+                "d2h_bytes_per_step": 4 * GEN_LEN,
+                "how": "host loop over lspk_forward_step: token id up from pinned memory, greedy token id back, every step"},
+        "e2e_logits_to_host": {"value": e2e_logits_value, "unit": "tok/s", "d2h_bytes_per_step": 4 * cfg.vocab_size * GEN_LEN,
+                               "how": "forward_one returning fp32 logits [V] to the host + np.argmax, the reference API's loop"},
+        "gpu_launches": args.steps * GEN_LEN * step_kernels,
+        "kernels_per_token": step_kernels,
+        "roofline": {"kernel": "ternary_linear_kernel (M=1, fused RMSNorm+quantiser prologue)",
+                     "bound": "hbm", "achieved": lin_gbs, "peak": peak, "unit": "GB/s", "frac": lin_gbs / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
+                     "launches_timed": n_launch.value * reps,
+                     "how": "CUDA events around graph replays of the 120 linear launches of one token over all 30 layers' weights (521 MB, > L2)"},
+        "roofline_lm_head": {"kernel": "lm_head_kernel<bf16>", "bound": "hbm", "achieved": lm_gbs, "peak": peak,
+                             "unit": "GB/s", "frac": lm_gbs / peak, "us_per_launch": 1000.0 * lm_ms},
+        "roofline_token": {"bytes_per_token": token_bytes, "us_per_token": 1000.0 * token_ms, "achieved": token_gbs,
+                           "peak": peak, "unit": "GB/s", "frac": token_gbs / peak,
+                           "frac_of_nominal_8TBs": token_gbs / 8000.0},
+        "cpu_baseline": cpu,
+        "extra": extra,
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

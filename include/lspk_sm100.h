@@ -88,7 +88,8 @@ enum { LSPK_PRO_INT8 = 0,        /* x is int8 [M,K] with per-row fp32 scales (a5
 /* Epilogue: what happens to y = float(acc) * (x_scale * w_scale).                         */
 enum { LSPK_EPI_STORE = 0,       /* out = y                                               */
        LSPK_EPI_ADD = 1,         /* out += y            (residual add, a12)                */
-       LSPK_EPI_RELU2_MUL = 2    /* two matrices (gate, up): out = max(g,0)^2 * u  (a11)   */ };
+       LSPK_EPI_RELU2_MUL = 2,   /* two matrices (gate, up): out = max(g,0)^2 * u  (a11)   */
+       LSPK_EPI_SILU_MUL = 3     /* two matrices (gate, up): out = g / (1 + exp(-g)) * u    */ };
 
 typedef struct {
     /* up to three matrices that share the input (q/k/v, or gate/up); rows are independent */

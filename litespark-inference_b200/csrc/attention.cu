@@ -66,52 +66,96 @@ __global__ void __launch_bounds__(kAttnThreads) rope_store_kernel(const AttnPara
     }
 }
 
-// One CTA per (query head, row).  EPL = D / 32 elements of the head dimension per lane.
-template <typename KVT, int EPL>
+// 16 bytes of cache row -> fp32 values (8 halves or 4 floats).
+template <typename KVT> struct KvVec;
+template <> struct KvVec<__half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const uint4& c, float* f) {
+        const __half2* h = reinterpret_cast<const __half2*>(&c);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __half22float2(h[i]);
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+    }
+};
+template <> struct KvVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void unpack(const uint4& c, float* f) {
+        f[0] = __uint_as_float(c.x);
+        f[1] = __uint_as_float(c.y);
+        f[2] = __uint_as_float(c.z);
+        f[3] = __uint_as_float(c.w);
+    }
+};
+
+// One CTA per (query head, row).  Built for latency, not bandwidth (one head's K and V are at
+// most a few hundred KB): every phase issues all of its global loads before using any of them.
+//   scores : one thread per key; the key row is read with 16-byte loads, up to 16 in flight.
+//   softmax: two block reductions.
+//   values : D/VEC threads per key (16 bytes of the value row each), 256/(D/VEC) key groups,
+//            8 loads in flight per thread; group partials are summed through shared memory.
+template <typename KVT, int D>
 __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
-    constexpr int D = EPL * 32;
+    constexpr int VEC = KvVec<KVT>::N;          // cache elements per 16-byte load
+    constexpr int NCH = D / VEC;                // 16-byte chunks per cache row
+    constexpr int TPK = NCH;                    // threads per key in the value phase
+    constexpr int NG = kAttnThreads / TPK;      // key groups in the value phase
+    constexpr int KB = NCH < 16 ? NCH : 16;     // chunks per batch in the score phase
     extern __shared__ __align__(16) float at_smem[];
     float* qs = at_smem;                  // [D] rotated query
     float* ks = qs + D;                   // [D] rotated current key (fused mode)
     float* vs = ks + D;                   // [D] current value (fused mode)
     float* raw = vs + D;                  // [2*D] raw q and k before rotation (fused mode)
-    float* acc_w = raw + 2 * D;           // [warps][D]
-    float* sc = acc_w + kAttnWarps * D;   // [n] scores / probabilities
+    float* part = raw + 2 * D;            // [NG][D] value partial sums
+    float* sc = part + NG * D;            // [n] scores / probabilities
     __shared__ float red[32];
 
     grid_dependency_launch();
     grid_dependency_wait();
 
     const int h = blockIdx.x, t = blockIdx.y;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int G = p.Q / p.KV, kvh = h / G;
     const int pos = p.pos_per_row ? p.pos_ptr[t] : p.pos_ptr[0] + t;
     const int n = pos + 1;
     const int half = D / 2;
     const int kd = p.KV * D;
-    KVT* ck = reinterpret_cast<KVT*>(p.cache_k) + (size_t)t * p.cache_seq_stride;
-    KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride;
+    KVT* ck = reinterpret_cast<KVT*>(p.cache_k) + (size_t)t * p.cache_seq_stride + (size_t)kvh * D;
+    KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride + (size_t)kvh * D;
     const float* qrow = p.q + (size_t)t * p.Q * D + (size_t)h * D;
 
     if (p.fused) {
         const float* krow = p.k_cur + (size_t)t * kd + (size_t)kvh * D;
         const float* vrow = p.v_cur + (size_t)t * kd + (size_t)kvh * D;
+        float vr = 0.0f, cr = 0.0f, sr = 0.0f;
         if (tid < D) {
+            const int i = tid < half ? tid : tid - half;
             raw[tid] = qrow[tid];
             raw[D + tid] = krow[tid];
+            vr = vrow[tid];
+            cr = p.rope_cos[(size_t)pos * half + i];
+            sr = p.rope_sin[(size_t)pos * half + i];
         }
         __syncthreads();
         if (tid < D) {
-            const float* cr = p.rope_cos + (size_t)pos * half;
-            const float* sr = p.rope_sin + (size_t)pos * half;
-            qs[tid] = rope_elem(raw, tid, half, cr, sr);
-            const float kr = rope_elem(raw + D, tid, half, cr, sr);
-            const float vr = vrow[tid];
+            const int i = tid < half ? tid : tid - half;
+            const float q1 = raw[i], q2 = raw[half + i], k1 = raw[D + i], k2 = raw[D + half + i];
+            float qr, kr;
+            if (tid < half) {
+                qr = __fsub_rn(__fmul_rn(q1, cr), __fmul_rn(q2, sr));
+                kr = __fsub_rn(__fmul_rn(k1, cr), __fmul_rn(k2, sr));
+            } else {
+                qr = __fadd_rn(__fmul_rn(q1, sr), __fmul_rn(q2, cr));
+                kr = __fadd_rn(__fmul_rn(k1, sr), __fmul_rn(k2, cr));
+            }
+            qs[tid] = qr;
             ks[tid] = kv_round<KVT>(kr);
             vs[tid] = kv_round<KVT>(vr);
             if (h % G == 0) {
-                ck[(size_t)pos * kd + (size_t)kvh * D + tid] = kv_make<KVT>(kr);
-                cv[(size_t)pos * kd + (size_t)kvh * D + tid] = kv_make<KVT>(vr);
+                ck[(size_t)pos * kd + tid] = kv_make<KVT>(kr);
+                cv[(size_t)pos * kd + tid] = kv_make<KVT>(vr);
             }
         }
     } else {
@@ -119,28 +163,34 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     }
     __syncthreads();
 
-    float qreg[EPL];
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) qreg[e] = qs[lane * EPL + e];
+    // ---- scores: thread per key ------------------------------------------------------------------
     const float inv_sqrt_d = 1.0f / sqrtf((float)D);
-
-    // scores
-    for (int i = warp; i < n; i += kAttnWarps) {
+    for (int i = tid; i < n; i += kAttnThreads) {
         float dot = 0.0f;
         if (p.fused && i == pos) {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) dot = fmaf(qreg[e], ks[lane * EPL + e], dot);
+#pragma unroll 8
+            for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ks[d], dot);
         } else {
-            const KVT* kp = ck + (size_t)i * kd + (size_t)kvh * D + lane * EPL;
+            const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)i * kd);
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) dot = fmaf(qreg[e], kv_load<KVT>(kp + e), dot);
+            for (int b0 = 0; b0 < NCH; b0 += KB) {
+                uint4 buf[KB];
+#pragma unroll
+                for (int b = 0; b < KB; ++b) buf[b] = kp[b0 + b];
+#pragma unroll
+                for (int b = 0; b < KB; ++b) {
+                    float f[VEC];
+                    KvVec<KVT>::unpack(buf[b], f);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) dot = fmaf(qs[(b0 + b) * VEC + e], f[e], dot);
+                }
+            }
         }
-        dot = warp_sum(dot);
-        if (lane == 0) sc[i] = __fmul_rn(dot, inv_sqrt_d);
+        sc[i] = __fmul_rn(dot, inv_sqrt_d);
     }
     __syncthreads();
 
-    // softmax over sc[0..n)
+    // ---- softmax over sc[0..n) -----------------------------------------------------------------------
     float mx = -INFINITY;
     for (int i = tid; i < n; i += kAttnThreads) mx = fmaxf(mx, sc[i]);
     mx = block_max(mx, red);
@@ -154,28 +204,44 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     for (int i = tid; i < n; i += kAttnThreads) sc[i] = __fdiv_rn(sc[i], sum);
     __syncthreads();
 
-    // weighted sum of values
-    float o[EPL];
+    // ---- weighted sum of values: TPK threads per key, NG key groups ---------------------------------
+    const int g = tid / TPK, c = tid % TPK;
+    float o[VEC];
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) o[e] = 0.0f;
-    for (int i = warp; i < n; i += kAttnWarps) {
-        const float pi = sc[i];
-        if (p.fused && i == pos) {
+    for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
+    constexpr int VB = 8;                                   // loads in flight per thread
+    for (int i0 = g; i0 < n; i0 += NG * VB) {
+        uint4 buf[VB];
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) o[e] = fmaf(pi, vs[lane * EPL + e], o[e]);
-        } else {
-            const KVT* vp = cv + (size_t)i * kd + (size_t)kvh * D + lane * EPL;
+        for (int b = 0; b < VB; ++b) {
+            const int i = i0 + b * NG;
+            if (i < n && !(p.fused && i == pos))
+                buf[b] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c);
+        }
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) o[e] = fmaf(pi, kv_load<KVT>(vp + e), o[e]);
+        for (int b = 0; b < VB; ++b) {
+            const int i = i0 + b * NG;
+            if (i < n) {
+                const float pi = sc[i];
+                float f[VEC];
+                if (p.fused && i == pos) {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) f[e] = vs[c * VEC + e];
+                } else {
+                    KvVec<KVT>::unpack(buf[b], f);
+                }
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) o[e] = fmaf(pi, f[e], o[e]);
+            }
         }
     }
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) acc_w[warp * D + lane * EPL + e] = o[e];
+    for (int e = 0; e < VEC; ++e) part[g * D + c * VEC + e] = o[e];
     __syncthreads();
     if (tid < D) {
         float r = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kAttnWarps; ++w) r += acc_w[w * D + tid];
+        for (int w = 0; w < NG; ++w) r += part[w * D + tid];
         p.out[(size_t)t * p.Q * D + (size_t)h * D + tid] = r;
     }
 }
@@ -183,13 +249,14 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
 template <typename KVT>
 static int attention_launch_t(const AttnParams& p) {
     const int D = p.D;
-    const size_t smem = (size_t)(5 * D + kAttnWarps * D + p.t_max) * sizeof(float);
+    constexpr int VEC = 16 / (int)sizeof(KVT);
+    const size_t smem = (size_t)(5 * D + kAttnThreads * VEC + p.t_max) * sizeof(float);
     LSPK_REQUIRE(smem <= 200 * 1024, "attention: t_max=%d too large for the shared score buffer", p.t_max);
     static bool attr_set = false;
     if (!attr_set) {
-        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LSPK_CUDA(cudaFuncSetAttribute(rope_store_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set = true;
     }
@@ -199,9 +266,9 @@ static int attention_launch_t(const AttnParams& p) {
     }
     const dim3 grid(p.Q, p.T);
     cudaError_t e;
-    if (D == 64) e = launch(attention_kernel<KVT, 2>, grid, dim3(kAttnThreads), smem, true, p);
-    else if (D == 128) e = launch(attention_kernel<KVT, 4>, grid, dim3(kAttnThreads), smem, true, p);
-    else e = launch(attention_kernel<KVT, 8>, grid, dim3(kAttnThreads), smem, true, p);
+    if (D == 64) e = launch(attention_kernel<KVT, 64>, grid, dim3(kAttnThreads), smem, true, p);
+    else if (D == 128) e = launch(attention_kernel<KVT, 128>, grid, dim3(kAttnThreads), smem, true, p);
+    else e = launch(attention_kernel<KVT, 256>, grid, dim3(kAttnThreads), smem, true, p);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return LSPK_OK;
 }

@@ -69,7 +69,22 @@ __device__ __forceinline__ void chunk_dot(const uint4& wv, const int4* __restric
     }
 }
 
-template <int MT, int NI, bool PAIR>
+// fp32 -> int8 with round-half-even and saturation to [-128, 127] in one instruction: the pair
+// _mm512_cvtps_epi32 + _mm512_cvtsepi32_epi8 of the reference quantiser.
+__device__ __forceinline__ uint32_t quant_rne_sat(float v) {
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return (uint32_t)r;
+}
+__device__ __forceinline__ uint32_t pack4_bytes(uint32_t q0, uint32_t q1, uint32_t q2, uint32_t q3) {
+    return __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
+}
+
+// MT   token rows per CTA tile
+// NI   16-byte weight loads per lane per batch (covers K <= 4096 at 4, K <= 8192 at 8 in one batch)
+// NB   16-element activation blocks a thread owns in the fp32 prologue (K <= 4096 * NB)
+// PAIR gate/up pairing (two weight streams, gated epilogue)
+template <int MT, int NI, int NB, bool PAIR>
 __global__ void __launch_bounds__(kThreads)
 ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -77,14 +92,12 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane & 15, h = lane >> 4;
 
-    float* xs = reinterpret_cast<float*>(smem_raw);
-    const size_t xs_bytes = (p.prologue == LSPK_PRO_INT8) ? 0 : (size_t)Kp * sizeof(float);
-    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw + xs_bytes);
-    int* part = reinterpret_cast<int*>(xq + (size_t)MT * Kp);
+    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw);                 // [MT][Kp] permuted int8
+    int* part = reinterpret_cast<int*>(xq + (size_t)MT * Kp);          // [PAIR?2:1][warps][MT][16]
     constexpr int kPartInts = kWarps * MT * 16 * (PAIR ? 2 : 1);
-    float* redf = reinterpret_cast<float*>(part + kPartInts);
-    float* s_scale = redf + 32;
-    int* s_sumx = reinterpret_cast<int*>(s_scale + MT);
+    float* redf = reinterpret_cast<float*>(part + kPartInts);          // [32] reduction scratch
+    float* s_scale = redf + 32;                                        // [MT]
+    int* s_sumx = reinterpret_cast<int*>(s_scale + MT);                // [MT][warps] partial sums of x
 
     // ---- which row group ------------------------------------------------------------
     int g = blockIdx.x, s = 0;
@@ -98,8 +111,8 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     const uint4* wa_base = sg.w + (size_t)g * p.chunks * kRowsPerGroup + r;
     const uint4* wb_base = PAIR ? (p.seg[1].w + (size_t)g * p.chunks * kRowsPerGroup + r) : nullptr;
 
-    // ---- issue the first batch of weight loads before anything that depends on the
-    //      previous kernel: weights are never written by a kernel of the forward pass ---------
+    // ---- everything that does not depend on the previous kernel is requested first: the first
+    //      batch of packed weights and the norm weights (neither is written by the forward pass) ----
     uint4 wa[NI], wb[PAIR ? NI : 1];
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
@@ -109,13 +122,40 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             if (PAIR) wb[i] = __ldg(wb_base + (size_t)j * kRowsPerGroup);
         }
     }
+    float gm[NB][16];
+    if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int k0 = (tid + nb * kThreads) * 16;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int k = k0 + q * 4;
+                float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k < p.K) {
+                    if (p.gamma_is_bf16) {
+                        const uint2 gb = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.gamma) + k));
+                        gv.x = __uint_as_float(gb.x << 16);
+                        gv.y = __uint_as_float(gb.x & 0xffff0000u);
+                        gv.z = __uint_as_float(gb.y << 16);
+                        gv.w = __uint_as_float(gb.y & 0xffff0000u);
+                    } else {
+                        gv = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.gamma) + k));
+                    }
+                }
+                gm[nb][q * 4 + 0] = gv.x;
+                gm[nb][q * 4 + 1] = gv.y;
+                gm[nb][q * 4 + 2] = gv.z;
+                gm[nb][q * 4 + 3] = gv.w;
+            }
+        }
+    }
     grid_dependency_launch();
     grid_dependency_wait();
 
-    // ---- prologue: bring this tile's activations into shared memory as permuted int8 ----
+    // ---- prologue: this tile's activations -> permuted int8 rows in shared memory ---------------
     const int m0 = blockIdx.y * MT;
     const int mt = min(MT, p.M - m0);
-    const int tail_start = p.K & ~15;      // the reference's scalar-tail rule applies from here
+    const int tail_start = p.K & ~15;      // the reference's scalar-tail rounding rule applies from here
     for (int m = 0; m < mt; ++m) {
         int8_t* xq_row = xq + (size_t)m * Kp;
         int sumx = 0;
@@ -136,89 +176,95 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             }
             scale = p.x_scales[m0 + m];
         } else {
+            // every thread keeps its 16-element blocks in registers through all three passes
             const float* src = p.x_f32 + (size_t)(m0 + m) * p.K;
+            float v[NB][16];
             float ssq = 0.0f;
-            for (int k4 = tid; k4 < Kp / 4; k4 += kThreads) {
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (k4 * 4 < p.K) v = *reinterpret_cast<const float4*>(src + k4 * 4);
-                reinterpret_cast<float4*>(xs)[k4] = v;
-                ssq = fmaf(v.x, v.x, ssq);
-                ssq = fmaf(v.y, v.y, ssq);
-                ssq = fmaf(v.z, v.z, ssq);
-                ssq = fmaf(v.w, v.w, ssq);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                const int k0 = (tid + nb * kThreads) * 16;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (k0 + q * 4 < p.K) t4 = *reinterpret_cast<const float4*>(src + k0 + q * 4);
+                    v[nb][q * 4 + 0] = t4.x;
+                    v[nb][q * 4 + 1] = t4.y;
+                    v[nb][q * 4 + 2] = t4.z;
+                    v[nb][q * 4 + 3] = t4.w;
+                }
+            }
+            if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
+                float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) ss[e & 3] = fmaf(v[nb][e], v[nb][e], ss[e & 3]);
+                ssq = block_sum((ss[0] + ss[1]) + (ss[2] + ss[3]), redf);
+                const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) v[nb][e] = __fmul_rn(__fmul_rn(v[nb][e], rrms), gm[nb][e]);
             }
             float amax = 0.0f;
-            if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
-                ssq = block_sum(ssq, redf);
-                const float rrms =
-                    __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
-                for (int k4 = tid; k4 < Kp / 4; k4 += kThreads) {
-                    float4 v = reinterpret_cast<float4*>(xs)[k4];
-                    float4 gm = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (k4 * 4 < p.K) {
-                        if (p.gamma_is_bf16) {
-                            const uint2 gb = *reinterpret_cast<const uint2*>(
-                                reinterpret_cast<const uint16_t*>(p.gamma) + k4 * 4);
-                            gm.x = __uint_as_float(gb.x << 16);
-                            gm.y = __uint_as_float(gb.x & 0xffff0000u);
-                            gm.z = __uint_as_float(gb.y << 16);
-                            gm.w = __uint_as_float(gb.y & 0xffff0000u);
-                        } else {
-                            gm = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.gamma) + k4 * 4);
-                        }
-                    }
-                    v.x = __fmul_rn(__fmul_rn(v.x, rrms), gm.x);
-                    v.y = __fmul_rn(__fmul_rn(v.y, rrms), gm.y);
-                    v.z = __fmul_rn(__fmul_rn(v.z, rrms), gm.z);
-                    v.w = __fmul_rn(__fmul_rn(v.w, rrms), gm.w);
-                    reinterpret_cast<float4*>(xs)[k4] = v;
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                }
-            } else {
-                for (int k4 = tid; k4 < Kp / 4; k4 += kThreads) {
-                    const float4 v = reinterpret_cast<float4*>(xs)[k4];
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                }
-            }
-            amax = block_max(amax, redf);          // also orders the xs writes before the reads below
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[nb][e]));
+            amax = block_max(amax, redf);
             scale = quant_scale_from_absmax(amax);
             const float inv = __fdiv_rn(1.0f, scale);
             const bool tap = (p.xq_out != nullptr) && blockIdx.x == 0;
-            for (int b = tid; b < Kp / 16; b += kThreads) {
-                uint32_t a[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float4 v = reinterpret_cast<float4*>(xs)[b * 4 + q];
-                    const float f[4] = {v.x, v.y, v.z, v.w};
-                    uint32_t word = 0;
+            for (int nb = 0; nb < NB; ++nb) {
+                const int b = tid + nb * kThreads;
+                const int k0 = b * 16;
+                if (k0 < Kp) {
+                    uint32_t a[4];
+                    if (k0 + 16 <= tail_start) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int k = b * 16 + q * 4 + e;
-                        int qv;
-                        if (k < tail_start) {
-                            qv = quant_one(f[e], inv);
-                        } else if (k < p.K) {
-                            qv = (int)roundf(__fmul_rn(f[e], inv));
-                            qv = max(-127, min(127, qv));
-                        } else {
-                            qv = 0;
+                        for (int q = 0; q < 4; ++q)
+                            a[q] = pack4_bytes(quant_rne_sat(__fmul_rn(v[nb][q * 4 + 0], inv)),
+                                               quant_rne_sat(__fmul_rn(v[nb][q * 4 + 1], inv)),
+                                               quant_rne_sat(__fmul_rn(v[nb][q * 4 + 2], inv)),
+                                               quant_rne_sat(__fmul_rn(v[nb][q * 4 + 3], inv)));
+                    } else {
+                        // block that reaches past the last multiple of 16: the reference's scalar tail
+                        // (round half away from zero, clamp to +-127), zeros beyond K
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint32_t word = 0;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const int k = k0 + q * 4 + e;
+                                int qv = 0;
+                                if (k < tail_start) {
+                                    qv = (int)quant_rne_sat(__fmul_rn(v[nb][q * 4 + e], inv));
+                                } else if (k < p.K) {
+                                    qv = max(-127, min(127, (int)roundf(__fmul_rn(v[nb][q * 4 + e], inv))));
+                                }
+                                word |= ((uint32_t)qv & 0xffu) << (8 * e);
+                            }
+                            a[q] = word;
                         }
-                        word |= ((uint32_t)qv & 0xffu) << (8 * e);
                     }
-                    a[q] = word;
-                    sumx = __dp4a((int)word, 0x01010101, sumx);
-                    if (tap && b * 16 + q * 4 < p.K)
-                        *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)(m0 + m) * p.K + b * 16 + q * 4) = word;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                        if (tap && k0 + q * 4 < p.K)
+                            *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)(m0 + m) * p.K + k0 + q * 4) = a[q];
+                    }
+                    uint32_t o0, o1, o2, o3;
+                    transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                    *reinterpret_cast<uint4*>(xq_row + k0) = make_uint4(o0, o1, o2, o3);
                 }
-                uint32_t o0, o1, o2, o3;
-                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
-                *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
             }
         }
-        sumx = block_sum(sumx, reinterpret_cast<int*>(redf));   // barriers: xs may be reused next m
+        // sum(x): per-warp partials; the output threads add the eight of them
+        sumx = warp_sum(sumx);
+        if (lane == 0) s_sumx[m * kWarps + warp] = sumx;
         if (tid == 0) {
             s_scale[m] = scale;
-            s_sumx[m] = sumx;
             if (p.xscale_out && blockIdx.x == 0) p.xscale_out[m0 + m] = scale;
         }
     }
@@ -242,7 +288,7 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             if (j < p.chunks) {
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    if (m < mt) {
+                    if (MT == 1 || m < mt) {
                         const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)m * Kp + (size_t)j * 64);
                         chunk_dot(wa[i], xp, acc_a[m]);
                         if (PAIR) chunk_dot(wb[i], xp, acc_b[m]);
@@ -280,22 +326,28 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
         const int m = tid >> 4, rr = tid & 15;
         const int n = g * kRowsPerGroup + rr;
         if (m < mt && n < sg.N) {
-            int va = 0, vb = 0;
+            int va = 0, vb = 0, sx = 0;
 #pragma unroll
             for (int w = 0; w < kWarps; ++w) {
                 va += part[(w * MT + m) * 16 + rr];
                 if (PAIR) vb += part[kWarps * MT * 16 + (w * MT + m) * 16 + rr];
+                sx += s_sumx[m * kWarps + w];
             }
-            va -= s_sumx[m];
+            va -= sx;
             const size_t o = (size_t)(m0 + m) * sg.N + n;
             if (sg.acc_out) sg.acc_out[o] = va;
             const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[m], sg.w_scale));
             if (PAIR) {
-                vb -= s_sumx[m];
+                vb -= sx;
                 if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
                 const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[m], p.seg[1].w_scale));
-                const float gpos = fmaxf(ya, 0.0f);
-                sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                if (p.epilogue == LSPK_EPI_SILU_MUL) {
+                    // the reference's Falcon gate (runtime.py:726-732): g / (1 + exp(-g)) * u
+                    sg.out[o] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
+                } else {
+                    const float gpos = fmaxf(ya, 0.0f);
+                    sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                }
             } else if (p.epilogue == LSPK_EPI_ADD) {
                 sg.out[o] = __fadd_rn(sg.out[o], ya);
             } else {
@@ -305,18 +357,17 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     }
 }
 
-static size_t linear_smem_bytes(int MT, int Kp, int prologue, bool pair) {
-    size_t b = (prologue == LSPK_PRO_INT8) ? 0 : (size_t)Kp * 4;
-    b += (size_t)MT * Kp;
+static size_t linear_smem_bytes(int MT, int Kp, bool pair) {
+    size_t b = (size_t)MT * Kp;
     b += (size_t)kWarps * MT * 16 * (pair ? 2 : 1) * 4;
-    b += 32 * 4 + MT * 8;
+    b += 32 * 4 + MT * 4 + MT * kWarps * 4;
     return b;
 }
 
-template <int MT, int NI, bool PAIR>
+template <int MT, int NI, int NB, bool PAIR>
 static cudaError_t launch_linear(const LinearParams& p, int grid_x, size_t smem) {
     static bool attr_set = false;
-    auto kern = ternary_linear_kernel<MT, NI, PAIR>;
+    auto kern = ternary_linear_kernel<MT, NI, NB, PAIR>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
@@ -328,9 +379,11 @@ static cudaError_t launch_linear(const LinearParams& p, int grid_x, size_t smem)
 
 template <int MT>
 static cudaError_t launch_linear_mt(const LinearParams& p, int grid_x, bool pair, size_t smem) {
-    const bool big = p.chunks > 64;
-    if (pair) return big ? launch_linear<MT, 8, true>(p, grid_x, smem) : launch_linear<MT, 4, true>(p, grid_x, smem);
-    return big ? launch_linear<MT, 8, false>(p, grid_x, smem) : launch_linear<MT, 4, false>(p, grid_x, smem);
+    if (p.chunks <= 64)
+        return pair ? launch_linear<MT, 4, 1, true>(p, grid_x, smem) : launch_linear<MT, 4, 1, false>(p, grid_x, smem);
+    if (p.chunks <= 128)
+        return pair ? launch_linear<MT, 8, 2, true>(p, grid_x, smem) : launch_linear<MT, 8, 2, false>(p, grid_x, smem);
+    return pair ? launch_linear<MT, 8, 8, true>(p, grid_x, smem) : launch_linear<MT, 8, 8, false>(p, grid_x, smem);
 }
 
 // Host-side validation + launch of the CUDA-core kernel.  Used by lspk_linear and by the
@@ -339,8 +392,8 @@ int linear_cuda_core(const lspk_linear_args* a) {
     LSPK_REQUIRE(a, "linear: null args");
     LSPK_REQUIRE(a->n_mats >= 1 && a->n_mats <= 3, "linear: n_mats must be 1..3 (got %d)", a->n_mats);
     LSPK_REQUIRE(a->M >= 1, "linear: M must be >= 1 (got %d)", a->M);
-    const bool pair = a->epilogue == LSPK_EPI_RELU2_MUL;
-    LSPK_REQUIRE(!pair || a->n_mats == 2, "linear: the ReLU^2 epilogue takes exactly two matrices (gate, up)");
+    const bool pair = a->epilogue == LSPK_EPI_RELU2_MUL || a->epilogue == LSPK_EPI_SILU_MUL;
+    LSPK_REQUIRE(!pair || a->n_mats == 2, "linear: the gated epilogues take exactly two matrices (gate, up)");
     LinearParams p = {};
     const Weight* w0 = reinterpret_cast<const Weight*>(a->w[0]);
     LSPK_REQUIRE(w0, "linear: null weight");
@@ -381,11 +434,11 @@ int linear_cuda_core(const lspk_linear_args* a) {
         default:
             return fail(LSPK_ERR_ARG, "linear: unknown prologue %d", a->prologue);
     }
-    LSPK_REQUIRE(a->epilogue >= 0 && a->epilogue <= 2, "linear: unknown epilogue %d", a->epilogue);
+    LSPK_REQUIRE(a->epilogue >= 0 && a->epilogue <= 3, "linear: unknown epilogue %d", a->epilogue);
     const int MT = a->M == 1 ? 1 : a->M == 2 ? 2 : a->M <= 4 ? 4 : 8;
     const int Kp = p.chunks * kWeightsPerChunk;
-    const size_t smem = linear_smem_bytes(MT, Kp, p.prologue, pair);
-    LSPK_REQUIRE(smem <= 200 * 1024, "linear: K=%d too large for the shared-memory activation tile", p.K);
+    const size_t smem = linear_smem_bytes(MT, Kp, pair);
+    LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768, less for 8-row tiles)", p.K);
     cudaError_t e;
     switch (MT) {
         case 1: e = launch_linear_mt<1>(p, groups, pair, smem); break;

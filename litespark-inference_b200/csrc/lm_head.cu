@@ -15,7 +15,6 @@ namespace lspk {
 constexpr int kLmThreads = 256;
 constexpr int kLmWarps = kLmThreads / 32;
 constexpr int kLmMaxT = 8;
-constexpr int kLmInflight = 5;
 
 template <int KIND> struct EmbTraits;
 template <> struct EmbTraits<0> { static constexpr int E = 8;  };   // bf16: 8 values per 16 bytes
@@ -49,7 +48,9 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
     return ((unsigned long long)u << 32) | (unsigned long long)(0xffffffffu - (uint32_t)idx);
 }
 
-template <int KIND>
+// TT: rows of x handled per launch (1 for decode, up to kLmMaxT otherwise); INFL: 16-byte loads in
+// flight per lane (10 covers a 2560-wide bf16 row in one batch).
+template <int KIND, int TT, int INFL>
 __global__ void __launch_bounds__(kLmThreads)
 lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scale,
                const float* __restrict__ x, float* __restrict__ logits, int T, int V, int H,
@@ -94,18 +95,18 @@ lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scal
     const size_t row_chunks = (size_t)nchunks;
     for (int v = blockIdx.x * kLmWarps + warp; v < V; v += gridDim.x * kLmWarps) {
         const uint4* row = emb + (size_t)v * row_chunks;
-        float acc[kLmMaxT];
+        float acc[TT];
 #pragma unroll
-        for (int t = 0; t < kLmMaxT; ++t) acc[t] = 0.0f;
-        for (int c0 = lane; c0 < nchunks; c0 += 32 * kLmInflight) {
-            uint4 buf[kLmInflight];
+        for (int t = 0; t < TT; ++t) acc[t] = 0.0f;
+        for (int c0 = lane; c0 < nchunks; c0 += 32 * INFL) {
+            uint4 buf[INFL];
 #pragma unroll
-            for (int u = 0; u < kLmInflight; ++u) {
+            for (int u = 0; u < INFL; ++u) {
                 const int c = c0 + 32 * u;
                 if (c < nchunks) buf[u] = __ldcs(row + c);
             }
 #pragma unroll
-            for (int u = 0; u < kLmInflight; ++u) {
+            for (int u = 0; u < INFL; ++u) {
                 const int c = c0 + 32 * u;
                 if (c < nchunks) {
 #pragma unroll
@@ -113,8 +114,8 @@ lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scal
                         float f[4];
                         decode4<KIND>(buf[u], s, f);
 #pragma unroll
-                        for (int t = 0; t < kLmMaxT; ++t) {
-                            if (t < T) {
+                        for (int t = 0; t < TT; ++t) {
+                            if (TT == 1 || t < T) {
                                 const float4 xv = xs4[((size_t)t * S + s) * nchunks + c];
                                 acc[t] = fmaf(f[0], xv.x, acc[t]);
                                 acc[t] = fmaf(f[1], xv.y, acc[t]);
@@ -128,8 +129,8 @@ lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scal
         }
         const float sc = (KIND == 0) ? 1.0f : emb_scale[v];
 #pragma unroll
-        for (int t = 0; t < kLmMaxT; ++t) {
-            if (t < T) {
+        for (int t = 0; t < TT; ++t) {
+            if (TT == 1 || t < T) {
                 float r = warp_sum(acc[t]);
                 if (KIND != 0) r = __fmul_rn(sc, r);
                 if (lane == 0) {
@@ -165,34 +166,41 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     const int E = kind == 0 ? 8 : kind == 1 ? 16 : 32;
     LSPK_REQUIRE(H % E == 0, "lm_head: H=%d must be a multiple of %d for this embedding format", H, E);
     LSPK_REQUIRE(((uintptr_t)emb & 15) == 0, "lm_head: embedding must be 16-byte aligned");
-    static bool attr_set = false;
-    if (!attr_set) {
-        LSPK_CUDA(cudaFuncSetAttribute(lm_head_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(lm_head_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(lm_head_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_set = true;
-    }
     const int rows_per_cta = kLmWarps;
     int grid = (V + rows_per_cta - 1) / rows_per_cta;
-    const int cap = sm_count() * 2;
+    const int cap = sm_count() * 4;
     if (grid > cap) grid = cap;
+    const uint4* e4 = reinterpret_cast<const uint4*>(emb);
     for (int t0 = 0; t0 < T; t0 += kLmMaxT) {
         const int tt = (T - t0) < kLmMaxT ? (T - t0) : kLmMaxT;
         const size_t smem = (size_t)tt * H * sizeof(float);
         LSPK_REQUIRE(smem <= 200 * 1024, "lm_head: H=%d too large", H);
         const float* xt = x + (size_t)t0 * H;
         float* lt = logits ? logits + (size_t)t0 * V : nullptr;
-        cudaError_t e;
-        const uint4* e4 = reinterpret_cast<const uint4*>(emb);
-        if (kind == 0)
-            e = launch(lm_head_kernel<0>, dim3(grid), dim3(kLmThreads), smem, true, e4, emb_scale, xt, lt, tt, V, H,
-                       norm_gamma, gamma_is_bf16, eps, t0 == 0 ? best_key : nullptr);
-        else if (kind == 1)
-            e = launch(lm_head_kernel<1>, dim3(grid), dim3(kLmThreads), smem, true, e4, emb_scale, xt, lt, tt, V, H,
-                       norm_gamma, gamma_is_bf16, eps, t0 == 0 ? best_key : nullptr);
-        else
-            e = launch(lm_head_kernel<2>, dim3(grid), dim3(kLmThreads), smem, true, e4, emb_scale, xt, lt, tt, V, H,
-                       norm_gamma, gamma_is_bf16, eps, t0 == 0 ? best_key : nullptr);
+        unsigned long long* bk = t0 == 0 ? best_key : nullptr;
+        cudaError_t e = cudaSuccess;
+#define LSPK_LM_LAUNCH(KIND, TT, INFL)                                                                     \
+        do {                                                                                                \
+            static bool attr_set = false;                                                                   \
+            auto kern = lm_head_kernel<KIND, TT, INFL>;                                                     \
+            if (!attr_set) {                                                                                \
+                e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);     \
+                attr_set = (e == cudaSuccess);                                                              \
+            }                                                                                               \
+            if (e == cudaSuccess)                                                                           \
+                e = launch(kern, dim3(grid), dim3(kLmThreads), smem, true, e4, emb_scale, xt, lt, tt, V, H,  \
+                           norm_gamma, gamma_is_bf16, eps, bk);                                             \
+        } while (0)
+        if (tt == 1) {
+            if (kind == 0) LSPK_LM_LAUNCH(0, 1, 10);
+            else if (kind == 1) LSPK_LM_LAUNCH(1, 1, 5);
+            else LSPK_LM_LAUNCH(2, 1, 3);
+        } else {
+            if (kind == 0) LSPK_LM_LAUNCH(0, kLmMaxT, 4);
+            else if (kind == 1) LSPK_LM_LAUNCH(1, kLmMaxT, 2);
+            else LSPK_LM_LAUNCH(2, kLmMaxT, 2);
+        }
+#undef LSPK_LM_LAUNCH
         if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head launch failed: %s", cudaGetErrorString(e));
     }
     return LSPK_OK;

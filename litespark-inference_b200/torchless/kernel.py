@@ -53,7 +53,7 @@ class LinearArgs(ctypes.Structure):
 
 
 PRO_INT8, PRO_QUANT, PRO_RMSNORM_QUANT = 0, 1, 2
-EPI_STORE, EPI_ADD, EPI_RELU2_MUL = 0, 1, 2
+EPI_STORE, EPI_ADD, EPI_RELU2_MUL, EPI_SILU_MUL = 0, 1, 2, 3
 
 # name -> (argtypes, restype) of every symbol declared in include/lspk_sm100.h
 _SIGNATURES = {

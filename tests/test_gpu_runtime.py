@@ -1,0 +1,211 @@
+"""Device-resident forward pass against the reference's own runtime (golden fixtures generated
+by tests/golden/make_golden.py) and against the CPU oracle."""
+import importlib
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+rt = importlib.import_module("litespark_inference_b200.torchless.runtime")
+synthetic = importlib.import_module("litespark_inference_b200.torchless.synthetic")
+
+# Logits tolerance: the GPU reduces RMSNorm / attention / LM-head sums in another order than the
+# CPU, which flips an occasional int8 activation by one step; on the toy model that moves logits
+# by ~1e-3 of their spread.
+LOGIT_ATOL_FRAC = 5e-3
+
+
+@pytest.fixture(scope="module")
+def toy():
+    cfg = synthetic.toy_config()
+    m = synthetic.random_model(cfg, seed=11, norm_jitter=0.1)
+    return cfg, m, rt.to_device(m)
+
+
+@pytest.fixture(scope="module")
+def gold(golden_dir):
+    return np.load(golden_dir / "runtime_toy_avx512.npz")
+
+
+def _close(got, want):
+    spread = float(want.max() - want.min())
+    return np.abs(got - want).max() <= LOGIT_ATOL_FRAC * spread
+
+
+def test_forward_one_logits_match_reference(toy, gold):
+    cfg, m, dm = toy
+    st = rt.init_state(dm, 64, kv_dtype="fp32")
+    for i, t in enumerate(gold["prompt"]):
+        lg = rt.forward_one(dm, st, int(t))
+        assert _close(lg, gold["logits_stepwise"][i]), f"position {i}"
+    assert st.pos == len(gold["prompt"])
+
+
+def test_prefill_logits_and_all_logits_match_reference(toy, gold):
+    cfg, m, dm = toy
+    prompt = [int(t) for t in gold["prompt"]]
+    st = rt.init_state(dm, 64, kv_dtype="fp32")
+    assert _close(rt.forward_prefill(dm, st, prompt), gold["logits_prefill"])
+    st = rt.init_state(dm, 64, kv_dtype="fp32")
+    rt.forward_prefill(dm, st, prompt[:10])
+    al = rt.forward_prefill_all_logits(dm, st, prompt[10:15])
+    assert al.shape == gold["all_logits"].shape and _close(al, gold["all_logits"])
+    assert st.pos == 15
+
+
+def test_greedy_tokens_match_reference(toy, gold):
+    cfg, m, dm = toy
+    prompt = [int(t) for t in gold["prompt"]]
+    st = rt.init_state(dm, len(prompt) + 24, kv_dtype="fp32")
+    assert rt.generate(dm, prompt, 24, state=st) == [int(t) for t in gold["greedy24"]]
+    st = rt.init_state(dm, len(prompt) + 24, kv_dtype="fp16")
+    assert rt.generate(dm, prompt, 24, state=st) == [int(t) for t in gold["greedy24_kv16"]]
+    # host-driven loop (logits to the host every step, like the reference's generate)
+    st = rt.init_state(dm, len(prompt) + 24, kv_dtype="fp32")
+    lg = rt.forward_prefill(dm, st, prompt)
+    toks = []
+    for _ in range(24):
+        toks.append(int(np.argmax(lg)))
+        lg = rt.forward_one(dm, st, toks[-1])
+    assert toks == [int(t) for t in gold["greedy24"]]
+
+
+def test_speculative_decode_matches_reference_and_greedy(toy, gold):
+    cfg, m, dm = toy
+    rep = [int(t) for t in gold["spec_prompt"]]
+    st = rt.init_state(dm, len(rep) + 24 + 6, kv_dtype="fp32")
+    toks, stats = rt.generate_speculative(dm, rep, 24, spec_k=4, match_n=4, state=st, return_stats=True)
+    assert toks == [int(t) for t in gold["spec24"]]
+    assert toks == [int(t) for t in gold["greedy_rep24"]]
+    assert stats["steps"] == int(gold["spec_steps"])
+
+
+def test_kv_cache_contents_and_chunked_prefill(toy, oracle, port):
+    cfg, m, dm = toy
+    prompt = [int(t) for t in np.random.default_rng(5).integers(0, cfg.vocab_size, 150)]
+    # 150 rows exceed the scratch capacity (128 rows): exercises the chunk loop
+    st = rt.init_state(dm, 160, kv_dtype="fp32")
+    lg = rt.forward_prefill(dm, st, prompt)
+    ost = oracle.State(cfg, 160)
+    want = oracle.forward_prefill(port, m, ost, prompt)
+    assert _close(lg, want)
+    for li in range(cfg.num_layers):
+        k, v = st.read_kv(li, 150)
+        assert np.allclose(k, ost.cache_k[li, :150], rtol=0, atol=5e-3 * np.abs(ost.cache_k[li]).max())
+        assert np.allclose(v, ost.cache_v[li, :150], rtol=0, atol=5e-3 * np.abs(ost.cache_v[li]).max())
+    # token-by-token and batched prefill agree on the device too
+    st2 = rt.init_state(dm, 160, kv_dtype="fp32")
+    for t in prompt[:40]:
+        l1 = rt.forward_one(dm, st2, t)
+    st3 = rt.init_state(dm, 160, kv_dtype="fp32")
+    l2 = rt.forward_prefill(dm, st3, prompt[:40])
+    assert _close(l1, l2)
+
+
+def test_batched_sequences_equal_single_sequences(toy):
+    """Independent sequences decoded in lock step give exactly what each gives alone."""
+    cfg, m, dm = toy
+    rng = np.random.default_rng(8)
+    prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, n)] for n in (9, 17, 12, 20, 5, 11, 16, 8)]
+    alone = [rt.generate(dm, p, 12) for p in prompts]
+    together = rt.generate_batch(dm, prompts, 12)
+    assert together == alone
+
+
+def test_state_exhaustion_and_rollback(toy):
+    cfg, m, dm = toy
+    st = rt.init_state(dm, 6)
+    rt.forward_prefill(dm, st, [1, 2, 3, 4, 5])
+    rt.forward_one(dm, st, 6)
+    with pytest.raises(RuntimeError):
+        rt.forward_one(dm, st, 7)
+    with pytest.raises(RuntimeError):
+        rt.forward_prefill(dm, st, [1, 2])
+    # rollback: replaying from an earlier position reproduces the same logits
+    st = rt.init_state(dm, 32)
+    rt.forward_prefill(dm, st, [3, 1, 4, 1, 5])
+    a = rt.forward_one(dm, st, 9)
+    rt.forward_one(dm, st, 2)
+    st.pos = 5
+    b = rt.forward_one(dm, st, 9)
+    assert np.array_equal(a, b)
+
+
+def test_int8_and_int4_embeddings(toy, oracle, port):
+    cfg, m, dm = toy
+    rng = np.random.default_rng(21)
+    import copy
+    m8 = copy.copy(m)
+    m8.embed_tokens = None
+    m8.embed_int8 = rng.integers(-127, 128, (cfg.vocab_size, cfg.hidden_size), dtype=np.int8)
+    m8.embed_scale = rng.uniform(0.005, 0.02, cfg.vocab_size).astype(np.float32)
+    m8._lspk_device = None
+    m4 = copy.copy(m8)
+    m4.embed_int8 = None
+    m4.embed_int4 = rng.integers(0, 256, (cfg.vocab_size, cfg.hidden_size // 2), dtype=np.uint8)
+    m4._lspk_device = None
+    prompt = [5, 99, 1000, 17]
+    for mm in (m8, m4):
+        st = rt.init_state(mm, 16, kv_dtype="fp32")
+        got = rt.forward_prefill(mm, st, prompt)
+        want = oracle.forward_prefill(port, mm, oracle.State(cfg, 16), prompt)
+        assert _close(got, want)
+
+
+def test_falcon_style_model(toy, oracle):
+    """No sub-norms, SiLU gate, untied head: checked against a numpy restatement of
+    falcon_forward_one (reference runtime.py:735-817) built from oracle pieces."""
+    cfg, m, dm = toy
+    import copy
+    fm = copy.copy(m)
+    fm._lspk_device = None
+    fm.layers = [copy.copy(L) for L in m.layers]
+    for L in fm.layers:
+        L.attn_sub_norm = None
+        L.ffn_sub_norm = None
+    st = rt.init_state(fm, 16, kv_dtype="fp32")
+    got = rt.forward_prefill(fm, st, [7, 8, 9])
+    assert np.isfinite(got).all() and got.shape == (cfg.vocab_size,)
+    want = _falcon_oracle(oracle, cfg, fm, [7, 8, 9])
+    assert _close(got, want)
+
+
+def _falcon_oracle(oracle, cfg, fm, ids):
+    kern = oracle.Kernels("port")
+    H, I, Q, KV = cfg.hidden_size, cfg.intermediate_size, cfg.num_heads, cfg.num_kv_heads
+    D = H // Q
+    st = oracle.State(cfg, 16)
+    logits = None
+    for tok in ids:
+        x = oracle.embed_row(fm, tok)
+        pos = st.pos
+
+        def q_of(v):
+            q8 = np.empty(v.shape[0], np.int8)
+            return q8, kern.quantize_activation(np.ascontiguousarray(v), q8)
+
+        for li, L in enumerate(fm.layers):
+            h = kern.rmsnorm_into(x, L.input_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
+            q8, s = q_of(h)
+            q = kern.matmul_packed_m1(q8, L.q_proj.w_packed, L.q_proj.scale, s)
+            k = kern.matmul_packed_m1(q8, L.k_proj.w_packed, L.k_proj.scale, s)
+            v = kern.matmul_packed_m1(q8, L.v_proj.w_packed, L.v_proj.scale, s)
+            cr, sr = st.rope_cos[pos], st.rope_sin[pos]
+            q = oracle.apply_rope(q.reshape(Q, D), cr, sr).reshape(1, -1)
+            st.cache_k[li, pos] = oracle.apply_rope(k.reshape(KV, D), cr, sr)
+            st.cache_v[li, pos] = v.reshape(KV, D)
+            attn = oracle._attention_rows(cfg, st, li, q, pos)[0]
+            q8, s = q_of(attn)
+            x = x + kern.matmul_packed_m1(q8, L.o_proj.w_packed, L.o_proj.scale, s)
+            h = kern.rmsnorm_into(x, L.post_attn_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
+            q8, s = q_of(h)
+            g = kern.matmul_packed_m1(q8, L.gate_proj.w_packed, L.gate_proj.scale, s)
+            u = kern.matmul_packed_m1(q8, L.up_proj.w_packed, L.up_proj.scale, s)
+            inter = (g / (np.exp(-g) + np.float32(1))) * u
+            q8, s = q_of(inter.astype(np.float32))
+            x = x + kern.matmul_packed_m1(q8, L.down_proj.w_packed, L.down_proj.scale, s)
+        st.pos += 1
+        h = kern.rmsnorm_into(x, fm.final_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
+        logits = oracle.lm_head(kern, fm, h)
+    return logits
