@@ -65,6 +65,13 @@ int lspk_flush_l2(void);                /* overwrite a buffer larger than L2    
 int lspk_timer_start(void);
 int lspk_timer_stop(float* ms_out);
 
+/* In-kernel phase trace (measurement aid): after lspk_trace_begin, CTA 0 of each traced kernel
+ * appends a record of 16 uint64 words [kernel id, globaltimer ns at entry, SM clock at phase marks
+ * ..., globaltimer ns at exit]; lspk_trace_read copies the records out and clears the counter.
+ * Kernels captured into a CUDA graph before lspk_trace_begin do not record. */
+int lspk_trace_begin(int max_records);
+int lspk_trace_read(unsigned long long* host_out, int max_records, int* n_out);
+
 /* ------------------------------------------------------------------------------------ */
 /* (a) Packed-weight upload: reference layout <-> device layout                          */
 /*     Reference layout: uint8 [N, K/4], byte = (w0+1)|(w1+1)<<2|(w2+1)<<4|(w3+1)<<6       */

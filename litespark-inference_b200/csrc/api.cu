@@ -38,6 +38,11 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+static unsigned long long* g_trace = nullptr;
+static int g_trace_cap = 0;
+unsigned long long* trace_buffer() { return g_trace; }
+int trace_capacity() { return g_trace_cap; }
+
 cudaStream_t stream() { return g_stream; }
 bool pdl_enabled() { return g_pdl; }
 int sm_count() { return g_sm_count; }
@@ -173,6 +178,34 @@ int lspk_flush_l2(void) {
     if (!g_flush_buf) LSPK_CUDA(cudaMalloc(&g_flush_buf, kFlushBytes));
     static int v = 0;
     LSPK_CUDA(cudaMemsetAsync(g_flush_buf, ++v & 0xff, kFlushBytes, g_stream));
+    return LSPK_OK;
+}
+
+// Install a device buffer for in-kernel phase traces.  Kernels launched (or captured into a graph)
+// afterwards record into it; lspk_trace_read copies the records out and resets the counter.
+int lspk_trace_begin(int max_records) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_REQUIRE(max_records >= 1, "lspk_trace_begin: max_records must be positive");
+    if (g_trace) cudaFree(g_trace);
+    g_trace = nullptr;
+    const size_t bytes = (1 + (size_t)max_records * kTraceWords) * 8;
+    LSPK_CUDA(cudaMalloc((void**)&g_trace, bytes));
+    LSPK_CUDA(cudaMemset(g_trace, 0, bytes));
+    LSPK_CUDA(cudaDeviceSynchronize());
+    g_trace_cap = max_records;
+    return LSPK_OK;
+}
+
+int lspk_trace_read(unsigned long long* host_out, int max_records, int* n_out) {
+    LSPK_REQUIRE(g_trace && host_out && n_out, "lspk_trace_read: no trace buffer installed");
+    LSPK_CUDA(cudaStreamSynchronize(g_stream));
+    unsigned long long n = 0;
+    LSPK_CUDA(cudaMemcpy(&n, g_trace, 8, cudaMemcpyDeviceToHost));
+    if (n > (unsigned long long)g_trace_cap) n = g_trace_cap;
+    if (n > (unsigned long long)max_records) n = max_records;
+    LSPK_CUDA(cudaMemcpy(host_out, g_trace + 1, (size_t)n * kTraceWords * 8, cudaMemcpyDeviceToHost));
+    LSPK_CUDA(cudaMemset(g_trace, 0, 8));
+    *n_out = (int)n;
     return LSPK_OK;
 }
 

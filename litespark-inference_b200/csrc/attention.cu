@@ -111,9 +111,13 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     float* part = raw + 2 * D;            // [NG][D] value partial sums
     float* sc = part + NG * D;            // [n] scores / probabilities
     __shared__ float red[32];
+    PhaseTrace tr;
+    tr.begin(p.trace, p.trace_cap, 2);
+    tr.mark();                                   // 0: entry
 
     grid_dependency_launch();
     grid_dependency_wait();
+    tr.mark();                                   // 1: predecessor finished
 
     const int h = blockIdx.x, t = blockIdx.y;
     const int tid = threadIdx.x;
@@ -126,17 +130,39 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride + (size_t)kvh * D;
     const float* qrow = p.q + (size_t)t * p.Q * D + (size_t)h * D;
 
-    if (p.fused) {
-        const float* krow = p.k_cur + (size_t)t * kd + (size_t)kvh * D;
-        const float* vrow = p.v_cur + (size_t)t * kd + (size_t)kvh * D;
-        float vr = 0.0f, cr = 0.0f, sr = 0.0f;
-        if (tid < D) {
+    // ---- request everything up front: the row's own q/k/v and rope factors, this thread's key
+    //      row for the score phase and its first 16 value chunks for the value phase ----------------
+    constexpr int VB0 = 16;                     // value chunks requested before the scores exist
+    const int g = tid / TPK, c = tid % TPK;
+    float q_raw = 0.0f, k_raw = 0.0f, vr = 0.0f, cr = 0.0f, sr = 0.0f;
+    if (tid < D) {
+        q_raw = qrow[tid];
+        if (p.fused) {
             const int i = tid < half ? tid : tid - half;
-            raw[tid] = qrow[tid];
-            raw[D + tid] = krow[tid];
-            vr = vrow[tid];
+            k_raw = p.k_cur[(size_t)t * kd + (size_t)kvh * D + tid];
+            vr = p.v_cur[(size_t)t * kd + (size_t)kvh * D + tid];
             cr = p.rope_cos[(size_t)pos * half + i];
             sr = p.rope_sin[(size_t)pos * half + i];
+        }
+    }
+    uint4 kbuf[KB];
+    const bool k_from_cache = tid < n && !(p.fused && tid == pos);
+    if (k_from_cache) {
+        const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)tid * kd);
+#pragma unroll
+        for (int b = 0; b < KB; ++b) kbuf[b] = kp[b];
+    }
+    uint4 vbuf[VB0];
+#pragma unroll
+    for (int b = 0; b < VB0; ++b) {
+        const int i = g + b * NG;
+        if (i < n && !(p.fused && i == pos)) vbuf[b] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c);
+    }
+
+    if (p.fused) {
+        if (tid < D) {
+            raw[tid] = q_raw;
+            raw[D + tid] = k_raw;
         }
         __syncthreads();
         if (tid < D) {
@@ -159,9 +185,10 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
             }
         }
     } else {
-        if (tid < D) qs[tid] = qrow[tid];
+        if (tid < D) qs[tid] = q_raw;
     }
     __syncthreads();
+    tr.mark();                                   // 2: q/k rotated (own loads arrived)
 
     // ---- scores: thread per key ------------------------------------------------------------------
     const float inv_sqrt_d = 1.0f / sqrtf((float)D);
@@ -174,13 +201,14 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
             const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)i * kd);
 #pragma unroll
             for (int b0 = 0; b0 < NCH; b0 += KB) {
-                uint4 buf[KB];
+                if (b0 > 0 || i != tid) {
 #pragma unroll
-                for (int b = 0; b < KB; ++b) buf[b] = kp[b0 + b];
+                    for (int b = 0; b < KB; ++b) kbuf[b] = kp[b0 + b];
+                }
 #pragma unroll
                 for (int b = 0; b < KB; ++b) {
                     float f[VEC];
-                    KvVec<KVT>::unpack(buf[b], f);
+                    KvVec<KVT>::unpack(kbuf[b], f);
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) dot = fmaf(qs[(b0 + b) * VEC + e], f[e], dot);
                 }
@@ -188,7 +216,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         }
         sc[i] = __fmul_rn(dot, inv_sqrt_d);
     }
+    tr.mark();                                   // 3: own score done (key row arrived)
     __syncthreads();
+    tr.mark();                                   // 4: all scores visible
 
     // ---- softmax over sc[0..n) -----------------------------------------------------------------------
     float mx = -INFINITY;
@@ -203,14 +233,31 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     sum = block_sum(sum, red);
     for (int i = tid; i < n; i += kAttnThreads) sc[i] = __fdiv_rn(sc[i], sum);
     __syncthreads();
+    tr.mark();                                   // 5: softmax done
 
     // ---- weighted sum of values: TPK threads per key, NG key groups ---------------------------------
-    const int g = tid / TPK, c = tid % TPK;
     float o[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
-    constexpr int VB = 8;                                   // loads in flight per thread
-    for (int i0 = g; i0 < n; i0 += NG * VB) {
+    auto accumulate = [&](int i, const uint4& chunk) {
+        const float pi = sc[i];
+        float f[VEC];
+        if (p.fused && i == pos) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) f[e] = vs[c * VEC + e];
+        } else {
+            KvVec<KVT>::unpack(chunk, f);
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[e] = fmaf(pi, f[e], o[e]);
+    };
+#pragma unroll
+    for (int b = 0; b < VB0; ++b) {
+        const int i = g + b * NG;
+        if (i < n) accumulate(i, vbuf[b]);
+    }
+    constexpr int VB = 8;                                   // loads in flight per thread afterwards
+    for (int i0 = g + VB0 * NG; i0 < n; i0 += NG * VB) {
         uint4 buf[VB];
 #pragma unroll
         for (int b = 0; b < VB; ++b) {
@@ -221,20 +268,10 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
 #pragma unroll
         for (int b = 0; b < VB; ++b) {
             const int i = i0 + b * NG;
-            if (i < n) {
-                const float pi = sc[i];
-                float f[VEC];
-                if (p.fused && i == pos) {
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) f[e] = vs[c * VEC + e];
-                } else {
-                    KvVec<KVT>::unpack(buf[b], f);
-                }
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) o[e] = fmaf(pi, f[e], o[e]);
-            }
+            if (i < n) accumulate(i, buf[b]);
         }
     }
+    tr.mark();                                   // 6: values accumulated
 #pragma unroll
     for (int e = 0; e < VEC; ++e) part[g * D + c * VEC + e] = o[e];
     __syncthreads();
@@ -244,6 +281,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
         for (int w = 0; w < NG; ++w) r += part[w * D + tid];
         p.out[(size_t)t * p.Q * D + (size_t)h * D + tid] = r;
     }
+    tr.mark();                                   // 7: output stored
+    tr.end();
 }
 
 template <typename KVT>
@@ -273,7 +312,10 @@ static int attention_launch_t(const AttnParams& p) {
     return LSPK_OK;
 }
 
-int attention_launch(const AttnParams& p, int kv_is_fp16) {
+int attention_launch(const AttnParams& p_in, int kv_is_fp16) {
+    AttnParams p = p_in;
+    p.trace = trace_buffer();
+    p.trace_cap = trace_capacity();
     LSPK_REQUIRE(p.D == 64 || p.D == 128 || p.D == 256, "attention: head_dim must be 64, 128 or 256 (got %d)", p.D);
     LSPK_REQUIRE(p.Q % p.KV == 0, "attention: num_heads must be a multiple of num_kv_heads");
     LSPK_REQUIRE(!p.fused || p.T == 1 || p.pos_per_row, "attention: the fused form needs rows that do not attend to each other");

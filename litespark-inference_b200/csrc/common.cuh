@@ -67,6 +67,47 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// ---- optional in-kernel phase trace (measurement aid) -------------------------------------------
+// When a trace buffer is installed (lspk_trace_begin), CTA 0 of every traced kernel appends one
+// record of kTraceWords 64-bit words: [kernel id, globaltimer at entry, SM clock at up to 12 phase
+// marks, globaltimer at exit].  Word 0 of the buffer is the record counter.
+constexpr int kTraceWords = 16;
+unsigned long long* trace_buffer();       // device pointer or nullptr
+int trace_capacity();                     // records
+
+#ifdef __CUDACC__
+struct PhaseTrace {
+    unsigned long long* rec;
+    int n;
+    __device__ __forceinline__ void begin(unsigned long long* buf, int cap, int kernel_id) {
+        rec = nullptr;
+        n = 0;
+        if (buf && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+            const unsigned long long slot = atomicAdd(buf, 1ull);
+            if (slot < (unsigned long long)cap) {
+                rec = buf + 1 + slot * kTraceWords;
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                rec[0] = (unsigned long long)kernel_id;
+                rec[1] = t;
+                for (int i = 2; i < kTraceWords; ++i) rec[i] = 0;
+                n = 2;
+            }
+        }
+    }
+    __device__ __forceinline__ void mark() {
+        if (rec && n < kTraceWords - 1) rec[n++] = (unsigned long long)clock64();
+    }
+    __device__ __forceinline__ void end() {
+        if (rec) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            rec[kTraceWords - 1] = t;
+        }
+    }
+};
+#endif
+
 #ifdef __CUDACC__
 // ---- device helpers --------------------------------------------------------------
 

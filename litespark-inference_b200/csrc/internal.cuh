@@ -31,6 +31,8 @@ struct AttnParams {
     size_t cache_seq_stride;  // elements between the caches of consecutive sequences (pos_per_row)
     int T, Q, KV, D, t_max;
     int fused;             // 1: rotate + cache write inside the attention kernel (independent rows)
+    unsigned long long* trace;
+    int trace_cap;
 };
 int attention_launch(const AttnParams& p, int kv_is_fp16);
 

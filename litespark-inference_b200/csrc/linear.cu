@@ -14,6 +14,8 @@
 // a packed word with four masks (no shifts): the four 2-bit fields stay at their bit offset
 // and are accumulated in four separate int32 sums that are scaled back by exact shifts at the
 // end.  Like the reference the codes stay unsigned {0,1,2}; sum(x) is subtracted once per row.
+#include <stdlib.h>
+
 #include "internal.cuh"
 
 namespace lspk {
@@ -33,6 +35,7 @@ struct LinearSeg {
 struct LinearParams {
     LinearSeg seg[3];
     int n_seg;
+    int total_groups;      // row groups over all segments (of one matrix for the gated pairing)
     int K, chunks;
     int M;
     int prologue, epilogue;
@@ -44,6 +47,9 @@ struct LinearParams {
     float eps;
     int8_t* xq_out;
     float* xscale_out;
+    int stream_weights;    // 1: weights are read once by this launch -> evict-first loads
+    unsigned long long* trace;
+    int trace_cap;
 };
 
 __device__ __forceinline__ void transpose4x4_bytes(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -99,29 +105,50 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     float* s_scale = redf + 32;                                        // [MT]
     int* s_sumx = reinterpret_cast<int*>(s_scale + MT);                // [MT][warps] partial sums of x
 
-    // ---- which row group ------------------------------------------------------------
-    int g = blockIdx.x, s = 0;
-    if (!PAIR) {
-        while (s < p.n_seg - 1 && g >= p.seg[s].groups) {
-            g -= p.seg[s].groups;
-            ++s;
+    // ---- row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... (flat over the segments) ----
+    auto locate = [&](int flat, int& seg_i, int& grp) {
+        seg_i = 0;
+        grp = flat;
+        if (!PAIR) {
+            while (seg_i < p.n_seg - 1 && grp >= p.seg[seg_i].groups) {
+                grp -= p.seg[seg_i].groups;
+                ++seg_i;
+            }
         }
-    }
-    const LinearSeg& sg = p.seg[s];
-    const uint4* wa_base = sg.w + (size_t)g * p.chunks * kRowsPerGroup + r;
-    const uint4* wb_base = PAIR ? (p.seg[1].w + (size_t)g * p.chunks * kRowsPerGroup + r) : nullptr;
+    };
+    auto load_batch = [&](int seg_i, int grp, int base, uint4* dst_a, uint4* dst_b) {
+        const uint4* wa_base = p.seg[seg_i].w + (size_t)grp * p.chunks * kRowsPerGroup + r;
+        const uint4* wb_base = PAIR ? (p.seg[1].w + (size_t)grp * p.chunks * kRowsPerGroup + r) : nullptr;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            const int j = 2 * (warp + kWarps * (base + i)) + h;
+            if (j < p.chunks) {
+                // read-once weights bypass the L2 replacement queue so that the KV cache, the
+                // activations and the norm weights stay resident from token to token
+                if (p.stream_weights) {
+                    dst_a[i] = __ldcs(wa_base + (size_t)j * kRowsPerGroup);
+                    if (PAIR) dst_b[i] = __ldcs(wb_base + (size_t)j * kRowsPerGroup);
+                } else {
+                    dst_a[i] = __ldg(wa_base + (size_t)j * kRowsPerGroup);
+                    if (PAIR) dst_b[i] = __ldg(wb_base + (size_t)j * kRowsPerGroup);
+                }
+            }
+        }
+    };
+    PhaseTrace tr;
+    tr.begin(p.trace, p.trace_cap, 1);
+    tr.mark();                                   // 0: entry
+    const int pairs = (p.chunks + 1) / 2;
+    const bool one_batch = kWarps * NI >= pairs;     // a row group's weights fit one register batch
+
+    int flat = blockIdx.x, s, g;
+    locate(flat, s, g);
 
     // ---- everything that does not depend on the previous kernel is requested first: the first
     //      batch of packed weights and the norm weights (neither is written by the forward pass) ----
     uint4 wa[NI], wb[PAIR ? NI : 1];
-#pragma unroll
-    for (int i = 0; i < NI; ++i) {
-        const int j = 2 * (warp + kWarps * i) + h;
-        if (j < p.chunks) {
-            wa[i] = __ldg(wa_base + (size_t)j * kRowsPerGroup);
-            if (PAIR) wb[i] = __ldg(wb_base + (size_t)j * kRowsPerGroup);
-        }
-    }
+    uint4 na[NI], nb_[PAIR ? NI : 1];                // the next row group's first batch
+    load_batch(s, g, 0, wa, wb);
     float gm[NB][16];
     if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
 #pragma unroll
@@ -151,10 +178,21 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     }
     grid_dependency_launch();
     grid_dependency_wait();
+    tr.mark();                                   // 1: predecessor finished
 
-    // ---- prologue: this tile's activations -> permuted int8 rows in shared memory ---------------
     const int m0 = blockIdx.y * MT;
     const int mt = min(MT, p.M - m0);
+    // residual value of this thread's output element (ADD epilogue), requested as early as possible
+    const int out_m = tid >> 4, out_r = tid & 15;
+    auto residual_of = [&](int seg_i, int grp) -> float {
+        if (p.epilogue != LSPK_EPI_ADD || tid >= MT * 16 || out_m >= mt) return 0.0f;
+        const int n = grp * kRowsPerGroup + out_r;
+        if (n >= p.seg[seg_i].N) return 0.0f;
+        return p.seg[seg_i].out[(size_t)(m0 + out_m) * p.seg[seg_i].N + n];
+    };
+    float resid = residual_of(s, g);
+
+    // ---- prologue: this tile's activations -> permuted int8 rows in shared memory ---------------
     const int tail_start = p.K & ~15;      // the reference's scalar-tail rounding rule applies from here
     for (int m = 0; m < mt; ++m) {
         int8_t* xq_row = xq + (size_t)m * Kp;
@@ -199,8 +237,11 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
                 for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
                     for (int e = 0; e < 16; ++e) ss[e & 3] = fmaf(v[nb][e], v[nb][e], ss[e & 3]);
+                tr.mark();                       // 2: x arrived, local squares summed
                 ssq = block_sum((ss[0] + ss[1]) + (ss[2] + ss[3]), redf);
-                const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
+                tr.mark();                       // 3: sum of squares reduced
+                // __frcp_rn is the correctly rounded reciprocal, i.e. exactly 1.0f / x
+                const float rrms = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -211,9 +252,11 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
                 for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[nb][e]));
+            tr.mark();                           // 4: normalised, local absmax
             amax = block_max(amax, redf);
+            tr.mark();                           // 5: absmax reduced
             scale = quant_scale_from_absmax(amax);
-            const float inv = __fdiv_rn(1.0f, scale);
+            const float inv = __frcp_rn(scale);
             const bool tap = (p.xq_out != nullptr) && blockIdx.x == 0;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
@@ -268,93 +311,116 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             if (p.xscale_out && blockIdx.x == 0) p.xscale_out[m0 + m] = scale;
         }
     }
+    tr.mark();                                   // 6: quantised row written
     __syncthreads();
+    tr.mark();                                   // 7: activations visible to all warps
 
-    // ---- integer dot products ----------------------------------------------------------
-    int acc_a[MT][4], acc_b[PAIR ? MT : 1][4];
-#pragma unroll
-    for (int m = 0; m < MT; ++m)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            acc_a[m][c] = 0;
-            if (PAIR) acc_b[m][c] = 0;
+    // ---- loop over this CTA's row groups: integer dot products, reduction, epilogue --------------------
+    while (true) {
+        const int next_flat = flat + gridDim.x;
+        const bool has_next = next_flat < p.total_groups;
+        int ns = 0, ng = 0;
+        float next_resid = 0.0f;
+        if (has_next) {
+            locate(next_flat, ns, ng);
+            if (one_batch) load_batch(ns, ng, 0, na, nb_);       // in flight while this group is computed
+            next_resid = residual_of(ns, ng);
         }
 
-    const int pairs = (p.chunks + 1) / 2;
-    for (int base = 0;; ) {
+        int acc_a[MT][4], acc_b[PAIR ? MT : 1][4];
 #pragma unroll
-        for (int i = 0; i < NI; ++i) {
-            const int j = 2 * (warp + kWarps * (base + i)) + h;
-            if (j < p.chunks) {
+        for (int m = 0; m < MT; ++m)
 #pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    if (MT == 1 || m < mt) {
-                        const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)m * Kp + (size_t)j * 64);
-                        chunk_dot(wa[i], xp, acc_a[m]);
-                        if (PAIR) chunk_dot(wb[i], xp, acc_b[m]);
+            for (int c = 0; c < 4; ++c) {
+                acc_a[m][c] = 0;
+                if (PAIR) acc_b[m][c] = 0;
+            }
+        for (int base = 0;; ) {
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                const int j = 2 * (warp + kWarps * (base + i)) + h;
+                if (j < p.chunks) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        if (MT == 1 || m < mt) {
+                            const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)m * Kp + (size_t)j * 64);
+                            chunk_dot(wa[i], xp, acc_a[m]);
+                            if (PAIR) chunk_dot(wb[i], xp, acc_b[m]);
+                        }
                     }
                 }
             }
+            base += NI;
+            if (kWarps * base >= pairs) break;
+            load_batch(s, g, base, wa, wb);
         }
-        base += NI;
-        if (kWarps * base >= pairs) break;
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-            const int j = 2 * (warp + kWarps * (base + i)) + h;
-            if (j < p.chunks) {
-                wa[i] = __ldg(wa_base + (size_t)j * kRowsPerGroup);
-                if (PAIR) wb[i] = __ldg(wb_base + (size_t)j * kRowsPerGroup);
-            }
-        }
-    }
 
-    // ---- reduce: fields -> one int, odd/even chunk halves by shuffle, warps through smem ----
+        tr.mark();                               // 8+: dot products of a row group done
+        // fields -> one int, odd/even chunk halves by shuffle, warps through shared memory
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        int v = acc_a[m][0] + (acc_a[m][1] >> 2) + (acc_a[m][2] >> 4) + (acc_a[m][3] >> 6);
-        v += __shfl_down_sync(0xffffffffu, v, 16);
-        if (h == 0) part[(warp * MT + m) * 16 + r] = v;
-        if (PAIR) {
-            int u = acc_b[m][0] + (acc_b[m][1] >> 2) + (acc_b[m][2] >> 4) + (acc_b[m][3] >> 6);
-            u += __shfl_down_sync(0xffffffffu, u, 16);
-            if (h == 0) part[kWarps * MT * 16 + (warp * MT + m) * 16 + r] = u;
-        }
-    }
-    __syncthreads();
-
-    if (tid < MT * 16) {
-        const int m = tid >> 4, rr = tid & 15;
-        const int n = g * kRowsPerGroup + rr;
-        if (m < mt && n < sg.N) {
-            int va = 0, vb = 0, sx = 0;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) {
-                va += part[(w * MT + m) * 16 + rr];
-                if (PAIR) vb += part[kWarps * MT * 16 + (w * MT + m) * 16 + rr];
-                sx += s_sumx[m * kWarps + w];
-            }
-            va -= sx;
-            const size_t o = (size_t)(m0 + m) * sg.N + n;
-            if (sg.acc_out) sg.acc_out[o] = va;
-            const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[m], sg.w_scale));
+        for (int m = 0; m < MT; ++m) {
+            int v = acc_a[m][0] + (acc_a[m][1] >> 2) + (acc_a[m][2] >> 4) + (acc_a[m][3] >> 6);
+            v += __shfl_down_sync(0xffffffffu, v, 16);
+            if (h == 0) part[(warp * MT + m) * 16 + r] = v;
             if (PAIR) {
-                vb -= sx;
-                if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
-                const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[m], p.seg[1].w_scale));
-                if (p.epilogue == LSPK_EPI_SILU_MUL) {
-                    // the reference's Falcon gate (runtime.py:726-732): g / (1 + exp(-g)) * u
-                    sg.out[o] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
-                } else {
-                    const float gpos = fmaxf(ya, 0.0f);
-                    sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
-                }
-            } else if (p.epilogue == LSPK_EPI_ADD) {
-                sg.out[o] = __fadd_rn(sg.out[o], ya);
-            } else {
-                sg.out[o] = ya;
+                int u = acc_b[m][0] + (acc_b[m][1] >> 2) + (acc_b[m][2] >> 4) + (acc_b[m][3] >> 6);
+                u += __shfl_down_sync(0xffffffffu, u, 16);
+                if (h == 0) part[kWarps * MT * 16 + (warp * MT + m) * 16 + r] = u;
             }
         }
+        __syncthreads();
+
+        if (tid < MT * 16) {
+            const LinearSeg& sg = p.seg[s];
+            const int n = g * kRowsPerGroup + out_r;
+            if (out_m < mt && n < sg.N) {
+                int va = 0, vb = 0, sx = 0;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) {
+                    va += part[(w * MT + out_m) * 16 + out_r];
+                    if (PAIR) vb += part[kWarps * MT * 16 + (w * MT + out_m) * 16 + out_r];
+                    sx += s_sumx[out_m * kWarps + w];
+                }
+                va -= sx;
+                const size_t o = (size_t)(m0 + out_m) * sg.N + n;
+                if (sg.acc_out) sg.acc_out[o] = va;
+                const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[out_m], sg.w_scale));
+                if (PAIR) {
+                    vb -= sx;
+                    if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
+                    const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[out_m], p.seg[1].w_scale));
+                    if (p.epilogue == LSPK_EPI_SILU_MUL) {
+                        // the reference's Falcon gate (runtime.py:726-732): g / (1 + exp(-g)) * u
+                        sg.out[o] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
+                    } else {
+                        const float gpos = fmaxf(ya, 0.0f);
+                        sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                    }
+                } else if (p.epilogue == LSPK_EPI_ADD) {
+                    sg.out[o] = __fadd_rn(resid, ya);
+                } else {
+                    sg.out[o] = ya;
+                }
+            }
+        }
+        tr.mark();                               // 9+: row group reduced and stored
+        if (!has_next) break;
+        __syncthreads();                      // `part` is rewritten by the next group
+        flat = next_flat;
+        s = ns;
+        g = ng;
+        resid = next_resid;
+        if (one_batch) {
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                wa[i] = na[i];
+                if (PAIR) wb[i] = nb_[i];
+            }
+        } else {
+            load_batch(s, g, 0, wa, wb);
+        }
     }
+    tr.end();
 }
 
 static size_t linear_smem_bytes(int MT, int Kp, bool pair) {
@@ -410,6 +476,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
         groups += w->groups;
     }
     if (pair) groups = w0->groups;
+    p.total_groups = groups;
     p.M = a->M;
     p.prologue = a->prologue;
     p.epilogue = a->epilogue;
@@ -421,6 +488,8 @@ int linear_cuda_core(const lspk_linear_args* a) {
     p.eps = a->eps;
     p.xq_out = a->xq_out;
     p.xscale_out = a->xscale_out;
+    p.trace = trace_buffer();
+    p.trace_cap = trace_capacity();
     switch (a->prologue) {
         case LSPK_PRO_INT8:
             LSPK_REQUIRE(a->x_i8 && a->x_scales, "linear: INT8 prologue needs x_i8 and x_scales");
@@ -439,12 +508,25 @@ int linear_cuda_core(const lspk_linear_args* a) {
     const int Kp = p.chunks * kWeightsPerChunk;
     const size_t smem = linear_smem_bytes(MT, Kp, pair);
     LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768, less for 8-row tiles)", p.K);
+    // At most two CTAs per SM when there is a single token tile (measured best on B200: the prologue
+    // runs once per CTA, which then loops over its row groups).  With several token tiles the grid's
+    // second dimension already fills the machine.
+    const int tiles = (a->M + MT - 1) / MT;
+    static const int knob_stream = getenv("LSPK_STREAM_WEIGHTS") ? atoi(getenv("LSPK_STREAM_WEIGHTS")) : 1;
+    static const int knob_ctas_per_sm = getenv("LSPK_LINEAR_CTAS_PER_SM") ? atoi(getenv("LSPK_LINEAR_CTAS_PER_SM")) : 2;
+    p.stream_weights = (tiles == 1 && knob_stream) ? 1 : 0;
+    int ctas = groups;
+    if (knob_ctas_per_sm > 0) {
+        const int per_wave = tiles == 1 ? knob_ctas_per_sm * sm_count()
+                                        : (2 * sm_count() + tiles - 1) / tiles;
+        if (ctas > per_wave) ctas = per_wave > 0 ? per_wave : 1;
+    }
     cudaError_t e;
     switch (MT) {
-        case 1: e = launch_linear_mt<1>(p, groups, pair, smem); break;
-        case 2: e = launch_linear_mt<2>(p, groups, pair, smem); break;
-        case 4: e = launch_linear_mt<4>(p, groups, pair, smem); break;
-        default: e = launch_linear_mt<8>(p, groups, pair, smem); break;
+        case 1: e = launch_linear_mt<1>(p, ctas, pair, smem); break;
+        case 2: e = launch_linear_mt<2>(p, ctas, pair, smem); break;
+        case 4: e = launch_linear_mt<4>(p, ctas, pair, smem); break;
+        default: e = launch_linear_mt<8>(p, ctas, pair, smem); break;
     }
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear launch failed: %s", cudaGetErrorString(e));
     return LSPK_OK;

@@ -75,6 +75,8 @@ _SIGNATURES = {
     "lspk_d2h_async": ([_vp, _vp, _sz], _ci),
     "lspk_memset": ([_vp, _ci, _sz], _ci),
     "lspk_flush_l2": ([], _ci),
+    "lspk_trace_begin": ([_ci], _ci),
+    "lspk_trace_read": ([_vp, _ci, ctypes.POINTER(_ci)], _ci),
     "lspk_timer_start": ([], _ci),
     "lspk_timer_stop": ([ctypes.POINTER(_cf)], _ci),
     "lspk_upload_packed": ([_U8, _ci, _ci, _cf], _vp),
