@@ -184,6 +184,23 @@ void lm_head_int4_fp32_sm100(const uint8_t* emb, const float* emb_scale, const f
 int matmul_lut_sm100_has_omp(void);
 int matmul_lut_sm100_max_threads(void);
 
+/* Same product as matmul_lut_sm100_m1, for callers that cannot allocate device memory at call time
+ * (a server that handed all GPU memory to its own pool at start-up; a loop that must stay out of the
+ * CUDA allocator's lock).  It has no counterpart in the reference, whose kernels work in host memory.
+ * All device scratch (staging of the packed rows, their re-tiled copy, x and y) lives in one
+ * file-scope device array of LSPK_NOALLOC_SCRATCH_BYTES that every GPU loading the library holds
+ * until exit; the call makes no cudaMalloc / cudaFree.  Host pointers in and out, like the drop-in.
+ * Returns LSPK_OK, or LSPK_ERR_ARG when the matrix does not fit the array (about N*K/2 + K + 4N
+ * bytes are needed: 6912 x 2560 fits, 6912 x 6912 does not).
+ * The first call on a device also creates the library's stream and looks up the array's device
+ * address: make that first call before any stream capture begins.  Every call reuses the same
+ * array, and the array keeps what the previous call left; nothing needs clearing because each call
+ * overwrites what it reads.  Calls are serialised on the host and run on one stream; work issued by
+ * other means that touched the array at the same time on the GPU would race with them. */
+#define LSPK_NOALLOC_SCRATCH_BYTES (12u << 20)
+int matmul_lut_sm100_m1_noalloc(const int8_t* x, const uint8_t* packed_w, float w_scale, float x_scale,
+                                float* y, int N, int K);
+
 /* Weight residency for the drop-ins.  By default a drop-in uploads the packed matrix (or the
  * embedding) on every call.  Registering a host buffer keeps a device copy keyed by its
  * address: later drop-in calls given the same pointer and shape skip the upload.  The caller

@@ -4,6 +4,9 @@
 
 namespace lspk {
 
+// layout.cu: reference byte layout (device copy) -> device chunk layout, on the library stream.
+cudaError_t retile_to_device_launch(const uint8_t* src_dev, uint4* dst_dev, int N, int Kb, int groups, int chunks);
+
 // linear.cu: validate + launch the CUDA-core ternary linear kernel on the library stream.
 int linear_cuda_core(const lspk_linear_args* a);
 

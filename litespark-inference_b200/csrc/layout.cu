@@ -48,6 +48,15 @@ __global__ void retile_to_reference_kernel(const uint8_t* __restrict__ dev_bytes
     }
 }
 
+// Launch the re-tiling kernel on the library stream (both pointers are device pointers).
+cudaError_t retile_to_device_launch(const uint8_t* src_dev, uint4* dst_dev, int N, int Kb, int groups, int chunks) {
+    const long long total = (long long)groups * chunks * kRowsPerGroup;
+    const int block = 256;
+    const int grid = (int)((total + block - 1) / block < 65535 ? (total + block - 1) / block : 65535);
+    retile_to_device_kernel<<<grid, block, 0, stream()>>>(src_dev, dst_dev, N, Kb, groups, chunks);
+    return cudaGetLastError();
+}
+
 }  // namespace lspk
 
 using namespace lspk;

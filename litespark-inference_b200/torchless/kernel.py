@@ -109,6 +109,7 @@ _SIGNATURES = {
     "lm_head_bf16_fp32_sm100": ([_U16, _F32, _F32, _ci, _ci], None),
     "lm_head_int8_fp32_sm100": ([_I8, _F32, _F32, _F32, _ci, _ci], None),
     "lm_head_int4_fp32_sm100": ([_U8, _F32, _F32, _F32, _ci, _ci], None),
+    "matmul_lut_sm100_m1_noalloc": ([_I8, _U8, _cf, _cf, _F32, _ci, _ci], _ci),
     "matmul_lut_sm100_has_omp": ([], _ci),
     "matmul_lut_sm100_max_threads": ([], _ci),
     "lspk_register_packed": ([_U8, _ci, _ci], _ci),
@@ -341,6 +342,18 @@ def matmul_packed_m1(x_int8, packed_w, w_scale: float, x_scale: float, out=None)
         out = np.empty(N, dtype=np.float32)
     with _ErrorGuard() as lib:
         lib.matmul_lut_m1(x_int8, packed_w, w_scale, x_scale, out, N, Kb * 4)
+    return out
+
+
+def matmul_packed_m1_noalloc(x_int8, packed_w, w_scale: float, x_scale: float, out=None):
+    """``matmul_packed_m1`` for hosts that may not allocate GPU memory when they call (all memory
+    already owned by a serving framework's pool, or an allocation-free real-time loop).  The device
+    scratch is a fixed 12 MiB array inside the library, so the matrix must fit it (6912 x 2560
+    does); a larger one raises KernelError.  Make the first call outside any CUDA stream capture."""
+    N, Kb = packed_w.shape
+    if out is None:
+        out = np.empty(N, dtype=np.float32)
+    check(_load().matmul_lut_sm100_m1_noalloc(x_int8, packed_w, w_scale, x_scale, out, N, Kb * 4))
     return out
 
 
