@@ -91,7 +91,8 @@ int lspk_weight_shape(lspk_weight_t w, int* N, int* K, float* scale, size_t* dev
 /* Prologue: what the kernel does to its input before the integer dot products.           */
 enum { LSPK_PRO_INT8 = 0,        /* x is int8 [M,K] with per-row fp32 scales (a5/a6 contract) */
        LSPK_PRO_QUANT = 1,       /* x is fp32: per-token absmax int8 quantiser fused (a4)     */
-       LSPK_PRO_RMSNORM_QUANT = 2 /* x is fp32: RMSNorm(gamma, eps) then quantiser (a10)       */ };
+       LSPK_PRO_RMSNORM_QUANT = 2,/* x is fp32: RMSNorm(gamma, eps) then quantiser (a10)       */
+       LSPK_PRO_GATED_RMSNORM_QUANT = 3 /* x * SiLU(gate_f32), then RMSNorm and quantiser (Mamba-2 output norm) */ };
 /* Epilogue: what happens to y = float(acc) * (x_scale * w_scale).                         */
 enum { LSPK_EPI_STORE = 0,       /* out = y                                               */
        LSPK_EPI_ADD = 1,         /* out += y            (residual add, a12)                */
@@ -115,6 +116,7 @@ typedef struct {
     int32_t* acc_out[3];         /* int32 [M, N_i]: the exact integer accumulators          */
     int8_t* xq_out;              /* int8 [M,K]: the quantised activations the kernel used   */
     float* xscale_out;           /* fp32 [M]                                                */
+    const float* gate_f32;       /* [M,K] for GATED_RMSNORM_QUANT                           */
 } lspk_linear_args;
 
 #define LSPK_MAX_GEMV_M 8

@@ -7,6 +7,49 @@ namespace lspk {
 // layout.cu: reference byte layout (device copy) -> device chunk layout, on the library stream.
 cudaError_t retile_to_device_launch(const uint8_t* src_dev, uint4* dst_dev, int N, int Kb, int groups, int chunks);
 
+// linear.cu: kernel parameters (filled by linear_cuda_core, or directly by the MoE layer for its
+// expert-grouped launches).
+struct LinearSeg {
+    const uint4* w;
+    float* out;
+    int32_t* acc_out;
+    int N;
+    int groups;
+    float w_scale;
+    int scale_idx;         // grouped mode: index of this matrix inside an expert's scale triple
+};
+
+struct LinearParams {
+    LinearSeg seg[3];
+    int n_seg;
+    int total_groups;      // row groups over all segments (of one matrix for the gated pairing)
+    int K, chunks;
+    int M;
+    int prologue, epilogue;
+    const float* x_f32;
+    const float* gate_f32; // GATED_RMSNORM_QUANT: x is multiplied by SiLU(gate) before the norm
+    const int8_t* x_i8;
+    const float* x_scales;
+    const void* gamma;
+    int gamma_is_bf16;
+    float eps;
+    int8_t* xq_out;
+    float* xscale_out;
+    int stream_weights;    // 1: weights are read once by this launch -> evict-first loads
+    unsigned long long* trace;
+    int trace_cap;
+    // ---- expert-grouped mode (blockIdx.z = expert): rows and their count come from device arrays ----
+    const int* grp_counts;     // [experts] rows routed to each expert
+    const int* grp_rows;       // [experts][grp_rows_stride] output row of each routed row
+    int grp_rows_stride;
+    int grp_in_shift;          // input row = output row >> shift (1: two routed rows share one input row)
+    size_t grp_w_stride;       // uint4 units between consecutive experts' copies of a matrix
+    const float* grp_scales;   // [experts][3] weight scales
+};
+
+// Launch the CUDA-core kernel with fully prepared parameters.  mt: rows per CTA tile (1, 2, 4 or 8).
+int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);
+
 // linear.cu: validate + launch the CUDA-core ternary linear kernel on the library stream.
 int linear_cuda_core(const lspk_linear_args* a);
 
@@ -18,6 +61,22 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled);
 int lm_head_launch(int kind, const void* emb, const float* emb_scale, const float* x, float* logits,
                    int T, int V, int H, const void* norm_gamma, int gamma_is_bf16, float eps,
                    unsigned long long* best_key);
+
+// runtime.cu: small kernels of a decode step, shared with the hybrid runtime.
+//   ctl layout: pos[batch], token[batch], step counter.
+int launch_embed(const int* tokens, int rows, int kind, const void* emb, const float* scale, float* x, int H, int V);
+int launch_argmax_rows(const float* logits, int rows, int V, unsigned long long* best);
+int launch_finish_step(int* ctl, unsigned long long* best, int* tokens_out, int batch, int out_cap);
+
+// moe.cu / mamba.cu: layer objects of the hybrid configuration.
+struct Moe;
+struct Mamba;
+int moe_reserve(Moe* m, int B);
+int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int32_t* acc_gate, int32_t* acc_up,
+                int32_t* acc_down);
+int mamba_reserve(Mamba* m, int B);
+int mamba_step(Mamba* m, float* x, float* state, const int* pos, int B);
+size_t mamba_state_floats(const Mamba* m);
 
 // attention.cu
 struct AttnParams {

@@ -17,80 +17,20 @@
 #include <stdlib.h>
 
 #include "internal.cuh"
+#include "ternary_core.cuh"
 
 namespace lspk {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 
-struct LinearSeg {
-    const uint4* w;
-    float* out;
-    int32_t* acc_out;
-    int N;
-    int groups;
-    float w_scale;
-};
-
-struct LinearParams {
-    LinearSeg seg[3];
-    int n_seg;
-    int total_groups;      // row groups over all segments (of one matrix for the gated pairing)
-    int K, chunks;
-    int M;
-    int prologue, epilogue;
-    const float* x_f32;
-    const int8_t* x_i8;
-    const float* x_scales;
-    const void* gamma;
-    int gamma_is_bf16;
-    float eps;
-    int8_t* xq_out;
-    float* xscale_out;
-    int stream_weights;    // 1: weights are read once by this launch -> evict-first loads
-    unsigned long long* trace;
-    int trace_cap;
-};
-
-__device__ __forceinline__ void transpose4x4_bytes(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                                   uint32_t& o0, uint32_t& o1, uint32_t& o2, uint32_t& o3) {
-    const uint32_t t0 = __byte_perm(a0, a1, 0x5140), t1 = __byte_perm(a2, a3, 0x5140);
-    const uint32_t t2 = __byte_perm(a0, a1, 0x7362), t3 = __byte_perm(a2, a3, 0x7362);
-    o0 = __byte_perm(t0, t1, 0x5410);
-    o1 = __byte_perm(t0, t1, 0x7632);
-    o2 = __byte_perm(t2, t3, 0x5410);
-    o3 = __byte_perm(t2, t3, 0x7632);
-}
-
-// Accumulate one 16-byte weight chunk (64 weights) against the matching 64 permuted activations.
-__device__ __forceinline__ void chunk_dot(const uint4& wv, const int4* __restrict__ xp, int acc[4]) {
-    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-    for (int m = 0; m < 4; ++m) {
-        const int4 xv = xp[m];
-        acc[0] = dp4a_us(w[m] & 0x03030303u, xv.x, acc[0]);
-        acc[1] = dp4a_us(w[m] & 0x0C0C0C0Cu, xv.y, acc[1]);
-        acc[2] = dp4a_us(w[m] & 0x30303030u, xv.z, acc[2]);
-        acc[3] = dp4a_us(w[m] & 0xC0C0C0C0u, xv.w, acc[3]);
-    }
-}
-
-// fp32 -> int8 with round-half-even and saturation to [-128, 127] in one instruction: the pair
-// _mm512_cvtps_epi32 + _mm512_cvtsepi32_epi8 of the reference quantiser.
-__device__ __forceinline__ uint32_t quant_rne_sat(float v) {
-    int r;
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
-    return (uint32_t)r;
-}
-__device__ __forceinline__ uint32_t pack4_bytes(uint32_t q0, uint32_t q1, uint32_t q2, uint32_t q3) {
-    return __byte_perm(__byte_perm(q0, q1, 0x0040), __byte_perm(q2, q3, 0x0040), 0x5410);
-}
-
-// MT   token rows per CTA tile
-// NI   16-byte weight loads per lane per batch (covers K <= 4096 at 4, K <= 8192 at 8 in one batch)
-// NB   16-element activation blocks a thread owns in the fp32 prologue (K <= 4096 * NB)
-// PAIR gate/up pairing (two weight streams, gated epilogue)
-template <int MT, int NI, int NB, bool PAIR>
+// MT      token rows per CTA tile
+// NI      16-byte weight loads per lane per batch (covers K <= 4096 at 4, K <= 8192 at 8 in one batch)
+// NB      16-element activation blocks a thread owns in the fp32 prologue (K <= 4096 * NB)
+// PAIR    gate/up pairing (two weight streams, gated epilogue)
+// GROUPED expert-grouped launch: blockIdx.z is the expert; its row list and row count are read from
+//         device arrays, its weights and scales are found by stride (packed-expert MoE GEMV)
+template <int MT, int NI, int NB, bool PAIR, bool GROUPED>
 __global__ void __launch_bounds__(kThreads)
 ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -105,6 +45,9 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     float* s_scale = redf + 32;                                        // [MT]
     int* s_sumx = reinterpret_cast<int*>(s_scale + MT);                // [MT][warps] partial sums of x
 
+    const int z = GROUPED ? blockIdx.z : 0;
+    const size_t w_off = GROUPED ? (size_t)z * p.grp_w_stride : 0;
+
     // ---- row groups of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ... (flat over the segments) ----
     auto locate = [&](int flat, int& seg_i, int& grp) {
         seg_i = 0;
@@ -117,8 +60,8 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
         }
     };
     auto load_batch = [&](int seg_i, int grp, int base, uint4* dst_a, uint4* dst_b) {
-        const uint4* wa_base = p.seg[seg_i].w + (size_t)grp * p.chunks * kRowsPerGroup + r;
-        const uint4* wb_base = PAIR ? (p.seg[1].w + (size_t)grp * p.chunks * kRowsPerGroup + r) : nullptr;
+        const uint4* wa_base = p.seg[seg_i].w + w_off + (size_t)grp * p.chunks * kRowsPerGroup + r;
+        const uint4* wb_base = PAIR ? (p.seg[1].w + w_off + (size_t)grp * p.chunks * kRowsPerGroup + r) : nullptr;
 #pragma unroll
         for (int i = 0; i < NI; ++i) {
             const int j = 2 * (warp + kWarps * (base + i)) + h;
@@ -140,17 +83,20 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     tr.mark();                                   // 0: entry
     const int pairs = (p.chunks + 1) / 2;
     const bool one_batch = kWarps * NI >= pairs;     // a row group's weights fit one register batch
+    const bool fp32_in = p.prologue != LSPK_PRO_INT8;
+    const bool normed = p.prologue == LSPK_PRO_RMSNORM_QUANT || p.prologue == LSPK_PRO_GATED_RMSNORM_QUANT;
 
-    int flat = blockIdx.x, s, g;
-    locate(flat, s, g);
+    int flat0 = blockIdx.x, s0, g0;
+    locate(flat0, s0, g0);
 
     // ---- everything that does not depend on the previous kernel is requested first: the first
-    //      batch of packed weights and the norm weights (neither is written by the forward pass) ----
+    //      batch of packed weights and the norm weights (neither is written by the forward pass).
+    //      An expert-grouped launch cannot: whether this expert has any row is device data. ----
     uint4 wa[NI], wb[PAIR ? NI : 1];
     uint4 na[NI], nb_[PAIR ? NI : 1];                // the next row group's first batch
-    load_batch(s, g, 0, wa, wb);
+    if (!GROUPED) load_batch(s0, g0, 0, wa, wb);
     float gm[NB][16];
-    if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
+    if (normed) {
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
             const int k0 = (tid + nb * kThreads) * 16;
@@ -180,244 +126,275 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     grid_dependency_wait();
     tr.mark();                                   // 1: predecessor finished
 
-    const int m0 = blockIdx.y * MT;
-    const int mt = min(MT, p.M - m0);
-    // residual value of this thread's output element (ADD epilogue), requested as early as possible
+    const int M_eff = GROUPED ? p.grp_counts[z] : p.M;
+    const int* rows = GROUPED ? p.grp_rows + (size_t)z * p.grp_rows_stride : nullptr;
     const int out_m = tid >> 4, out_r = tid & 15;
-    auto residual_of = [&](int seg_i, int grp) -> float {
-        if (p.epilogue != LSPK_EPI_ADD || tid >= MT * 16 || out_m >= mt) return 0.0f;
-        const int n = grp * kRowsPerGroup + out_r;
-        if (n >= p.seg[seg_i].N) return 0.0f;
-        return p.seg[seg_i].out[(size_t)(m0 + out_m) * p.seg[seg_i].N + n];
-    };
-    float resid = residual_of(s, g);
-
-    // ---- prologue: this tile's activations -> permuted int8 rows in shared memory ---------------
     const int tail_start = p.K & ~15;      // the reference's scalar-tail rounding rule applies from here
-    for (int m = 0; m < mt; ++m) {
-        int8_t* xq_row = xq + (size_t)m * Kp;
-        int sumx = 0;
-        float scale = 1.0f;
-        if (p.prologue == LSPK_PRO_INT8) {
-            const int8_t* src = p.x_i8 + (size_t)(m0 + m) * p.K;
-            for (int b = tid; b < Kp / 16; b += kThreads) {
-                uint32_t a[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int k = b * 16 + q * 4;
-                    a[q] = (k < p.K) ? *reinterpret_cast<const uint32_t*>(src + k) : 0u;
-                    sumx = __dp4a((int)a[q], 0x01010101, sumx);
-                }
-                uint32_t o0, o1, o2, o3;
-                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
-                *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
-            }
-            scale = p.x_scales[m0 + m];
-        } else {
-            // every thread keeps its 16-element blocks in registers through all three passes
-            const float* src = p.x_f32 + (size_t)(m0 + m) * p.K;
-            float v[NB][16];
-            float ssq = 0.0f;
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                const int k0 = (tid + nb * kThreads) * 16;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (k0 + q * 4 < p.K) t4 = *reinterpret_cast<const float4*>(src + k0 + q * 4);
-                    v[nb][q * 4 + 0] = t4.x;
-                    v[nb][q * 4 + 1] = t4.y;
-                    v[nb][q * 4 + 2] = t4.z;
-                    v[nb][q * 4 + 3] = t4.w;
-                }
-            }
-            if (p.prologue == LSPK_PRO_RMSNORM_QUANT) {
-                float ss[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) ss[e & 3] = fmaf(v[nb][e], v[nb][e], ss[e & 3]);
-                tr.mark();                       // 2: x arrived, local squares summed
-                ssq = block_sum((ss[0] + ss[1]) + (ss[2] + ss[3]), redf);
-                tr.mark();                       // 3: sum of squares reduced
-                // __frcp_rn is the correctly rounded reciprocal, i.e. exactly 1.0f / x
-                const float rrms = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
-#pragma unroll
-                for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) v[nb][e] = __fmul_rn(__fmul_rn(v[nb][e], rrms), gm[nb][e]);
-            }
-            float amax = 0.0f;
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[nb][e]));
-            tr.mark();                           // 4: normalised, local absmax
-            amax = block_max(amax, redf);
-            tr.mark();                           // 5: absmax reduced
-            scale = quant_scale_from_absmax(amax);
-            const float inv = __frcp_rn(scale);
-            const bool tap = (p.xq_out != nullptr) && blockIdx.x == 0;
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                const int b = tid + nb * kThreads;
-                const int k0 = b * 16;
-                if (k0 < Kp) {
+    bool first_tile = true;
+
+    for (int m0 = blockIdx.y * MT; m0 < M_eff; m0 += gridDim.y * MT) {
+        const int mt = min(MT, M_eff - m0);
+        auto out_row = [&](int m) -> int { return GROUPED ? rows[m0 + m] : m0 + m; };
+        auto in_row = [&](int m) -> int { return GROUPED ? (rows[m0 + m] >> p.grp_in_shift) : m0 + m; };
+        int flat = flat0, s = s0, g = g0;
+        // residual value of this thread's output element (ADD epilogue), requested as early as possible
+        auto residual_of = [&](int seg_i, int grp) -> float {
+            if (p.epilogue != LSPK_EPI_ADD || tid >= MT * 16 || out_m >= mt) return 0.0f;
+            const int n = grp * kRowsPerGroup + out_r;
+            if (n >= p.seg[seg_i].N) return 0.0f;
+            return p.seg[seg_i].out[(size_t)out_row(out_m) * p.seg[seg_i].N + n];
+        };
+        float resid = residual_of(s, g);
+        if (GROUPED || !first_tile) load_batch(s, g, 0, wa, wb);
+        first_tile = false;
+
+        // ---- prologue: this tile's activations -> permuted int8 rows in shared memory ---------------
+        for (int m = 0; m < mt; ++m) {
+            int8_t* xq_row = xq + (size_t)m * Kp;
+            int sumx = 0;
+            float scale = 1.0f;
+            if (!fp32_in) {
+                const int8_t* src = p.x_i8 + (size_t)in_row(m) * p.K;
+                for (int b = tid; b < Kp / 16; b += kThreads) {
                     uint32_t a[4];
-                    if (k0 + 16 <= tail_start) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            a[q] = pack4_bytes(quant_rne_sat(__fmul_rn(v[nb][q * 4 + 0], inv)),
-                                               quant_rne_sat(__fmul_rn(v[nb][q * 4 + 1], inv)),
-                                               quant_rne_sat(__fmul_rn(v[nb][q * 4 + 2], inv)),
-                                               quant_rne_sat(__fmul_rn(v[nb][q * 4 + 3], inv)));
-                    } else {
-                        // block that reaches past the last multiple of 16: the reference's scalar tail
-                        // (round half away from zero, clamp to +-127), zeros beyond K
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint32_t word = 0;
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const int k = k0 + q * 4 + e;
-                                int qv = 0;
-                                if (k < tail_start) {
-                                    qv = (int)quant_rne_sat(__fmul_rn(v[nb][q * 4 + e], inv));
-                                } else if (k < p.K) {
-                                    qv = max(-127, min(127, (int)roundf(__fmul_rn(v[nb][q * 4 + e], inv))));
-                                }
-                                word |= ((uint32_t)qv & 0xffu) << (8 * e);
-                            }
-                            a[q] = word;
-                        }
-                    }
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
+                        const int k = b * 16 + q * 4;
+                        a[q] = (k < p.K) ? *reinterpret_cast<const uint32_t*>(src + k) : 0u;
                         sumx = __dp4a((int)a[q], 0x01010101, sumx);
-                        if (tap && k0 + q * 4 < p.K)
-                            *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)(m0 + m) * p.K + k0 + q * 4) = a[q];
                     }
                     uint32_t o0, o1, o2, o3;
                     transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
-                    *reinterpret_cast<uint4*>(xq_row + k0) = make_uint4(o0, o1, o2, o3);
+                    *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
                 }
-            }
-        }
-        // sum(x): per-warp partials; the output threads add the eight of them
-        sumx = warp_sum(sumx);
-        if (lane == 0) s_sumx[m * kWarps + warp] = sumx;
-        if (tid == 0) {
-            s_scale[m] = scale;
-            if (p.xscale_out && blockIdx.x == 0) p.xscale_out[m0 + m] = scale;
-        }
-    }
-    tr.mark();                                   // 6: quantised row written
-    __syncthreads();
-    tr.mark();                                   // 7: activations visible to all warps
-
-    // ---- loop over this CTA's row groups: integer dot products, reduction, epilogue --------------------
-    while (true) {
-        const int next_flat = flat + gridDim.x;
-        const bool has_next = next_flat < p.total_groups;
-        int ns = 0, ng = 0;
-        float next_resid = 0.0f;
-        if (has_next) {
-            locate(next_flat, ns, ng);
-            if (one_batch) load_batch(ns, ng, 0, na, nb_);       // in flight while this group is computed
-            next_resid = residual_of(ns, ng);
-        }
-
-        int acc_a[MT][4], acc_b[PAIR ? MT : 1][4];
+                scale = p.x_scales[in_row(m)];
+            } else {
+                // every thread keeps its 16-element blocks in registers through all three passes
+                const float* src = p.x_f32 + (size_t)in_row(m) * p.K;
+                float v[NB][16];
+                float ssq = 0.0f;
 #pragma unroll
-        for (int m = 0; m < MT; ++m)
+                for (int nb = 0; nb < NB; ++nb) {
+                    const int k0 = (tid + nb * kThreads) * 16;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                acc_a[m][c] = 0;
-                if (PAIR) acc_b[m][c] = 0;
-            }
-        for (int base = 0;; ) {
+                    for (int q = 0; q < 4; ++q) {
+                        float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (k0 + q * 4 < p.K) t4 = *reinterpret_cast<const float4*>(src + k0 + q * 4);
+                        v[nb][q * 4 + 0] = t4.x;
+                        v[nb][q * 4 + 1] = t4.y;
+                        v[nb][q * 4 + 2] = t4.z;
+                        v[nb][q * 4 + 3] = t4.w;
+                    }
+                }
+                if (p.prologue == LSPK_PRO_GATED_RMSNORM_QUANT) {
+                    // v = x * SiLU(gate), SiLU(g) = g / (1 + exp(-g)); each step a single rounding
+                    const float* gsrc = p.gate_f32 + (size_t)in_row(m) * p.K;
 #pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                const int j = 2 * (warp + kWarps * (base + i)) + h;
-                if (j < p.chunks) {
+                    for (int nb = 0; nb < NB; ++nb) {
+                        const int k0 = (tid + nb * kThreads) * 16;
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        if (MT == 1 || m < mt) {
-                            const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)m * Kp + (size_t)j * 64);
-                            chunk_dot(wa[i], xp, acc_a[m]);
-                            if (PAIR) chunk_dot(wb[i], xp, acc_b[m]);
+                        for (int q = 0; q < 4; ++q) {
+                            float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (k0 + q * 4 < p.K) t4 = *reinterpret_cast<const float4*>(gsrc + k0 + q * 4);
+                            const float gg[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float sg = __fdiv_rn(gg[e], __fadd_rn(expf(-gg[e]), 1.0f));
+                                v[nb][q * 4 + e] = __fmul_rn(v[nb][q * 4 + e], sg);
+                            }
                         }
                     }
                 }
-            }
-            base += NI;
-            if (kWarps * base >= pairs) break;
-            load_batch(s, g, base, wa, wb);
-        }
-
-        tr.mark();                               // 8+: dot products of a row group done
-        // fields -> one int, odd/even chunk halves by shuffle, warps through shared memory
+                if (normed) {
+                    float ss[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            int v = acc_a[m][0] + (acc_a[m][1] >> 2) + (acc_a[m][2] >> 4) + (acc_a[m][3] >> 6);
-            v += __shfl_down_sync(0xffffffffu, v, 16);
-            if (h == 0) part[(warp * MT + m) * 16 + r] = v;
-            if (PAIR) {
-                int u = acc_b[m][0] + (acc_b[m][1] >> 2) + (acc_b[m][2] >> 4) + (acc_b[m][3] >> 6);
-                u += __shfl_down_sync(0xffffffffu, u, 16);
-                if (h == 0) part[kWarps * MT * 16 + (warp * MT + m) * 16 + r] = u;
-            }
-        }
-        __syncthreads();
-
-        if (tid < MT * 16) {
-            const LinearSeg& sg = p.seg[s];
-            const int n = g * kRowsPerGroup + out_r;
-            if (out_m < mt && n < sg.N) {
-                int va = 0, vb = 0, sx = 0;
+                    for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-                for (int w = 0; w < kWarps; ++w) {
-                    va += part[(w * MT + out_m) * 16 + out_r];
-                    if (PAIR) vb += part[kWarps * MT * 16 + (w * MT + out_m) * 16 + out_r];
-                    sx += s_sumx[out_m * kWarps + w];
+                        for (int e = 0; e < 16; ++e) ss[e & 3] = fmaf(v[nb][e], v[nb][e], ss[e & 3]);
+                    tr.mark();                       // 2: x arrived, local squares summed
+                    ssq = block_sum((ss[0] + ss[1]) + (ss[2] + ss[3]), redf);
+                    tr.mark();                       // 3: sum of squares reduced
+                    // __frcp_rn is the correctly rounded reciprocal, i.e. exactly 1.0f / x
+                    const float rrms = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) v[nb][e] = __fmul_rn(__fmul_rn(v[nb][e], rrms), gm[nb][e]);
                 }
-                va -= sx;
-                const size_t o = (size_t)(m0 + out_m) * sg.N + n;
-                if (sg.acc_out) sg.acc_out[o] = va;
-                const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[out_m], sg.w_scale));
-                if (PAIR) {
-                    vb -= sx;
-                    if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
-                    const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[out_m], p.seg[1].w_scale));
-                    if (p.epilogue == LSPK_EPI_SILU_MUL) {
-                        // the reference's Falcon gate (runtime.py:726-732): g / (1 + exp(-g)) * u
-                        sg.out[o] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
-                    } else {
-                        const float gpos = fmaxf(ya, 0.0f);
-                        sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                float amax = 0.0f;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[nb][e]));
+                tr.mark();                           // 4: normalised, local absmax
+                amax = block_max(amax, redf);
+                tr.mark();                           // 5: absmax reduced
+                scale = quant_scale_from_absmax(amax);
+                const float inv = __frcp_rn(scale);
+                const bool tap = (p.xq_out != nullptr) && blockIdx.x == 0;
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    const int b = tid + nb * kThreads;
+                    const int k0 = b * 16;
+                    if (k0 < Kp) {
+                        uint32_t a[4];
+                        if (k0 + 16 <= tail_start) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                a[q] = pack4_bytes(quant_rne_sat(__fmul_rn(v[nb][q * 4 + 0], inv)),
+                                                   quant_rne_sat(__fmul_rn(v[nb][q * 4 + 1], inv)),
+                                                   quant_rne_sat(__fmul_rn(v[nb][q * 4 + 2], inv)),
+                                                   quant_rne_sat(__fmul_rn(v[nb][q * 4 + 3], inv)));
+                        } else {
+                            // block that reaches past the last multiple of 16: the reference's scalar tail
+                            // (round half away from zero, clamp to +-127), zeros beyond K
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                uint32_t word = 0;
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int k = k0 + q * 4 + e;
+                                    int qv = 0;
+                                    if (k < tail_start) {
+                                        qv = (int)quant_rne_sat(__fmul_rn(v[nb][q * 4 + e], inv));
+                                    } else if (k < p.K) {
+                                        qv = max(-127, min(127, (int)roundf(__fmul_rn(v[nb][q * 4 + e], inv))));
+                                    }
+                                    word |= ((uint32_t)qv & 0xffu) << (8 * e);
+                                }
+                                a[q] = word;
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                            if (tap && k0 + q * 4 < p.K)
+                                *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)out_row(m) * p.K + k0 + q * 4) = a[q];
+                        }
+                        uint32_t o0, o1, o2, o3;
+                        transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                        *reinterpret_cast<uint4*>(xq_row + k0) = make_uint4(o0, o1, o2, o3);
                     }
-                } else if (p.epilogue == LSPK_EPI_ADD) {
-                    sg.out[o] = __fadd_rn(resid, ya);
-                } else {
-                    sg.out[o] = ya;
                 }
             }
-        }
-        tr.mark();                               // 9+: row group reduced and stored
-        if (!has_next) break;
-        __syncthreads();                      // `part` is rewritten by the next group
-        flat = next_flat;
-        s = ns;
-        g = ng;
-        resid = next_resid;
-        if (one_batch) {
-#pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                wa[i] = na[i];
-                if (PAIR) wb[i] = nb_[i];
+            // sum(x): per-warp partials; the output threads add the eight of them
+            sumx = warp_sum(sumx);
+            if (lane == 0) s_sumx[m * kWarps + warp] = sumx;
+            if (tid == 0) {
+                s_scale[m] = scale;
+                if (p.xscale_out && blockIdx.x == 0) p.xscale_out[out_row(m)] = scale;
             }
-        } else {
-            load_batch(s, g, 0, wa, wb);
+        }
+        tr.mark();                                   // 6: quantised rows written
+        __syncthreads();
+        tr.mark();                                   // 7: activations visible to all warps
+
+        // ---- loop over this CTA's row groups: integer dot products, reduction, epilogue ----------------
+        while (true) {
+            const int next_flat = flat + gridDim.x;
+            const bool has_next = next_flat < p.total_groups;
+            int ns = 0, ng = 0;
+            float next_resid = 0.0f;
+            if (has_next) {
+                locate(next_flat, ns, ng);
+                if (one_batch) load_batch(ns, ng, 0, na, nb_);       // in flight while this group is computed
+                next_resid = residual_of(ns, ng);
+            }
+
+            int acc_a[MT][4], acc_b[PAIR ? MT : 1][4];
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    acc_a[m][c] = 0;
+                    if (PAIR) acc_b[m][c] = 0;
+                }
+            for (int base = 0;; ) {
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    const int j = 2 * (warp + kWarps * (base + i)) + h;
+                    if (j < p.chunks) {
+#pragma unroll
+                        for (int m = 0; m < MT; ++m) {
+                            if (MT == 1 || m < mt) {
+                                const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)m * Kp + (size_t)j * 64);
+                                chunk_dot(wa[i], xp, acc_a[m]);
+                                if (PAIR) chunk_dot(wb[i], xp, acc_b[m]);
+                            }
+                        }
+                    }
+                }
+                base += NI;
+                if (kWarps * base >= pairs) break;
+                load_batch(s, g, base, wa, wb);
+            }
+
+            tr.mark();                               // 8+: dot products of a row group done
+            // fields -> one int, odd/even chunk halves by shuffle, warps through shared memory
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                int v = acc_a[m][0] + (acc_a[m][1] >> 2) + (acc_a[m][2] >> 4) + (acc_a[m][3] >> 6);
+                v += __shfl_down_sync(0xffffffffu, v, 16);
+                if (h == 0) part[(warp * MT + m) * 16 + r] = v;
+                if (PAIR) {
+                    int u = acc_b[m][0] + (acc_b[m][1] >> 2) + (acc_b[m][2] >> 4) + (acc_b[m][3] >> 6);
+                    u += __shfl_down_sync(0xffffffffu, u, 16);
+                    if (h == 0) part[kWarps * MT * 16 + (warp * MT + m) * 16 + r] = u;
+                }
+            }
+            __syncthreads();
+
+            if (tid < MT * 16) {
+                const LinearSeg& sg = p.seg[s];
+                const int n = g * kRowsPerGroup + out_r;
+                if (out_m < mt && n < sg.N) {
+                    int va = 0, vb = 0, sx = 0;
+#pragma unroll
+                    for (int w = 0; w < kWarps; ++w) {
+                        va += part[(w * MT + out_m) * 16 + out_r];
+                        if (PAIR) vb += part[kWarps * MT * 16 + (w * MT + out_m) * 16 + out_r];
+                        sx += s_sumx[out_m * kWarps + w];
+                    }
+                    va -= sx;
+                    const size_t o = (size_t)out_row(out_m) * sg.N + n;
+                    if (sg.acc_out) sg.acc_out[o] = va;
+                    const float wsa = GROUPED ? p.grp_scales[z * 3 + sg.scale_idx] : sg.w_scale;
+                    const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[out_m], wsa));
+                    if (PAIR) {
+                        vb -= sx;
+                        if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
+                        const float wsb = GROUPED ? p.grp_scales[z * 3 + p.seg[1].scale_idx] : p.seg[1].w_scale;
+                        const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[out_m], wsb));
+                        if (p.epilogue == LSPK_EPI_SILU_MUL) {
+                            // the reference's Falcon gate (runtime.py:726-732): g / (1 + exp(-g)) * u
+                            sg.out[o] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
+                        } else {
+                            const float gpos = fmaxf(ya, 0.0f);
+                            sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                        }
+                    } else if (p.epilogue == LSPK_EPI_ADD) {
+                        sg.out[o] = __fadd_rn(resid, ya);
+                    } else {
+                        sg.out[o] = ya;
+                    }
+                }
+            }
+            tr.mark();                               // 9+: row group reduced and stored
+            __syncthreads();                         // `part` (and, at the end of a tile, xq) is rewritten next
+            if (!has_next) break;
+            flat = next_flat;
+            s = ns;
+            g = ng;
+            resid = next_resid;
+            if (one_batch) {
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    wa[i] = na[i];
+                    if (PAIR) wb[i] = nb_[i];
+                }
+            } else {
+                load_batch(s, g, 0, wa, wb);
+            }
         }
     }
     tr.end();
@@ -430,26 +407,50 @@ static size_t linear_smem_bytes(int MT, int Kp, bool pair) {
     return b;
 }
 
-template <int MT, int NI, int NB, bool PAIR>
-static cudaError_t launch_linear(const LinearParams& p, int grid_x, size_t smem) {
+template <int MT, int NI, int NB, bool PAIR, bool GROUPED>
+static cudaError_t launch_linear(const LinearParams& p, dim3 grid, size_t smem) {
     static bool attr_set = false;
-    auto kern = ternary_linear_kernel<MT, NI, NB, PAIR>;
+    auto kern = ternary_linear_kernel<MT, NI, NB, PAIR, GROUPED>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const dim3 grid(grid_x, (p.M + MT - 1) / MT);
     return launch(kern, grid, dim3(kThreads), smem, true, p);
 }
 
 template <int MT>
-static cudaError_t launch_linear_mt(const LinearParams& p, int grid_x, bool pair, size_t smem) {
+static cudaError_t launch_linear_mt(const LinearParams& p, dim3 grid, bool pair, size_t smem) {
     if (p.chunks <= 64)
-        return pair ? launch_linear<MT, 4, 1, true>(p, grid_x, smem) : launch_linear<MT, 4, 1, false>(p, grid_x, smem);
+        return pair ? launch_linear<MT, 4, 1, true, false>(p, grid, smem) : launch_linear<MT, 4, 1, false, false>(p, grid, smem);
     if (p.chunks <= 128)
-        return pair ? launch_linear<MT, 8, 2, true>(p, grid_x, smem) : launch_linear<MT, 8, 2, false>(p, grid_x, smem);
-    return pair ? launch_linear<MT, 8, 8, true>(p, grid_x, smem) : launch_linear<MT, 8, 8, false>(p, grid_x, smem);
+        return pair ? launch_linear<MT, 8, 2, true, false>(p, grid, smem) : launch_linear<MT, 8, 2, false, false>(p, grid, smem);
+    return pair ? launch_linear<MT, 8, 8, true, false>(p, grid, smem) : launch_linear<MT, 8, 8, false, false>(p, grid, smem);
+}
+
+int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z) {
+    const int Kp = p.chunks * kWeightsPerChunk;
+    const size_t smem = linear_smem_bytes(mt, Kp, pair);
+    LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768, less for 8-row tiles)", p.K);
+    const dim3 grid(grid_x, grid_y, grid_z);
+    cudaError_t e;
+    if (grouped) {
+        // expert-grouped launches take int8 rows (the fp32 prologue is not instantiated for them)
+        LSPK_REQUIRE(mt == 8 && p.prologue == LSPK_PRO_INT8 && p.chunks <= 128, "linear: unsupported grouped launch");
+        if (p.chunks <= 64)
+            e = pair ? launch_linear<8, 4, 1, true, true>(p, grid, smem) : launch_linear<8, 4, 1, false, true>(p, grid, smem);
+        else
+            e = pair ? launch_linear<8, 8, 1, true, true>(p, grid, smem) : launch_linear<8, 8, 1, false, true>(p, grid, smem);
+    } else {
+        switch (mt) {
+            case 1: e = launch_linear_mt<1>(p, grid, pair, smem); break;
+            case 2: e = launch_linear_mt<2>(p, grid, pair, smem); break;
+            case 4: e = launch_linear_mt<4>(p, grid, pair, smem); break;
+            default: e = launch_linear_mt<8>(p, grid, pair, smem); break;
+        }
+    }
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear launch failed: %s", cudaGetErrorString(e));
+    return LSPK_OK;
 }
 
 // Host-side validation + launch of the CUDA-core kernel.  Used by lspk_linear and by the
@@ -472,7 +473,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
         LSPK_REQUIRE(w && w->K == p.K, "linear: matrices must share K");
         LSPK_REQUIRE(pair ? (i == 1 || a->out[i] != nullptr) : a->out[i] != nullptr, "linear: null output");
         LSPK_REQUIRE(!pair || w->N == w0->N, "linear: gate and up must have the same N");
-        p.seg[i] = LinearSeg{w->dev, a->out[i], a->acc_out[i], w->N, w->groups, w->scale};
+        p.seg[i] = LinearSeg{w->dev, a->out[i], a->acc_out[i], w->N, w->groups, w->scale, i};
         groups += w->groups;
     }
     if (pair) groups = w0->groups;
@@ -481,6 +482,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
     p.prologue = a->prologue;
     p.epilogue = a->epilogue;
     p.x_f32 = a->x_f32;
+    p.gate_f32 = a->gate_f32;
     p.x_i8 = a->x_i8;
     p.x_scales = a->x_scales;
     p.gamma = a->gamma;
@@ -494,6 +496,9 @@ int linear_cuda_core(const lspk_linear_args* a) {
         case LSPK_PRO_INT8:
             LSPK_REQUIRE(a->x_i8 && a->x_scales, "linear: INT8 prologue needs x_i8 and x_scales");
             break;
+        case LSPK_PRO_GATED_RMSNORM_QUANT:
+            LSPK_REQUIRE(a->gate_f32, "linear: GATED_RMSNORM_QUANT prologue needs gate_f32");
+            /* fallthrough */
         case LSPK_PRO_RMSNORM_QUANT:
             LSPK_REQUIRE(a->gamma, "linear: RMSNORM_QUANT prologue needs gamma");
             /* fallthrough */
@@ -505,9 +510,6 @@ int linear_cuda_core(const lspk_linear_args* a) {
     }
     LSPK_REQUIRE(a->epilogue >= 0 && a->epilogue <= 3, "linear: unknown epilogue %d", a->epilogue);
     const int MT = a->M == 1 ? 1 : a->M == 2 ? 2 : a->M <= 4 ? 4 : 8;
-    const int Kp = p.chunks * kWeightsPerChunk;
-    const size_t smem = linear_smem_bytes(MT, Kp, pair);
-    LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768, less for 8-row tiles)", p.K);
     // At most two CTAs per SM when there is a single token tile (measured best on B200: the prologue
     // runs once per CTA, which then loops over its row groups).  With several token tiles the grid's
     // second dimension already fills the machine.
@@ -521,15 +523,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
                                         : (2 * sm_count() + tiles - 1) / tiles;
         if (ctas > per_wave) ctas = per_wave > 0 ? per_wave : 1;
     }
-    cudaError_t e;
-    switch (MT) {
-        case 1: e = launch_linear_mt<1>(p, ctas, pair, smem); break;
-        case 2: e = launch_linear_mt<2>(p, ctas, pair, smem); break;
-        case 4: e = launch_linear_mt<4>(p, ctas, pair, smem); break;
-        default: e = launch_linear_mt<8>(p, ctas, pair, smem); break;
-    }
-    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear launch failed: %s", cudaGetErrorString(e));
-    return LSPK_OK;
+    return linear_launch_params(p, MT, pair, false, ctas, tiles, 1);
 }
 
 }  // namespace lspk
@@ -548,8 +542,10 @@ extern "C" int lspk_linear(const lspk_linear_args* a) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(a, "lspk_linear: null args");
     if (a->prologue != LSPK_PRO_INT8) {
-        LSPK_REQUIRE(((uintptr_t)a->x_f32 & 15) == 0, "lspk_linear: x_f32 must be 16-byte aligned");
-        LSPK_REQUIRE(a->prologue != LSPK_PRO_RMSNORM_QUANT || ((uintptr_t)a->gamma & (a->gamma_is_bf16 ? 7 : 15)) == 0,
+        LSPK_REQUIRE(((uintptr_t)a->x_f32 & 15) == 0 && ((uintptr_t)a->gate_f32 & 15) == 0,
+                     "lspk_linear: x_f32 / gate_f32 must be 16-byte aligned");
+        LSPK_REQUIRE((a->prologue != LSPK_PRO_RMSNORM_QUANT && a->prologue != LSPK_PRO_GATED_RMSNORM_QUANT) ||
+                         ((uintptr_t)a->gamma & (a->gamma_is_bf16 ? 7 : 15)) == 0,
                      "lspk_linear: gamma must be 8-byte (bf16) / 16-byte (fp32) aligned");
     } else {
         LSPK_REQUIRE(((uintptr_t)a->x_i8 & 3) == 0, "lspk_linear: x_i8 must be 4-byte aligned");

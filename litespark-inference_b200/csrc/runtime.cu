@@ -157,6 +157,21 @@ __global__ void advance_pos_kernel(int* __restrict__ ctl, int seq, int by) {
     if (threadIdx.x == 0) ctl[seq] += by;
 }
 
+// ---- launch wrappers shared with the hybrid runtime (kernels must be launched from this file) ----
+int launch_embed(const int* tokens, int rows, int kind, const void* emb, const float* scale, float* x, int H, int V) {
+    LSPK_CUDA(launch(embed_kernel, dim3(rows), dim3(256), 0, true, tokens, kind, emb, scale, x, H, V));
+    return LSPK_OK;
+}
+int launch_argmax_rows(const float* logits, int rows, int V, unsigned long long* best) {
+    LSPK_CUDA(launch(argmax_rows_kernel, dim3(rows), dim3(1024), 0, true, logits, V, best));
+    return LSPK_OK;
+}
+int launch_finish_step(int* ctl, unsigned long long* best, int* tokens_out, int batch, int out_cap) {
+    LSPK_CUDA(launch(finish_step_kernel, dim3(1), dim3(((batch + 31) / 32) * 32), 0, true, ctl, best, tokens_out,
+                     batch, out_cap));
+    return LSPK_OK;
+}
+
 // ---- helpers -------------------------------------------------------------------------------
 
 static int dev_alloc(void** p, size_t bytes, size_t* tally) {

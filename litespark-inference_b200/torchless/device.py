@@ -94,7 +94,8 @@ class DeviceWeight:
 
 def linear(weights: Sequence, outs: Sequence[Optional[DeviceArray]], M: int, *, x_f32: Optional[DeviceArray] = None,
            x_i8: Optional[DeviceArray] = None, x_scales: Optional[DeviceArray] = None,
-           gamma: Optional[DeviceArray] = None, eps: float = 1e-5, epilogue: int = _k.EPI_STORE,
+           gamma: Optional[DeviceArray] = None, gate_f32: Optional[DeviceArray] = None, eps: float = 1e-5,
+           epilogue: int = _k.EPI_STORE,
            acc_outs: Sequence[Optional[DeviceArray]] = (), xq_out: Optional[DeviceArray] = None,
            xscale_out: Optional[DeviceArray] = None) -> None:
     """Call ``lspk_linear``.  The prologue follows from the inputs given: int8 + scales ->
@@ -117,8 +118,10 @@ def linear(weights: Sequence, outs: Sequence[Optional[DeviceArray]], M: int, *, 
         a.x_scales = x_scales.ptr
     else:
         a.x_f32 = x_f32.ptr
+        if gate_f32 is not None:
+            a.gate_f32 = gate_f32.ptr
         if gamma is not None:
-            a.prologue = _k.PRO_RMSNORM_QUANT
+            a.prologue = _k.PRO_GATED_RMSNORM_QUANT if gate_f32 is not None else _k.PRO_RMSNORM_QUANT
             a.gamma = gamma.ptr
             a.gamma_is_bf16 = int(gamma.dtype == np.uint16)
         else:

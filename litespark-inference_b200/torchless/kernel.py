@@ -48,11 +48,11 @@ class LinearArgs(ctypes.Structure):
         ("prologue", _ci), ("epilogue", _ci),
         ("x_f32", _vp), ("x_i8", _vp), ("x_scales", _vp),
         ("gamma", _vp), ("gamma_is_bf16", _ci), ("eps", _cf),
-        ("acc_out", _vp * 3), ("xq_out", _vp), ("xscale_out", _vp),
+        ("acc_out", _vp * 3), ("xq_out", _vp), ("xscale_out", _vp), ("gate_f32", _vp),
     ]
 
 
-PRO_INT8, PRO_QUANT, PRO_RMSNORM_QUANT = 0, 1, 2
+PRO_INT8, PRO_QUANT, PRO_RMSNORM_QUANT, PRO_GATED_RMSNORM_QUANT = 0, 1, 2, 3
 EPI_STORE, EPI_ADD, EPI_RELU2_MUL, EPI_SILU_MUL = 0, 1, 2, 3
 
 # name -> (argtypes, restype) of every symbol declared in include/lspk_sm100.h
