@@ -174,6 +174,70 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+def run_sweep(args):
+    """Config 2: the five BitNet-2B projection shapes x token counts; fused-quantiser linear launches
+    rotated over enough device copies of the matrix to exceed the L2 (about 300 MB per shape)."""
+    entry.load_package()
+    from litespark_inference_b200.torchless import device as dev
+    from litespark_inference_b200.torchless import kernel as K
+    from litespark_inference_b200.torchless import synthetic
+    lib = K.load_library(True)
+    peak, peak_kind = load_peaks()
+    rng = np.random.default_rng(0)
+    rows = []
+    for name in ("q", "k", "gate", "down"):
+        N, Kd = synthetic.BITNET_2B_SHAPES[name]
+        proj = synthetic.random_projection_fast(rng, N, Kd)
+        n_copies = max(2, int(np.ceil(300e6 / (N * Kd / 4))))
+        copies = [dev.DeviceWeight(proj.w_packed, proj.scale) for _ in range(n_copies)]
+        handles = (ctypes.c_void_p * n_copies)(*[c.handle for c in copies])
+        for M in (1, 8, 32, 128, 512):
+            x = dev.DeviceArray.from_numpy(rng.standard_normal((M, Kd)).astype(np.float32))
+            y = dev.DeviceArray((M, N), np.float32)
+            ms = ctypes.c_float(0.0)
+            reps = 20 if M <= 8 else 5
+            K.check(lib.lspk_bench_linear_copies(handles, n_copies, x.ptr, y.ptr, M, reps, ctypes.byref(ms)))
+            K.check(lib.lspk_tc_check_error())
+            us = 1000.0 * ms.value / (reps * n_copies)
+            nbytes = N * Kd / 4 + 4 * M * Kd + 4 * M * N
+            ops = 2.0 * M * N * Kd
+            rows.append({"shape": name, "N": N, "K": Kd, "M": M, "us": us, "GBps": nbytes / us / 1e3,
+                         "frac_hbm": nbytes / us / 1e3 / peak, "TOPS": ops / us / 1e6,
+                         "path": "tcgen05" if M >= 32 else "cuda-core"})
+            x.free()
+            y.free()
+        for c in copies:
+            c.free()
+    print(json.dumps({"workload": "sweep", "peak_GBps": peak, "peak_kind": peak_kind, "rows": rows}))
+
+
+def run_hybrid(args):
+    """Config 5: 24-layer Mamba-2 + MoE decoder, 128 greedy steps after a 128-token prompt at batch 1 and 16."""
+    entry.load_package()
+    from litespark_inference_b200.torchless import hybrid as hyb
+    from litespark_inference_b200.torchless import kernel as K
+    lib = K.load_library(True)
+    cfg = hyb.HybridConfig()
+    model = hyb.random_hybrid(cfg, seed=0, fast=True)
+    d = hyb.DeviceHybrid(model)
+    out = {"workload": "hybrid", "device_bytes": d.device_bytes, "batches": []}
+    ms = ctypes.c_float(0.0)
+    for B in (1, 16):
+        st = hyb.HybridState(d, batch=B, max_steps=GEN_LEN)
+        prompts = np.random.default_rng(7).integers(0, cfg.vocab_size, (PROMPT_LEN, B)).astype(np.int32)
+        first = st.prefill(prompts)
+        best = None
+        for _ in range(max(args.steps, 1) + 1):
+            K.check(lib.lspk_timer_start())
+            st.decode_greedy(first, GEN_LEN)
+            K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
+            best = ms.value if best is None else min(best, ms.value)
+        out["batches"].append({"batch": B, "tok_s": B * GEN_LEN / (best / 1000.0), "ms_per_step": best / GEN_LEN,
+                               "kernels_per_step": st.step_kernel_count})
+        st.close()
+    print(json.dumps(out))
+
+
 def main():
     global PROMPT_LEN, GEN_LEN
     ap = argparse.ArgumentParser()
@@ -182,6 +246,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="tg128", choices=["tg128", "sweep", "hybrid"],
+                    help="tg128: the headline line; sweep: per-shape x token-count table of the ternary linear "
+                         "kernels; hybrid: Mamba-2 + MoE decode (extra lines, not the headline)")
     ap.add_argument("--seqs-per-gpu", type=int, default=8, help="batch of the extra data-parallel measurement")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompt for profiler captures")
     ap.add_argument("--gen-len", type=int, default=GEN_LEN, help="fewer decode steps for profiler captures")
@@ -193,6 +260,12 @@ def main():
         run_reference_arm(args)
         return
     args.warmup = max(args.warmup, 3)
+    if args.workload == "sweep":
+        run_sweep(args)
+        return
+    if args.workload == "hybrid":
+        run_hybrid(args)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -219,6 +292,16 @@ def main():
     K.check(lib.lspk_forward_prefill(state.handle, 0, ids.ctypes.data, PROMPT_LEN, None, None, first.ctypes.data))
     toks = np.empty(GEN_LEN, np.int32)
     ms = ctypes.c_float(0.0)
+
+    def pp_device():
+        state.pos = 0
+        K.check(lib.lspk_timer_start())
+        K.check(lib.lspk_forward_prefill(state.handle, 0, ids.ctypes.data, PROMPT_LEN, None, None, first.ctypes.data))
+        K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
+        return float(ms.value)
+
+    pp_device()
+    pp_ms = min(pp_device() for _ in range(3))
 
     def tg128_device():
         state.pos = PROMPT_LEN
@@ -358,6 +441,8 @@ def main():
                 "how": "host loop over lspk_forward_step: token id up from pinned memory, greedy token id back, every step"},
         "e2e_logits_to_host": {"value": e2e_logits_value, "unit": "tok/s", "d2h_bytes_per_step": 4 * cfg.vocab_size * GEN_LEN,
                                "how": "forward_one returning fp32 logits [V] to the host + np.argmax, the reference API's loop"},
+        "prefill": {"tokens": PROMPT_LEN, "ms": pp_ms, "tok_s": PROMPT_LEN / (pp_ms / 1000.0),
+                    "how": "lspk_forward_prefill of the prompt (tcgen05 GEMM for the projections), CUDA events, best of 3"},
         "gpu_launches": args.steps * GEN_LEN * step_kernels,
         "kernels_per_token": step_kernels,
         "roofline": {"kernel": "ternary_linear_kernel (M=1, fused RMSNorm+quantiser prologue)",

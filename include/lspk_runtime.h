@@ -82,6 +82,9 @@ int lspk_state_step_kernel_count(lspk_state_t s);
  * LM-head kernel alone.  Both report CUDA-event milliseconds and the algorithmic bytes of ONE pass. */
 int lspk_bench_linears(lspk_state_t s, int reps, float* ms_out, int* launches_out, double* bytes_out);
 int lspk_bench_lm_head(lspk_state_t s, int reps, float* ms_out, double* bytes_out);
+/* Time y = W_i (quant x) over n_w device copies of one matrix visited round-robin (reps passes). */
+int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
+                             float* ms_out);
 /* Floor cost of a kernel boundary: a graph of n_kernels empty dependent kernels, replayed reps times. */
 int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out);
 

@@ -126,6 +126,9 @@ typedef struct {
  * GEMM instead when M is large enough and the shape allows it. */
 int lspk_linear(const lspk_linear_args* a);
 int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tcgen05 only */
+/* The tcgen05 kernel bounds every device-side wait; this reads and clears its expiry flag
+ * (LSPK_ERR_DEVICE_WAIT if a wait ran out since the last call).  Synchronises the stream. */
+int lspk_tc_check_error(void);
 
 /* ------------------------------------------------------------------------------------ */
 /* Element-wise helpers on device-resident rows (batched over T rows)                     */

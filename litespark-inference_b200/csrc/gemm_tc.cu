@@ -1,12 +1,455 @@
-// Tensor-core (tcgen05) path of the ternary linear layer for large token counts.
+// Prefill path of the ternary linear layer on the 5th-generation tensor cores (tcgen05).
+//
+//   acc[t, n] = sum_k w[n, k] * xq[t, k]      int8 x int8 -> int32 in tensor memory (exact)
+//   y[t, n]   = float(acc) * (xscale[t] * wscale)
+//
+// Replaces, for many token rows, what the reference does with its batched kernel
+// (matmul_lut_avx512_mT, matmul_lut_avx512_extern_c.cpp:258-339) and, as the tensor-unit analogue,
+// its AMX tile GEMM (matmul_amx_int8_mT_v2, :819-933).
+//
+// One CTA owns 128 output features (the MMA's M side: one TMEM lane per feature) and TN token rows
+// (the MMA's N side: one TMEM column per token).  Per 128-wide K block, through a 4-stage ring:
+//   warp 0      TMA: 4 KB of packed 2-bit weights (128 rows x 32 bytes of the device chunk layout)
+//               and the TN x 128-byte tile of int8 activations (128-byte swizzle) -> shared memory
+//   warps 2-5   expand the packed rows to signed int8 {-1,0,+1} in the canonical K-major,
+//               128-byte-swizzled operand layout (thread = weight row; one packed word -> 16 bytes)
+//   warp 1      one thread issues 4 x tcgen05.mma.kind::i8 (M=128, N=TN, K=32) per block and
+//               commits the stage back to the producer
+// then warps 2-5 read the accumulators with tcgen05.ld and write fp32 (and, if asked, the int32).
+// The activations are stored with the 4x4 index transpose inside every 16-element block that the
+// masked decode of a packed word implies (same trick as the CUDA-core kernel), so a packed word
+// expands with 4 x (shift, and, byte-subtract) and lands as one aligned 16-byte chunk.
+//
+// Every wait on an mbarrier is bounded; on expiry the kernel records an error code, stops issuing
+// work, drains its own copies, frees its tensor memory and returns.
+#include <cuda.h>
+#include <stdlib.h>
+
 #include "internal.cuh"
 
 namespace lspk {
 
+constexpr int kTcThreads = 192;          // 6 warps: TMA, MMA, 4 x expand/epilogue
+constexpr int kTcStages = 4;
+constexpr int kTcBK = 128;               // K elements per pipeline block
+constexpr int kTcRows = 128;             // output features per CTA
+constexpr unsigned kSpinLimit = 1u << 22;
+
+struct TcParams {
+    float* out;
+    int32_t* acc_out;
+    const float* x_scales;
+    float w_scale;
+    int M, N, K;
+    int k_blocks;
+    int epilogue;            // LSPK_EPI_STORE or LSPK_EPI_ADD
+    int* error_flag;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached or
+// another thread already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart (stride field 64), leading field 1, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused for this layout)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                                // version
+    d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+    return d;
+}
+
+template <int TN>
+__global__ void __launch_bounds__(kTcThreads)
+ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       const TcParams p) {
+    constexpr int kPackedBytes = kTcRows * kTcBK / 4;       // 4096
+    constexpr int kATileBytes = kTcRows * kTcBK;            // 16384
+    constexpr int kBTileBytes = TN * kTcBK;
+    constexpr int kStageBytes = kPackedBytes + kATileBytes + kBTileBytes;
+    constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;       // power of two >= 32
+    // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = TN, M = 128
+    constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((128u >> 4) << 24);
+
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_tma[kTcStages];
+    __shared__ __align__(8) uint64_t full_a[kTcStages];
+    __shared__ __align__(8) uint64_t empty[kTcStages];
+    __shared__ __align__(8) uint64_t acc_ready;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * kTcRows;
+    const int m0 = blockIdx.y * TN;
+
+    auto a_tile = [&](int s) { return smem + (size_t)s * kStageBytes; };
+    auto b_tile = [&](int s) { return smem + (size_t)s * kStageBytes + kATileBytes; };
+    auto packed = [&](int s) { return smem + (size_t)s * kStageBytes + kATileBytes + kBTileBytes; };
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(&full_tma[s], 1);
+            mbar_init(&full_a[s], 128);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(&acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abortp = &abort_flag;
+
+    grid_dependency_launch();
+    grid_dependency_wait();                 // the activations come from the previous kernel
+
+    if (warp == 0) {
+        // ---------------- producer ------------------------------------------------------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                const int s = kb % kTcStages;
+                if (kb >= kTcStages && !mbar_wait(&empty[s], ((kb / kTcStages) - 1) & 1, abortp)) break;
+                if (*abortp) break;
+                mbar_expect_tx(&full_tma[s], kPackedBytes + kBTileBytes);
+                // packed weights: inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes
+                // = 128 units per row group), outer coordinate = row group
+                tma_load_2d(packed(s), &map_w, kb * 128, n0 / kRowsPerGroup, &full_tma[s]);
+                tma_load_2d(b_tile(s), &map_x, kb * kTcBK, m0, &full_tma[s]);
+                ++issued;
+            }
+            if (*abortp) {
+                // drain: wait (bounded) for every copy this thread started
+                for (int kb = 0; kb < issued; ++kb) {
+                    const int s = kb % kTcStages;
+                    if (kb + kTcStages >= issued)
+                        for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&full_tma[s], (kb / kTcStages) & 1); ++i) {}
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ------------------------------------------------------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+                const int s = kb % kTcStages;
+                const uint32_t ph = (kb / kTcStages) & 1;
+                ok = mbar_wait(&full_tma[s], ph, abortp) && mbar_wait(&full_a[s], ph, abortp);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da = umma_desc_sw128(smem_u32(a_tile(s)));
+                const uint64_t db = umma_desc_sw128(smem_u32(b_tile(s)));
+#pragma unroll
+                for (int k4 = 0; k4 < kTcBK / 32; ++k4) {
+                    const uint32_t accumulate = (kb | k4) ? 1u : 0u;
+                    // advancing 32 int8 along K = 32 bytes = 2 descriptor address units
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem_base), "l"(da + (uint64_t)(k4 * 2)), "l"(db + (uint64_t)(k4 * 2)), "r"(kIdesc),
+                        "r"(accumulate)
+                        : "memory");
+                }
+                // frees the stage for the producer once the MMAs above have read it
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 smem_u32(&empty[s]))
+                             : "memory");
+            }
+            if (ok)
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 smem_u32(&acc_ready))
+                             : "memory");
+        }
+    } else {
+        // ---------------- expand packed weights -> int8 operand tile, then epilogue ---------------
+        const int row = tid - 64;                         // 0..127: weight row inside the CTA tile
+        const int gi = row >> 4, rr = row & 15;
+        bool ok = true;
+        for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+            const int s = kb % kTcStages;
+            ok = mbar_wait(&full_tma[s], (kb / kTcStages) & 1, abortp);
+            if (!ok) break;
+            const unsigned char* pk = packed(s);
+            unsigned char* arow = a_tile(s) + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {                  // the two 64-weight chunks of this K block
+                const uint4 w = *reinterpret_cast<const uint4*>(pk + gi * 512 + c * 256 + rr * 16);
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    uint4 o;
+                    o.x = __vsub4(words[m] & 0x03030303u, 0x01010101u);
+                    o.y = __vsub4((words[m] >> 2) & 0x03030303u, 0x01010101u);
+                    o.z = __vsub4((words[m] >> 4) & 0x03030303u, 0x01010101u);
+                    o.w = __vsub4((words[m] >> 6) & 0x03030303u, 0x01010101u);
+                    const int chunk = c * 4 + m;           // 16-byte chunk index inside the 128-byte row
+                    *reinterpret_cast<uint4*>(arow + ((chunk ^ (row & 7)) << 4)) = o;
+                }
+            }
+            fence_async_smem();                            // generic-proxy writes -> visible to the tensor unit
+            mbar_arrive(&full_a[s]);
+        }
+        // epilogue: TMEM lane = weight row, column = token
+        if (ok) ok = mbar_wait(&acc_ready, 0, abortp);
+        ok = __all_sync(0xffffffffu, ok);              // the tensor-memory loads below need the whole warp
+        if (ok) {
+            tc_fence_after();
+            const int quarter = warp & 3;                  // TMEM lanes this warp may read
+            const int n = n0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int cb = 0; cb < TN / 32; ++cb) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]),
+                      "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]),
+                      "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int t = m0 + cb * 32 + j;
+                        if (t < p.M) {
+                            const int a = (int)v[j];
+                            const size_t o = (size_t)t * p.N + n;
+                            if (p.acc_out) p.acc_out[o] = a;
+                            const float y = __fmul_rn((float)a, __fmul_rn(p.x_scales[t], p.w_scale));
+                            p.out[o] = p.epilogue == LSPK_EPI_ADD ? __fadd_rn(p.out[o], y) : y;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (tid == 0 && abort_flag && p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+}
+
+// int8 rows [M, K] in natural order -> [M, Kp] with the 4x4 transpose inside every 16-element block
+// (Kp = K rounded up to 64, zero padded), the order the expanded weights come out in.
+__global__ void permute_rows_kernel(const int8_t* __restrict__ src, int8_t* __restrict__ dst, int M, int K, int Kp) {
+    grid_dependency_launch();
+    grid_dependency_wait();
+    const size_t total = (size_t)M * Kp;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / Kp), kp = (int)(i % Kp);
+        const int k = perm_index(kp);                      // the transpose is its own inverse
+        dst[i] = k < K ? src[(size_t)t * K + k] : (int8_t)0;
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+struct TcScratch {
+    int8_t *xq = nullptr, *xq_perm = nullptr;
+    float* xs = nullptr;
+    int* err = nullptr;
+    size_t cap_xq = 0, cap_perm = 0, cap_xs = 0;
+};
+static TcScratch g_tc;
+
+static int grow(void** p, size_t* cap, size_t need) {
+    if (need <= *cap) return LSPK_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    LSPK_CUDA(cudaMalloc(p, need + need / 4 + 256));
+    *cap = need + need / 4 + 256;
+    return LSPK_OK;
+}
+
+template <int TN>
+static cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid) {
+    constexpr size_t smem = (size_t)kTcStages * (kTcRows * kTcBK / 4 + kTcRows * kTcBK + TN * kTcBK) + 1024;
+    static bool attr_set = false;
+    auto kern = ternary_gemm_tc_kernel<TN>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    return launch(kern, grid, dim3(kTcThreads), smem, true, mw, mx, p);
+}
+
+// Tensor-core path.  Handles STORE / ADD epilogues of one or several matrices sharing the input
+// (each matrix is its own launch); the gated pairings stay on the CUDA-core kernel.
 int linear_tensor_core(const lspk_linear_args* a, int* handled) {
-    (void)a;
     *handled = 0;
+    static const int min_m = getenv("LSPK_TC_MIN_M") ? atoi(getenv("LSPK_TC_MIN_M")) : 32;
+    if (a->M < min_m) return LSPK_OK;
+    if (a->epilogue != LSPK_EPI_STORE && a->epilogue != LSPK_EPI_ADD) return LSPK_OK;
+    if (a->prologue == LSPK_PRO_GATED_RMSNORM_QUANT) return LSPK_OK;
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return LSPK_OK;
+    const Weight* w0 = reinterpret_cast<const Weight*>(a->w[0]);
+    if (!w0) return LSPK_OK;
+    const int M = a->M, K = w0->K, Kp = w0->chunks * kWeightsPerChunk;
+
+    // ---- activations: int8 rows + scales, then the permuted, padded copy the tensor map reads ----
+    const int8_t* xq = a->x_i8;
+    const float* xs = a->x_scales;
+    if (a->prologue != LSPK_PRO_INT8) {
+        if (int rc = grow((void**)&g_tc.xq, &g_tc.cap_xq, (size_t)M * K)) return rc;
+        if (int rc = grow((void**)&g_tc.xs, &g_tc.cap_xs, (size_t)M * 4)) return rc;
+        int rc = a->prologue == LSPK_PRO_RMSNORM_QUANT
+                     ? lspk_rmsnorm_quantize_rows(a->x_f32, a->gamma, a->gamma_is_bf16, g_tc.xq, g_tc.xs, M, K, a->eps)
+                     : lspk_quantize_rows(a->x_f32, g_tc.xq, g_tc.xs, M, K);
+        if (rc) return rc;
+        xq = g_tc.xq;
+        xs = g_tc.xs;
+    }
+    if (int rc = grow((void**)&g_tc.xq_perm, &g_tc.cap_perm, (size_t)M * Kp)) return rc;
+    if (!g_tc.err) {
+        LSPK_CUDA(cudaMalloc((void**)&g_tc.err, 16));
+        LSPK_CUDA(cudaMemset(g_tc.err, 0, 16));
+    }
+    {
+        const size_t total = (size_t)M * Kp;
+        int grid = (int)((total + 255) / 256);
+        if (grid > sm_count() * 8) grid = sm_count() * 8;
+        LSPK_CUDA(launch(permute_rows_kernel, dim3(grid), dim3(256), 0, true, xq, g_tc.xq_perm, M, K, Kp));
+    }
+    if (a->xq_out) LSPK_CUDA(cudaMemcpyAsync(a->xq_out, xq, (size_t)M * K, cudaMemcpyDeviceToDevice, stream()));
+    if (a->xscale_out) LSPK_CUDA(cudaMemcpyAsync(a->xscale_out, xs, (size_t)M * 4, cudaMemcpyDeviceToDevice, stream()));
+
+    const int TN = M >= 128 ? 128 : M > 32 ? 64 : 32;
+    CUtensorMap mx;
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)M};
+        const cuuint64_t strides[1] = {(cuuint64_t)Kp};
+        const cuuint32_t box[2] = {(cuuint32_t)kTcBK, (cuuint32_t)TN};
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&mx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, g_tc.xq_perm, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LSPK_ERR_CUDA, "tensor map (activations) failed: %d", (int)r);
+    }
+    for (int i = 0; i < a->n_mats; ++i) {
+        const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
+        LSPK_REQUIRE(w && w->K == K && a->out[i], "linear (tensor-core): matrices must share K and have outputs");
+        CUtensorMap mw;
+        const cuuint64_t row_words = (cuuint64_t)w->chunks * 64;          // 4-byte units per row group
+        const cuuint64_t dims[2] = {row_words, (cuuint64_t)w->groups};
+        const cuuint64_t strides[1] = {row_words * 4};
+        const cuuint32_t box[2] = {128, 8};                               // 512 bytes x 8 row groups
+        const cuuint32_t estr[2] = {1, 1};
+        CUresult r = enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w->dev, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(LSPK_ERR_CUDA, "tensor map (weights) failed: %d", (int)r);
+        TcParams p = {};
+        p.out = a->out[i];
+        p.acc_out = a->acc_out[i];
+        p.x_scales = xs;
+        p.w_scale = w->scale;
+        p.M = M;
+        p.N = w->N;
+        p.K = K;
+        p.k_blocks = (Kp + kTcBK - 1) / kTcBK;
+        p.epilogue = a->epilogue;
+        p.error_flag = g_tc.err;
+        const dim3 grid((w->N + kTcRows - 1) / kTcRows, (M + TN - 1) / TN);
+        cudaError_t e = TN == 128 ? launch_tc<128>(mw, mx, p, grid)
+                       : TN == 64 ? launch_tc<64>(mw, mx, p, grid)
+                                  : launch_tc<32>(mw, mx, p, grid);
+        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
+    }
+    *handled = 1;
+    return LSPK_OK;
+}
+
+// Reads (and clears) the device-side wait-expiry flag of the tensor-core kernel.
+int tensor_core_check_error() {
+    if (!g_tc.err) return LSPK_OK;
+    int v = 0;
+    LSPK_CUDA(cudaMemcpyAsync(&v, g_tc.err, 4, cudaMemcpyDeviceToHost, stream()));
+    LSPK_CUDA(cudaStreamSynchronize(stream()));
+    if (v) {
+        cudaMemsetAsync(g_tc.err, 0, 4, stream());
+        return fail(LSPK_ERR_DEVICE_WAIT, "tensor-core GEMM: a bounded device-side wait expired");
+    }
     return LSPK_OK;
 }
 
 }  // namespace lspk
+
+extern "C" int lspk_tc_check_error(void) { return lspk::tensor_core_check_error(); }

@@ -67,8 +67,8 @@ row_norm_quant_kernel(const float* __restrict__ x, const void* __restrict__ gamm
     if (tid == 0) scales[t] = scale;
 }
 
-__global__ void relu2_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up,
-                                 float* __restrict__ out, size_t n) {
+// `out` may alias `gate` (in-place gating): no restrict qualifiers.
+__global__ void relu2_mul_kernel(const float* gate, const float* up, float* out, size_t n) {
     grid_dependency_launch();
     grid_dependency_wait();
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {

@@ -50,7 +50,7 @@ struct State {
     int* ctl = nullptr;               // device: pos[batch], token[batch], step
     unsigned long long* best = nullptr;   // device: argmax keys [batch]
     int* tokens_out = nullptr;        // device: [t_max * batch]
-    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *inter = nullptr;
+    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *inter = nullptr, *inter2 = nullptr;
     float *logits = nullptr;          // [max(batch, 8), V]
     int logits_rows = 0;
     int8_t *xq_h = nullptr, *xq_i = nullptr;
@@ -278,7 +278,13 @@ static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool
                             LSPK_EPI_ADD)) return rc;
     }
     // MLP block
-    {
+    if (rows >= 32 && bitnet) {
+        // many rows: gate and up as two plain products (they take the tensor-core path), then the gate
+        const int which[2] = {LSPK_PROJ_GATE, LSPK_PROJ_UP};
+        float* outs[2] = {s->inter, s->inter2};
+        if (int rc = linear(2, which, outs, s->x, s->xq_h, &L.norm[LSPK_NORM_POST_ATTN], H, LSPK_EPI_STORE)) return rc;
+        if (int rc = lspk_relu2_mul_rows(s->inter, s->inter2, s->inter, rows, I)) return rc;
+    } else {
         const int which[2] = {LSPK_PROJ_GATE, LSPK_PROJ_UP};
         float* outs[2] = {s->inter, nullptr};
         if (int rc = linear(2, which, outs, s->x, s->xq_h, &L.norm[LSPK_NORM_POST_ATTN], H,
@@ -507,6 +513,7 @@ lspk_state_t lspk_state_create(lspk_model_t h, int t_max, int batch, int kv_fp16
     rc |= dev_alloc((void**)&s->v, R * kv * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->attn, R * H * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->inter, R * I * 4, &s->bytes);
+    rc |= dev_alloc((void**)&s->inter2, R * I * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->logits, (size_t)s->logits_rows * V * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->xq_h, R * H, &s->bytes);
     rc |= dev_alloc((void**)&s->xq_i, R * I, &s->bytes);
@@ -539,7 +546,7 @@ int lspk_state_free(lspk_state_t h) {
     for (auto& g : s->graph)
         if (g) cudaGraphExecDestroy(g);
     void* dev[] = {s->cache_k, s->cache_v, s->rope_cos, s->rope_sin, s->ctl, s->best, s->tokens_out, s->x, s->q, s->k,
-                   s->v, s->attn, s->inter, s->logits, s->xq_h, s->xq_i, s->xs, s->tok_rows};
+                   s->v, s->attn, s->inter, s->inter2, s->logits, s->xq_h, s->xq_i, s->xs, s->tok_rows};
     for (void* p : dev) cudaFree(p);
     if (s->h_int) cudaFreeHost(s->h_int);
     if (s->h_logits) cudaFreeHost(s->h_logits);
@@ -755,6 +762,49 @@ int lspk_bench_lm_head(lspk_state_t h, int reps, float* ms_out, double* bytes_ou
     LSPK_CUDA(cudaMemsetAsync(s->best, 0, 8, stream()));
     if (bytes_out) *bytes_out = (double)table_bytes(head.kind, c.vocab_size, c.hidden_size) + 4.0 * c.hidden_size;
     return LSPK_OK;
+}
+
+// Time the fused-quantiser linear product y = W_i (quant x) over `n_w` device copies of a matrix,
+// visited round-robin so that consecutive launches read different HBM (defeats the L2 when the
+// copies together exceed it).  One pass over all copies is captured into a graph and replayed.
+int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
+                             float* ms_out) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_REQUIRE(w && n_w >= 1 && x_f32 && y && M >= 1 && reps >= 1 && ms_out, "lspk_bench_linear_copies: bad arguments");
+    auto enqueue = [&]() -> int {
+        for (int i = 0; i < n_w; ++i) {
+            lspk_linear_args a = {};
+            a.w[0] = w[i];
+            a.out[0] = y;
+            a.n_mats = 1;
+            a.M = M;
+            a.prologue = LSPK_PRO_QUANT;
+            a.epilogue = LSPK_EPI_STORE;
+            a.x_f32 = x_f32;
+            if (int rc = lspk_linear(&a)) return rc;
+        }
+        return LSPK_OK;
+    };
+    if (int rc = enqueue()) return rc;                   // sizes scratch, sets kernel attributes
+    LSPK_CUDA(cudaStreamSynchronize(stream()));
+    cudaGraph_t g = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue();
+    cudaError_t e = cudaStreamEndCapture(stream(), &g);
+    if (rc) return rc;
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    cudaGraphLaunch(exec, stream());
+    rc = lspk_timer_start();
+    for (int i = 0; i < reps && !rc; ++i)
+        if (cudaGraphLaunch(exec, stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
+    if (!rc) rc = lspk_timer_stop(ms_out);
+    cudaStreamSynchronize(stream());
+    cudaGraphExecDestroy(exec);
+    return rc;
 }
 
 // Floor cost of a dependent kernel boundary: replay a graph of `n_kernels` kernels of `grid` CTAs x

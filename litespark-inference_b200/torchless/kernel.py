@@ -86,6 +86,7 @@ _SIGNATURES = {
                            ctypes.POINTER(_sz)], _ci),
     "lspk_linear": ([ctypes.POINTER(LinearArgs)], _ci),
     "lspk_linear_force_path": ([_ci], _ci),
+    "lspk_tc_check_error": ([], _ci),
     "lspk_quantize_rows": ([_vp, _vp, _vp, _ci, _ci], _ci),
     "lspk_rmsnorm_rows": ([_vp, _vp, _ci, _vp, _ci, _ci, _cf], _ci),
     "lspk_rmsnorm_quantize_rows": ([_vp, _vp, _ci, _vp, _vp, _ci, _ci, _cf], _ci),

@@ -256,3 +256,40 @@ def test_device_row_helpers_and_lm_head_rows(port):
     wq, wsc = np.empty((T, Kd), np.int8), np.empty(T, np.float32)
     port.quantize_activation_batched(x, wq, wsc)
     assert np.array_equal(xq.numpy(), wq) and np.array_equal(xs.numpy(), wsc)
+
+
+# ---- tensor-core (tcgen05) path ------------------------------------------------------------------
+@pytest.mark.parametrize("N,Kd,M", [(128, 128, 32), (2560, 2560, 128), (640, 2560, 64), (6912, 2560, 512),
+                                    (2560, 6912, 100), (130, 448, 33), (17, 64, 40), (300, 1000, 130)])
+def test_tensor_core_path_bit_exact(port, N, Kd, M):
+    """The tcgen05 int8 GEMM against the oracle and against the CUDA-core kernel: int32 accumulators
+    bit-exact, fp32 outputs bit-exact (same two multiplies), at model shapes and at ragged ones
+    (feature count off the 128-row tile, K off the 128-wide block, token count off the tile)."""
+    lib = K.load_library()
+    w, packed, x, ws = _rand_case(N * 3 + Kd + M, N, Kd, M)
+    xq, xs = np.empty((M, Kd), np.int8), np.empty(M, np.float32)
+    port.quantize_activation_batched(x, xq, xs)
+    want_acc = port.acc_int32(xq, packed)
+    want_y = port.matmul_packed_mT(xq, xs, packed, ws)
+    W = dev.DeviceWeight(packed, ws)
+    dxq, dxs = dev.DeviceArray.from_numpy(xq), dev.DeviceArray.from_numpy(xs)
+    try:
+        K.check(lib.lspk_linear_force_path(2))
+        y, acc = dev.DeviceArray((M, N), np.float32), dev.DeviceArray((M, N), np.int32)
+        dev.linear([W], [y], M, x_i8=dxq, x_scales=dxs, acc_outs=[acc])
+        K.check(lib.lspk_tc_check_error())
+        assert np.array_equal(acc.numpy(), want_acc)
+        assert np.array_equal(y.numpy(), want_y)
+        # fused quantiser in front, residual-add behind
+        res = np.random.default_rng(1).standard_normal((M, N)).astype(np.float32)
+        dres = dev.DeviceArray.from_numpy(res)
+        dev.linear([W], [dres], M, x_f32=dev.DeviceArray.from_numpy(x), epilogue=K.EPI_ADD)
+        K.check(lib.lspk_tc_check_error())
+        assert np.array_equal(dres.numpy(), res + want_y)
+        K.check(lib.lspk_linear_force_path(1))
+        y1 = dev.DeviceArray((M, N), np.float32)
+        dev.linear([W], [y1], M, x_i8=dxq, x_scales=dxs)
+        assert np.array_equal(y1.numpy(), want_y)
+    finally:
+        lib.lspk_linear_force_path(0)
+    W.free()
