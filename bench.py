@@ -174,6 +174,42 @@ def run_reference_arm(args):
     print(json.dumps(line))
 
 
+def bench_tp_mlp(dist, rank, world, model, lib, K):
+    """Batch-1 MLP block (gate/up -> ReLU^2 -> SubLN+quant -> down) with the rows of gate/up/down split over
+    the ranks and the fp32 slices all-gathered by NCCL, against the same block unsplit on one GPU.  A graph of
+    the 30 layers' blocks is replayed; device time, max over ranks."""
+    import torch
+    from litespark_inference_b200.torchless import device as dev
+    from litespark_inference_b200.torchless import tp
+    uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        uid = torch.tensor(list(tp.DeviceTP.make_unique_id()), dtype=torch.uint8, device="cuda")
+    dist.broadcast(uid, 0)
+    group = tp.DeviceTP(rank, world, bytes(uid.cpu().tolist()))
+    H, I = model.config.hidden_size, model.config.intermediate_size
+    W = lambda p: dev.DeviceWeight(p.w_packed, p.scale)
+    sl = [[W(tp.slice_projection(getattr(L, n), world, rank)) for L in model.layers]
+          for n in ("gate_proj", "up_proj", "down_proj")]
+    arr = lambda ws: (ctypes.c_void_p * len(ws))(*[w.handle for w in ws])
+    x = dev.DeviceArray.from_numpy(np.random.default_rng(3).standard_normal((1, H)).astype(np.float32))
+    norm = dev.DeviceArray.from_numpy(np.ascontiguousarray(model.layers[0].post_attn_norm))
+    sub = dev.DeviceArray.from_numpy(np.ascontiguousarray(model.layers[0].ffn_sub_norm))
+    i_s, i_f = dev.DeviceArray((I // world,), np.float32), dev.DeviceArray((I,), np.float32)
+    d_s, y_f = dev.DeviceArray((H // world,), np.float32), dev.DeviceArray((H,), np.float32)
+    ms = ctypes.c_float(0.0)
+    n_blocks, reps = len(model.layers), 20
+    dist.barrier()
+    K.check(lib.lspk_tp_bench_mlp(arr(sl[0]), arr(sl[1]), arr(sl[2]), n_blocks, x.ptr, norm.ptr, sub.ptr, 1e-5,
+                                  i_s.ptr, i_f.ptr, d_s.ptr, y_f.ptr, reps, ctypes.byref(ms)))
+    t = torch.tensor([ms.value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    tp_us = 1000.0 * float(t.item()) / (reps * n_blocks)
+    group.close()
+    return {"degree": world, "us_per_mlp_block": tp_us,
+            "how": "row-split gate/up/down slices + 2 NCCL all-gathers per block, graph of 30 blocks, max over ranks",
+            "bytes_gathered_per_block": 4 * (I + H)}
+
+
 def run_sweep(args):
     """Config 2: the five BitNet-2B projection shapes x token counts; fused-quantiser linear launches
     rotated over enough device copies of the matrix to exceed the L2 (about 300 MB per shape)."""
@@ -363,6 +399,14 @@ def main():
     tg128_host_logits()
     e2e_logits_value = GEN_LEN / tg128_host_logits()
 
+    # ---- tensor-parallel variant of the MLP block (row-split gate/up/down + NCCL all-gather), N > 1 ----
+    tp_info = None
+    if dist is not None and not args.skip_extras:
+        try:
+            tp_info = bench_tp_mlp(dist, rank, world, model, lib, K)
+        except Exception as ex:
+            tp_info = {"error": str(ex)[:200]}
+
     if rank != 0:
         if dist is not None:
             dist.barrier()
@@ -458,6 +502,7 @@ def main():
                            "frac_of_nominal_8TBs": token_gbs / 8000.0},
         "cpu_baseline": cpu,
         "extra": extra,
+        "tp_mlp": tp_info,
     }
     print(json.dumps(line))
     if dist is not None:

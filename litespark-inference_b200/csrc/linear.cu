@@ -132,6 +132,9 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     const int tail_start = p.K & ~15;      // the reference's scalar-tail rounding rule applies from here
     bool first_tile = true;
 
+    // Plain launches give every row tile its own CTA (grid.y), so this loop runs once for them (and the
+    // compiler is told so: register lifetimes end with the single pass); expert-grouped launches, whose
+    // row count is device data, walk their tiles here.
     for (int m0 = blockIdx.y * MT; m0 < M_eff; m0 += gridDim.y * MT) {
         const int mt = min(MT, M_eff - m0);
         auto out_row = [&](int m) -> int { return GROUPED ? rows[m0 + m] : m0 + m; };
@@ -396,6 +399,7 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
                 load_batch(s, g, 0, wa, wb);
             }
         }
+        if (!GROUPED) break;
     }
     tr.end();
 }

@@ -34,10 +34,10 @@ def test_ctypes_layer_binds_every_declared_symbol():
     lib = K.load_library(require_device=False)
     rt_abi = importlib.import_module("litespark_inference_b200.torchless._runtime_abi")
     hyb = importlib.import_module("litespark_inference_b200.torchless.hybrid")
-    bound = set(K._SIGNATURES) | set(rt_abi.SIGNATURES) | set(hyb.SIGNATURES)
+    tpm = importlib.import_module("litespark_inference_b200.torchless.tp")
+    bound = set(K._SIGNATURES) | set(rt_abi.SIGNATURES) | set(hyb.SIGNATURES) | set(tpm.SIGNATURES)
     declared = _declared_symbols()
-    later = {n for n in declared if n.startswith("lspk_tp_")}
-    assert declared - bound - later == set(), f"declared but not bound in Python: {sorted(declared - bound - later)}"
+    assert declared - bound == set(), f"declared but not bound in Python: {sorted(declared - bound)}"
     assert bound - declared == set(), f"bound in Python but not declared: {sorted(bound - declared)}"
     for name in bound:
         assert hasattr(lib, name), name

@@ -1,0 +1,88 @@
+"""Two-GPU check of the tensor-parallel MLP block: NCCL all-gather of row slices must give, on every
+rank, exactly the unsplit product.  Needs two GPUs; skipped otherwise.  Runs as two child processes
+(one per GPU) that meet through an NCCL id passed in a file."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+WORKER = r'''
+import os, sys, time, importlib
+import numpy as np
+sys.path.insert(0, os.environ["LSPK_ROOT"])
+import __graft_entry__ as entry
+entry.load_package()
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+os.environ["LITESPARK_DEVICE"] = str(rank)
+K = importlib.import_module("litespark_inference_b200.torchless.kernel")
+dev = importlib.import_module("litespark_inference_b200.torchless.device")
+tp = importlib.import_module("litespark_inference_b200.torchless.tp")
+synthetic = importlib.import_module("litespark_inference_b200.torchless.synthetic")
+idfile = os.environ["LSPK_IDFILE"]
+if rank == 0:
+    uid = tp.DeviceTP.make_unique_id()
+    with open(idfile + ".tmp", "wb") as f:
+        f.write(uid)
+    os.replace(idfile + ".tmp", idfile)
+else:
+    for _ in range(600):
+        if os.path.exists(idfile):
+            break
+        time.sleep(0.1)
+    uid = open(idfile, "rb").read()
+group = tp.DeviceTP(rank, world, uid)
+cfg = synthetic.bitnet_2b_config(num_layers=1, vocab_size=256)
+rng = np.random.default_rng(4)                                    # same stream on both ranks
+gate, up = synthetic.random_projection_fast(rng, 6912, 2560), synthetic.random_projection_fast(rng, 6912, 2560)
+down = synthetic.random_projection_fast(rng, 2560, 6912)
+norm = synthetic.fp32_to_bf16_u16(rng.uniform(0.5, 1.5, 2560).astype(np.float32))
+sub = synthetic.fp32_to_bf16_u16(rng.uniform(0.5, 1.5, 6912).astype(np.float32))
+x = rng.standard_normal((1, 2560)).astype(np.float32)
+W = lambda p: dev.DeviceWeight(p.w_packed, p.scale)
+g_r, u_r, d_r = (W(tp.slice_projection(p, world, rank)) for p in (gate, up, down))
+dx, dn, ds = dev.DeviceArray.from_numpy(x), dev.DeviceArray.from_numpy(norm), dev.DeviceArray.from_numpy(sub)
+i_s, i_f = dev.DeviceArray((6912 // world,), np.float32), dev.DeviceArray((1, 6912), np.float32)
+d_s, y_f = dev.DeviceArray((2560 // world,), np.float32), dev.DeviceArray((1, 2560), np.float32)
+for _ in range(3):
+    group.mlp_block(g_r, u_r, d_r, dx, dn, ds, 1e-5, i_s, i_f, d_s, y_f)
+got = y_f.numpy()
+# unsplit on this GPU
+inter = dev.DeviceArray((1, 6912), np.float32)
+dev.linear([W(gate), W(up)], [inter, None], 1, x_f32=dx, gamma=dn, epilogue=K.EPI_RELU2_MUL)
+want = dev.DeviceArray((1, 2560), np.float32)
+dev.linear([W(down)], [want], 1, x_f32=inter, gamma=ds)
+assert np.array_equal(i_f.numpy(), inter.numpy()), "gathered gate/up slice differs"
+assert np.array_equal(got, want.numpy()), "gathered down slice differs"
+group.close()
+print("rank", rank, "ok")
+'''
+
+
+def _gpu_count():
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
+        return sum(1 for ln in out.splitlines() if ln.startswith("GPU "))
+    except (OSError, subprocess.TimeoutExpired):
+        return 0
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_tp_mlp_block_two_gpus(tmp_path):
+    script = tmp_path / "tp_gpu_worker.py"
+    script.write_text(WORKER)
+    idfile = tmp_path / "nccl_id.bin"
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LSPK_ROOT=str(ROOT), LSPK_IDFILE=str(idfile),
+                   NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
+        assert f"rank {r} ok" in o
