@@ -491,7 +491,10 @@ def main():
         "kernels_per_token": step_kernels,
         "roofline": {"kernel": "ternary_linear_kernel (M=1, fused RMSNorm+quantiser prologue)",
                      "bound": "hbm", "achieved": lin_gbs, "peak": peak, "unit": "GB/s", "frac": lin_gbs / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": None,
+                     "peak_kind": f"of {peak_kind}",
+                     # dram read + write per launch from the ncu capture summarised in
+                     # profiles/ternary_linear_kernel_m1_bitnet2b.md (mean of the four launches of a layer)
+                     "traffic": (2514432 + 1705472 + 8908032 + 4539648) / 4.0,
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                      "launches_timed": n_launch.value * reps,
                      "how": "CUDA events around graph replays of the 120 linear launches of one token over all 30 layers' weights (521 MB, > L2)"},

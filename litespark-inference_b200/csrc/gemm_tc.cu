@@ -337,6 +337,16 @@ static int grow(void** p, size_t* cap, size_t need) {
     return LSPK_OK;
 }
 
+// Library-owned int8 rows + scales for callers that hand fp32 rows to a many-row product.  Grows with
+// cudaMalloc: the first call of a given size must happen outside stream capture.
+int quant_scratch(size_t M, size_t K, int8_t** q, float** s) {
+    if (int rc = grow((void**)&g_tc.xq, &g_tc.cap_xq, M * K)) return rc;
+    if (int rc = grow((void**)&g_tc.xs, &g_tc.cap_xs, M * 4)) return rc;
+    *q = g_tc.xq;
+    *s = g_tc.xs;
+    return LSPK_OK;
+}
+
 template <int TN>
 static cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid) {
     constexpr size_t smem = (size_t)kTcStages * (kTcRows * kTcBK / 4 + kTcRows * kTcBK + TN * kTcBK) + 1024;

@@ -47,6 +47,13 @@ struct LinearParams {
     const float* grp_scales;   // [experts][3] weight scales
 };
 
+// linear_mma.cu: the eight-row tile kernel (mma.sync int8), also used for expert-grouped launches.
+// Quantise (and normalise) M > 1 rows once into caller scratch and turn the call into an int8-prologue one.
+int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* scale_scratch);
+// Library-owned scratch for that (grown with cudaMalloc: size it once outside stream capture).
+int quant_scratch(size_t M, size_t K, int8_t** q, float** s);
+int linear_mma_launch(const LinearParams& p, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);
+
 // Launch the CUDA-core kernel with fully prepared parameters.  mt: rows per CTA tile (1, 2, 4 or 8).
 int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);
 

@@ -433,26 +433,13 @@ static cudaError_t launch_linear_mt(const LinearParams& p, dim3 grid, bool pair,
 }
 
 int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z) {
+    // more than one token row per tile (and every expert-grouped launch): the eight-row mma kernel
+    if (mt > 1 || grouped) return linear_mma_launch(p, pair, grouped, grid_x, grid_y, grid_z);
     const int Kp = p.chunks * kWeightsPerChunk;
-    const size_t smem = linear_smem_bytes(mt, Kp, pair);
-    LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768, less for 8-row tiles)", p.K);
+    const size_t smem = linear_smem_bytes(1, Kp, pair);
+    LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768)", p.K);
     const dim3 grid(grid_x, grid_y, grid_z);
-    cudaError_t e;
-    if (grouped) {
-        // expert-grouped launches take int8 rows (the fp32 prologue is not instantiated for them)
-        LSPK_REQUIRE(mt == 8 && p.prologue == LSPK_PRO_INT8 && p.chunks <= 128, "linear: unsupported grouped launch");
-        if (p.chunks <= 64)
-            e = pair ? launch_linear<8, 4, 1, true, true>(p, grid, smem) : launch_linear<8, 4, 1, false, true>(p, grid, smem);
-        else
-            e = pair ? launch_linear<8, 8, 1, true, true>(p, grid, smem) : launch_linear<8, 8, 1, false, true>(p, grid, smem);
-    } else {
-        switch (mt) {
-            case 1: e = launch_linear_mt<1>(p, grid, pair, smem); break;
-            case 2: e = launch_linear_mt<2>(p, grid, pair, smem); break;
-            case 4: e = launch_linear_mt<4>(p, grid, pair, smem); break;
-            default: e = launch_linear_mt<8>(p, grid, pair, smem); break;
-        }
-    }
+    const cudaError_t e = launch_linear_mt<1>(p, grid, pair, smem);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear launch failed: %s", cudaGetErrorString(e));
     return LSPK_OK;
 }
@@ -468,6 +455,27 @@ int linear_cuda_core(const lspk_linear_args* a) {
     LinearParams p = {};
     const Weight* w0 = reinterpret_cast<const Weight*>(a->w[0]);
     LSPK_REQUIRE(w0, "linear: null weight");
+    // Several rows of fp32 input: normalise + quantise them once in their own kernel (fused into the
+    // product, every CTA would repeat that work for all rows) and continue with the int8 prologue.
+    lspk_linear_args split;
+    if (a->M > 1 && a->prologue != LSPK_PRO_INT8) {
+        LSPK_REQUIRE(a->prologue >= LSPK_PRO_QUANT && a->prologue <= LSPK_PRO_GATED_RMSNORM_QUANT,
+                     "linear: unknown prologue %d", a->prologue);
+        LSPK_REQUIRE(a->x_f32, "linear: fp32 prologue needs x_f32");
+        LSPK_REQUIRE(a->prologue == LSPK_PRO_QUANT || a->gamma, "linear: RMSNORM_QUANT prologue needs gamma");
+        LSPK_REQUIRE(a->prologue != LSPK_PRO_GATED_RMSNORM_QUANT || a->gate_f32,
+                     "linear: GATED_RMSNORM_QUANT prologue needs gate_f32");
+        split = *a;
+        int8_t* q = nullptr;
+        float* sc = nullptr;
+        if (int rc = quant_scratch((size_t)a->M, (size_t)w0->K, &q, &sc)) return rc;
+        if (int rc = split_row_prologue(&split, w0->K, q, sc)) return rc;
+        if (a->xq_out) LSPK_CUDA(cudaMemcpyAsync(a->xq_out, q, (size_t)a->M * w0->K, cudaMemcpyDeviceToDevice, stream()));
+        if (a->xscale_out) LSPK_CUDA(cudaMemcpyAsync(a->xscale_out, sc, (size_t)a->M * 4, cudaMemcpyDeviceToDevice, stream()));
+        split.xq_out = nullptr;
+        split.xscale_out = nullptr;
+        a = &split;
+    }
     p.K = w0->K;
     p.chunks = w0->chunks;
     p.n_seg = a->n_mats;
@@ -513,7 +521,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
             return fail(LSPK_ERR_ARG, "linear: unknown prologue %d", a->prologue);
     }
     LSPK_REQUIRE(a->epilogue >= 0 && a->epilogue <= 3, "linear: unknown epilogue %d", a->epilogue);
-    const int MT = a->M == 1 ? 1 : a->M == 2 ? 2 : a->M <= 4 ? 4 : 8;
+    const int MT = a->M == 1 ? 1 : 8;
     // At most two CTAs per SM when there is a single token tile (measured best on B200: the prologue
     // runs once per CTA, which then loops over its row groups).  With several token tiles the grid's
     // second dimension already fills the machine.

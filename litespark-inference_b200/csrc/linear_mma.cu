@@ -1,0 +1,308 @@
+// Ternary linear layer for 2..8 int8 token rows per tile on the warp-level int8 tensor-core path
+// (mma.sync.m16n8k32.u8.s8): the weights of a 16-row group are the MMA's M side, up to eight
+// token rows its N side, so streaming a packed matrix once serves eight tokens for the instruction
+// count the one-token kernel spends on one.  Same contract and epilogues as
+// ternary_linear_kernel in linear.cu (matmul_lut_avx512_mT, matmul_lut_avx512_extern_c.cpp:258-339,
+// plus the fused helpers); this is the path of the small batches: speculative validation, several
+// sequences decoded in lock step, the rows an expert receives in the MoE layer.
+//
+// Operand mapping (no re-layout: the device chunk layout is read as is).  The 256-byte tile of
+// "16 rows x one 64-weight chunk" is 64 words; lane l of a warp loads word l (row l/4, the
+// (l%4)-th 16-weight word of the chunk) and word 32+l (row l/4 + 8).  Masking a packed word with
+// 0x03030303 << 2j leaves four codes (weights 16t + {j, 4+j, 8+j, 12+j}, scaled by 4^j) in the
+// byte positions of an A-fragment register; two consecutive chunks give the two K halves of one
+// m16n8k32 step.  The int8 activations sit in shared memory in the same transposed 16-element
+// blocks the one-token kernel uses, so lane (token l/4, word l%4) gets its four B registers for
+// the four masks with one 16-byte load per chunk.  One accumulator set per mask keeps the scales
+// apart; they are combined with exact shifts at the end.  Codes stay unsigned, sum(x) is
+// subtracted per row: all integer, bit-exact.
+#include <stdlib.h>
+
+#include "internal.cuh"
+#include "ternary_core.cuh"
+
+namespace lspk {
+
+constexpr int kMThreads = 256;
+constexpr int kMWarps = kMThreads / 32;
+constexpr int kMT = 8;            // token rows per tile (the MMA's N)
+constexpr int kMNI = 4;           // chunk pairs whose weights a lane keeps in flight
+
+__device__ __forceinline__ void mma_u8s8(int c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Row stride of the activation tile in shared memory: Kp rounded so that consecutive rows start 64
+// bytes apart modulo 128, which makes the quarter-warp 16-byte loads (two tokens x four words)
+// conflict-free.
+__host__ __device__ inline int mma_row_stride(int Kp) { return (Kp % 128 == 0) ? Kp + 64 : Kp; }
+
+template <bool PAIR, bool GROUPED>
+__global__ void __launch_bounds__(kMThreads)
+ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int Kp = p.chunks * kWeightsPerChunk;
+    const int rs = mma_row_stride(Kp);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, t4 = lane & 3;
+
+    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw);                         // [kMT][rs] permuted int8
+    int* part = reinterpret_cast<int*>(xq + (size_t)kMT * rs);                 // [PAIR?2:1][warps][kMT][16]
+    constexpr int kPartInts = kMWarps * kMT * 16 * (PAIR ? 2 : 1);
+    float* s_scale = reinterpret_cast<float*>(part + kPartInts);               // [kMT]
+    int* s_sumx = reinterpret_cast<int*>(s_scale + kMT);                       // [kMT]
+
+    const int z = GROUPED ? blockIdx.z : 0;
+    const size_t w_off = GROUPED ? (size_t)z * p.grp_w_stride : 0;
+    const int pairs = (p.chunks + 1) / 2;
+
+    auto locate = [&](int flat, int& seg_i, int& grp) {
+        seg_i = 0;
+        grp = flat;
+        if (!PAIR) {
+            while (seg_i < p.n_seg - 1 && grp >= p.seg[seg_i].groups) {
+                grp -= p.seg[seg_i].groups;
+                ++seg_i;
+            }
+        }
+    };
+    // weights of chunk pair (warp + 8*(base+i)) of a row group: for each of the two chunks the words of
+    // row gid and of row gid+8 -> 4 words per pair (8 with the gate/up pairing)
+    auto load_batch = [&](int seg_i, int grp, int base, uint32_t (*dst_a)[4], uint32_t (*dst_b)[4]) {
+        const uint32_t* wa = reinterpret_cast<const uint32_t*>(p.seg[seg_i].w + w_off + (size_t)grp * p.chunks * kRowsPerGroup);
+        const uint32_t* wb = PAIR ? reinterpret_cast<const uint32_t*>(p.seg[1].w + w_off + (size_t)grp * p.chunks * kRowsPerGroup)
+                                  : nullptr;
+#pragma unroll
+        for (int i = 0; i < kMNI; ++i) {
+            const int pr = warp + kMWarps * (base + i);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const int j = 2 * pr + c;
+                uint32_t a_lo = 0x55555555u, a_hi = 0x55555555u, b_lo = 0x55555555u, b_hi = 0x55555555u;
+                if (j < p.chunks) {
+                    const size_t o = (size_t)j * 64 + lane;           // 64 words per 16-row chunk tile
+                    if (p.stream_weights) {
+                        a_lo = __ldcs(wa + o);
+                        a_hi = __ldcs(wa + o + 32);
+                        if (PAIR) { b_lo = __ldcs(wb + o); b_hi = __ldcs(wb + o + 32); }
+                    } else {
+                        a_lo = __ldg(wa + o);
+                        a_hi = __ldg(wa + o + 32);
+                        if (PAIR) { b_lo = __ldg(wb + o); b_hi = __ldg(wb + o + 32); }
+                    }
+                }
+                dst_a[i][c * 2] = a_lo;
+                dst_a[i][c * 2 + 1] = a_hi;
+                if (PAIR) {
+                    dst_b[i][c * 2] = b_lo;
+                    dst_b[i][c * 2 + 1] = b_hi;
+                }
+            }
+        }
+    };
+
+    int flat0 = blockIdx.x, s0, g0;
+    locate(flat0, s0, g0);
+    uint32_t wa[kMNI][4], wb[PAIR ? kMNI : 1][4];
+    PhaseTrace tr;
+    tr.begin(p.trace, p.trace_cap, 3);
+    tr.mark();                                          // 0: entry
+    if (!GROUPED) load_batch(s0, g0, 0, wa, wb);       // weights never depend on the previous kernel
+    grid_dependency_launch();
+    grid_dependency_wait();
+    tr.mark();                                          // 1: predecessor finished
+
+    const int M_eff = GROUPED ? p.grp_counts[z] : p.M;
+    const int* rows = GROUPED ? p.grp_rows + (size_t)z * p.grp_rows_stride : nullptr;
+    const int out_m = tid >> 4, out_r = tid & 15;
+    bool first_tile = true;
+
+    for (int m0 = blockIdx.y * kMT; m0 < M_eff; m0 += gridDim.y * kMT) {
+        const int mt = min(kMT, M_eff - m0);
+        auto out_row = [&](int m) -> int { return GROUPED ? rows[m0 + m] : m0 + m; };
+        auto in_row = [&](int m) -> int { return GROUPED ? (rows[m0 + m] >> p.grp_in_shift) : m0 + m; };
+        int flat = flat0, s = s0, g = g0;
+        auto residual_of = [&](int seg_i, int grp) -> float {
+            if (p.epilogue != LSPK_EPI_ADD || tid >= kMT * 16 || out_m >= mt) return 0.0f;
+            const int n = grp * kRowsPerGroup + out_r;
+            if (n >= p.seg[seg_i].N) return 0.0f;
+            return p.seg[seg_i].out[(size_t)out_row(out_m) * p.seg[seg_i].N + n];
+        };
+        float resid = residual_of(s, g);
+        if (GROUPED || !first_tile) load_batch(s, g, 0, wa, wb);
+        first_tile = false;
+
+        // ---- prologue: the tile's rows -> permuted int8 rows in shared memory ------------------------------
+        {
+            // int8 rows (the only prologue of this kernel): one warp per row, a single pass of independent loads
+            const int m = warp;                                  // kMWarps == kMT
+            int8_t* xq_row = xq + (size_t)m * rs;
+            const int nblk = Kp / 16;
+            if (m >= mt) {
+                for (int b = lane; b < nblk; b += 32) *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(0, 0, 0, 0);
+                if (lane == 0) { s_scale[m] = 0.0f; s_sumx[m] = 0; }
+            } else {
+                const int8_t* src = p.x_i8 + (size_t)in_row(m) * p.K;
+                int sumx = 0;
+#pragma unroll 2
+                for (int b = lane; b < nblk; b += 32) {
+                    uint32_t a[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int k = b * 16 + q * 4;
+                        a[q] = (k < p.K) ? *reinterpret_cast<const uint32_t*>(src + k) : 0u;
+                        sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                    }
+                    uint32_t o0, o1, o2, o3;
+                    transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                    *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
+                }
+                sumx = warp_sum(sumx);
+                if (lane == 0) { s_scale[m] = p.x_scales[in_row(m)]; s_sumx[m] = sumx; }
+            }
+        }
+        tr.mark();                                                 // 2: rows staged
+        __syncthreads();
+        tr.mark();                                                 // 3: activations visible
+
+        // ---- row groups of this CTA ---------------------------------------------------------------------
+        while (true) {
+            const int next_flat = flat + gridDim.x;
+            const bool has_next = next_flat < p.total_groups;
+            int ns = 0, ng = 0;
+            float next_resid = 0.0f;
+            if (has_next) {
+                locate(next_flat, ns, ng);
+                next_resid = residual_of(ns, ng);
+            }
+            int acc_a[4][4], acc_b[PAIR ? 4 : 1][4];
+#pragma unroll
+            for (int f = 0; f < 4; ++f)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    acc_a[f][c] = 0;
+                    if (PAIR) acc_b[f][c] = 0;
+                }
+            const int8_t* xrow = xq + (size_t)gid * rs;            // B operand: token gid
+            for (int base = 0;; ) {
+#pragma unroll
+                for (int i = 0; i < kMNI; ++i) {
+                    const int pr = warp + kMWarps * (base + i);
+                    if (pr < pairs) {
+                        const int j0 = 2 * pr;
+                        // four masks' B registers of chunk j0 and of chunk j0+1 (zeros past the last chunk)
+                        const uint4 x0 = *reinterpret_cast<const uint4*>(xrow + (size_t)(4 * j0 + t4) * 16);
+                        uint4 x1 = make_uint4(0, 0, 0, 0);
+                        if (j0 + 1 < p.chunks) x1 = *reinterpret_cast<const uint4*>(xrow + (size_t)(4 * (j0 + 1) + t4) * 16);
+                        const uint32_t xb0[4] = {x0.x, x0.y, x0.z, x0.w};
+                        const uint32_t xb1[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                        for (int f = 0; f < 4; ++f) {
+                            const uint32_t mask = 0x03030303u << (2 * f);
+                            mma_u8s8(acc_a[f], wa[i][0] & mask, wa[i][1] & mask, wa[i][2] & mask, wa[i][3] & mask,
+                                     xb0[f], xb1[f]);
+                            if (PAIR)
+                                mma_u8s8(acc_b[f], wb[i][0] & mask, wb[i][1] & mask, wb[i][2] & mask, wb[i][3] & mask,
+                                         xb0[f], xb1[f]);
+                        }
+                    }
+                }
+                base += kMNI;
+                if (kMWarps * base >= pairs) break;
+                load_batch(s, g, base, wa, wb);
+            }
+            tr.mark();                                             // 4+: MMAs of a row group done
+            if (has_next) load_batch(ns, ng, 0, wa, wb);           // in flight during the reduction below
+
+            // masks -> one int; C fragment: c0,c1 = (row gid, tokens 2*t4, 2*t4+1), c2,c3 = (row gid+8, same)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int row = gid + ((c >> 1) << 3);
+                const int tok = 2 * t4 + (c & 1);
+                const int v = acc_a[0][c] + (acc_a[1][c] >> 2) + (acc_a[2][c] >> 4) + (acc_a[3][c] >> 6);
+                part[(warp * kMT + tok) * 16 + row] = v;
+                if (PAIR) {
+                    const int u = acc_b[0][c] + (acc_b[1][c] >> 2) + (acc_b[2][c] >> 4) + (acc_b[3][c] >> 6);
+                    part[kMWarps * kMT * 16 + (warp * kMT + tok) * 16 + row] = u;
+                }
+            }
+            __syncthreads();
+
+            if (tid < kMT * 16) {
+                const LinearSeg& sg = p.seg[s];
+                const int n = g * kRowsPerGroup + out_r;
+                if (out_m < mt && n < sg.N) {
+                    int va = 0, vb = 0;
+#pragma unroll
+                    for (int w = 0; w < kMWarps; ++w) {
+                        va += part[(w * kMT + out_m) * 16 + out_r];
+                        if (PAIR) vb += part[kMWarps * kMT * 16 + (w * kMT + out_m) * 16 + out_r];
+                    }
+                    const int sx = s_sumx[out_m];
+                    va -= sx;
+                    const size_t o = (size_t)out_row(out_m) * sg.N + n;
+                    if (sg.acc_out) sg.acc_out[o] = va;
+                    const float wsa = GROUPED ? p.grp_scales[z * 3 + sg.scale_idx] : sg.w_scale;
+                    const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[out_m], wsa));
+                    if (PAIR) {
+                        vb -= sx;
+                        if (p.seg[1].acc_out) p.seg[1].acc_out[o] = vb;
+                        const float wsb = GROUPED ? p.grp_scales[z * 3 + p.seg[1].scale_idx] : p.seg[1].w_scale;
+                        const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[out_m], wsb));
+                        if (p.epilogue == LSPK_EPI_SILU_MUL) {
+                            sg.out[o] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
+                        } else {
+                            const float gpos = fmaxf(ya, 0.0f);
+                            sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                        }
+                    } else if (p.epilogue == LSPK_EPI_ADD) {
+                        sg.out[o] = __fadd_rn(resid, ya);
+                    } else {
+                        sg.out[o] = ya;
+                    }
+                }
+            }
+            tr.mark();                                             // 5+: row group stored
+            __syncthreads();                       // `part` (and, at the end of a tile, xq) is rewritten next
+            if (!has_next) break;
+            flat = next_flat;
+            s = ns;
+            g = ng;
+            resid = next_resid;
+        }
+        if (!GROUPED) break;
+    }
+    tr.end();
+}
+
+template <bool PAIR, bool GROUPED>
+static cudaError_t launch_mma(const LinearParams& p, dim3 grid, size_t smem) {
+    static bool attr_set = false;
+    auto kern = ternary_linear_mma_kernel<PAIR, GROUPED>;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    return launch(kern, grid, dim3(kMThreads), smem, true, p);
+}
+
+// Launch the eight-row kernel.  K is limited by the shared-memory activation tile (8 rows of K bytes).
+// Rows arrive quantised (INT8 prologue); fp32 rows are quantised once by the row kernel beforehand.
+int linear_mma_launch(const LinearParams& p, bool pair, bool grouped, int grid_x, int grid_y, int grid_z) {
+    LSPK_REQUIRE(p.prologue == LSPK_PRO_INT8, "linear: the eight-row kernel takes int8 rows (prologue %d)", p.prologue);
+    const int Kp = p.chunks * kWeightsPerChunk;
+    const size_t smem = (size_t)kMT * mma_row_stride(Kp) + (size_t)kMWarps * kMT * 16 * (pair ? 2 : 1) * 4 + kMT * 8 + 64;
+    LSPK_REQUIRE(smem <= 200 * 1024, "linear: K=%d too large for the 8-row activation tile (limit about 24000)", p.K);
+    const dim3 grid(grid_x, grid_y, grid_z);
+    cudaError_t e = grouped ? (pair ? launch_mma<true, true>(p, grid, smem) : launch_mma<false, true>(p, grid, smem))
+                            : (pair ? launch_mma<true, false>(p, grid, smem) : launch_mma<false, false>(p, grid, smem));
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear (mma) launch failed: %s", cudaGetErrorString(e));
+    return LSPK_OK;
+}
+
+}  // namespace lspk

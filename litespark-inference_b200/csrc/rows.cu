@@ -9,7 +9,9 @@
 
 namespace lspk {
 
-constexpr int kRowThreads = 256;
+constexpr int kRowThreads = 512;
+
+__device__ __forceinline__ float silu_gate(float z) { return __fdiv_rn(z, __fadd_rn(expf(-z), 1.0f)); }
 
 __device__ __forceinline__ float gamma_at(const void* gamma, int is_bf16, int k) {
     return is_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(gamma)[k])
@@ -17,10 +19,13 @@ __device__ __forceinline__ float gamma_at(const void* gamma, int is_bf16, int k)
 }
 
 // mode bit 0: apply RMSNorm first; bit 1: quantise (else write fp32 rows to out_f32).
-// The normalised row is staged in shared memory (K floats) between the passes.
+// gate != nullptr: the row is x * SiLU(gate) (the gated norm of the Mamba-2 block) before anything else.
+// The normalised row is staged in shared memory (K floats) between the passes.  VEC: K is a
+// multiple of 4 and every pointer 16-byte aligned, so the passes move four elements at a time.
+template <bool VEC>
 __global__ void __launch_bounds__(kRowThreads)
-row_norm_quant_kernel(const float* __restrict__ x, const void* __restrict__ gamma, int gamma_is_bf16,
-                      float* __restrict__ out_f32, int8_t* __restrict__ out_i8,
+row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gate, const void* __restrict__ gamma,
+                      int gamma_is_bf16, float* __restrict__ out_f32, int8_t* __restrict__ out_i8,
                       float* __restrict__ scales, int K, float eps, int mode) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* xs = reinterpret_cast<float*>(smem_raw);
@@ -29,11 +34,76 @@ row_norm_quant_kernel(const float* __restrict__ x, const void* __restrict__ gamm
     grid_dependency_wait();
     const int t = blockIdx.x, tid = threadIdx.x;
     const float* src = x + (size_t)t * K;
+    const float* gsrc = gate ? gate + (size_t)t * K : nullptr;
     const bool norm = mode & 1, quant = mode & 2;
+    const int tail_start = K & ~15;
+
+    if (VEC) {
+        const int K4 = K >> 2;
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        float4* xs4 = reinterpret_cast<float4*>(xs);
+        float ssq = 0.0f, amax = 0.0f;
+        for (int i = tid; i < K4; i += kRowThreads) {
+            float4 v = src4[i];
+            if (gsrc) {
+                const float4 gz = reinterpret_cast<const float4*>(gsrc)[i];
+                v.x = __fmul_rn(v.x, silu_gate(gz.x));
+                v.y = __fmul_rn(v.y, silu_gate(gz.y));
+                v.z = __fmul_rn(v.z, silu_gate(gz.z));
+                v.w = __fmul_rn(v.w, silu_gate(gz.w));
+            }
+            xs4[i] = v;
+            ssq = fmaf(v.x, v.x, ssq);
+            ssq = fmaf(v.y, v.y, ssq);
+            ssq = fmaf(v.z, v.z, ssq);
+            ssq = fmaf(v.w, v.w, ssq);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+        if (norm) {
+            ssq = block_sum(ssq, red);
+            const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)K), eps)));
+            amax = 0.0f;
+            for (int i = tid; i < K4; i += kRowThreads) {
+                float4 v = xs4[i];
+                const int k = i << 2;
+                v.x = __fmul_rn(__fmul_rn(v.x, rrms), gamma_at(gamma, gamma_is_bf16, k));
+                v.y = __fmul_rn(__fmul_rn(v.y, rrms), gamma_at(gamma, gamma_is_bf16, k + 1));
+                v.z = __fmul_rn(__fmul_rn(v.z, rrms), gamma_at(gamma, gamma_is_bf16, k + 2));
+                v.w = __fmul_rn(__fmul_rn(v.w, rrms), gamma_at(gamma, gamma_is_bf16, k + 3));
+                if (quant) xs4[i] = v; else reinterpret_cast<float4*>(out_f32 + (size_t)t * K)[i] = v;
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+        }
+        if (!quant) return;
+        amax = block_max(amax, red);
+        const float scale = quant_scale_from_absmax(amax);
+        const float inv = __fdiv_rn(1.0f, scale);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * K);
+        for (int i = tid; i < K4; i += kRowThreads) {
+            const float4 v = xs4[i];
+            const float f[4] = {v.x, v.y, v.z, v.w};
+            uint32_t word = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int q;
+                if ((i << 2) < tail_start) {
+                    q = quant_one(f[e], inv);
+                } else {
+                    q = (int)roundf(__fmul_rn(f[e], inv));
+                    q = max(-127, min(127, q));
+                }
+                word |= ((uint32_t)q & 0xffu) << (8 * e);
+            }
+            dst[i] = word;
+        }
+        if (tid == 0) scales[t] = scale;
+        return;
+    }
 
     float ssq = 0.0f;
     for (int k = tid; k < K; k += kRowThreads) {
-        const float v = src[k];
+        float v = src[k];
+        if (gsrc) v = __fmul_rn(v, silu_gate(gsrc[k]));
         xs[k] = v;
         ssq = fmaf(v, v, ssq);
     }
@@ -53,7 +123,6 @@ row_norm_quant_kernel(const float* __restrict__ x, const void* __restrict__ gamm
     amax = block_max(amax, red);
     const float scale = quant_scale_from_absmax(amax);
     const float inv = __fdiv_rn(1.0f, scale);
-    const int tail_start = K & ~15;
     for (int k = tid; k < K; k += kRowThreads) {
         int q;
         if (k < tail_start) {
@@ -85,18 +154,43 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 }
 
 static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, float* out_f32, int8_t* out_i8,
-                       float* scales, int T, int K, float eps, int mode) {
+                       float* scales, int T, int K, float eps, int mode, const float* gate = nullptr) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(x && T >= 1 && K >= 1, "row helper: bad arguments (T=%d K=%d)", T, K);
     const size_t smem = (size_t)K * sizeof(float);
     LSPK_REQUIRE(smem <= 200 * 1024, "row helper: K=%d too large", K);
     static bool attr_set = false;
     if (!attr_set) {
-        LSPK_CUDA(cudaFuncSetAttribute(row_norm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(row_norm_quant_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(row_norm_quant_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set = true;
     }
-    LSPK_CUDA(launch(row_norm_quant_kernel, dim3(T), dim3(kRowThreads), smem, true, x, gamma, gamma_is_bf16,
-                     out_f32, out_i8, scales, K, eps, mode));
+    auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    const bool vec = (K % 4 == 0) && aligned(x) && aligned(out_f32) && aligned(out_i8) && aligned(gamma) && aligned(gate);
+    LSPK_CUDA(launch(vec ? row_norm_quant_kernel<true> : row_norm_quant_kernel<false>, dim3(T), dim3(kRowThreads), smem,
+                     true, x, gate, gamma, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode));
+    return LSPK_OK;
+}
+
+// For more than one token row, quantising inside the linear kernel would make every CTA repeat the
+// norm + quantiser of all rows (three passes over M*K floats per CTA): run it once here into the
+// caller's scratch and switch the call to the int8 prologue.  One row keeps the fused prologue.
+int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* scale_scratch) {
+    if (a->M <= 1) return LSPK_OK;
+    int mode;
+    const float* gate = nullptr;
+    if (a->prologue == LSPK_PRO_QUANT) mode = 2;
+    else if (a->prologue == LSPK_PRO_RMSNORM_QUANT) mode = 3;
+    else if (a->prologue == LSPK_PRO_GATED_RMSNORM_QUANT) { mode = 3; gate = a->gate_f32; }
+    else return LSPK_OK;
+    if (int rc = launch_rows(a->x_f32, a->gamma, a->gamma_is_bf16, nullptr, q_scratch, scale_scratch, a->M, K, a->eps, mode,
+                             gate))
+        return rc;
+    a->prologue = LSPK_PRO_INT8;
+    a->x_i8 = q_scratch;
+    a->x_scales = scale_scratch;
+    a->x_f32 = nullptr;
+    a->gate_f32 = nullptr;
     return LSPK_OK;
 }
 

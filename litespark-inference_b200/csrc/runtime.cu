@@ -200,8 +200,9 @@ static int upload_table(DevTable& t, int kind, const void* host, const float* sc
 }
 
 // One transformer layer for `rows` rows held in the state's scratch buffers.
-//   decode1: single row of a single sequence -> norm + quantiser fused into the linear kernels.
-//   otherwise rows go through the batched norm+quantise kernel and the INT8 prologue.
+//   one row: norm + quantiser fused into the linear kernels;
+//   otherwise rows go through the batched norm+quantise kernel once and the linear kernels (eight-row
+//   tensor-core tiles below 32 rows, the tcgen05 GEMM from there) take the int8 prologue.
 //   per_row_seq: rows are different sequences (batched decode) instead of consecutive positions.
 static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool skip_attention = false) {
     Model* m = s->m;
@@ -209,7 +210,7 @@ static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool
     const DevLayer& L = m->layers[li];
     const int H = c.hidden_size, I = c.intermediate_size;
     const bool bitnet = c.arch == 0;
-    const bool fused_quant = rows == 1;
+    const bool fused_quant = rows == 1;       // one row: the linear kernels normalise and quantise themselves
     const float eps = c.rms_norm_eps;
 
     auto linear = [&](int n_mats, const int* which, float* const* outs, const float* src, int8_t* src_q,
