@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
 
 #include "../../include/lspk_sm100.h"
 
@@ -187,9 +188,35 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 // (quantize_activation_avx512, matmul_lut_avx512_extern_c.cpp:443-456): every step is a
 // single correctly rounded fp32 operation, round-half-even conversion, saturation to
 // [-128, 127].
+// a / d, correctly rounded, for a divisor whose correctly rounded reciprocal rcp_d = 1.0f / d is at
+// hand: q = a * rcp_d is within one ulp of the quotient, the residual a - q * d is exact in a fused
+// multiply-add, and q + r * rcp_d then rounds to the true quotient (Markstein's division theorem; it
+// needs a divisor whose significand is not all ones -- see fma_division_ok -- and no overflow or
+// underflow, hence the range test).  Checked against a / d for every float in [1e-30, 1e30] for
+// 127 and for the K values of the model shapes.  Three dependent instructions instead of the
+// division subroutine, which sits on the critical path of every fused quantiser.
+__device__ __forceinline__ float div_const_rn(float a, float d, float rcp_d) {
+    if (!(a >= 1e-30f && a <= 1e30f)) return __fdiv_rn(a, d);
+    const float q = __fmul_rn(a, rcp_d);
+    const float r = __fmaf_rn(-q, d, a);
+    return __fmaf_rn(r, rcp_d, q);
+}
+// 1 / b, correctly rounded (== __frcp_rn(b) == 1.0f / b): hardware approximation (within one ulp)
+// followed by two residual corrections; from any start within two ulps the second one lands on the
+// correctly rounded reciprocal unless b's significand is all ones (checked for every float in
+// [1e-30, 1e30]); those and out-of-range inputs take the library routine.
+__device__ __forceinline__ float rcp_rn(float b) {
+    if (!(b >= 1e-30f && b <= 1e30f) || (__float_as_uint(b) & 0x7fffffu) == 0x7fffffu) return __frcp_rn(b);
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(b));
+    float r = __fmaf_rn(-b, y, 1.0f);
+    y = __fmaf_rn(r, y, y);
+    r = __fmaf_rn(-b, y, 1.0f);
+    return __fmaf_rn(r, y, y);
+}
 __device__ __forceinline__ float quant_scale_from_absmax(float absmax) {
     if (absmax < 1e-5f) absmax = 1e-5f;
-    return __fdiv_rn(absmax, 127.0f);
+    return div_const_rn(absmax, 127.0f, 1.0f / 127.0f);
 }
 __device__ __forceinline__ int quant_one(float v, float inv_scale) {
     int q = __float2int_rn(__fmul_rn(v, inv_scale));
@@ -204,5 +231,12 @@ __device__ __forceinline__ int perm_index(int k) {
     return (k & ~15) | ((k & 3) << 2) | ((k >> 2) & 3);
 }
 #endif  // __CUDACC__
+
+// Host side: may division by d use div_const_rn (significand of d not all ones)?
+inline bool fma_division_ok(float d) {
+    uint32_t u;
+    memcpy(&u, &d, 4);
+    return d > 0.0f && (u & 0x7fffffu) != 0x7fffffu;
+}
 
 }  // namespace lspk

@@ -33,6 +33,7 @@ struct LinearParams {
     const void* gamma;
     int gamma_is_bf16;
     float eps;
+    float rcp_K;           // 1.0f / K when division by K may use the fused multiply-add form, else 0
     int8_t* xq_out;
     float* xscale_out;
     int stream_weights;    // 1: weights are read once by this launch -> evict-first loads

@@ -24,6 +24,25 @@ namespace lspk {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 
+// Reductions over the eight warps of a CTA.  One barrier each: the result is read back from `slot`
+// (8 floats, 16-byte aligned) by every thread, so two consecutive reductions need two slots.
+static_assert(kWarps == 8, "cta8_* reductions assume eight warps");
+__device__ __forceinline__ float cta8_sum(float v, float* slot) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+    __syncthreads();
+    const float4 a = *reinterpret_cast<const float4*>(slot), b = *reinterpret_cast<const float4*>(slot + 4);
+    return ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+}
+// v >= 0: non-negative floats order like their bit patterns, so the warp stage is one integer redux
+__device__ __forceinline__ float cta8_max_nonneg(float v, float* slot) {
+    const uint32_t u = __reduce_max_sync(0xffffffffu, __float_as_uint(v));
+    if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = __uint_as_float(u);
+    __syncthreads();
+    const float4 a = *reinterpret_cast<const float4*>(slot), b = *reinterpret_cast<const float4*>(slot + 4);
+    return fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+}
+
 // MT      token rows per CTA tile
 // NI      16-byte weight loads per lane per batch (covers K <= 4096 at 4, K <= 8192 at 8 in one batch)
 // NB      16-element activation blocks a thread owns in the fp32 prologue (K <= 4096 * NB)
@@ -215,10 +234,11 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
 #pragma unroll
                         for (int e = 0; e < 16; ++e) ss[e & 3] = fmaf(v[nb][e], v[nb][e], ss[e & 3]);
                     tr.mark();                       // 2: x arrived, local squares summed
-                    ssq = block_sum((ss[0] + ss[1]) + (ss[2] + ss[3]), redf);
+                    ssq = cta8_sum((ss[0] + ss[1]) + (ss[2] + ss[3]), redf);
                     tr.mark();                       // 3: sum of squares reduced
                     // __frcp_rn is the correctly rounded reciprocal, i.e. exactly 1.0f / x
-                    const float rrms = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)p.K), p.eps)));
+                    const float mean = p.rcp_K != 0.0f ? div_const_rn(ssq, (float)p.K, p.rcp_K) : __fdiv_rn(ssq, (float)p.K);
+                    const float rrms = rcp_rn(__fsqrt_rn(__fadd_rn(mean, p.eps)));
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -230,27 +250,40 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
 #pragma unroll
                     for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[nb][e]));
                 tr.mark();                           // 4: normalised, local absmax
-                amax = block_max(amax, redf);
+                amax = cta8_max_nonneg(amax, redf + 8);
                 tr.mark();                           // 5: absmax reduced
                 scale = quant_scale_from_absmax(amax);
-                const float inv = __frcp_rn(scale);
+                const float inv = rcp_rn(scale);
                 const bool tap = (p.xq_out != nullptr) && blockIdx.x == 0;
 #pragma unroll
                 for (int nb = 0; nb < NB; ++nb) {
                     const int b = tid + nb * kThreads;
                     const int k0 = b * 16;
                     if (k0 < Kp) {
-                        uint32_t a[4];
+                        uint32_t o0, o1, o2, o3;
                         if (k0 + 16 <= tail_start) {
+                            // |v * inv| <= 127 by construction of inv, so the saturation of the reference's
+                            // conversion never acts and round-to-nearest-even can be taken from the adder:
+                            // v + 1.5 * 2^23 leaves the integer in the low mantissa byte.  The words are
+                            // packed directly in the transposed order the dot products read.
+                            uint32_t t[16];
 #pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                a[q] = pack4_bytes(quant_rne_sat(__fmul_rn(v[nb][q * 4 + 0], inv)),
-                                                   quant_rne_sat(__fmul_rn(v[nb][q * 4 + 1], inv)),
-                                                   quant_rne_sat(__fmul_rn(v[nb][q * 4 + 2], inv)),
-                                                   quant_rne_sat(__fmul_rn(v[nb][q * 4 + 3], inv)));
+                            for (int e = 0; e < 16; ++e)
+                                t[e] = __float_as_uint(__fadd_rn(__fmul_rn(v[nb][e], inv), 12582912.0f));
+                            o0 = pack4_bytes(t[0], t[4], t[8], t[12]);
+                            o1 = pack4_bytes(t[1], t[5], t[9], t[13]);
+                            o2 = pack4_bytes(t[2], t[6], t[10], t[14]);
+                            o3 = pack4_bytes(t[3], t[7], t[11], t[15]);
+                            if (tap) {
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)out_row(m) * p.K + k0 + q * 4) =
+                                        pack4_bytes(t[q * 4], t[q * 4 + 1], t[q * 4 + 2], t[q * 4 + 3]);
+                            }
                         } else {
                             // block that reaches past the last multiple of 16: the reference's scalar tail
                             // (round half away from zero, clamp to +-127), zeros beyond K
+                            uint32_t a[4];
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
                                 uint32_t word = 0;
@@ -266,22 +299,21 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
                                     word |= ((uint32_t)qv & 0xffu) << (8 * e);
                                 }
                                 a[q] = word;
+                                if (tap && k0 + q * 4 < p.K)
+                                    *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)out_row(m) * p.K + k0 + q * 4) = word;
                             }
+                            transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
                         }
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            sumx = __dp4a((int)a[q], 0x01010101, sumx);
-                            if (tap && k0 + q * 4 < p.K)
-                                *reinterpret_cast<uint32_t*>(p.xq_out + (size_t)out_row(m) * p.K + k0 + q * 4) = a[q];
-                        }
-                        uint32_t o0, o1, o2, o3;
-                        transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                        sumx = __dp4a((int)o0, 0x01010101, sumx);
+                        sumx = __dp4a((int)o1, 0x01010101, sumx);
+                        sumx = __dp4a((int)o2, 0x01010101, sumx);
+                        sumx = __dp4a((int)o3, 0x01010101, sumx);
                         *reinterpret_cast<uint4*>(xq_row + k0) = make_uint4(o0, o1, o2, o3);
                     }
                 }
             }
             // sum(x): per-warp partials; the output threads add the eight of them
-            sumx = warp_sum(sumx);
+            sumx = __reduce_add_sync(0xffffffffu, sumx);
             if (lane == 0) s_sumx[m * kWarps + warp] = sumx;
             if (tid == 0) {
                 s_scale[m] = scale;
@@ -494,6 +526,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
     p.prologue = a->prologue;
     p.epilogue = a->epilogue;
     p.x_f32 = a->x_f32;
+    p.rcp_K = fma_division_ok((float)w0->K) ? 1.0f / (float)w0->K : 0.0f;
     p.gate_f32 = a->gate_f32;
     p.x_i8 = a->x_i8;
     p.x_scales = a->x_scales;
