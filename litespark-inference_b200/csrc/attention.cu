@@ -8,6 +8,9 @@
 // probabilities normalised before the V product.  Query head h reads KV head h / (Q / KV).
 //
 // Cache layout is the reference's: [layer][position][kv_head][D], in fp32 or fp16.
+#include <cooperative_groups.h>
+#include <stdlib.h>
+
 #include "internal.cuh"
 
 namespace lspk {
@@ -90,19 +93,37 @@ template <> struct KvVec<float> {
     }
 };
 
+// Order-preserving map float -> uint32 (and back), so that a maximum over possibly negative floats
+// can use the integer warp reduction.
+__device__ __forceinline__ uint32_t float_to_ordered(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_to_float(uint32_t u) {
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
+
 // One CTA per (query head, row).  Built for latency, not bandwidth (one head's K and V are at
-// most a few hundred KB): every phase issues all of its global loads before using any of them.
-//   scores : one thread per key; the key row is read with 16-byte loads, up to 16 in flight.
-//   softmax: two block reductions.
-//   values : D/VEC threads per key (16 bytes of the value row each), 256/(D/VEC) key groups,
-//            8 loads in flight per thread; group partials are summed through shared memory.
+// most a few hundred KB): every phase issues all of its global loads before using any of them,
+// and every cache row is read by a group of adjacent lanes, 16 bytes each, so that a warp-wide
+// load touches whole 128-byte lines (a thread-per-key layout costs one L1 wavefront per lane
+// per load and was bound by exactly that).
+//   scores : TPK lanes per key; each lane's partial dot products for SB keys are combined with a
+//            halving exchange (SB + ... shuffles instead of SB * log2(TPK)), leaving lane c with
+//            the finished score of key c.
+//   softmax: two single-barrier block reductions.
+//   values : TPK lanes per key, NG key groups, 16 loads requested before the scores exist and
+//            8 in flight per thread afterwards; group partials are summed through shared memory.
 template <typename KVT, int D>
 __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
     constexpr int VEC = KvVec<KVT>::N;          // cache elements per 16-byte load
     constexpr int NCH = D / VEC;                // 16-byte chunks per cache row
-    constexpr int TPK = NCH;                    // threads per key in the value phase
-    constexpr int NG = kAttnThreads / TPK;      // key groups in the value phase
-    constexpr int KB = NCH < 16 ? NCH : 16;     // chunks per batch in the score phase
+    constexpr int TPK = NCH > 32 ? 32 : NCH;    // lanes per key
+    constexpr int CPT = NCH / TPK;              // chunks per lane (2 only for fp32 rows of 256)
+    constexpr int NG = kAttnThreads / TPK;      // key groups
+    constexpr int SB = (TPK < 16 ? TPK : 16) / CPT;   // keys per group whose rows are in flight together
+    constexpr int KPB = NG * SB;                // keys per batch of the score phase
+    static_assert(kAttnWarps == 8, "block reductions assume eight warps");
     extern __shared__ __align__(16) float at_smem[];
     float* qs = at_smem;                  // [D] rotated query
     float* ks = qs + D;                   // [D] rotated current key (fused mode)
@@ -110,7 +131,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     float* raw = vs + D;                  // [2*D] raw q and k before rotation (fused mode)
     float* part = raw + 2 * D;            // [NG][D] value partial sums
     float* sc = part + NG * D;            // [n] scores / probabilities
-    __shared__ float red[32];
+    __shared__ __align__(16) float red[16];
     PhaseTrace tr;
     tr.begin(p.trace, p.trace_cap, 2);
     tr.mark();                                   // 0: entry
@@ -120,7 +141,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     tr.mark();                                   // 1: predecessor finished
 
     const int h = blockIdx.x, t = blockIdx.y;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = p.Q / p.KV, kvh = h / G;
     const int pos = p.pos_per_row ? p.pos_ptr[t] : p.pos_ptr[0] + t;
     const int n = pos + 1;
@@ -130,8 +151,8 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride + (size_t)kvh * D;
     const float* qrow = p.q + (size_t)t * p.Q * D + (size_t)h * D;
 
-    // ---- request everything up front: the row's own q/k/v and rope factors, this thread's key
-    //      row for the score phase and its first 16 value chunks for the value phase ----------------
+    // ---- request everything up front: the row's own q/k/v and rope factors, the key rows of the
+    //      first score batch and the first 16 value chunks of this thread ---------------------------
     constexpr int VB0 = 16;                     // value chunks requested before the scores exist
     const int g = tid / TPK, c = tid % TPK;
     float q_raw = 0.0f, k_raw = 0.0f, vr = 0.0f, cr = 0.0f, sr = 0.0f;
@@ -145,18 +166,27 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
             sr = p.rope_sin[(size_t)pos * half + i];
         }
     }
-    uint4 kbuf[KB];
-    const bool k_from_cache = tid < n && !(p.fused && tid == pos);
-    if (k_from_cache) {
-        const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)tid * kd);
+    uint4 kbuf[SB][CPT];
+    auto request_keys = [&](int base) {
 #pragma unroll
-        for (int b = 0; b < KB; ++b) kbuf[b] = kp[b];
-    }
-    uint4 vbuf[VB0];
+        for (int j = 0; j < SB; ++j) {
+            const int i = base + g + j * NG;
+            if (i < n && !(p.fused && i == pos)) {
+                const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)i * kd);
 #pragma unroll
-    for (int b = 0; b < VB0; ++b) {
+                for (int u = 0; u < CPT; ++u) kbuf[j][u] = kp[c + u * TPK];
+            }
+        }
+    };
+    request_keys(0);
+    uint4 vbuf[VB0 / CPT][CPT];
+#pragma unroll
+    for (int b = 0; b < VB0 / CPT; ++b) {
         const int i = g + b * NG;
-        if (i < n && !(p.fused && i == pos)) vbuf[b] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c);
+        if (i < n && !(p.fused && i == pos)) {
+#pragma unroll
+            for (int u = 0; u < CPT; ++u) vbuf[b][u] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c + u * TPK);
+        }
     }
 
     if (p.fused) {
@@ -190,80 +220,125 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     __syncthreads();
     tr.mark();                                   // 2: q/k rotated (own loads arrived)
 
-    // ---- scores: thread per key ------------------------------------------------------------------
+    // ---- scores ------------------------------------------------------------------------------------
     const float inv_sqrt_d = 1.0f / sqrtf((float)D);
-    for (int i = tid; i < n; i += kAttnThreads) {
-        float dot = 0.0f;
-        if (p.fused && i == pos) {
-#pragma unroll 8
-            for (int d = 0; d < D; ++d) dot = fmaf(qs[d], ks[d], dot);
-        } else {
-            const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)i * kd);
+    float qreg[CPT][VEC];
 #pragma unroll
-            for (int b0 = 0; b0 < NCH; b0 += KB) {
-                if (b0 > 0 || i != tid) {
+    for (int u = 0; u < CPT; ++u)
 #pragma unroll
-                    for (int b = 0; b < KB; ++b) kbuf[b] = kp[b0 + b];
-                }
+        for (int e = 0; e < VEC; ++e) qreg[u][e] = qs[(c + u * TPK) * VEC + e];
+    for (int base = 0; base < n; base += KPB) {
+        if (base > 0) request_keys(base);
+        float dotp[SB];
 #pragma unroll
-                for (int b = 0; b < KB; ++b) {
+        for (int j = 0; j < SB; ++j) {
+            const int i = base + g + j * NG;
+            float d = 0.0f;
+            if (i < n) {
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) {
                     float f[VEC];
-                    KvVec<KVT>::unpack(kbuf[b], f);
+                    if (p.fused && i == pos) {
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) dot = fmaf(qs[(b0 + b) * VEC + e], f[e], dot);
+                        for (int e = 0; e < VEC; ++e) f[e] = ks[(c + u * TPK) * VEC + e];
+                    } else {
+                        KvVec<KVT>::unpack(kbuf[j][u], f);
+                    }
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) d = fmaf(qreg[u][e], f[e], d);
+                }
+            }
+            dotp[j] = d;
+        }
+        // combine the TPK lanes of a key: plain exchange while more lanes than keys remain, then each
+        // step halves the keys a lane still carries; lane c ends with the sum for key c % SB
+#pragma unroll
+        for (int o = TPK / 2; o >= 1; o >>= 1) {
+            if (o >= SB) {
+#pragma unroll
+                for (int j = 0; j < SB; ++j) dotp[j] += __shfl_xor_sync(0xffffffffu, dotp[j], o);
+            } else {
+                const bool upper = (c & o) != 0;
+#pragma unroll
+                for (int k = 0; k < o; ++k) {
+                    const float send = upper ? dotp[k] : dotp[k + o];
+                    const float keep = upper ? dotp[k + o] : dotp[k];
+                    dotp[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
             }
         }
-        sc[i] = __fmul_rn(dot, inv_sqrt_d);
+        if (c < SB) {
+            const int i = base + g + c * NG;
+            if (i < n) sc[i] = __fmul_rn(dotp[0], inv_sqrt_d);
+        }
     }
-    tr.mark();                                   // 3: own score done (key row arrived)
+    tr.mark();                                   // 3: own scores done (key rows arrived)
     __syncthreads();
     tr.mark();                                   // 4: all scores visible
 
     // ---- softmax over sc[0..n) -----------------------------------------------------------------------
     float mx = -INFINITY;
     for (int i = tid; i < n; i += kAttnThreads) mx = fmaxf(mx, sc[i]);
-    mx = block_max(mx, red);
+    {
+        const uint32_t u = __reduce_max_sync(0xffffffffu, float_to_ordered(mx));
+        if (lane == 0) red[warp] = ordered_to_float(u);
+        __syncthreads();
+        const float4 a = *reinterpret_cast<const float4*>(red), b = *reinterpret_cast<const float4*>(red + 4);
+        mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+    }
     float sum = 0.0f;
     for (int i = tid; i < n; i += kAttnThreads) {
         const float e = expf(sc[i] - mx);
         sc[i] = e;
         sum += e;
     }
-    sum = block_sum(sum, red);
+    {
+        sum = warp_sum(sum);
+        if (lane == 0) red[8 + warp] = sum;
+        __syncthreads();
+        const float4 a = *reinterpret_cast<const float4*>(red + 8), b = *reinterpret_cast<const float4*>(red + 12);
+        sum = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+    }
     for (int i = tid; i < n; i += kAttnThreads) sc[i] = __fdiv_rn(sc[i], sum);
     __syncthreads();
     tr.mark();                                   // 5: softmax done
 
-    // ---- weighted sum of values: TPK threads per key, NG key groups ---------------------------------
-    float o[VEC];
+    // ---- weighted sum of values: TPK lanes per key, NG key groups -----------------------------------
+    float o[CPT][VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) o[e] = 0.0f;
-    auto accumulate = [&](int i, const uint4& chunk) {
+    for (int u = 0; u < CPT; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[u][e] = 0.0f;
+    auto accumulate = [&](int i, const uint4* chunk) {
         const float pi = sc[i];
-        float f[VEC];
-        if (p.fused && i == pos) {
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) f[e] = vs[c * VEC + e];
-        } else {
-            KvVec<KVT>::unpack(chunk, f);
+        for (int u = 0; u < CPT; ++u) {
+            float f[VEC];
+            if (p.fused && i == pos) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) f[e] = vs[(c + u * TPK) * VEC + e];
+            } else {
+                KvVec<KVT>::unpack(chunk[u], f);
+            }
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o[u][e] = fmaf(pi, f[e], o[u][e]);
         }
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) o[e] = fmaf(pi, f[e], o[e]);
     };
 #pragma unroll
-    for (int b = 0; b < VB0; ++b) {
+    for (int b = 0; b < VB0 / CPT; ++b) {
         const int i = g + b * NG;
         if (i < n) accumulate(i, vbuf[b]);
     }
-    constexpr int VB = 8;                                   // loads in flight per thread afterwards
-    for (int i0 = g + VB0 * NG; i0 < n; i0 += NG * VB) {
-        uint4 buf[VB];
+    constexpr int VB = 8 / CPT;                             // keys in flight per thread afterwards
+    for (int i0 = g + (VB0 / CPT) * NG; i0 < n; i0 += NG * VB) {
+        uint4 buf[VB][CPT];
 #pragma unroll
         for (int b = 0; b < VB; ++b) {
             const int i = i0 + b * NG;
-            if (i < n && !(p.fused && i == pos))
-                buf[b] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c);
+            if (i < n && !(p.fused && i == pos)) {
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) buf[b][u] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c + u * TPK);
+            }
         }
 #pragma unroll
         for (int b = 0; b < VB; ++b) {
@@ -273,7 +348,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     }
     tr.mark();                                   // 6: values accumulated
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) part[g * D + c * VEC + e] = o[e];
+    for (int u = 0; u < CPT; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) part[g * D + (c + u * TPK) * VEC + e] = o[u][e];
     __syncthreads();
     if (tid < D) {
         float r = 0.0f;
@@ -285,11 +362,292 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
     tr.end();
 }
 
+// Decode form: the keys of one (query head, row) are split over a thread-block cluster of kSplit
+// CTAs, CTA r taking keys r, r + kSplit, ...  One head's K and V rows (100 KB at 200 positions) pulled
+// through a single SM bound the one-CTA form; eight SMs share them here, and the three scalars/vectors
+// the softmax needs from all keys (maximum, sum, output partials) cross the cluster through
+// distributed shared memory in ONE exchange: every CTA forms a softmax over its own keys (own maximum,
+// own sum, unnormalised output) and rank 0 merges the pieces with the weights exp(m_r - M) -- the same
+// function as the one-CTA form, rounded in a different order (compared within tolerance).  Only for rows that do not attend to each
+// other (a single row, or one sequence per row): the row's own key and value come from registers /
+// shared memory, the cache rows are written by the CTA that owns position `pos` (head h % G == 0).
+constexpr int kSplit = 8;
+
+template <typename KVT, int D>
+__global__ void __launch_bounds__(kAttnThreads) attention_split_kernel(const AttnParams p) {
+    namespace cg = cooperative_groups;
+    constexpr int VEC = KvVec<KVT>::N;
+    constexpr int NCH = D / VEC;
+    constexpr int TPK = NCH > 32 ? 32 : NCH;    // lanes per key
+    constexpr int CPT = NCH / TPK;              // chunks per lane
+    constexpr int NG = kAttnThreads / TPK;      // key groups
+    constexpr int SB = 4 / CPT;                 // keys per group in flight (requested before pos is known)
+    constexpr int KPB = NG * SB;                // local keys per batch
+    extern __shared__ __align__(16) float at_smem[];
+    float* qs = at_smem;                  // [D] rotated query
+    float* ks = qs + D;                   // [D] rotated current key
+    float* vs = ks + D;                   // [D] current value
+    float* raw = vs + D;                  // [2*D] raw q and k before rotation
+    float* part = raw + 2 * D;            // [NG][D] value partial sums of this CTA
+    float* fin = part + NG * D;           // [kSplit][D] CTA partials, gathered in rank 0
+    float* sc = fin + kSplit * D;         // [local keys] scores / probabilities
+    __shared__ __align__(16) float cl_max[kSplit], cl_sum[kSplit];
+    __shared__ __align__(16) float red[16];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int r = (int)cluster.block_rank();
+    PhaseTrace tr;
+    tr.begin(p.trace, p.trace_cap, 2);
+    tr.mark();                                   // 0: entry
+
+    grid_dependency_launch();
+    grid_dependency_wait();
+    tr.mark();                                   // 1: predecessor finished
+
+    const int h = blockIdx.x, t = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = p.Q / p.KV, kvh = h / G;
+    const int half = D / 2;
+    const int kd = p.KV * D;
+    KVT* ck = reinterpret_cast<KVT*>(p.cache_k) + (size_t)t * p.cache_seq_stride + (size_t)kvh * D;
+    KVT* cv = reinterpret_cast<KVT*>(p.cache_v) + (size_t)t * p.cache_seq_stride + (size_t)kvh * D;
+    const float* qrow = p.q + (size_t)t * p.Q * D + (size_t)h * D;
+    const int g = tid / TPK, c = tid % TPK;
+
+    // ---- requests that do not need the position: q, the row's k and v, and the first batch of this
+    //      CTA's key and value rows (any row below t_max is allocated; rows past the position are
+    //      never used) ---------------------------------------------------------------------------------
+    const int pos = p.pos_per_row ? p.pos_ptr[t] : p.pos_ptr[0] + t;
+    float q_raw = 0.0f, k_raw = 0.0f, vr = 0.0f, cr = 0.0f, sr = 0.0f;
+    if (tid < D) {
+        q_raw = qrow[tid];
+        k_raw = p.k_cur[(size_t)t * kd + (size_t)kvh * D + tid];
+        vr = p.v_cur[(size_t)t * kd + (size_t)kvh * D + tid];
+        if (p.rope_cur) {
+            const int i = tid < half ? tid : tid - half;
+            cr = p.rope_cur[(size_t)t * D + i];
+            sr = p.rope_cur[(size_t)t * D + half + i];
+        }
+    }
+    uint4 kbuf[SB][CPT], vbuf[SB][CPT];
+#pragma unroll
+    for (int j = 0; j < SB; ++j) {
+        const int i = r + kSplit * (g + j * NG);
+        if (i < p.t_max) {
+#pragma unroll
+            for (int u = 0; u < CPT; ++u) {
+                kbuf[j][u] = *(reinterpret_cast<const uint4*>(ck + (size_t)i * kd) + c + u * TPK);
+                vbuf[j][u] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c + u * TPK);
+            }
+        }
+    }
+    // ---- now the position: rope factors, rotation, cache write ----------------------------------------
+    const int n = pos + 1;
+    const int n_local = n > r ? (n - r + kSplit - 1) / kSplit : 0;     // keys r, r + kSplit, ... below n
+    const bool owner = (pos % kSplit) == r;
+    if (tid < D && !p.rope_cur) {
+        const int i = tid < half ? tid : tid - half;
+        cr = p.rope_cos[(size_t)pos * half + i];
+        sr = p.rope_sin[(size_t)pos * half + i];
+    }
+    if (tid < D) {
+        raw[tid] = q_raw;
+        raw[D + tid] = k_raw;
+    }
+    __syncthreads();                             // the rotation pairs element i with i + half
+    if (tid < D) {
+        const int i = tid < half ? tid : tid - half;
+        const float q1 = raw[i], q2 = raw[half + i], k1 = raw[D + i], k2 = raw[D + half + i];
+        float qr, kr;
+        if (tid < half) {
+            qr = __fsub_rn(__fmul_rn(q1, cr), __fmul_rn(q2, sr));
+            kr = __fsub_rn(__fmul_rn(k1, cr), __fmul_rn(k2, sr));
+        } else {
+            qr = __fadd_rn(__fmul_rn(q1, sr), __fmul_rn(q2, cr));
+            kr = __fadd_rn(__fmul_rn(k1, sr), __fmul_rn(k2, cr));
+        }
+        qs[tid] = qr;
+        ks[tid] = kv_round<KVT>(kr);
+        vs[tid] = kv_round<KVT>(vr);
+        if (owner && h % G == 0) {
+            ck[(size_t)pos * kd + tid] = kv_make<KVT>(kr);
+            cv[(size_t)pos * kd + tid] = kv_make<KVT>(vr);
+        }
+    }
+    __syncthreads();
+    tr.mark();                                   // 2: q/k rotated
+
+    // ---- scores of this CTA's keys -------------------------------------------------------------------------
+    const float inv_sqrt_d = 1.0f / sqrtf((float)D);
+    float qreg[CPT][VEC];
+#pragma unroll
+    for (int u = 0; u < CPT; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) qreg[u][e] = qs[(c + u * TPK) * VEC + e];
+    float mx = -INFINITY;
+    for (int base = 0; base < n_local; base += KPB) {
+        if (base > 0) {
+#pragma unroll
+            for (int j = 0; j < SB; ++j) {
+                const int i = r + kSplit * (base + g + j * NG);
+                if (i < n && i != pos) {
+#pragma unroll
+                    for (int u = 0; u < CPT; ++u)
+                        kbuf[j][u] = *(reinterpret_cast<const uint4*>(ck + (size_t)i * kd) + c + u * TPK);
+                }
+            }
+        }
+        float dotp[SB];
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+            const int i = r + kSplit * (base + g + j * NG);
+            float d = 0.0f;
+            if (i < n) {
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) {
+                    float f[VEC];
+                    if (i == pos) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) f[e] = ks[(c + u * TPK) * VEC + e];
+                    } else {
+                        KvVec<KVT>::unpack(kbuf[j][u], f);
+                    }
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) d = fmaf(qreg[u][e], f[e], d);
+                }
+            }
+            dotp[j] = d;
+        }
+#pragma unroll
+        for (int o = TPK / 2; o >= 1; o >>= 1) {
+            if (o >= SB) {
+#pragma unroll
+                for (int j = 0; j < SB; ++j) dotp[j] += __shfl_xor_sync(0xffffffffu, dotp[j], o);
+            } else {
+                const bool upper = (c & o) != 0;
+#pragma unroll
+                for (int k = 0; k < o; ++k) {
+                    const float send = upper ? dotp[k] : dotp[k + o];
+                    const float keep = upper ? dotp[k + o] : dotp[k];
+                    dotp[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                }
+            }
+        }
+        if (c < SB) {
+            const int jl = base + g + c * NG;                    // local key index
+            if (r + kSplit * jl < n) {
+                const float s = __fmul_rn(dotp[0], inv_sqrt_d);
+                sc[jl] = s;
+                mx = fmaxf(mx, s);
+            }
+        }
+    }
+    tr.mark();                                   // 3: own scores done
+
+    // ---- this CTA's maximum, exponentials relative to it, and their sum ------------------------------------
+    {
+        const uint32_t u = __reduce_max_sync(0xffffffffu, float_to_ordered(mx));
+        if (lane == 0) red[warp] = ordered_to_float(u);
+        __syncthreads();
+        const float4 a = *reinterpret_cast<const float4*>(red), b = *reinterpret_cast<const float4*>(red + 4);
+        mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+    }
+    float sum = 0.0f;
+    for (int j = tid; j < n_local; j += kAttnThreads) {
+        const float e = expf(sc[j] - mx);
+        sc[j] = e;
+        sum += e;
+    }
+    {
+        sum = warp_sum(sum);
+        if (lane == 0) red[8 + warp] = sum;
+        __syncthreads();                          // also publishes sc[] to the value phase
+        const float4 a = *reinterpret_cast<const float4*>(red + 8), b = *reinterpret_cast<const float4*>(red + 12);
+        sum = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+    }
+    tr.mark();                                   // 4: local softmax terms done
+
+    // ---- unnormalised weighted sum of this CTA's values ------------------------------------------------------
+    float o[CPT][VEC];
+#pragma unroll
+    for (int u = 0; u < CPT; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) o[u][e] = 0.0f;
+    for (int base = 0; base < n_local; base += KPB) {
+        if (base > 0) {
+#pragma unroll
+            for (int j = 0; j < SB; ++j) {
+                const int i = r + kSplit * (base + g + j * NG);
+                if (i < n && i != pos) {
+#pragma unroll
+                    for (int u = 0; u < CPT; ++u)
+                        vbuf[j][u] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c + u * TPK);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+            const int jl = base + g + j * NG;
+            const int i = r + kSplit * jl;
+            if (i < n) {
+                const float pi = sc[jl];
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) {
+                    float f[VEC];
+                    if (i == pos) {
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) f[e] = vs[(c + u * TPK) * VEC + e];
+                    } else {
+                        KvVec<KVT>::unpack(vbuf[j][u], f);
+                    }
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) o[u][e] = fmaf(pi, f[e], o[u][e]);
+                }
+            }
+        }
+    }
+    tr.mark();                                   // 5: values accumulated
+#pragma unroll
+    for (int u = 0; u < CPT; ++u)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) part[g * D + (c + u * TPK) * VEC + e] = o[u][e];
+    __syncthreads();
+    // ---- hand (maximum, sum, partial output) to rank 0, which merges the kSplit softmax pieces --------------
+    if (tid < D) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NG; ++w) acc += part[w * D + tid];
+        cluster.map_shared_rank(fin, 0)[r * D + tid] = acc;
+    }
+    if (tid == 0) {
+        cluster.map_shared_rank(cl_max, 0)[r] = mx;
+        cluster.map_shared_rank(cl_sum, 0)[r] = sum;
+    }
+    cluster.sync();
+    tr.mark();                                   // 6: cluster exchange done
+    if (r == 0 && tid < D) {
+        // softmax over all keys from the pieces: weights exp(m_r - M), denominators and outputs rescaled
+        float M = cl_max[0];
+#pragma unroll
+        for (int w = 1; w < kSplit; ++w) M = fmaxf(M, cl_max[w]);
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kSplit; ++w) {
+            const float wgt = expf(cl_max[w] - M);               // 0 for a piece without keys (maximum -inf)
+            L = fmaf(cl_sum[w], wgt, L);
+            acc = fmaf(fin[w * D + tid], wgt, acc);
+        }
+        p.out[(size_t)t * p.Q * D + (size_t)h * D + tid] = __fdiv_rn(acc, L);
+    }
+    tr.mark();                                   // 7: output stored
+    tr.end();
+}
+
 template <typename KVT>
 static int attention_launch_t(const AttnParams& p) {
     const int D = p.D;
     constexpr int VEC = 16 / (int)sizeof(KVT);
-    const size_t smem = (size_t)(5 * D + kAttnThreads * VEC + p.t_max) * sizeof(float);
+    const int nch = D / VEC, tpk = nch > 32 ? 32 : nch;
+    const size_t smem = (size_t)(5 * D + (kAttnThreads / tpk) * D + p.t_max) * sizeof(float);
     LSPK_REQUIRE(smem <= 200 * 1024, "attention: t_max=%d too large for the shared score buffer", p.t_max);
     static bool attr_set = false;
     if (!attr_set) {
@@ -302,6 +660,28 @@ static int attention_launch_t(const AttnParams& p) {
     if (!p.fused) {
         const size_t rs = (size_t)(p.Q + p.KV) * D * sizeof(float);
         LSPK_CUDA(launch(rope_store_kernel<KVT>, dim3(p.T), dim3(kAttnThreads), rs, true, p));
+    }
+    static const int knob_split = getenv("LSPK_ATTN_SPLIT") ? atoi(getenv("LSPK_ATTN_SPLIT")) : 1;
+    if (p.fused && knob_split && p.Q * p.T * kSplit <= 2 * sm_count() + kSplit) {
+        // decode rows: keys split over a cluster of kSplit CTAs
+        const int nch = D / VEC, tpk = nch > 32 ? 32 : nch;
+        const int local_keys = (p.t_max + kSplit - 1) / kSplit + 1;
+        const size_t sm = (size_t)(5 * D + (kAttnThreads / tpk) * D + kSplit * D + local_keys) * sizeof(float);
+        static bool split_attr_set = false;
+        if (!split_attr_set) {
+            LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            split_attr_set = true;
+        }
+        LSPK_REQUIRE(sm <= 200 * 1024, "attention: t_max=%d too large for the shared score buffer", p.t_max);
+        const dim3 sgrid(p.Q, p.T, kSplit), cl(1, 1, kSplit);
+        cudaError_t se;
+        if (D == 64) se = launch_cluster(attention_split_kernel<KVT, 64>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
+        else if (D == 128) se = launch_cluster(attention_split_kernel<KVT, 128>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
+        else se = launch_cluster(attention_split_kernel<KVT, 256>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
+        if (se != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention (split) launch failed: %s", cudaGetErrorString(se));
+        return LSPK_OK;
     }
     const dim3 grid(p.Q, p.T);
     cudaError_t e;

@@ -96,6 +96,7 @@ struct AttnParams {
     void* cache_v;
     const float* rope_cos; // [t_max, D/2]
     const float* rope_sin;
+    const float* rope_cur; // optional [T][D]: cos | sin of each row's position at a fixed address (decode step)
     const int* pos_ptr;    // device ints: position of row 0, or one position per row
     int pos_per_row;       // 0: rows are consecutive positions of one sequence; 1: one sequence per row
     size_t cache_seq_stride;  // elements between the caches of consecutive sequences (pos_per_row)

@@ -47,6 +47,8 @@ struct State {
     int cap_rows = 0;                 // rows the scratch buffers hold
     void *cache_k = nullptr, *cache_v = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
+    float* rope_cur = nullptr;        // [batch][D]: cos | sin rows of each sequence's current position (decode step)
+    bool rope_cur_valid = false;      // true while the kernels of a decode step are being enqueued
     int* ctl = nullptr;               // device: pos[batch], token[batch], step
     unsigned long long* best = nullptr;   // device: argmax keys [batch]
     int* tokens_out = nullptr;        // device: [t_max * batch]
@@ -71,11 +73,22 @@ struct State {
 
 // x[r, :] = embedding row of token[r] as fp32 (bf16 / int8*scale / int4*scale), the lookup of
 // runtime.py:151-168.
+// When rope_cur is given, also copies the rope factors of row r's position into rope_cur[r] (cos | sin),
+// so that the attention kernels of the step find them at a fixed address instead of behind the position.
 __global__ void embed_kernel(const int* __restrict__ tokens, int kind, const void* __restrict__ emb,
-                             const float* __restrict__ scale, float* __restrict__ x, int H, int V) {
+                             const float* __restrict__ scale, float* __restrict__ x, int H, int V,
+                             const int* __restrict__ pos, const float* __restrict__ rope_cos,
+                             const float* __restrict__ rope_sin, float* __restrict__ rope_cur, int half) {
     grid_dependency_launch();
     grid_dependency_wait();
     const int r = blockIdx.x;
+    if (rope_cur) {
+        const int ps = pos[r];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            rope_cur[(size_t)r * 2 * half + i] = rope_cos[(size_t)ps * half + i];
+            rope_cur[(size_t)r * 2 * half + half + i] = rope_sin[(size_t)ps * half + i];
+        }
+    }
     int tok = tokens[r];
     tok = min(max(tok, 0), V - 1);
     float* dst = x + (size_t)r * H;
@@ -159,7 +172,8 @@ __global__ void advance_pos_kernel(int* __restrict__ ctl, int seq, int by) {
 
 // ---- launch wrappers shared with the hybrid runtime (kernels must be launched from this file) ----
 int launch_embed(const int* tokens, int rows, int kind, const void* emb, const float* scale, float* x, int H, int V) {
-    LSPK_CUDA(launch(embed_kernel, dim3(rows), dim3(256), 0, true, tokens, kind, emb, scale, x, H, V));
+    LSPK_CUDA(launch(embed_kernel, dim3(rows), dim3(256), 0, true, tokens, kind, emb, scale, x, H, V, (const int*)nullptr,
+                     (const float*)nullptr, (const float*)nullptr, (float*)nullptr, 0));
     return LSPK_OK;
 }
 int launch_argmax_rows(const float* logits, int rows, int V, unsigned long long* best) {
@@ -261,6 +275,7 @@ static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool
         p.cache_v = (char*)s->cache_v + off * s->kv_elem();
         p.rope_cos = s->rope_cos;
         p.rope_sin = s->rope_sin;
+        p.rope_cur = s->rope_cur_valid ? s->rope_cur : nullptr;
         p.pos_ptr = s->ctl + (per_row_seq ? 0 : seq);
         p.pos_per_row = per_row_seq ? 1 : 0;
         p.cache_seq_stride = per_row_seq ? s->seq_stride() : 0;
@@ -307,9 +322,15 @@ static int enqueue_step(State* s, bool store_logits) {
     const lspk_model_config& c = m->cfg;
     const int B = s->batch, H = c.hidden_size, V = c.vocab_size;
     LSPK_CUDA(launch(embed_kernel, dim3(B), dim3(256), 0, true, (const int*)(s->ctl + B), m->emb.kind,
-                     (const void*)m->emb.data, (const float*)m->emb.scale, s->x, H, V));
+                     (const void*)m->emb.data, (const float*)m->emb.scale, s->x, H, V, (const int*)s->ctl,
+                     (const float*)s->rope_cos, (const float*)s->rope_sin, s->rope_cur, m->D() / 2));
+    s->rope_cur_valid = true;
     for (int li = 0; li < c.num_layers; ++li)
-        if (int rc = run_layer(s, li, B, B > 1, 0)) return rc;
+        if (int rc = run_layer(s, li, B, B > 1, 0)) {
+            s->rope_cur_valid = false;
+            return rc;
+        }
+    s->rope_cur_valid = false;
     const DevTable& head = m->head.data ? m->head : m->emb;
     if (B == 1) {
         if (int rc = lm_head_launch(head.kind, head.data, head.scale, s->x, store_logits ? s->logits : nullptr, 1, V, H,
@@ -505,6 +526,7 @@ lspk_state_t lspk_state_create(lspk_model_t h, int t_max, int batch, int kv_fp16
     rc |= dev_alloc(&s->cache_v, cache_bytes, &s->bytes);
     rc |= dev_alloc((void**)&s->rope_cos, (size_t)t_max * (D / 2) * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->rope_sin, (size_t)t_max * (D / 2) * 4, &s->bytes);
+    rc |= dev_alloc((void**)&s->rope_cur, (size_t)batch * D * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->ctl, (size_t)(2 * batch + 1) * 4, &s->bytes);
     rc |= dev_alloc((void**)&s->best, (size_t)batch * 8, &s->bytes);
     rc |= dev_alloc((void**)&s->tokens_out, (size_t)t_max * batch * 4, &s->bytes);
@@ -546,7 +568,7 @@ int lspk_state_free(lspk_state_t h) {
     cudaStreamSynchronize(stream());
     for (auto& g : s->graph)
         if (g) cudaGraphExecDestroy(g);
-    void* dev[] = {s->cache_k, s->cache_v, s->rope_cos, s->rope_sin, s->ctl, s->best, s->tokens_out, s->x, s->q, s->k,
+    void* dev[] = {s->cache_k, s->cache_v, s->rope_cos, s->rope_sin, s->rope_cur, s->ctl, s->best, s->tokens_out, s->x, s->q, s->k,
                    s->v, s->attn, s->inter, s->inter2, s->logits, s->xq_h, s->xq_i, s->xs, s->tok_rows};
     for (void* p : dev) cudaFree(p);
     if (s->h_int) cudaFreeHost(s->h_int);
@@ -656,8 +678,7 @@ int lspk_forward_prefill(lspk_state_t h, int seq, const int* tokens_host, int T,
         const int rows = (T - t0) < s->cap_rows ? (T - t0) : s->cap_rows;
         memcpy(s->h_int, tokens_host + t0, (size_t)rows * 4);
         LSPK_CUDA(cudaMemcpyAsync(s->tok_rows, s->h_int, (size_t)rows * 4, cudaMemcpyHostToDevice, stream()));
-        LSPK_CUDA(launch(embed_kernel, dim3(rows), dim3(256), 0, true, (const int*)s->tok_rows, m->emb.kind,
-                         (const void*)m->emb.data, (const float*)m->emb.scale, s->x, H, V));
+        if (int rc = launch_embed(s->tok_rows, rows, m->emb.kind, m->emb.data, m->emb.scale, s->x, H, V)) return rc;
         for (int li = 0; li < c.num_layers; ++li)
             if (int rc = run_layer(s, li, rows, false, seq)) return rc;
         if (all_logits_host) {
@@ -708,8 +729,8 @@ int lspk_bench_linears(lspk_state_t h, int reps, float* ms_out, int* launches_ou
     static cudaGraphExec_t exec = nullptr;
     static State* exec_for = nullptr;
     auto enqueue = [&]() -> int {
-        LSPK_CUDA(launch(embed_kernel, dim3(1), dim3(256), 0, true, (const int*)(s->ctl + 1), m->emb.kind,
-                         (const void*)m->emb.data, (const float*)m->emb.scale, s->x, c.hidden_size, c.vocab_size));
+        if (int rc = launch_embed(s->ctl + 1, 1, m->emb.kind, m->emb.data, m->emb.scale, s->x, c.hidden_size, c.vocab_size))
+            return rc;
         for (int li = 0; li < c.num_layers; ++li)
             if (int rc = run_layer(s, li, 1, false, 0, true)) return rc;
         return LSPK_OK;
