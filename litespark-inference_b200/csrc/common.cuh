@@ -106,10 +106,11 @@ int trace_capacity();                     // records
 struct PhaseTrace {
     unsigned long long* rec;
     int n;
-    __device__ __forceinline__ void begin(unsigned long long* buf, int cap, int kernel_id) {
+    // the recording thread is thread `thread` of block (0, 0, 0)
+    __device__ __forceinline__ void begin(unsigned long long* buf, int cap, int kernel_id, int thread = 0) {
         rec = nullptr;
         n = 0;
-        if (buf && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+        if (buf && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == thread) {
             const unsigned long long slot = atomicAdd(buf, 1ull);
             if (slot < (unsigned long long)cap) {
                 rec = buf + 1 + slot * kTraceWords;

@@ -53,6 +53,9 @@ struct LinearParams {
 int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* scale_scratch);
 // Library-owned scratch for that (grown with cudaMalloc: size it once outside stream capture).
 int quant_scratch(size_t M, size_t K, int8_t** q, float** s);
+// rows.cu: RMSNorm + quantiser of T rows, row t with the gamma_sel[t]-th bf16 weight vector.
+int norm_quant_rows_selected(const float* x, const void* gamma_bf16, const int* gamma_sel, int8_t* out, float* scales,
+                             int T, int K, float eps);
 int linear_mma_launch(const LinearParams& p, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);
 
 // Launch the CUDA-core kernel with fully prepared parameters.  mt: rows per CTA tile (1, 2, 4 or 8).

@@ -7,10 +7,11 @@
 //
 // Kernel sequence (all on the library stream, no host synchronisation):
 //   moe_router_kernel        one CTA per token: norm, quantise, router logits, softmax, top-2
-//   moe_group_kernel         rows (token, slot) listed per expert, ascending
-//   ternary_linear_kernel    expert-grouped launch, gate/up pair, ReLU^2 epilogue  (grid.z = expert)
-//   moe_subnorm_quant_kernel per routed row: RMSNorm with the row's expert's weights + quantiser
-//   ternary_linear_kernel    expert-grouped launch, down projection
+//   moe_group_kernel         rows (token, slot) listed per expert, ascending (more than one token;
+//                            the router kernel lists a single token's two rows itself)
+//   ternary_linear_mma_kernel expert-grouped launch, gate/up pair, ReLU^2 epilogue  (grid.z = expert)
+//   row_norm_quant_kernel    per routed row: RMSNorm with the row's expert's weights + quantiser
+//   ternary_linear_mma_kernel expert-grouped launch, down projection
 //   moe_combine_kernel       x += w_0 y_0 + w_1 y_1
 // The expert matrices live in one device buffer [expert][gate|up|down] in the device chunk layout;
 // an expert with no routed row costs no weight traffic.
@@ -43,84 +44,119 @@ struct Moe {
     size_t bytes = 0;
 };
 
-// One CTA per token row.
+// One CTA per token row: RMSNorm, quantiser, router logits (one warp per expert, round-robin), softmax
+// and top-2 inside warp 0.  With a single token (gridDim.x == 1) the per-expert row lists are written
+// here as well, which saves the grouping kernel.  H is a multiple of 4 (checked at creation).
 __global__ void __launch_bounds__(kMoeThreads)
 moe_router_kernel(const float* __restrict__ x, const uint16_t* __restrict__ gamma, const float* __restrict__ router,
                   int8_t* __restrict__ xq, float* __restrict__ xs, int* __restrict__ sel, float* __restrict__ selw,
-                  int H, int E, float eps) {
+                  int* __restrict__ counts, int* __restrict__ rows, int rows_stride, int H, int E, float eps) {
     extern __shared__ __align__(16) float hs[];           // [H] normalised row
-    __shared__ float red[32];
-    __shared__ float s_logit[kMaxExperts][kMoeThreads / 32];
+    __shared__ __align__(16) float red[16];
+    __shared__ float s_logit[kMaxExperts];
     grid_dependency_launch();
     grid_dependency_wait();
     const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const float* src = x + (size_t)t * H;
+    const int H4 = H >> 2;
+    const float4* src4 = reinterpret_cast<const float4*>(x + (size_t)t * H);
+    float4* hs4 = reinterpret_cast<float4*>(hs);
     float ssq = 0.0f;
-    for (int k = tid; k < H; k += kMoeThreads) {
-        const float v = src[k];
-        hs[k] = v;
-        ssq = fmaf(v, v, ssq);
+    for (int i = tid; i < H4; i += kMoeThreads) {
+        const float4 v = src4[i];
+        hs4[i] = v;
+        ssq = fmaf(v.x, v.x, ssq);
+        ssq = fmaf(v.y, v.y, ssq);
+        ssq = fmaf(v.z, v.z, ssq);
+        ssq = fmaf(v.w, v.w, ssq);
     }
-    ssq = block_sum(ssq, red);
-    const float rrms = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)H), eps)));
+    ssq = warp_sum(ssq);
+    if (lane == 0) red[warp] = ssq;
+    __syncthreads();
+    {
+        const float4 a = *reinterpret_cast<const float4*>(red), b = *reinterpret_cast<const float4*>(red + 4);
+        ssq = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+    }
+    const float rrms = rcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)H), eps)));
     float amax = 0.0f;
-    for (int k = tid; k < H; k += kMoeThreads) {
-        const float v = __fmul_rn(__fmul_rn(hs[k], rrms), bf16_bits_to_f32(gamma[k]));
-        hs[k] = v;
-        amax = fmaxf(amax, fabsf(v));
+    for (int i = tid; i < H4; i += kMoeThreads) {
+        float4 v = hs4[i];
+        const uint2 gb = *reinterpret_cast<const uint2*>(gamma + 4 * i);
+        v.x = __fmul_rn(__fmul_rn(v.x, rrms), __uint_as_float(gb.x << 16));
+        v.y = __fmul_rn(__fmul_rn(v.y, rrms), __uint_as_float(gb.x & 0xffff0000u));
+        v.z = __fmul_rn(__fmul_rn(v.z, rrms), __uint_as_float(gb.y << 16));
+        v.w = __fmul_rn(__fmul_rn(v.w, rrms), __uint_as_float(gb.y & 0xffff0000u));
+        hs4[i] = v;
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
     }
-    amax = block_max(amax, red);
+    {
+        const uint32_t u = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
+        if (lane == 0) red[8 + warp] = __uint_as_float(u);
+        __syncthreads();                                   // also publishes the normalised row
+        const float4 a = *reinterpret_cast<const float4*>(red + 8), b = *reinterpret_cast<const float4*>(red + 12);
+        amax = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+    }
     const float scale = quant_scale_from_absmax(amax);
-    const float inv = __frcp_rn(scale);
+    const float inv = rcp_rn(scale);
     const int tail_start = H & ~15;
-    for (int k = tid; k < H; k += kMoeThreads) {
-        int q;
-        if (k < tail_start) {
-            q = (int)quant_rne_sat(__fmul_rn(hs[k], inv));
-        } else {
-            q = max(-127, min(127, (int)roundf(__fmul_rn(hs[k], inv))));
+    uint32_t* xq4 = reinterpret_cast<uint32_t*>(xq + (size_t)t * H);
+    for (int i = tid; i < H4; i += kMoeThreads) {
+        const float4 v = hs4[i];
+        const float f[4] = {v.x, v.y, v.z, v.w};
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            int q;
+            if (4 * i < tail_start) q = (int)quant_rne_sat(__fmul_rn(f[e], inv));
+            else q = max(-127, min(127, (int)roundf(__fmul_rn(f[e], inv))));
+            word |= ((uint32_t)q & 0xffu) << (8 * e);
         }
-        xq[(size_t)t * H + k] = (int8_t)q;
+        xq4[i] = word;
     }
     if (tid == 0) xs[t] = scale;
-    // router logits: every thread holds a partial of each expert's dot product
-    for (int e = 0; e < E; ++e) {
-        const float* wr = router + (size_t)e * H;
-        float acc = 0.0f;
-        for (int k = tid; k < H; k += kMoeThreads) acc = fmaf(hs[k], wr[k], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) s_logit[e][warp] = acc;
+    // router logits: warp w takes experts w, w + 8, ...
+    for (int e = warp; e < E; e += kMoeThreads / 32) {
+        const float4* wr4 = reinterpret_cast<const float4*>(router + (size_t)e * H);
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        for (int i = lane; i < H4; i += 32) {
+            const float4 h = hs4[i], w = __ldg(wr4 + i);
+            a0 = fmaf(h.x, w.x, a0);
+            a1 = fmaf(h.y, w.y, a1);
+            a2 = fmaf(h.z, w.z, a2);
+            a3 = fmaf(h.w, w.w, a3);
+        }
+        const float acc = warp_sum((a0 + a1) + (a2 + a3));
+        if (lane == 0) s_logit[e] = acc;
     }
     __syncthreads();
-    if (tid == 0) {
-        float logit[kMaxExperts], mx = -INFINITY;
-        for (int e = 0; e < E; ++e) {
-            float a = 0.0f;
-            for (int w = 0; w < kMoeThreads / 32; ++w) a += s_logit[e][w];
-            logit[e] = a;
-            mx = fmaxf(mx, a);
-        }
-        float sum = 0.0f;
-        for (int e = 0; e < E; ++e) {
-            logit[e] = expf(logit[e] - mx);
-            sum += logit[e];
-        }
-        int i0 = 0, i1 = -1;
-        float p0 = -1.0f, p1 = -1.0f;
-        for (int e = 0; e < E; ++e) {
-            const float pe = __fdiv_rn(logit[e], sum);
-            if (pe > p0) {
-                p1 = p0; i1 = i0;
-                p0 = pe; i0 = e;
-            } else if (pe > p1) {
-                p1 = pe; i1 = e;
-            }
-        }
+    if (warp == 0) {
+        // softmax over the experts (E <= 32: one lane each), then the two largest (ties to the lower index)
+        const bool valid = lane < E;
+        const float l = valid ? s_logit[lane] : -INFINITY;
+        const float mx = warp_max(l);
+        const float ex = valid ? expf(l - mx) : 0.0f;
+        const float sum = warp_sum(ex);
+        const float pe = valid ? __fdiv_rn(ex, sum) : 0.0f;
+        // probabilities are in [0, 1]: bits + 1 orders them and leaves 0 for "no candidate"
+        const uint32_t key = valid ? __float_as_uint(pe) + 1u : 0u;
+        const uint32_t k0 = __reduce_max_sync(0xffffffffu, key);
+        const int i0 = (int)__reduce_min_sync(0xffffffffu, key == k0 ? (uint32_t)lane : 32u);
+        const uint32_t key1 = lane == i0 ? 0u : key;
+        const uint32_t k1 = __reduce_max_sync(0xffffffffu, key1);
+        const int i1 = (int)__reduce_min_sync(0xffffffffu, (key1 == k1 && lane != i0) ? (uint32_t)lane : 32u);
+        const float p0 = __shfl_sync(0xffffffffu, pe, i0), p1 = __shfl_sync(0xffffffffu, pe, i1);
         const float den = __fadd_rn(p0, p1);
-        sel[2 * t] = i0;
-        sel[2 * t + 1] = i1;
-        selw[2 * t] = __fdiv_rn(p0, den);
-        selw[2 * t + 1] = __fdiv_rn(p1, den);
+        if (lane == 0) {
+            sel[2 * t] = i0;
+            sel[2 * t + 1] = i1;
+            selw[2 * t] = __fdiv_rn(p0, den);
+            selw[2 * t + 1] = __fdiv_rn(p1, den);
+        }
+        if (gridDim.x == 1 && valid) {
+            // single token: routed row 0 goes to expert i0, routed row 1 to expert i1
+            counts[lane] = (lane == i0 || lane == i1) ? 1 : 0;
+            if (lane == i0) rows[(size_t)lane * rows_stride] = 0;
+            if (lane == i1) rows[(size_t)lane * rows_stride] = 1;
+        }
     }
 }
 
@@ -136,47 +172,6 @@ __global__ void moe_group_kernel(const int* __restrict__ sel, int n_rows, int E,
             if (sel[r] == e) rows[(size_t)e * rows_stride + c++] = r;
         counts[e] = c;
     }
-}
-
-// One CTA per routed row: RMSNorm with the weights of the row's expert, then the int8 quantiser.
-__global__ void __launch_bounds__(kMoeThreads)
-moe_subnorm_quant_kernel(const float* __restrict__ inter, const int* __restrict__ sel, const uint16_t* __restrict__ gamma,
-                         int8_t* __restrict__ out, float* __restrict__ scales, int K, float eps) {
-    extern __shared__ __align__(16) float vs[];
-    __shared__ float red[32];
-    grid_dependency_launch();
-    grid_dependency_wait();
-    const int r = blockIdx.x, tid = threadIdx.x;
-    const float* src = inter + (size_t)r * K;
-    const uint16_t* g = gamma + (size_t)sel[r] * K;
-    float ssq = 0.0f;
-    for (int k = tid; k < K; k += kMoeThreads) {
-        const float v = src[k];
-        vs[k] = v;
-        ssq = fmaf(v, v, ssq);
-    }
-    ssq = block_sum(ssq, red);
-    const float rrms = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)K), eps)));
-    float amax = 0.0f;
-    for (int k = tid; k < K; k += kMoeThreads) {
-        const float v = __fmul_rn(__fmul_rn(vs[k], rrms), bf16_bits_to_f32(g[k]));
-        vs[k] = v;
-        amax = fmaxf(amax, fabsf(v));
-    }
-    amax = block_max(amax, red);
-    const float scale = quant_scale_from_absmax(amax);
-    const float inv = __frcp_rn(scale);
-    const int tail_start = K & ~15;
-    for (int k = tid; k < K; k += kMoeThreads) {
-        int q;
-        if (k < tail_start) {
-            q = (int)quant_rne_sat(__fmul_rn(vs[k], inv));
-        } else {
-            q = max(-127, min(127, (int)roundf(__fmul_rn(vs[k], inv))));
-        }
-        out[(size_t)r * K + k] = (int8_t)q;
-    }
-    if (tid == 0) scales[r] = scale;
 }
 
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ selw,
@@ -227,14 +222,18 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     static bool attr_set = false;
     if (!attr_set) {
         LSPK_CUDA(cudaFuncSetAttribute(moe_router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(moe_subnorm_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set = true;
     }
     LSPK_CUDA(launch(moe_router_kernel, dim3(B), dim3(kMoeThreads), (size_t)H * 4, true, (const float*)x,
-                     (const uint16_t*)m->norm, (const float*)m->router, m->xq, m->xs, m->sel, m->selw, H, E, m->eps));
-    LSPK_CUDA(launch(moe_group_kernel, dim3(1), dim3(32), 0, true, (const int*)m->sel, R, E, m->counts, m->rows, R));
+                     (const uint16_t*)m->norm, (const float*)m->router, m->xq, m->xs, m->sel, m->selw, m->counts, m->rows, R,
+                     H, E, m->eps));
+    if (B > 1)      // a single token's two rows are listed by the router kernel itself
+        LSPK_CUDA(launch(moe_group_kernel, dim3(1), dim3(32), 0, true, (const int*)m->sel, R, E, m->counts, m->rows, R));
 
-    const int ctas = 2 * sm_count() / (E < 4 ? E : 4);     // a few experts are active; keep each one's grid wide
+    // At most min(E, R) experts have rows; CTAs of the others leave at once.  Two resident CTAs per SM
+    // over the experts that can be active keeps enough weight bytes in flight.
+    const int active = E < R ? E : R;
+    const int ctas = (2 * sm_count() + active - 1) / active;
     LinearParams p = {};
     p.trace = nullptr;
     p.prologue = LSPK_PRO_INT8;
@@ -258,8 +257,7 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     p.grp_in_shift = 1;                // routed row 2*token + slot reads token's activations
     if (int rc = linear_launch_params(p, 8, true, true, ctas < m->groups_gu ? ctas : m->groups_gu, 1, E)) return rc;
     // SubLN + quantiser per routed row, with the row's expert's norm weights
-    LSPK_CUDA(launch(moe_subnorm_quant_kernel, dim3(R), dim3(kMoeThreads), (size_t)I * 4, true, (const float*)m->inter,
-                     (const int*)m->sel, (const uint16_t*)m->sub_norm, m->xq2, m->xs2, I, m->eps));
+    if (int rc = norm_quant_rows_selected(m->inter, m->sub_norm, m->sel, m->xq2, m->xs2, R, I, m->eps)) return rc;
     // down
     p.K = I;
     p.chunks = m->chunks_d;

@@ -24,9 +24,9 @@ __device__ __forceinline__ float gamma_at(const void* gamma, int is_bf16, int k)
 // multiple of 4 and every pointer 16-byte aligned, so the passes move four elements at a time.
 template <bool VEC>
 __global__ void __launch_bounds__(kRowThreads)
-row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gate, const void* __restrict__ gamma,
-                      int gamma_is_bf16, float* __restrict__ out_f32, int8_t* __restrict__ out_i8,
-                      float* __restrict__ scales, int K, float eps, int mode) {
+row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gate, const void* __restrict__ gamma_base,
+                      const int* __restrict__ gamma_sel, int gamma_is_bf16, float* __restrict__ out_f32,
+                      int8_t* __restrict__ out_i8, float* __restrict__ scales, int K, float eps, int mode) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* xs = reinterpret_cast<float*>(smem_raw);
     __shared__ float red[32];
@@ -35,6 +35,9 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
     const int t = blockIdx.x, tid = threadIdx.x;
     const float* src = x + (size_t)t * K;
     const float* gsrc = gate ? gate + (size_t)t * K : nullptr;
+    // gamma_sel: row t uses the gamma_sel[t]-th vector of K norm weights (per-expert sub-norms)
+    const void* gamma = gamma_base;
+    if (gamma_sel) gamma = reinterpret_cast<const char*>(gamma_base) + (size_t)gamma_sel[t] * K * (gamma_is_bf16 ? 2 : 4);
     const bool norm = mode & 1, quant = mode & 2;
     const int tail_start = K & ~15;
 
@@ -154,7 +157,8 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 }
 
 static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, float* out_f32, int8_t* out_i8,
-                       float* scales, int T, int K, float eps, int mode, const float* gate = nullptr) {
+                       float* scales, int T, int K, float eps, int mode, const float* gate = nullptr,
+                       const int* gamma_sel = nullptr) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(x && T >= 1 && K >= 1, "row helper: bad arguments (T=%d K=%d)", T, K);
     const size_t smem = (size_t)K * sizeof(float);
@@ -166,9 +170,10 @@ static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, flo
         attr_set = true;
     }
     auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    const bool vec = (K % 4 == 0) && aligned(x) && aligned(out_f32) && aligned(out_i8) && aligned(gamma) && aligned(gate);
+    const bool vec = (K % 4 == 0) && aligned(x) && aligned(out_f32) && aligned(out_i8) && aligned(gamma) && aligned(gate) &&
+                     (!gamma_sel || K % 8 == 0);
     LSPK_CUDA(launch(vec ? row_norm_quant_kernel<true> : row_norm_quant_kernel<false>, dim3(T), dim3(kRowThreads), smem,
-                     true, x, gate, gamma, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode));
+                     true, x, gate, gamma, gamma_sel, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode));
     return LSPK_OK;
 }
 
@@ -192,6 +197,12 @@ int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* sca
     a->x_f32 = nullptr;
     a->gate_f32 = nullptr;
     return LSPK_OK;
+}
+
+// RMSNorm + quantiser of T rows where row t takes the gamma_sel[t]-th weight vector (bf16, K each).
+int norm_quant_rows_selected(const float* x, const void* gamma_bf16, const int* gamma_sel, int8_t* out, float* scales,
+                             int T, int K, float eps) {
+    return launch_rows(x, gamma_bf16, 1, nullptr, out, scales, T, K, eps, 3, nullptr, gamma_sel);
 }
 
 static int grid_for(size_t n, int block) {
