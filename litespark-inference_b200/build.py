@@ -57,7 +57,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     def compile_one(job):
         src, obj = job
-        cmd = [_nvcc(), *_host_compiler_args(), *NVCC_FLAGS, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
+        extra = os.environ.get("LSPK_NVCC_FLAGS", "").split()        # e.g. -DLSPK_LINEAR_MIN_BLOCKS=3 for experiments
+        cmd = [_nvcc(), *_host_compiler_args(), *NVCC_FLAGS, *extra, "-I", str(INCLUDE), "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         log = OBJ / (src.stem + ".ptxas.log")
         log.write_text(r.stdout + r.stderr)

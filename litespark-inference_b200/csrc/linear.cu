@@ -50,10 +50,11 @@ __device__ __forceinline__ float cta8_max_nonneg(float v, float* slot) {
 // GROUPED expert-grouped launch: blockIdx.z is the expert; its row list and row count are read from
 //         device arrays, its weights and scales are found by stride (packed-expert MoE GEMV)
 template <int MT, int NI, int NB, bool PAIR, bool GROUPED>
-#ifndef LSPK_LINEAR_MIN_BLOCKS
-#define LSPK_LINEAR_MIN_BLOCKS 1
-#endif
+#ifdef LSPK_LINEAR_MIN_BLOCKS
 __global__ void __launch_bounds__(kThreads, LSPK_LINEAR_MIN_BLOCKS)
+#else
+__global__ void __launch_bounds__(kThreads)
+#endif
 ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int Kp = p.chunks * kWeightsPerChunk;

@@ -49,8 +49,11 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
 }
 
 // TT: rows of x handled per launch (1 for decode, up to kLmMaxT otherwise); INFL: 16-byte loads in
-// flight per lane (10 covers a 2560-wide bf16 row in one batch).
-template <int KIND, int TT, int INFL>
+// flight per lane and vocabulary row (10 covers a 2560-wide bf16 row in one batch); RW: vocabulary
+// rows a warp works on at once.  With several rows of x the kernel would be bound by shared-memory
+// reads of x (32 bytes per row of x and 16-byte chunk of the table); a warp that holds RW table
+// rows reuses every x value it fetched RW times.
+template <int KIND, int TT, int INFL, int RW>
 __global__ void __launch_bounds__(kLmThreads)
 lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scale,
                const float* __restrict__ x, float* __restrict__ logits, int T, int V, int H,
@@ -93,17 +96,27 @@ lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scal
 
     unsigned long long best = 0ull;
     const size_t row_chunks = (size_t)nchunks;
-    for (int v = blockIdx.x * kLmWarps + warp; v < V; v += gridDim.x * kLmWarps) {
-        const uint4* row = emb + (size_t)v * row_chunks;
-        float acc[TT];
+    for (int v0 = (blockIdx.x * kLmWarps + warp) * RW; v0 < V; v0 += gridDim.x * kLmWarps * RW) {
+        float acc[TT][RW];
 #pragma unroll
-        for (int t = 0; t < TT; ++t) acc[t] = 0.0f;
+        for (int t = 0; t < TT; ++t)
+#pragma unroll
+            for (int r = 0; r < RW; ++r) acc[t][r] = 0.0f;
         for (int c0 = lane; c0 < nchunks; c0 += 32 * INFL) {
-            uint4 buf[INFL];
+            uint4 buf[RW][INFL];
 #pragma unroll
-            for (int u = 0; u < INFL; ++u) {
-                const int c = c0 + 32 * u;
-                if (c < nchunks) buf[u] = __ldcs(row + c);
+            for (int r = 0; r < RW; ++r) {
+                if (RW == 1 || v0 + r < V) {
+                    const uint4* row = emb + (size_t)(v0 + r) * row_chunks;
+#pragma unroll
+                    for (int u = 0; u < INFL; ++u) {
+                        const int c = c0 + 32 * u;
+                        if (c < nchunks) buf[r][u] = __ldcs(row + c);
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < INFL; ++u) buf[r][u] = make_uint4(0, 0, 0, 0);
+                }
             }
 #pragma unroll
             for (int u = 0; u < INFL; ++u) {
@@ -111,33 +124,42 @@ lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scal
                 if (c < nchunks) {
 #pragma unroll
                     for (int s = 0; s < S; ++s) {
-                        float f[4];
-                        decode4<KIND>(buf[u], s, f);
+                        float f[RW][4];
+#pragma unroll
+                        for (int r = 0; r < RW; ++r) decode4<KIND>(buf[r][u], s, f[r]);
 #pragma unroll
                         for (int t = 0; t < TT; ++t) {
                             if (TT == 1 || t < T) {
                                 const float4 xv = xs4[((size_t)t * S + s) * nchunks + c];
-                                acc[t] = fmaf(f[0], xv.x, acc[t]);
-                                acc[t] = fmaf(f[1], xv.y, acc[t]);
-                                acc[t] = fmaf(f[2], xv.z, acc[t]);
-                                acc[t] = fmaf(f[3], xv.w, acc[t]);
+#pragma unroll
+                                for (int r = 0; r < RW; ++r) {
+                                    acc[t][r] = fmaf(f[r][0], xv.x, acc[t][r]);
+                                    acc[t][r] = fmaf(f[r][1], xv.y, acc[t][r]);
+                                    acc[t][r] = fmaf(f[r][2], xv.z, acc[t][r]);
+                                    acc[t][r] = fmaf(f[r][3], xv.w, acc[t][r]);
+                                }
                             }
                         }
                     }
                 }
             }
         }
-        const float sc = (KIND == 0) ? 1.0f : emb_scale[v];
 #pragma unroll
-        for (int t = 0; t < TT; ++t) {
-            if (TT == 1 || t < T) {
-                float r = warp_sum(acc[t]);
-                if (KIND != 0) r = __fmul_rn(sc, r);
-                if (lane == 0) {
-                    if (logits) logits[(size_t)t * V + v] = r;
-                    if (best_key && t == 0) {
-                        const unsigned long long key = argmax_key(r, v);
-                        best = key > best ? key : best;
+        for (int r = 0; r < RW; ++r) {
+            const int v = v0 + r;
+            if (RW > 1 && v >= V) break;
+            const float sc = (KIND == 0) ? 1.0f : emb_scale[v];
+#pragma unroll
+            for (int t = 0; t < TT; ++t) {
+                if (TT == 1 || t < T) {
+                    float rr = warp_sum(acc[t][r]);
+                    if (KIND != 0) rr = __fmul_rn(sc, rr);
+                    if (lane == 0) {
+                        if (logits) logits[(size_t)t * V + v] = rr;
+                        if (best_key && t == 0) {
+                            const unsigned long long key = argmax_key(rr, v);
+                            best = key > best ? key : best;
+                        }
                     }
                 }
             }
@@ -166,7 +188,7 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     const int E = kind == 0 ? 8 : kind == 1 ? 16 : 32;
     LSPK_REQUIRE(H % E == 0, "lm_head: H=%d must be a multiple of %d for this embedding format", H, E);
     LSPK_REQUIRE(((uintptr_t)emb & 15) == 0, "lm_head: embedding must be 16-byte aligned");
-    const int rows_per_cta = kLmWarps;
+    const int rows_per_cta = kLmWarps * (T == 1 ? 1 : kind == 0 ? 4 : 2);   // RW of the instantiation chosen below
     int grid = (V + rows_per_cta - 1) / rows_per_cta;
     const int cap = sm_count() * 4;
     if (grid > cap) grid = cap;
@@ -179,10 +201,10 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
         float* lt = logits ? logits + (size_t)t0 * V : nullptr;
         unsigned long long* bk = t0 == 0 ? best_key : nullptr;
         cudaError_t e = cudaSuccess;
-#define LSPK_LM_LAUNCH(KIND, TT, INFL)                                                                     \
+#define LSPK_LM_LAUNCH(KIND, TT, INFL, RW)                                                                  \
         do {                                                                                                \
             static bool attr_set = false;                                                                   \
-            auto kern = lm_head_kernel<KIND, TT, INFL>;                                                     \
+            auto kern = lm_head_kernel<KIND, TT, INFL, RW>;                                                   \
             if (!attr_set) {                                                                                \
                 e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);     \
                 attr_set = (e == cudaSuccess);                                                              \
@@ -192,13 +214,13 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
                            norm_gamma, gamma_is_bf16, eps, bk);                                             \
         } while (0)
         if (tt == 1) {
-            if (kind == 0) LSPK_LM_LAUNCH(0, 1, 10);
-            else if (kind == 1) LSPK_LM_LAUNCH(1, 1, 5);
-            else LSPK_LM_LAUNCH(2, 1, 3);
+            if (kind == 0) LSPK_LM_LAUNCH(0, 1, 10, 1);
+            else if (kind == 1) LSPK_LM_LAUNCH(1, 1, 5, 1);
+            else LSPK_LM_LAUNCH(2, 1, 3, 1);
         } else {
-            if (kind == 0) LSPK_LM_LAUNCH(0, kLmMaxT, 4);
-            else if (kind == 1) LSPK_LM_LAUNCH(1, kLmMaxT, 2);
-            else LSPK_LM_LAUNCH(2, kLmMaxT, 2);
+            if (kind == 0) LSPK_LM_LAUNCH(0, kLmMaxT, 3, 4);
+            else if (kind == 1) LSPK_LM_LAUNCH(1, kLmMaxT, 2, 2);
+            else LSPK_LM_LAUNCH(2, kLmMaxT, 1, 2);
         }
 #undef LSPK_LM_LAUNCH
         if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head launch failed: %s", cudaGetErrorString(e));
