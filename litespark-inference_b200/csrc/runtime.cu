@@ -156,12 +156,46 @@ __global__ void finish_step_kernel(int* __restrict__ ctl, unsigned long long* __
     if (b == 0) ctl[2 * batch] += 1;
 }
 
-// Does nothing but take part in the dependency chain: measures the floor cost of one kernel
-// boundary inside a graph (see lspk_bench_launch_floor).
-__global__ void chain_probe_kernel(int* __restrict__ sink, int early_trigger) {
-    if (early_trigger) grid_dependency_launch();
+// Takes part in a dependency chain and does what a decode kernel does at its boundaries: every CTA
+// reads a 10 KB vector the previous kernel wrote (16 floats per thread, 160 threads), reduces over
+// the CTA, and writes its 64-float slice of the next vector.  Measures the floor cost of a kernel
+// boundary plus the first read of freshly written data (see lspk_bench_launch_floor).
+//   mode bit 0: trigger dependents early; bits 1-2: load flavour (0 plain, 1 .cg, 2 volatile);
+//   bit 3: store flavour (0 plain, 1 .cg); bit 4: skip the vector traffic (empty kernel)
+__global__ void chain_probe_kernel(int* __restrict__ sink, const float* __restrict__ vin, float* __restrict__ vout,
+                                   int mode, unsigned long long* trace, int trace_cap) {
+    __shared__ float red[32];
+    PhaseTrace tr;
+    tr.begin(trace, trace_cap, 5);
+    tr.mark();
+    if (mode & 1) grid_dependency_launch();
     grid_dependency_wait();
+    tr.mark();                                   // 1: predecessor finished
+    if (!(mode & 16)) {
+        const int tid = threadIdx.x, lf = (mode >> 1) & 3;
+        float acc = 0.0f;
+        if (tid < 160) {
+            const float4* src = reinterpret_cast<const float4*>(vin) + tid * 4;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 v;
+                if (lf == 1) v = __ldcg(src + q);
+                else if (lf == 2) asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src + q));
+                else v = src[q];
+                acc += (v.x + v.y) + (v.z + v.w);
+            }
+        }
+        tr.mark();                               // 2: this thread's 64 bytes arrived
+        acc = block_sum(acc, red);
+        tr.mark();                               // 3: all warps' data arrived and reduced
+        if (tid < 64 && blockIdx.x < 160) {
+            const float o = acc * 1e-3f + (float)tid;
+            float* dst = vout + blockIdx.x * 64 + tid;
+            if (mode & 8) __stcg(dst, o); else *dst = o;
+        }
+    }
     if (sink && threadIdx.x == 0 && blockIdx.x == 0) sink[0] += 1;
+    tr.end();
 }
 
 __global__ void advance_pos_kernel(int* __restrict__ ctl, int seq, int by) {
@@ -835,15 +869,19 @@ int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(n_kernels >= 1 && grid >= 1 && reps >= 1 && ms_out, "lspk_bench_launch_floor: bad arguments");
     int* sink = nullptr;
-    LSPK_CUDA(cudaMalloc(&sink, 16));
-    LSPK_CUDA(cudaMemset(sink, 0, 16));
+    LSPK_CUDA(cudaMalloc(&sink, 16 + 2 * 10240 * 4));
+    LSPK_CUDA(cudaMemset(sink, 0, 16 + 2 * 10240 * 4));
+    float* va = reinterpret_cast<float*>(sink + 4);
+    float* vb = va + 10240;
+    static const int mode = getenv("LSPK_PROBE_MODE") ? atoi(getenv("LSPK_PROBE_MODE")) : 17;   // empty kernels, early trigger
     LSPK_CUDA(cudaDeviceSynchronize());
     cudaGraph_t g = nullptr;
     cudaGraphExec_t exec = nullptr;
     LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
     cudaError_t le = cudaSuccess;
     for (int i = 0; i < n_kernels && le == cudaSuccess; ++i)
-        le = launch(chain_probe_kernel, dim3(grid), dim3(256), 0, true, sink, 1);
+        le = launch(chain_probe_kernel, dim3(grid), dim3(256), 0, true, sink, (const float*)((i & 1) ? vb : va), (i & 1) ? va : vb, mode,
+                    trace_buffer(), trace_capacity());
     cudaError_t e = cudaStreamEndCapture(stream(), &g);
     if (le != cudaSuccess || e != cudaSuccess) {
         cudaFree(sink);
