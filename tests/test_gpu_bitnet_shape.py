@@ -1,0 +1,92 @@
+"""Forward pass at the BitNet-2B layer shape (hidden 2560, 20 query / 5 KV heads of 128, intermediate
+6912) with a few layers and a small vocabulary, against the CPU oracle.
+
+What can be asserted at this shape.  Every linear layer quantises its input to int8 after an fp32
+RMSNorm; an fp32 sum that rounds one ulp differently moves an activation across a rounding boundary
+with probability of a few percent per 2560-vector, and one flipped activation perturbs the following
+quantisers enough to flip a few percent of theirs.  A random-init network of this width is chaotic
+under that: the reference's own two x86 builds (AVX-512 and AVX2 kernels: 16-lane and 8-lane sums),
+teacher-forced along the same tokens, differ by a median 0.28 in relative L2 of the logits and agree on
+55 % of the greedy choices; left to themselves they emit different tokens within the first five steps
+(on the toy model after 60-114 steps).  Bit-exact tokens are therefore asserted where the reference's
+builds agree with each other too (the toy fixtures of test_gpu_runtime.py); here the device is held to
+the band the reference's two builds keep between themselves, and to exactness where no activation has
+had a chance to flip yet.
+"""
+import importlib
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+rt = importlib.import_module("litespark_inference_b200.torchless.runtime")
+synthetic = importlib.import_module("litespark_inference_b200.torchless.synthetic")
+
+STEPS = 128
+PROMPT = 32
+MEDIAN_REL_L2_NO_REF = 0.35   # absolute fallback where the compiled reference kernels cannot run
+
+@pytest.fixture(scope="module")
+def shaped():
+    cfg = synthetic.bitnet_2b_config(num_layers=3, vocab_size=4096)
+    m = synthetic.random_model(cfg, seed=5, norm_jitter=0.1, fast=True)
+    return cfg, m, rt.to_device(m)
+
+
+def _rel_l2(got, want):
+    return float(np.linalg.norm(got - want) / np.linalg.norm(want - want.mean()))
+
+
+def _trajectory(oracle, kern, m, cfg, prompt, kv_dtype):
+    """The oracle's greedy tokens and the logits it saw before choosing each of them."""
+    toks, logits = oracle.generate(kern, m, prompt, STEPS, kv_dtype=kv_dtype, return_logits=True)
+    return [int(t) for t in toks], logits
+
+
+def _device_teacher_forced(dm, prompt, toks, kv):
+    st = rt.init_state(dm, len(prompt) + STEPS + 1, kv_dtype=kv)
+    out = [rt.forward_prefill(dm, st, prompt)]
+    for t in toks[:-1]:
+        out.append(rt.forward_one(dm, st, t))
+    return out
+
+
+def _agreement(logits, toks):
+    return sum(int(np.argmax(l)) == t for l, t in zip(logits, toks)) / len(toks)
+
+
+@pytest.mark.parametrize("kv", ["fp32", "fp16"])
+def test_error_band_is_the_reference_builds_own(shaped, oracle, port, kv):
+    """Teacher-forced over 128 decode steps, the device stays at least as close to the reference's AVX-512
+    arithmetic as the reference's AVX2 build does, in logits and in greedy choices."""
+    cfg, m, dm = shaped
+    np_kv = np.float32 if kv == "fp32" else np.float16
+    prompt = [int(t) for t in np.random.default_rng(2).integers(0, cfg.vocab_size, PROMPT)]
+    try:
+        k512, k2 = oracle.Kernels("ref", "avx512"), oracle.Kernels("ref", "avx2")
+    except (RuntimeError, OSError):
+        k512 = k2 = None
+    toks, want = _trajectory(oracle, k512 or port, m, cfg, prompt, np_kv)
+    got = _device_teacher_forced(dm, prompt, toks, kv)
+    err = float(np.median([_rel_l2(g, w) for g, w in zip(got, want)]))
+    if k2 is None:
+        assert err <= MEDIAN_REL_L2_NO_REF, f"device median error {err:.3e}"
+        return
+    st2 = oracle.State(cfg, len(prompt) + STEPS + 1, np_kv)
+    other = [oracle.forward_prefill(k2, m, st2, prompt)]
+    for t in toks[:-1]:
+        other.append(oracle.forward_one(k2, m, st2, t))
+    band = float(np.median([_rel_l2(o, w) for o, w in zip(other, want)]))
+    assert err <= band + 1e-3, f"device median error {err:.3e} vs the reference builds' own {band:.3e}"
+    assert _agreement(got, toks) >= _agreement(other, toks) - 0.1
+
+
+def test_first_positions_are_exact(shaped, oracle, port):
+    """Before any activation has had a chance to flip (one or two positions), logits agree to fp32 rounding."""
+    cfg, m, dm = shaped
+    prompt = [int(t) for t in np.random.default_rng(3).integers(0, cfg.vocab_size, 2)]
+    st, ost = rt.init_state(dm, 8, kv_dtype="fp32"), oracle.State(cfg, 8)
+    for t in prompt:
+        got, want = rt.forward_one(dm, st, t), oracle.forward_one(port, m, ost, t)
+        assert _rel_l2(got, want) <= 1e-5

@@ -130,7 +130,7 @@ def test_dropin_registered_weights_and_errors():
 
 # ---- device-resident linear: BitNet-2B shapes, every token count of the sweep ------------------
 @pytest.mark.parametrize("name", ["q", "k", "gate", "down"])
-@pytest.mark.parametrize("M", [1, 2, 3, 8, 32, 128, 512])
+@pytest.mark.parametrize("M", [1, 2, 3, 8, 20, 32, 128, 512])
 def test_linear_int32_bit_exact_at_model_shapes(port, name, M):
     N, Kd = SHAPES[name]
     w, packed, x, ws = _rand_case(sum(map(ord, name)) * 1000 + M, N, Kd, M)
@@ -256,6 +256,37 @@ def test_device_row_helpers_and_lm_head_rows(port):
     wq, wsc = np.empty((T, Kd), np.int8), np.empty(T, np.float32)
     port.quantize_activation_batched(x, wq, wsc)
     assert np.array_equal(xq.numpy(), wq) and np.array_equal(xs.numpy(), wsc)
+
+
+@pytest.mark.parametrize("kind,T", [(0, 2), (0, 11), (0, 16), (1, 3), (1, 9), (2, 4), (2, 16)])
+def test_lm_head_many_rows_all_formats(port, kind, T):
+    """Several rows of x: each warp holds a few table rows (reuse of the x values it fetched), more than
+    eight rows take two passes; the vocabulary size is not a multiple of the rows a CTA covers."""
+    rng = np.random.default_rng(40 + kind * 17 + T)
+    Kd, V = 2560, 1001
+    lib = K.load_library()
+    x = rng.standard_normal((T, Kd)).astype(np.float32)
+    dx = dev.DeviceArray.from_numpy(x)
+    dl = dev.DeviceArray((T, V), np.float32)
+    if kind == 0:
+        emb = synthetic.fp32_to_bf16_u16(rng.standard_normal((V, Kd)).astype(np.float32))
+        de = dev.DeviceArray.from_numpy(emb)
+        K.check(lib.lspk_lm_head(0, de.ptr, None, dx.ptr, dl.ptr, T, V, Kd))
+        want = np.stack([port.lm_head_bf16(emb, np.ascontiguousarray(x[t]), np.empty(V, np.float32)) for t in range(T)])
+        mag = 4.0
+    else:
+        sc = rng.uniform(0.005, 0.02, V).astype(np.float32)
+        if kind == 1:
+            emb = rng.integers(-127, 128, (V, Kd), dtype=np.int8)
+            want = np.stack([port.lm_head_int8(emb, sc, np.ascontiguousarray(x[t]), np.empty(V, np.float32)) for t in range(T)])
+            mag = 127 * 0.02
+        else:
+            emb = rng.integers(0, 256, (V, Kd // 2), dtype=np.uint8)
+            want = np.stack([port.lm_head_int4(emb, sc, np.ascontiguousarray(x[t]), np.empty(V, np.float32), Kd) for t in range(T)])
+            mag = 8 * 0.02
+        de, dsc = dev.DeviceArray.from_numpy(emb), dev.DeviceArray.from_numpy(sc)
+        K.check(lib.lspk_lm_head(kind, de.ptr, dsc.ptr, dx.ptr, dl.ptr, T, V, Kd))
+    assert np.allclose(dl.numpy(), want, rtol=1e-5, atol=4e-7 * mag * np.abs(x).sum(axis=1).max())
 
 
 # ---- tensor-core (tcgen05) path ------------------------------------------------------------------
