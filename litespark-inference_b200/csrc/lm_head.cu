@@ -8,6 +8,8 @@
 //
 // Replaces lm_head_bf16_fp32 / lm_head_int8_fp32 / lm_head_int4_fp32
 // (matmul_lut_avx512_extern_c.cpp:470-498, 501-525, 535-587).
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace lspk {
@@ -188,7 +190,7 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     const int E = kind == 0 ? 8 : kind == 1 ? 16 : 32;
     LSPK_REQUIRE(H % E == 0, "lm_head: H=%d must be a multiple of %d for this embedding format", H, E);
     LSPK_REQUIRE(((uintptr_t)emb & 15) == 0, "lm_head: embedding must be 16-byte aligned");
-    const int rows_per_cta = kLmWarps * (T == 1 ? 1 : kind == 0 ? 4 : 2);   // RW of the instantiation chosen below
+    const int rows_per_cta = kLmWarps;
     int grid = (V + rows_per_cta - 1) / rows_per_cta;
     const int cap = sm_count() * 4;
     if (grid > cap) grid = cap;
@@ -218,7 +220,10 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
             else if (kind == 1) LSPK_LM_LAUNCH(1, 1, 5, 1);
             else LSPK_LM_LAUNCH(2, 1, 3, 1);
         } else {
-            if (kind == 0) LSPK_LM_LAUNCH(0, kLmMaxT, 3, 4);
+            // measured at V = 128256, H = 2560, 8 rows (loads in flight, table rows per warp): (4,1) 396 us,
+            // (4,2) 315, (3,4) 482, (6,2) 514, (2,4) 255: with eight rows the kernel is bound by its
+            // fused multiply-adds and registers, not by loads in flight
+            if (kind == 0) LSPK_LM_LAUNCH(0, kLmMaxT, 2, 4);
             else if (kind == 1) LSPK_LM_LAUNCH(1, kLmMaxT, 2, 2);
             else LSPK_LM_LAUNCH(2, kLmMaxT, 1, 2);
         }
