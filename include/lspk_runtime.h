@@ -36,6 +36,9 @@ enum { LSPK_NORM_INPUT = 0, LSPK_NORM_POST_ATTN, LSPK_NORM_ATTN_SUB, LSPK_NORM_F
 lspk_model_t lspk_model_create(const lspk_model_config* cfg);
 int lspk_model_set_projection(lspk_model_t m, int layer, int which, const uint8_t* packed_host,
                               int N, int K, float scale);
+/* Same from bf16 master weights, ternarised on the device (lspk_upload_bf16_ternary). */
+int lspk_model_set_projection_bf16(lspk_model_t m, int layer, int which, const uint16_t* w_bf16_host,
+                                   int N, int K, double absmean);
 int lspk_model_set_norm(lspk_model_t m, int layer, int which, const void* gamma_host, int is_bf16, int K);
 /* kind: 0 bf16 bits [V,H], 1 int8 [V,H] + scale[V], 2 int4 [V,H/2] + scale[V].  The same table is
  * the LM head unless lspk_model_set_lm_head supplies an untied one. */

@@ -81,6 +81,12 @@ int lspk_trace_read(unsigned long long* host_out, int max_records, int* n_out);
 /* ------------------------------------------------------------------------------------ */
 typedef struct lspk_weight_s* lspk_weight_t;
 lspk_weight_t lspk_upload_packed(const uint8_t* packed_host, int N, int K, float w_scale);
+/* The load-time quantiser on the device (quantize_ternary_absmean, torchless/quantize.py:24-60, then
+ * pack_ternary_4_per_byte, pack.py:16-45): bf16 master weights [N, K] are ternarised with
+ * t = clip(rint(w * float32(1 / absmean)), -1, 1), packed and re-tiled without leaving the GPU.  absmean
+ * = mean |W| is computed by the host in the reference's summation order and passed in as a double;
+ * the handle's scale is float32(absmean). */
+lspk_weight_t lspk_upload_bf16_ternary(const uint16_t* w_bf16_host, int N, int K, double absmean);
 int lspk_download_packed(lspk_weight_t w, uint8_t* packed_host_out);   /* exact inverse   */
 int lspk_weight_free(lspk_weight_t w);
 int lspk_weight_shape(lspk_weight_t w, int* N, int* K, float* scale, size_t* device_bytes);

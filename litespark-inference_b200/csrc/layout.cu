@@ -57,6 +57,27 @@ cudaError_t retile_to_device_launch(const uint8_t* src_dev, uint4* dst_dev, int 
     return cudaGetLastError();
 }
 
+
+// bf16 master weights [N, K] (row-major) -> ternary codes, four per byte in the reference layout
+// [N, K/4].  t = clip(rint(w * inv), -1, 1) with rint = round-half-even, as the reference's host
+// quantiser does in fp32 (quantize.py:24-60); code = t + 1.  K is a multiple of 4, so a byte never
+// straddles two rows and the kernel is a flat map over bytes.
+__global__ void ternarize_pack_kernel(const uint16_t* __restrict__ w, uint8_t* __restrict__ packed, long long n_bytes,
+                                      float inv) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n_bytes; i += (long long)gridDim.x * blockDim.x) {
+        const uint2 four = *reinterpret_cast<const uint2*>(w + 4 * i);
+        const float f[4] = {__uint_as_float(four.x << 16), __uint_as_float(four.x & 0xffff0000u),
+                            __uint_as_float(four.y << 16), __uint_as_float(four.y & 0xffff0000u)};
+        uint32_t byte = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float t = fminf(fmaxf(rintf(__fmul_rn(f[e], inv)), -1.0f), 1.0f);
+            byte |= (uint32_t)((int)t + 1) << (2 * e);
+        }
+        packed[i] = (uint8_t)byte;
+    }
+}
+
 }  // namespace lspk
 
 using namespace lspk;
@@ -94,6 +115,57 @@ lspk_weight_t lspk_upload_packed(const uint8_t* packed_host, int N, int K, float
     if (staging) cudaFree(staging);
     if (e != cudaSuccess) {
         fail(LSPK_ERR_CUDA, "lspk_upload_packed: %s", cudaGetErrorString(e));
+        if (w->dev) cudaFree(w->dev);
+        delete w;
+        return nullptr;
+    }
+    return reinterpret_cast<lspk_weight_t>(w);
+}
+
+lspk_weight_t lspk_upload_bf16_ternary(const uint16_t* w_bf16_host, int N, int K, double absmean) {
+    if (ensure_init()) return nullptr;
+    if (!w_bf16_host || N <= 0 || K <= 0 || (K & 3) || !(absmean > 0.0)) {
+        fail(LSPK_ERR_ARG, "lspk_upload_bf16_ternary: need N > 0, K > 0, K %% 4 == 0, absmean > 0 (got N=%d K=%d)", N, K);
+        return nullptr;
+    }
+    // the reference multiplies fp32 weights by float32(1 / absmean) and hands float32(absmean) to its kernels
+    const float inv = (float)(1.0 / absmean);
+    const float scale = (float)absmean;
+    const int Kb = K / 4;
+    Weight* w = new Weight();
+    w->N = N;
+    w->K = K;
+    w->groups = (N + kRowsPerGroup - 1) / kRowsPerGroup;
+    w->chunks = (K + kWeightsPerChunk - 1) / kWeightsPerChunk;
+    w->scale = scale;
+    w->bytes = (size_t)w->groups * w->chunks * kRowsPerGroup * 16;
+    w->dev = nullptr;
+    uint16_t* master = nullptr;
+    uint8_t* staging = nullptr;
+    cudaError_t e = cudaMalloc(&w->dev, w->bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&master, (size_t)N * K * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&staging, (size_t)N * Kb);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(master, w_bf16_host, (size_t)N * K * 2, cudaMemcpyHostToDevice, stream());
+    if (e == cudaSuccess) {
+        const long long n_bytes = (long long)N * Kb;
+        const int block = 256;
+        long long g = (n_bytes + block - 1) / block;
+        const long long cap = (long long)sm_count() * 16;
+        ternarize_pack_kernel<<<(int)(g < cap ? g : cap), block, 0, stream()>>>(master, staging, n_bytes, inv);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) {
+        const long long total = (long long)w->groups * w->chunks * kRowsPerGroup;
+        const int block = 256;
+        const int grid = (int)((total + block - 1) / block < 65535 ? (total + block - 1) / block : 65535);
+        retile_to_device_kernel<<<grid, block, 0, stream()>>>(staging, w->dev, N, Kb, w->groups, w->chunks);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream());
+    if (master) cudaFree(master);
+    if (staging) cudaFree(staging);
+    if (e != cudaSuccess) {
+        fail(LSPK_ERR_CUDA, "lspk_upload_bf16_ternary: %s", cudaGetErrorString(e));
         if (w->dev) cudaFree(w->dev);
         delete w;
         return nullptr;

@@ -456,6 +456,26 @@ int lspk_model_set_projection(lspk_model_t h, int layer, int which, const uint8_
     return LSPK_OK;
 }
 
+int lspk_model_set_projection_bf16(lspk_model_t h, int layer, int which, const uint16_t* w_bf16_host, int N, int K,
+                                   double absmean) {
+    LSPK_REQUIRE(h, "lspk_model_set_projection_bf16: null model");
+    Model* m = reinterpret_cast<Model*>(h);
+    LSPK_REQUIRE(layer >= 0 && layer < m->cfg.num_layers && which >= 0 && which < 7,
+                 "lspk_model_set_projection_bf16: layer/which out of range");
+    const int H = m->cfg.hidden_size, I = m->cfg.intermediate_size, kv = m->kv_dim();
+    const int wantN[7] = {H, kv, kv, H, I, I, H};
+    const int wantK[7] = {H, H, H, H, H, H, I};
+    LSPK_REQUIRE(N == wantN[which] && K == wantK[which], "lspk_model_set_projection_bf16: shape %dx%d, expected %dx%d",
+                 N, K, wantN[which], wantK[which]);
+    lspk_weight_t w = lspk_upload_bf16_ternary(w_bf16_host, N, K, absmean);
+    if (!w) return LSPK_ERR_CUDA;
+    DevLayer& L = m->layers[layer];
+    if (L.proj[which]) lspk_weight_free(L.proj[which]);
+    L.proj[which] = w;
+    m->bytes += reinterpret_cast<Weight*>(w)->bytes;
+    return LSPK_OK;
+}
+
 int lspk_model_set_norm(lspk_model_t h, int layer, int which, const void* gamma_host, int is_bf16, int K) {
     LSPK_REQUIRE(h && gamma_host, "lspk_model_set_norm: null argument");
     Model* m = reinterpret_cast<Model*>(h);

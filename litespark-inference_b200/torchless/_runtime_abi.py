@@ -13,6 +13,7 @@ class ModelConfig(ctypes.Structure):
 SIGNATURES = {
     "lspk_model_create": ([ctypes.POINTER(ModelConfig)], _vp),
     "lspk_model_set_projection": ([_vp, _ci, _ci, _vp, _ci, _ci, _cf], _ci),
+    "lspk_model_set_projection_bf16": ([_vp, _ci, _ci, _vp, _ci, _ci, ctypes.c_double], _ci),
     "lspk_model_set_norm": ([_vp, _ci, _ci, _vp, _ci, _ci], _ci),
     "lspk_model_set_embedding": ([_vp, _ci, _vp, _vp], _ci),
     "lspk_model_set_lm_head": ([_vp, _ci, _vp, _vp], _ci),

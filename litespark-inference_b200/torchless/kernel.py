@@ -80,6 +80,7 @@ _SIGNATURES = {
     "lspk_timer_start": ([], _ci),
     "lspk_timer_stop": ([ctypes.POINTER(_cf)], _ci),
     "lspk_upload_packed": ([_U8, _ci, _ci, _cf], _vp),
+    "lspk_upload_bf16_ternary": ([_vp, _ci, _ci, ctypes.c_double], _vp),
     "lspk_download_packed": ([_vp, _U8], _ci),
     "lspk_weight_free": ([_vp], _ci),
     "lspk_weight_shape": ([_vp, ctypes.POINTER(_ci), ctypes.POINTER(_ci), ctypes.POINTER(_cf),

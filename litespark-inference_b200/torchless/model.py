@@ -29,11 +29,14 @@ class BitNetConfig:
 class PackedProjection:
     """One ternary projection: uint8 [N, ceil(K/4)] packed weights + per-tensor scale
     (reference model.py:26-49)."""
-    w_packed: np.ndarray
+    w_packed: Optional[np.ndarray]
     w_sum: Optional[np.ndarray]
     scale: float
     in_features: int
     out_features: int
+    # bf16 master weights (uint16 bits, [N, K]) of a projection that is ternarised on the device at
+    # upload instead of on the host: w_packed is then None and scale is mean |W| as a Python float
+    w_bf16: Optional[np.ndarray] = None
 
 
 @dataclass

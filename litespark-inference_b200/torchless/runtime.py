@@ -48,6 +48,12 @@ class DeviceModel:
         for li, L in enumerate(host_model.layers):
             for wi, name in enumerate(_PROJ):
                 p = getattr(L, name)
+                if p.w_packed is None:
+                    # bf16 master weights: ternarise, pack and re-tile on the device
+                    w = np.ascontiguousarray(p.w_bf16, dtype=np.uint16)
+                    _k.check(lib.lspk_model_set_projection_bf16(h, li, wi, _ptr(w), p.out_features, p.in_features,
+                                                                float(p.scale)))
+                    continue
                 w = np.ascontiguousarray(p.w_packed)
                 _k.check(lib.lspk_model_set_projection(h, li, wi, _ptr(w), p.out_features, p.in_features,
                                                        float(np.float32(p.scale))))
@@ -250,21 +256,34 @@ def generate(model, prompt_token_ids, max_new_tokens: int, state: Optional[Infer
     if max_new_tokens <= 0:
         forward_prefill(model, state, prompt)
         return []
-    ids = np.ascontiguousarray(prompt, dtype=np.int32)
+    return decode_greedy(state, prefill_first_token(state, prompt), max_new_tokens)
+
+
+def prefill_first_token(state: InferState, prompt_token_ids, seq: int = 0) -> int:
+    """Batched prefill of the prompt; returns the greedy choice after it (first maximum), computed on
+    the device -- the logits never leave it."""
+    ids = np.ascontiguousarray(list(prompt_token_ids), dtype=np.int32)
     first = np.empty(1, dtype=np.int32)
-    rc = state.lib.lspk_forward_prefill(state.handle, 0, _ptr(ids), int(ids.size), None, None, _ptr(first))
+    rc = state.lib.lspk_forward_prefill(state.handle, seq, _ptr(ids), int(ids.size), None, None, _ptr(first))
     if rc:
         _raise_state(state.lib, rc)
-    out = [int(first[0])]
+    return int(first[0])
+
+
+def decode_greedy(state: InferState, first_token: int, max_new_tokens: int) -> list:
+    """The greedy ids starting with ``first_token`` (already chosen after the prefill): the decode loop
+    runs on the device, the argmax of each step feeding the next, and the ids come back in one copy."""
+    out = [int(first_token)]
     if max_new_tokens > 1:
         # the reference's loop also runs a forward for the last generated token; only its cache
         # write is observable, and it does not change the returned ids, so stop one step earlier
+        first = np.array([first_token], dtype=np.int32)
         toks = np.empty(max_new_tokens - 1, dtype=np.int32)
         rc = state.lib.lspk_decode_greedy(state.handle, _ptr(first), max_new_tokens - 1, _ptr(toks))
         if rc:
             _raise_state(state.lib, rc)
         out.extend(int(t) for t in toks)
-    return out
+    return out[:max(max_new_tokens, 0)]
 
 
 def generate_batch(model, prompts, max_new_tokens: int, kv_dtype: Optional[str] = None) -> list:

@@ -80,3 +80,30 @@ def toy_config(hidden=256, layers=2, heads=4, kv_heads=2, inter=512, vocab=1024)
     return BitNetConfig(hidden_size=hidden, num_layers=layers, num_heads=heads, num_kv_heads=kv_heads,
                         intermediate_size=inter, vocab_size=vocab, max_position_embeddings=4096,
                         rms_norm_eps=1e-5, rope_theta=500000.0)
+
+
+def random_checkpoint_tensors(cfg: BitNetConfig, seed: int = 0) -> dict:
+    """Random bf16 MASTER weights of a BitNet checkpoint under their Hugging Face tensor names (uint16 bits):
+    what ``loader.save_bitnet_dir`` writes and ``loader.load_bitnet_dir`` quantises."""
+    rng = np.random.default_rng(seed)
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    kv = cfg.num_kv_heads * (H // cfg.num_heads)
+
+    def bf16(shape, std=0.02):
+        return fp32_to_bf16_u16((rng.standard_normal(shape) * std).astype(np.float32))
+
+    def gamma(n):
+        return fp32_to_bf16_u16(rng.uniform(0.9, 1.1, n).astype(np.float32))
+
+    t = {"model.embed_tokens.weight": bf16((cfg.vocab_size, H), 1.0), "model.norm.weight": gamma(H)}
+    shapes = {".self_attn.q_proj.weight": (H, H), ".self_attn.k_proj.weight": (kv, H), ".self_attn.v_proj.weight": (kv, H),
+              ".self_attn.o_proj.weight": (H, H), ".mlp.gate_proj.weight": (I, H), ".mlp.up_proj.weight": (I, H),
+              ".mlp.down_proj.weight": (H, I)}
+    norms = {".input_layernorm.weight": H, ".post_attention_layernorm.weight": H,
+             ".self_attn.attn_sub_norm.weight": H, ".mlp.ffn_sub_norm.weight": I}
+    for i in range(cfg.num_layers):
+        for suf, shape in shapes.items():
+            t[f"model.layers.{i}{suf}"] = bf16(shape)
+        for suf, n in norms.items():
+            t[f"model.layers.{i}{suf}"] = gamma(n)
+    return t

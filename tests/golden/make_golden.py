@@ -154,6 +154,16 @@ def gen_host():
     out["q_in"] = wb16
     out["q_ternary"] = t
     out["q_scale"] = np.float64(s)
+    # embedding quantisers of the reference's loader (loader.py:153-219) on a small bf16 table, with a row
+    # block smaller than the table so that the block loop is exercised
+    import importlib
+    loader = importlib.import_module("litespark_inference.torchless.loader")
+    e32 = rng.standard_normal((70, 48)).astype(np.float32)
+    e32[5] = 0.0                                            # an all-zero row takes the 1e-5 floor
+    e16 = (e32.view(np.uint32) >> 16).astype(np.uint16)
+    out["emb_in"] = e16
+    out["emb_int8"], out["emb_int8_scale"] = loader._quantize_embedding_int8(e16, row_block=32)
+    out["emb_int4"], out["emb_int4_scale"] = loader._quantize_embedding_int4(e16, row_block=32)
     cos, sin = ops.rope_tables(128, 300, 500000.0)
     out["rope_cos128"] = cos
     out["rope_sin128"] = sin
