@@ -179,6 +179,156 @@ lm_head_kernel(const uint4* __restrict__ emb, const float* __restrict__ emb_scal
     }
 }
 
+// ---- several rows of x against a bf16 table on the warp-level tensor cores -------------------------
+// With 2..16 rows of x the CUDA-core kernel above is bound by its fused multiply-adds (V * H * T of them)
+// and by shared-memory reads of x.  Here a warp owns 16 table rows (the MMA's M side), the rows of x are
+// the N side (one or two tiles of eight), and the table bytes go from global memory straight into A
+// fragments: lane (g, t) loads 16 bytes of row g and of row g + 8 per 32-wide K step; which eight k's a
+// lane holds is a permutation of K that the x fragments repeat, so no shuffle is needed.
+// x stays fp32-exact: it is split into three bf16 terms (x = hi + mid + lo up to 2^-24 |x|), each product
+// bf16 x bf16 is exact in the fp32 accumulator, so the result differs from the fp32 dot product only in
+// summation order, like every other reduction here.
+constexpr int kLmmStepsInFlight = 6;      // 32-wide K steps of table data in flight per lane (12 x 16 bytes)
+
+__device__ __forceinline__ void mma_bf16_16816(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t bf16_rn_bits(float v) {          // round to nearest even, as a 16-bit pattern
+    const uint32_t u = __float_as_uint(v);
+    return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+}
+
+// NT: tiles of eight rows of x (1 or 2).  Shared memory: [3 terms][8 * NT rows][H + 32] bf16.
+template <int NT>
+__global__ void __launch_bounds__(kLmThreads)
+lm_head_mma_kernel(const uint4* __restrict__ emb, const float* __restrict__ x, float* __restrict__ logits, int T, int V,
+                   int H, const void* __restrict__ norm_gamma, int gamma_is_bf16, float eps) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);
+    __shared__ float red[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    constexpr int R = 8 * NT;
+    const int ld = H + 32;                                 // row stride in bf16: 64 bytes of padding make the quarter-warp 16-byte loads conflict-free
+    const int steps = H / 32;                              // host guarantees H % 32 == 0
+    const size_t row_chunks = (size_t)H / 8;
+
+    // table rows of this warp's first tile can be requested before the activations exist
+    auto tile_of = [&](int i) { return (blockIdx.x * kLmWarps + warp) + i * gridDim.x * kLmWarps; };
+    uint4 buf[kLmmStepsInFlight][2];
+    auto request = [&](int v0, int s0) {
+#pragma unroll
+        for (int u = 0; u < kLmmStepsInFlight; ++u) {
+            const int sidx = s0 + u;
+            if (sidx < steps) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int v = v0 + g + 8 * hh;
+                    buf[u][hh] = v < V ? __ldcs(emb + (size_t)v * row_chunks + (size_t)sidx * 4 + t4) : make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+    };
+    int tile = tile_of(0);
+    if (tile * 16 < V) request(tile * 16, 0);
+
+    grid_dependency_launch();
+    grid_dependency_wait();
+
+    // rows of x (optionally RMS-normalised) -> three bf16 terms in shared memory
+    for (int r = 0; r < R; ++r) {
+        if (r < T) {
+            const float* xr = x + (size_t)r * H;
+            float rrms = 1.0f;
+            if (norm_gamma) {
+                float ssq = 0.0f;
+                for (int k = tid; k < H; k += kLmThreads) ssq = fmaf(xr[k], xr[k], ssq);
+                ssq = block_sum(ssq, red);
+                rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)H), eps)));
+            }
+            for (int k = tid; k < H; k += kLmThreads) {
+                float v = xr[k];
+                if (norm_gamma) {
+                    const float gm = gamma_is_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(norm_gamma)[k])
+                                                   : reinterpret_cast<const float*>(norm_gamma)[k];
+                    v = __fmul_rn(__fmul_rn(v, rrms), gm);
+                }
+                const uint32_t hi = bf16_rn_bits(v);
+                const float r1 = v - __uint_as_float(hi << 16);
+                const uint32_t mid = bf16_rn_bits(r1);
+                const float r2 = r1 - __uint_as_float(mid << 16);
+                const uint32_t lo = bf16_rn_bits(r2);
+                xs[(size_t)(0 * R + r) * ld + k] = (uint16_t)hi;
+                xs[(size_t)(1 * R + r) * ld + k] = (uint16_t)mid;
+                xs[(size_t)(2 * R + r) * ld + k] = (uint16_t)lo;
+            }
+        } else {
+            for (int k = tid; k < H; k += kLmThreads) {
+                xs[(size_t)(0 * R + r) * ld + k] = 0;
+                xs[(size_t)(1 * R + r) * ld + k] = 0;
+                xs[(size_t)(2 * R + r) * ld + k] = 0;
+            }
+        }
+    }
+    __syncthreads();
+
+    for (int it = 0; tile * 16 < V; ++it) {
+        const int v0 = tile * 16;
+        float acc[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[n][c] = 0.0f;
+        for (int s0 = 0; s0 < steps; s0 += kLmmStepsInFlight) {
+            uint4 cur[kLmmStepsInFlight][2];
+#pragma unroll
+            for (int u = 0; u < kLmmStepsInFlight; ++u) {
+                cur[u][0] = buf[u][0];
+                cur[u][1] = buf[u][1];
+            }
+            // next batch of this tile, or the first batch of the next tile, goes out before the math
+            if (s0 + kLmmStepsInFlight < steps) {
+                request(v0, s0 + kLmmStepsInFlight);
+            } else {
+                const int nt = tile_of(it + 1);
+                if (nt * 16 < V) request(nt * 16, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < kLmmStepsInFlight; ++u) {
+                const int sidx = s0 + u;
+                if (sidx < steps) {
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                        for (int term = 0; term < 3; ++term) {
+                            // this lane's B data: token row (8 n + g), k = 32 sidx + 8 t4 .. + 7
+                            const uint4 b = *reinterpret_cast<const uint4*>(
+                                xs + (size_t)(term * R + 8 * n + g) * ld + (size_t)sidx * 32 + t4 * 8);
+                            mma_bf16_16816(acc[n], cur[u][0].x, cur[u][1].x, cur[u][0].y, cur[u][1].y, b.x, b.y);
+                            mma_bf16_16816(acc[n], cur[u][0].z, cur[u][1].z, cur[u][0].w, cur[u][1].w, b.z, b.w);
+                        }
+                    }
+                }
+            }
+        }
+        // C fragment: c0, c1 = (table row g, tokens 2 t4, 2 t4 + 1), c2, c3 = (table row g + 8, same tokens)
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int v = v0 + g + 8 * (c >> 1);
+                const int tok = 8 * n + 2 * t4 + (c & 1);
+                if (v < V && tok < T) logits[(size_t)tok * V + v] = acc[n][c];
+            }
+        tile = tile_of(it + 1);
+    }
+}
+
 // norm_gamma / best_key may be null.  T <= kLmMaxT per launch; larger T is tiled here.
 int lm_head_launch(int kind, const void* emb, const float* emb_scale, const float* x, float* logits,
                    int T, int V, int H, const void* norm_gamma, int gamma_is_bf16, float eps,
@@ -195,6 +345,38 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     const int cap = sm_count() * 4;
     if (grid > cap) grid = cap;
     const uint4* e4 = reinterpret_cast<const uint4*>(emb);
+    static const int knob_mma = getenv("LSPK_LM_MMA") ? atoi(getenv("LSPK_LM_MMA")) : 1;
+    if (knob_mma && kind == 0 && T > 1 && H % 32 == 0 && logits && !best_key) {
+        // several rows against the bf16 table: tensor-core kernel, up to sixteen rows per pass
+        // sixteen rows per pass where their three bf16 terms fit the shared memory (H <= 2100), else eight
+        const int per_pass = ((size_t)3 * 16 * (H + 32) * 2 <= 200 * 1024 && T > 8) ? 16 : 8;
+        for (int t0 = 0; t0 < T; t0 += per_pass) {
+            const int tt = (T - t0) < per_pass ? (T - t0) : per_pass;
+            const int nt = tt > 8 ? 2 : 1;
+            const size_t smem = (size_t)3 * 8 * nt * (H + 32) * 2;
+            LSPK_REQUIRE(smem <= 200 * 1024, "lm_head: H=%d too large for %d rows", H, tt);
+            int mgrid = (V + 16 * kLmWarps - 1) / (16 * kLmWarps);
+            const int mcap = sm_count();
+            if (mgrid > mcap) mgrid = mcap;
+            static bool attr1 = false, attr2 = false;
+            cudaError_t e = cudaSuccess;
+            if (nt == 1) {
+                if (!attr1) e = cudaFuncSetAttribute(lm_head_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                attr1 = attr1 || e == cudaSuccess;
+                if (e == cudaSuccess)
+                    e = launch(lm_head_mma_kernel<1>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x + (size_t)t0 * H,
+                               logits + (size_t)t0 * V, tt, V, H, norm_gamma, gamma_is_bf16, eps);
+            } else {
+                if (!attr2) e = cudaFuncSetAttribute(lm_head_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                attr2 = attr2 || e == cudaSuccess;
+                if (e == cudaSuccess)
+                    e = launch(lm_head_mma_kernel<2>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x + (size_t)t0 * H,
+                               logits + (size_t)t0 * V, tt, V, H, norm_gamma, gamma_is_bf16, eps);
+            }
+            if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head (mma) launch failed: %s", cudaGetErrorString(e));
+        }
+        return LSPK_OK;
+    }
     for (int t0 = 0; t0 < T; t0 += kLmMaxT) {
         const int tt = (T - t0) < kLmMaxT ? (T - t0) : kLmMaxT;
         const size_t smem = (size_t)tt * H * sizeof(float);
