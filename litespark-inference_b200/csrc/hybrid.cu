@@ -57,9 +57,11 @@ static int enqueue_hybrid_step(HybridState* s) {
         if (int rc = lm_head_launch(0, m->emb, nullptr, s->x, s->logits, 1, m->V, m->H, m->final_norm, 1, m->eps, s->best))
             return rc;
     } else {
-        if (int rc = lm_head_launch(0, m->emb, nullptr, s->x, s->logits, B, m->V, m->H, m->final_norm, 1, m->eps, nullptr))
+        // several sequences: the LM head returns each row's greedy choice itself (logits only where its
+        // tensor-core form does not apply and a row argmax has to read them)
+        if (int rc = lm_head_launch(0, m->emb, nullptr, s->x, (m->H % 32) ? s->logits : nullptr, B, m->V, m->H,
+                                    m->final_norm, 1, m->eps, s->best))
             return rc;
-        if (int rc = launch_argmax_rows(s->logits, B, m->V, s->best)) return rc;
     }
     return launch_finish_step(s->ctl, s->best, s->tokens_out, B, s->max_steps);
 }

@@ -10,7 +10,7 @@
 // (matmul_lut_avx512_extern_c.cpp:470-498, 501-525, 535-587).
 #include <stdlib.h>
 
-#include "common.cuh"
+#include "internal.cuh"
 
 namespace lspk {
 
@@ -207,10 +207,15 @@ __device__ __forceinline__ uint32_t bf16_rn_bits(float v) {          // round to
 template <int NT>
 __global__ void __launch_bounds__(kLmThreads)
 lm_head_mma_kernel(const uint4* __restrict__ emb, const float* __restrict__ x, float* __restrict__ logits, int T, int V,
-                   int H, const void* __restrict__ norm_gamma, int gamma_is_bf16, float eps) {
+                   int H, const void* __restrict__ norm_gamma, int gamma_is_bf16, float eps,
+                   unsigned long long* __restrict__ best_keys) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);
     __shared__ float red[32];
+    __shared__ unsigned long long s_best[kLmWarps][8 * NT];
+    unsigned long long best[NT][2];                          // greedy argmax keys of tokens 8 n + 2 t4 + {0, 1}
+#pragma unroll
+    for (int n = 0; n < NT; ++n) best[n][0] = best[n][1] = 0ull;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     constexpr int R = 8 * NT;
@@ -323,17 +328,45 @@ lm_head_mma_kernel(const uint4* __restrict__ emb, const float* __restrict__ x, f
             for (int c = 0; c < 4; ++c) {
                 const int v = v0 + g + 8 * (c >> 1);
                 const int tok = 8 * n + 2 * t4 + (c & 1);
-                if (v < V && tok < T) logits[(size_t)tok * V + v] = acc[n][c];
+                if (v < V && tok < T) {
+                    if (logits) logits[(size_t)tok * V + v] = acc[n][c];
+                    const unsigned long long key = argmax_key(acc[n][c], v);
+                    best[n][c & 1] = key > best[n][c & 1] ? key : best[n][c & 1];
+                }
             }
         tile = tile_of(it + 1);
     }
+    if (best_keys) {
+        // lanes with the same t4 hold the same tokens: combine over g, then over the warps, one atomic per token
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                unsigned long long k = best[n][e];
+#pragma unroll
+                for (int o = 4; o < 32; o <<= 1) {
+                    const unsigned long long other = __shfl_xor_sync(0xffffffffu, k, o);
+                    k = other > k ? other : k;
+                }
+                if (g == 0) s_best[warp][8 * n + 2 * t4 + e] = k;
+            }
+        __syncthreads();
+        if (tid < 8 * NT && tid < T) {
+            unsigned long long k = s_best[0][tid];
+#pragma unroll
+            for (int w = 1; w < kLmWarps; ++w) k = s_best[w][tid] > k ? s_best[w][tid] : k;
+            atomicMax(best_keys + tid, k);
+        }
+    }
 }
 
-// norm_gamma / best_key may be null.  T <= kLmMaxT per launch; larger T is tiled here.
+// norm_gamma / best_key may be null; best_key points at T keys (one greedy argmax per row of x, combined with
+// atomicMax: the caller clears them).  Larger T is tiled here.
 int lm_head_launch(int kind, const void* emb, const float* emb_scale, const float* x, float* logits,
                    int T, int V, int H, const void* norm_gamma, int gamma_is_bf16, float eps,
                    unsigned long long* best_key) {
     if (int rc = ensure_init()) return rc;
+    unsigned long long* const best_key_in = best_key;
     LSPK_REQUIRE(emb && x && T >= 1 && V >= 1 && H >= 1, "lm_head: bad arguments");
     LSPK_REQUIRE(kind >= 0 && kind <= 2, "lm_head: kind must be 0 (bf16), 1 (int8) or 2 (int4)");
     LSPK_REQUIRE(kind == 0 || emb_scale, "lm_head: int8/int4 need emb_scale");
@@ -346,7 +379,7 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     if (grid > cap) grid = cap;
     const uint4* e4 = reinterpret_cast<const uint4*>(emb);
     static const int knob_mma = getenv("LSPK_LM_MMA") ? atoi(getenv("LSPK_LM_MMA")) : 1;
-    if (knob_mma && kind == 0 && T > 1 && H % 32 == 0 && logits && !best_key) {
+    if (knob_mma && kind == 0 && T > 1 && H % 32 == 0 && (logits || best_key)) {
         // several rows against the bf16 table: tensor-core kernel, up to sixteen rows per pass
         // sixteen rows per pass where their three bf16 terms fit the shared memory (H <= 2100), else eight
         const int per_pass = ((size_t)3 * 16 * (H + 32) * 2 <= 200 * 1024 && T > 8) ? 16 : 8;
@@ -365,18 +398,25 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
                 attr1 = attr1 || e == cudaSuccess;
                 if (e == cudaSuccess)
                     e = launch(lm_head_mma_kernel<1>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x + (size_t)t0 * H,
-                               logits + (size_t)t0 * V, tt, V, H, norm_gamma, gamma_is_bf16, eps);
+                               logits ? logits + (size_t)t0 * V : (float*)nullptr, tt, V, H, norm_gamma, gamma_is_bf16, eps,
+                               best_key ? best_key + t0 : (unsigned long long*)nullptr);
             } else {
                 if (!attr2) e = cudaFuncSetAttribute(lm_head_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
                 attr2 = attr2 || e == cudaSuccess;
                 if (e == cudaSuccess)
                     e = launch(lm_head_mma_kernel<2>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x + (size_t)t0 * H,
-                               logits + (size_t)t0 * V, tt, V, H, norm_gamma, gamma_is_bf16, eps);
+                               logits ? logits + (size_t)t0 * V : (float*)nullptr, tt, V, H, norm_gamma, gamma_is_bf16, eps,
+                               best_key ? best_key + t0 : (unsigned long long*)nullptr);
             }
             if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head (mma) launch failed: %s", cudaGetErrorString(e));
         }
         return LSPK_OK;
     }
+    // several rows with a greedy choice wanted, on the CUDA-core kernels: logits are stored and a row argmax follows
+    const bool argmax_after = T > 1 && best_key != nullptr;
+    LSPK_REQUIRE(!argmax_after || logits, "lm_head: several rows with argmax need a logits buffer for this table format");
+    if (argmax_after) best_key = nullptr;
+    unsigned long long* const keys_after = argmax_after ? const_cast<unsigned long long*>(best_key_in) : nullptr;
     for (int t0 = 0; t0 < T; t0 += kLmMaxT) {
         const int tt = (T - t0) < kLmMaxT ? (T - t0) : kLmMaxT;
         const size_t smem = (size_t)tt * H * sizeof(float);
@@ -412,6 +452,7 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
 #undef LSPK_LM_LAUNCH
         if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head launch failed: %s", cudaGetErrorString(e));
     }
+    if (keys_after) return launch_argmax_rows(logits, T, V, keys_after);
     return LSPK_OK;
 }
 

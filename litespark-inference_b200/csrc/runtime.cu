@@ -370,9 +370,11 @@ static int enqueue_step(State* s, bool store_logits) {
         if (int rc = lm_head_launch(head.kind, head.data, head.scale, s->x, store_logits ? s->logits : nullptr, 1, V, H,
                                     m->final_norm.g, m->final_norm.is_bf16, c.rms_norm_eps, s->best)) return rc;
     } else {
-        if (int rc = lm_head_launch(head.kind, head.data, head.scale, s->x, s->logits, B, V, H, m->final_norm.g,
-                                    m->final_norm.is_bf16, c.rms_norm_eps, nullptr)) return rc;
-        LSPK_CUDA(launch(argmax_rows_kernel, dim3(B), dim3(1024), 0, true, (const float*)s->logits, V, s->best));
+        // the greedy choice of every row comes out of the LM head itself (bf16 table) or of a row argmax it
+        // launches (int8 / int4 tables); logits are written only where something reads them
+        const bool need_logits = store_logits || head.kind != 0 || (H % 32) != 0;
+        if (int rc = lm_head_launch(head.kind, head.data, head.scale, s->x, need_logits ? s->logits : nullptr, B, V, H,
+                                    m->final_norm.g, m->final_norm.is_bf16, c.rms_norm_eps, s->best)) return rc;
     }
     LSPK_CUDA(launch(finish_step_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, true, s->ctl, s->best,
                      s->tokens_out, B, s->t_max));
