@@ -41,7 +41,9 @@ struct TcParams {
     const float* x_scales;
     float w_scale;
     int M, N, K;
-    int k_blocks;
+    int k_blocks;            // K blocks of the whole product
+    int kb_per_split;        // K blocks per CTA along gridDim.z (== k_blocks when K is not split)
+    int32_t* split_ws;       // K split: int32 partial sums are added here ([M, N], zeroed by the host side)
     int epilogue;            // LSPK_EPI_STORE or LSPK_EPI_ADD
     int* error_flag;
 };
@@ -125,6 +127,9 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * kTcRows;
     const int m0 = blockIdx.y * TN;
+    // K split: this CTA's K blocks are [kb0, kb0 + nkb)
+    const int kb0 = blockIdx.z * p.kb_per_split;
+    const int nkb = min(p.kb_per_split, p.k_blocks - kb0);
 
     auto a_tile = [&](int s) { return smem + (size_t)s * kStageBytes; };
     auto b_tile = [&](int s) { return smem + (size_t)s * kStageBytes + kATileBytes; };
@@ -159,15 +164,15 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         // ---------------- producer ------------------------------------------------------------
         if (lane == 0) {
             int issued = 0;
-            for (int kb = 0; kb < p.k_blocks; ++kb) {
+            for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % kTcStages;
                 if (kb >= kTcStages && !mbar_wait(&empty[s], ((kb / kTcStages) - 1) & 1, abortp)) break;
                 if (*abortp) break;
                 mbar_expect_tx(&full_tma[s], kPackedBytes + kBTileBytes);
                 // packed weights: inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes
                 // = 128 units per row group), outer coordinate = row group
-                tma_load_2d(packed(s), &map_w, kb * 128, n0 / kRowsPerGroup, &full_tma[s]);
-                tma_load_2d(b_tile(s), &map_x, kb * kTcBK, m0, &full_tma[s]);
+                tma_load_2d(packed(s), &map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_tma[s]);
+                tma_load_2d(b_tile(s), &map_x, (kb0 + kb) * kTcBK, m0, &full_tma[s]);
                 ++issued;
             }
             if (*abortp) {
@@ -183,7 +188,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         // ---------------- MMA issuer ------------------------------------------------------------
         if (lane == 0) {
             bool ok = true;
-            for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+            for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kTcStages;
                 const uint32_t ph = (kb / kTcStages) & 1;
                 ok = mbar_wait(&full_tma[s], ph, abortp) && mbar_wait(&full_a[s], ph, abortp);
@@ -218,7 +223,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         const int row = tid - 64;                         // 0..127: weight row inside the CTA tile
         const int gi = row >> 4, rr = row & 15;
         bool ok = true;
-        for (int kb = 0; kb < p.k_blocks && ok; ++kb) {
+        for (int kb = 0; kb < nkb && ok; ++kb) {
             const int s = kb % kTcStages;
             ok = mbar_wait(&full_tma[s], (kb / kTcStages) & 1, abortp);
             if (!ok) break;
@@ -272,6 +277,10 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                         if (t < p.M) {
                             const int a = (int)v[j];
                             const size_t o = (size_t)t * p.N + n;
+                            if (p.split_ws) {                      // partial sum of this K range: exact in int32
+                                atomicAdd(p.split_ws + o, a);
+                                continue;
+                            }
                             if (p.acc_out) p.acc_out[o] = a;
                             const float y = __fmul_rn((float)a, __fmul_rn(p.x_scales[t], p.w_scale));
                             p.out[o] = p.epilogue == LSPK_EPI_ADD ? __fadd_rn(p.out[o], y) : y;
@@ -288,6 +297,22 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (tid == 0 && abort_flag && p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+}
+
+// K split: int32 sums of all K ranges -> fp32 outputs (rescale, optional residual add), and the raw
+// accumulators where asked for.
+__global__ void splitk_finish_kernel(const int32_t* __restrict__ ws, float* __restrict__ out, int32_t* __restrict__ acc_out,
+                                     const float* __restrict__ x_scales, float w_scale, int M, int N, int epilogue) {
+    grid_dependency_launch();
+    grid_dependency_wait();
+    const size_t total = (size_t)M * N;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / N);
+        const int a = ws[i];
+        if (acc_out) acc_out[i] = a;
+        const float y = __fmul_rn((float)a, __fmul_rn(x_scales[t], w_scale));
+        out[i] = epilogue == LSPK_EPI_ADD ? __fadd_rn(out[i], y) : y;
+    }
 }
 
 // int8 rows [M, K] in natural order -> [M, Kp] with the 4x4 transpose inside every 16-element block
@@ -324,7 +349,8 @@ struct TcScratch {
     int8_t *xq = nullptr, *xq_perm = nullptr;
     float* xs = nullptr;
     int* err = nullptr;
-    size_t cap_xq = 0, cap_perm = 0, cap_xs = 0;
+    int32_t* split_ws = nullptr;
+    size_t cap_xq = 0, cap_perm = 0, cap_xs = 0, cap_ws = 0;
 };
 static TcScratch g_tc;
 
@@ -437,10 +463,35 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
         p.k_blocks = (Kp + kTcBK - 1) / kTcBK;
         p.epilogue = a->epilogue;
         p.error_flag = g_tc.err;
-        const dim3 grid((w->N + kTcRows - 1) / kTcRows, (M + TN - 1) / TN);
+        const int n_tiles = (w->N + kTcRows - 1) / kTcRows, m_tiles = (M + TN - 1) / TN;
+        // K split when the output tiles alone leave most SMs idle: every CTA then streams a fraction of the
+        // bytes and runs a fraction of the K loop; partial sums meet in an int32 workspace (exact)
+        static const int knob_split = getenv("LSPK_TC_SPLITK") ? atoi(getenv("LSPK_TC_SPLITK")) : 1;
+        int splits = 1;
+        if (knob_split && n_tiles * m_tiles * 2 <= sm_count()) {
+            splits = sm_count() / (n_tiles * m_tiles);
+            if (splits > 8) splits = 8;
+            if (splits > p.k_blocks / 2) splits = p.k_blocks / 2;      // at least two K blocks per CTA
+            if (splits < 1) splits = 1;
+        }
+        p.kb_per_split = (p.k_blocks + splits - 1) / splits;
+        splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no CTA without work
+        if (splits > 1) {
+            if (int rc = grow((void**)&g_tc.split_ws, &g_tc.cap_ws, (size_t)M * w->N * 4)) return rc;
+            LSPK_CUDA(cudaMemsetAsync(g_tc.split_ws, 0, (size_t)M * w->N * 4, stream()));
+            p.split_ws = g_tc.split_ws;
+        }
+        const dim3 grid(n_tiles, m_tiles, splits);
         cudaError_t e = TN == 128 ? launch_tc<128>(mw, mx, p, grid)
                        : TN == 64 ? launch_tc<64>(mw, mx, p, grid)
                                   : launch_tc<32>(mw, mx, p, grid);
+        if (e == cudaSuccess && splits > 1) {
+            const size_t total = (size_t)M * w->N;
+            int fgrid = (int)((total + 255) / 256);
+            if (fgrid > sm_count() * 4) fgrid = sm_count() * 4;
+            e = launch(splitk_finish_kernel, dim3(fgrid), dim3(256), 0, true, (const int32_t*)g_tc.split_ws, p.out, p.acc_out,
+                       xs, w->scale, M, w->N, a->epilogue);
+        }
         if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
     }
     *handled = 1;
