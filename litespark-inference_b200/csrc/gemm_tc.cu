@@ -403,22 +403,29 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
     // ---- activations: int8 rows + scales, then the permuted, padded copy the tensor map reads ----
     const int8_t* xq = a->x_i8;
     const float* xs = a->x_scales;
-    if (a->prologue != LSPK_PRO_INT8) {
-        if (int rc = grow((void**)&g_tc.xq, &g_tc.cap_xq, (size_t)M * K)) return rc;
-        if (int rc = grow((void**)&g_tc.xs, &g_tc.cap_xs, (size_t)M * 4)) return rc;
-        int rc = a->prologue == LSPK_PRO_RMSNORM_QUANT
-                     ? lspk_rmsnorm_quantize_rows(a->x_f32, a->gamma, a->gamma_is_bf16, g_tc.xq, g_tc.xs, M, K, a->eps)
-                     : lspk_quantize_rows(a->x_f32, g_tc.xq, g_tc.xs, M, K);
-        if (rc) return rc;
-        xq = g_tc.xq;
-        xs = g_tc.xs;
-    }
     if (int rc = grow((void**)&g_tc.xq_perm, &g_tc.cap_perm, (size_t)M * Kp)) return rc;
     if (!g_tc.err) {
         LSPK_CUDA(cudaMalloc((void**)&g_tc.err, 16));
         LSPK_CUDA(cudaMemset(g_tc.err, 0, 16));
     }
-    {
+    int permuted = 0;
+    if (a->prologue != LSPK_PRO_INT8) {
+        if (int rc = grow((void**)&g_tc.xs, &g_tc.cap_xs, (size_t)M * 4)) return rc;
+        xs = g_tc.xs;
+        // fp32 rows: one kernel quantises straight into the permuted layout (unless the caller wants the
+        // natural-order int8 rows back as well)
+        if (!a->xq_out)
+            if (int rc = quantize_rows_permuted(a, K, Kp, g_tc.xq_perm, g_tc.xs, &permuted)) return rc;
+        if (!permuted) {
+            if (int rc = grow((void**)&g_tc.xq, &g_tc.cap_xq, (size_t)M * K)) return rc;
+            int rc = a->prologue == LSPK_PRO_RMSNORM_QUANT
+                         ? lspk_rmsnorm_quantize_rows(a->x_f32, a->gamma, a->gamma_is_bf16, g_tc.xq, g_tc.xs, M, K, a->eps)
+                         : lspk_quantize_rows(a->x_f32, g_tc.xq, g_tc.xs, M, K);
+            if (rc) return rc;
+            xq = g_tc.xq;
+        }
+    }
+    if (!permuted) {
         const size_t total = (size_t)M * Kp;
         int grid = (int)((total + 255) / 256);
         if (grid > sm_count() * 8) grid = sm_count() * 8;

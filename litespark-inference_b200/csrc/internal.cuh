@@ -53,6 +53,9 @@ struct LinearParams {
 int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* scale_scratch);
 // Library-owned scratch for that (grown with cudaMalloc: size it once outside stream capture).
 int quant_scratch(size_t M, size_t K, int8_t** q, float** s);
+// rows.cu: fp32 rows -> int8 rows in the tensor-core GEMM's permuted, padded layout (one kernel instead of
+// quantise + permute); *done = 0 when the shape / alignment does not allow it.
+int quantize_rows_permuted(const lspk_linear_args* a, int K, int Kp, int8_t* out_perm, float* scales, int* done);
 // rows.cu: RMSNorm + quantiser of T rows, row t with the gamma_sel[t]-th bf16 weight vector.
 int norm_quant_rows_selected(const float* x, const void* gamma_bf16, const int* gamma_sel, int8_t* out, float* scales,
                              int T, int K, float eps);

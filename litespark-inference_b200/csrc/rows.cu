@@ -5,7 +5,8 @@
 // rmsnorm_{bf16,fp32}gamma_fp32(_batched) (:590-650, 1074-1096),
 // rmsnorm_quantize_bf16gamma(_batched) (:975-1067), relu2_mul_fp32(_batched) (:653-670,
 // 1111-1123) and add_inplace_fp32 (:1127-1137).
-#include "common.cuh"
+#include "internal.cuh"
+#include "ternary_core.cuh"
 
 namespace lspk {
 
@@ -20,13 +21,15 @@ __device__ __forceinline__ float gamma_at(const void* gamma, int is_bf16, int k)
 
 // mode bit 0: apply RMSNorm first; bit 1: quantise (else write fp32 rows to out_f32).
 // gate != nullptr: the row is x * SiLU(gate) (the gated norm of the Mamba-2 block) before anything else.
+// perm_kp > 0 (VEC only): the int8 row is written in the layout the tensor-core GEMM reads, rows of perm_kp
+// bytes (K rounded up to 64, zero padded) with the 4x4 index transpose inside every 16-element block.
 // The normalised row is staged in shared memory (K floats) between the passes.  VEC: K is a
 // multiple of 4 and every pointer 16-byte aligned, so the passes move four elements at a time.
 template <bool VEC>
 __global__ void __launch_bounds__(kRowThreads)
 row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gate, const void* __restrict__ gamma_base,
                       const int* __restrict__ gamma_sel, int gamma_is_bf16, float* __restrict__ out_f32,
-                      int8_t* __restrict__ out_i8, float* __restrict__ scales, int K, float eps, int mode) {
+                      int8_t* __restrict__ out_i8, float* __restrict__ scales, int K, float eps, int mode, int perm_kp) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* xs = reinterpret_cast<float*>(smem_raw);
     __shared__ float red[32];
@@ -81,8 +84,7 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
         amax = block_max(amax, red);
         const float scale = quant_scale_from_absmax(amax);
         const float inv = __fdiv_rn(1.0f, scale);
-        uint32_t* dst = reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * K);
-        for (int i = tid; i < K4; i += kRowThreads) {
+        auto quant4 = [&](int i) -> uint32_t {
             const float4 v = xs4[i];
             const float f[4] = {v.x, v.y, v.z, v.w};
             uint32_t word = 0;
@@ -97,7 +99,21 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
                 }
                 word |= ((uint32_t)q & 0xffu) << (8 * e);
             }
-            dst[i] = word;
+            return word;
+        };
+        if (perm_kp > 0) {
+            uint4* dst = reinterpret_cast<uint4*>(out_i8 + (size_t)t * perm_kp);
+            for (int b = tid; b < perm_kp / 16; b += kRowThreads) {
+                uint32_t a[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) a[q] = (4 * b + q) < K4 ? quant4(4 * b + q) : 0u;
+                uint32_t o0, o1, o2, o3;
+                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                dst[b] = make_uint4(o0, o1, o2, o3);
+            }
+        } else {
+            uint32_t* dst = reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * K);
+            for (int i = tid; i < K4; i += kRowThreads) dst[i] = quant4(i);
         }
         if (tid == 0) scales[t] = scale;
         return;
@@ -158,7 +174,7 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 
 static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, float* out_f32, int8_t* out_i8,
                        float* scales, int T, int K, float eps, int mode, const float* gate = nullptr,
-                       const int* gamma_sel = nullptr) {
+                       const int* gamma_sel = nullptr, int perm_kp = 0) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(x && T >= 1 && K >= 1, "row helper: bad arguments (T=%d K=%d)", T, K);
     const size_t smem = (size_t)K * sizeof(float);
@@ -172,8 +188,9 @@ static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, flo
     auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     const bool vec = (K % 4 == 0) && aligned(x) && aligned(out_f32) && aligned(out_i8) && aligned(gamma) && aligned(gate) &&
                      (!gamma_sel || K % 8 == 0);
+    LSPK_REQUIRE(perm_kp == 0 || vec, "row helper: the permuted output needs K %% 4 == 0 and 16-byte aligned buffers");
     LSPK_CUDA(launch(vec ? row_norm_quant_kernel<true> : row_norm_quant_kernel<false>, dim3(T), dim3(kRowThreads), smem,
-                     true, x, gate, gamma, gamma_sel, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode));
+                     true, x, gate, gamma, gamma_sel, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode, vec ? perm_kp : 0));
     return LSPK_OK;
 }
 
@@ -203,6 +220,23 @@ int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* sca
 int norm_quant_rows_selected(const float* x, const void* gamma_bf16, const int* gamma_sel, int8_t* out, float* scales,
                              int T, int K, float eps) {
     return launch_rows(x, gamma_bf16, 1, nullptr, out, scales, T, K, eps, 3, nullptr, gamma_sel);
+}
+
+// Quantise (mode as in split_row_prologue: QUANT or RMSNORM_QUANT) straight into the GEMM's permuted, padded
+// activation layout.  Returns LSPK_ERR_ARG-free 'not applicable' through *done = 0 when the vector path cannot run.
+int quantize_rows_permuted(const lspk_linear_args* a, int K, int Kp, int8_t* out_perm, float* scales, int* done) {
+    *done = 0;
+    auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if ((K % 4) || !aligned(a->x_f32) || !aligned(a->gamma) || !aligned(out_perm)) return LSPK_OK;
+    int mode;
+    if (a->prologue == LSPK_PRO_QUANT) mode = 2;
+    else if (a->prologue == LSPK_PRO_RMSNORM_QUANT) mode = 3;
+    else return LSPK_OK;
+    if (int rc = launch_rows(a->x_f32, a->gamma, a->gamma_is_bf16, nullptr, out_perm, scales, a->M, K, a->eps, mode, nullptr,
+                             nullptr, Kp))
+        return rc;
+    *done = 1;
+    return LSPK_OK;
 }
 
 static int grid_for(size_t n, int block) {

@@ -258,7 +258,9 @@ static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool
     const DevLayer& L = m->layers[li];
     const int H = c.hidden_size, I = c.intermediate_size;
     const bool bitnet = c.arch == 0;
-    const bool fused_quant = rows == 1;       // one row: the linear kernels normalise and quantise themselves
+    // one row: the linear kernels normalise and quantise themselves; from 32 rows the tensor-core path takes
+    // fp32 rows too and quantises them straight into its own activation layout (one kernel, not two)
+    const bool fused_quant = rows == 1 || rows >= 32;
     const float eps = c.rms_norm_eps;
 
     auto linear = [&](int n_mats, const int* which, float* const* outs, const float* src, int8_t* src_q,
