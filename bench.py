@@ -164,7 +164,7 @@ def run_reference_arm(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * n_decode / value,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": {"workload": "BitNet-2B-shaped decoder, pp128+tg128 batch 1 (bounded CPU sample)",
                    "l2": "inputs larger than L2"},
@@ -471,14 +471,15 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary(2-bit) -> int32, fp32 rescale",
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": {"workload": "BitNet-2B-shaped decoder (30 layers, H=2560, I=6912, 20/5 heads, V=128256, "
                                f"bf16 tied embedding), {PROMPT_LEN}-token random prompt + {GEN_LEN} greedy steps, "
                                "batch 1 per GPU, fp16 KV",
                    "parallelism": f"dp{world} (independent sequence per GPU, no collective)",
                    "l2": "inputs larger than L2 (1.18 GB of weights streamed per token)",
-                   "step": "one tg128 pass = 128 chained decode steps"},
+                   "step": "one tg128 pass = 128 chained decode steps",
+                   "arithmetic": "int8 activations x ternary (2-bit packed) weights -> int32, fp32 rescale"},
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * GEN_LEN,
                 "d2h_bytes_per_step": 4 * GEN_LEN,
