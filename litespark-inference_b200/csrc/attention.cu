@@ -114,14 +114,17 @@ __device__ __forceinline__ float ordered_to_float(uint32_t u) {
 //   softmax: two single-barrier block reductions.
 //   values : TPK lanes per key, NG key groups, 16 loads requested before the scores exist and
 //            8 in flight per thread afterwards; group partials are summed through shared memory.
-template <typename KVT, int D>
+// VB0: value chunks a thread requests before the scores exist (16 hides the latency when a launch has few
+// CTAs; with many rows a small number keeps the registers low enough for two CTAs per SM).
+template <typename KVT, int D, int VB0>
 __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParams p) {
     constexpr int VEC = KvVec<KVT>::N;          // cache elements per 16-byte load
     constexpr int NCH = D / VEC;                // 16-byte chunks per cache row
     constexpr int TPK = NCH > 32 ? 32 : NCH;    // lanes per key
     constexpr int CPT = NCH / TPK;              // chunks per lane (2 only for fp32 rows of 256)
     constexpr int NG = kAttnThreads / TPK;      // key groups
-    constexpr int SB = (TPK < 16 ? TPK : 16) / CPT;   // keys per group whose rows are in flight together
+    constexpr int SBCAP = VB0 >= 16 ? 16 : 8;    // fewer key rows in flight in the many-CTA variant (registers)
+    constexpr int SB = (TPK < SBCAP ? TPK : SBCAP) / CPT;   // keys per group whose rows are in flight together
     constexpr int KPB = NG * SB;                // keys per batch of the score phase
     static_assert(kAttnWarps == 8, "block reductions assume eight warps");
     extern __shared__ __align__(16) float at_smem[];
@@ -153,7 +156,6 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
 
     // ---- request everything up front: the row's own q/k/v and rope factors, the key rows of the
     //      first score batch and the first 16 value chunks of this thread ---------------------------
-    constexpr int VB0 = 16;                     // value chunks requested before the scores exist
     const int g = tid / TPK, c = tid % TPK;
     float q_raw = 0.0f, k_raw = 0.0f, vr = 0.0f, cr = 0.0f, sr = 0.0f;
     if (tid < D) {
@@ -651,9 +653,12 @@ static int attention_launch_t(const AttnParams& p) {
     LSPK_REQUIRE(smem <= 200 * 1024, "attention: t_max=%d too large for the shared score buffer", p.t_max);
     static bool attr_set = false;
     if (!attr_set) {
-        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 64, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 128, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 256, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        LSPK_CUDA(cudaFuncSetAttribute(attention_kernel<KVT, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         LSPK_CUDA(cudaFuncSetAttribute(rope_store_kernel<KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set = true;
     }
@@ -685,9 +690,13 @@ static int attention_launch_t(const AttnParams& p) {
     }
     const dim3 grid(p.Q, p.T);
     cudaError_t e;
-    if (D == 64) e = launch(attention_kernel<KVT, 64>, grid, dim3(kAttnThreads), smem, true, p);
-    else if (D == 128) e = launch(attention_kernel<KVT, 128>, grid, dim3(kAttnThreads), smem, true, p);
-    else e = launch(attention_kernel<KVT, 256>, grid, dim3(kAttnThreads), smem, true, p);
+    const bool many = p.Q * p.T > 2 * sm_count();      // enough CTAs to hide latency by themselves
+    if (D == 64) e = many ? launch(attention_kernel<KVT, 64, 2>, grid, dim3(kAttnThreads), smem, true, p)
+                          : launch(attention_kernel<KVT, 64, 16>, grid, dim3(kAttnThreads), smem, true, p);
+    else if (D == 128) e = many ? launch(attention_kernel<KVT, 128, 2>, grid, dim3(kAttnThreads), smem, true, p)
+                                : launch(attention_kernel<KVT, 128, 16>, grid, dim3(kAttnThreads), smem, true, p);
+    else e = many ? launch(attention_kernel<KVT, 256, 2>, grid, dim3(kAttnThreads), smem, true, p)
+                  : launch(attention_kernel<KVT, 256, 16>, grid, dim3(kAttnThreads), smem, true, p);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
     return LSPK_OK;
 }
