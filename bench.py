@@ -34,6 +34,15 @@ import threading
 import time
 from pathlib import Path
 
+# The CPU legs (the reference arm, the cpu_baseline of the default arm) use every host core this process
+# may run on.  torchrun exports OMP_NUM_THREADS=1 to its workers; that setting is the launcher's, not the
+# user's, so it is replaced before any OpenMP runtime is loaded (numpy's included).
+if os.environ.get("TORCHELASTIC_RUN_ID") or os.environ.get("OMP_NUM_THREADS") == "1":
+    try:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    except AttributeError:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
 import numpy as np
 
 ROOT = Path(__file__).resolve().parent
