@@ -350,7 +350,8 @@ struct TcScratch {
     float* xs = nullptr;
     int* err = nullptr;
     int32_t* split_ws = nullptr;
-    size_t cap_xq = 0, cap_perm = 0, cap_xs = 0, cap_ws = 0;
+    int* xsum = nullptr;
+    size_t cap_xq = 0, cap_perm = 0, cap_xs = 0, cap_ws = 0, cap_xsum = 0;
 };
 static TcScratch g_tc;
 
@@ -365,11 +366,15 @@ static int grow(void** p, size_t* cap, size_t need) {
 
 // Library-owned int8 rows + scales for callers that hand fp32 rows to a many-row product.  Grows with
 // cudaMalloc: the first call of a given size must happen outside stream capture.
-int quant_scratch(size_t M, size_t K, int8_t** q, float** s) {
+int quant_scratch(size_t M, size_t K, int8_t** q, float** s, int** sums) {
     if (int rc = grow((void**)&g_tc.xq, &g_tc.cap_xq, M * K)) return rc;
     if (int rc = grow((void**)&g_tc.xs, &g_tc.cap_xs, M * 4)) return rc;
     *q = g_tc.xq;
     *s = g_tc.xs;
+    if (sums) {
+        if (int rc = grow((void**)&g_tc.xsum, &g_tc.cap_xsum, M * 4)) return rc;
+        *sums = g_tc.xsum;
+    }
     return LSPK_OK;
 }
 

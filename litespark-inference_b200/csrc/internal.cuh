@@ -19,6 +19,10 @@ struct LinearSeg {
     int scale_idx;         // grouped mode: index of this matrix inside an expert's scale triple
 };
 
+// Internal prologue of the eight-row kernel: int8 rows already in its shared-memory layout (permuted 16-element
+// blocks, rows mma_row_stride(Kp) bytes apart) with their sums, so that a tile is a plain copy.
+constexpr int kProInt8Tiled = 16;
+
 struct LinearParams {
     LinearSeg seg[3];
     int n_seg;
@@ -30,6 +34,7 @@ struct LinearParams {
     const float* gate_f32; // GATED_RMSNORM_QUANT: x is multiplied by SiLU(gate) before the norm
     const int8_t* x_i8;
     const float* x_scales;
+    const int* x_sums;     // tiled int8 prologue: sum of each row's int8 values
     const void* gamma;
     int gamma_is_bf16;
     float eps;
@@ -52,14 +57,16 @@ struct LinearParams {
 // Quantise (and normalise) M > 1 rows once into caller scratch and turn the call into an int8-prologue one.
 int split_row_prologue(lspk_linear_args* a, int K, int8_t* q_scratch, float* scale_scratch);
 // Library-owned scratch for that (grown with cudaMalloc: size it once outside stream capture).
-int quant_scratch(size_t M, size_t K, int8_t** q, float** s);
+int quant_scratch(size_t M, size_t K, int8_t** q, float** s, int** sums = nullptr);
 // rows.cu: fp32 rows -> int8 rows in the tensor-core GEMM's permuted, padded layout (one kernel instead of
 // quantise + permute); *done = 0 when the shape / alignment does not allow it.
-int quantize_rows_permuted(const lspk_linear_args* a, int K, int Kp, int8_t* out_perm, float* scales, int* done);
+int quantize_rows_permuted(const lspk_linear_args* a, int K, int Kp, int8_t* out_perm, float* scales, int* done,
+                           int stride = 0, int* sums = nullptr);
 // rows.cu: RMSNorm + quantiser of T rows, row t with the gamma_sel[t]-th bf16 weight vector.
 int norm_quant_rows_selected(const float* x, const void* gamma_bf16, const int* gamma_sel, int8_t* out, float* scales,
                              int T, int K, float eps);
 int linear_mma_launch(const LinearParams& p, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);
+__host__ __device__ inline int mma_row_stride(int Kp) { return (Kp % 128 == 0) ? Kp + 64 : Kp; }
 
 // Launch the CUDA-core kernel with fully prepared parameters.  mt: rows per CTA tile (1, 2, 4 or 8).
 int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);

@@ -494,6 +494,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
     // Several rows of fp32 input: normalise + quantise them once in their own kernel (fused into the
     // product, every CTA would repeat that work for all rows) and continue with the int8 prologue.
     lspk_linear_args split;
+    const int* tiled_sums = nullptr;
     if (a->M > 1 && a->prologue != LSPK_PRO_INT8) {
         LSPK_REQUIRE(a->prologue >= LSPK_PRO_QUANT && a->prologue <= LSPK_PRO_GATED_RMSNORM_QUANT,
                      "linear: unknown prologue %d", a->prologue);
@@ -504,9 +505,25 @@ int linear_cuda_core(const lspk_linear_args* a) {
         split = *a;
         int8_t* q = nullptr;
         float* sc = nullptr;
-        if (int rc = quant_scratch((size_t)a->M, (size_t)w0->K, &q, &sc)) return rc;
-        if (int rc = split_row_prologue(&split, w0->K, q, sc)) return rc;
-        if (a->xq_out) LSPK_CUDA(cudaMemcpyAsync(a->xq_out, q, (size_t)a->M * w0->K, cudaMemcpyDeviceToDevice, stream()));
+        int* sums = nullptr;
+        const int Kp = w0->chunks * kWeightsPerChunk, rs = mma_row_stride(Kp);
+        if (int rc = quant_scratch((size_t)a->M, (size_t)rs, &q, &sc, &sums)) return rc;
+        int tiled = 0;
+        // below the tensor-core GEMM's threshold the rows go to the eight-row kernel: quantise them straight into
+        // its tile layout (a plain copy there); the natural-order rows are produced only when the caller wants them
+        if (!a->xq_out)
+            if (int rc = quantize_rows_permuted(a, w0->K, Kp, q, sc, &tiled, rs, sums)) return rc;
+        if (tiled) {
+            split.prologue = kProInt8Tiled;
+            split.x_i8 = q;
+            split.x_scales = sc;
+            split.x_f32 = nullptr;
+            split.gate_f32 = nullptr;
+            tiled_sums = sums;
+        } else {
+            if (int rc = split_row_prologue(&split, w0->K, q, sc)) return rc;
+            if (a->xq_out) LSPK_CUDA(cudaMemcpyAsync(a->xq_out, q, (size_t)a->M * w0->K, cudaMemcpyDeviceToDevice, stream()));
+        }
         if (a->xscale_out) LSPK_CUDA(cudaMemcpyAsync(a->xscale_out, sc, (size_t)a->M * 4, cudaMemcpyDeviceToDevice, stream()));
         split.xq_out = nullptr;
         split.xscale_out = nullptr;
@@ -534,6 +551,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
     p.gate_f32 = a->gate_f32;
     p.x_i8 = a->x_i8;
     p.x_scales = a->x_scales;
+    p.x_sums = tiled_sums;
     p.gamma = a->gamma;
     p.gamma_is_bf16 = a->gamma_is_bf16;
     p.eps = a->eps;
@@ -542,6 +560,9 @@ int linear_cuda_core(const lspk_linear_args* a) {
     p.trace = trace_buffer();
     p.trace_cap = trace_capacity();
     switch (a->prologue) {
+        case kProInt8Tiled:                      // set above, never by a caller
+            LSPK_REQUIRE(tiled_sums != nullptr, "linear: unknown prologue %d", a->prologue);
+            break;
         case LSPK_PRO_INT8:
             LSPK_REQUIRE(a->x_i8 && a->x_scales, "linear: INT8 prologue needs x_i8 and x_scales");
             break;

@@ -36,10 +36,9 @@ __device__ __forceinline__ void mma_u8s8(int c[4], uint32_t a0, uint32_t a1, uin
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Row stride of the activation tile in shared memory: Kp rounded so that consecutive rows start 64
-// bytes apart modulo 128, which makes the quarter-warp 16-byte loads (two tokens x four words)
-// conflict-free.
-__host__ __device__ inline int mma_row_stride(int Kp) { return (Kp % 128 == 0) ? Kp + 64 : Kp; }
+// Row stride of the activation tile in shared memory (mma_row_stride, internal.cuh): Kp rounded so that
+// consecutive rows start 64 bytes apart modulo 128, which makes the quarter-warp 16-byte loads (two tokens x
+// four words) conflict-free.
 
 template <bool PAIR, bool GROUPED>
 __global__ void __launch_bounds__(kMThreads)
@@ -137,8 +136,19 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
         first_tile = false;
 
         // ---- prologue: the tile's rows -> permuted int8 rows in shared memory ------------------------------
-        {
-            // int8 rows (the only prologue of this kernel): one warp per row, a single pass of independent loads
+        if (p.prologue == kProInt8Tiled) {
+            // rows already permuted and spaced like the shared-memory tile: a plain 16-byte copy
+            const int chunks_per_row = rs / 16;
+            const uint4* src = reinterpret_cast<const uint4*>(p.x_i8 + (size_t)m0 * rs);
+            uint4* dst = reinterpret_cast<uint4*>(xq);
+            for (int i = tid; i < kMT * chunks_per_row; i += kMThreads)
+                dst[i] = (i / chunks_per_row) < mt ? src[i] : make_uint4(0, 0, 0, 0);
+            if (tid < kMT) {
+                s_scale[tid] = tid < mt ? p.x_scales[m0 + tid] : 0.0f;
+                s_sumx[tid] = tid < mt ? p.x_sums[m0 + tid] : 0;
+            }
+        } else {
+            // plain int8 rows: one warp per row, a single pass of independent loads
             const int m = warp;                                  // kMWarps == kMT
             int8_t* xq_row = xq + (size_t)m * rs;
             const int nblk = Kp / 16;
@@ -294,7 +304,8 @@ static cudaError_t launch_mma(const LinearParams& p, dim3 grid, size_t smem) {
 // Launch the eight-row kernel.  K is limited by the shared-memory activation tile (8 rows of K bytes).
 // Rows arrive quantised (INT8 prologue); fp32 rows are quantised once by the row kernel beforehand.
 int linear_mma_launch(const LinearParams& p, bool pair, bool grouped, int grid_x, int grid_y, int grid_z) {
-    LSPK_REQUIRE(p.prologue == LSPK_PRO_INT8, "linear: the eight-row kernel takes int8 rows (prologue %d)", p.prologue);
+    LSPK_REQUIRE(p.prologue == LSPK_PRO_INT8 || (p.prologue == kProInt8Tiled && !grouped),
+                 "linear: the eight-row kernel takes int8 rows (prologue %d)", p.prologue);
     const int Kp = p.chunks * kWeightsPerChunk;
     const size_t smem = (size_t)kMT * mma_row_stride(Kp) + (size_t)kMWarps * kMT * 16 * (pair ? 2 : 1) * 4 + kMT * 8 + 64;
     LSPK_REQUIRE(smem <= 200 * 1024, "linear: K=%d too large for the 8-row activation tile (limit about 24000)", p.K);

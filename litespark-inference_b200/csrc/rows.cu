@@ -21,15 +21,17 @@ __device__ __forceinline__ float gamma_at(const void* gamma, int is_bf16, int k)
 
 // mode bit 0: apply RMSNorm first; bit 1: quantise (else write fp32 rows to out_f32).
 // gate != nullptr: the row is x * SiLU(gate) (the gated norm of the Mamba-2 block) before anything else.
-// perm_kp > 0 (VEC only): the int8 row is written in the layout the tensor-core GEMM reads, rows of perm_kp
-// bytes (K rounded up to 64, zero padded) with the 4x4 index transpose inside every 16-element block.
+// perm_kp > 0 (VEC only): the int8 row is written in the layout the tensor-core kernels read: perm_kp bytes (K
+// rounded up to 64, zero padded) with the 4x4 index transpose inside every 16-element block, rows perm_stride
+// bytes apart; sums (optional) receives the sum of the row's int8 values.
 // The normalised row is staged in shared memory (K floats) between the passes.  VEC: K is a
 // multiple of 4 and every pointer 16-byte aligned, so the passes move four elements at a time.
 template <bool VEC>
 __global__ void __launch_bounds__(kRowThreads)
 row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gate, const void* __restrict__ gamma_base,
                       const int* __restrict__ gamma_sel, int gamma_is_bf16, float* __restrict__ out_f32,
-                      int8_t* __restrict__ out_i8, float* __restrict__ scales, int K, float eps, int mode, int perm_kp) {
+                      int8_t* __restrict__ out_i8, float* __restrict__ scales, int K, float eps, int mode, int perm_kp,
+                      int perm_stride, int* __restrict__ sums) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* xs = reinterpret_cast<float*>(smem_raw);
     __shared__ float red[32];
@@ -102,14 +104,22 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
             return word;
         };
         if (perm_kp > 0) {
-            uint4* dst = reinterpret_cast<uint4*>(out_i8 + (size_t)t * perm_kp);
+            uint4* dst = reinterpret_cast<uint4*>(out_i8 + (size_t)t * perm_stride);
+            int sumx = 0;
             for (int b = tid; b < perm_kp / 16; b += kRowThreads) {
                 uint32_t a[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) a[q] = (4 * b + q) < K4 ? quant4(4 * b + q) : 0u;
+                for (int q = 0; q < 4; ++q) {
+                    a[q] = (4 * b + q) < K4 ? quant4(4 * b + q) : 0u;
+                    sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                }
                 uint32_t o0, o1, o2, o3;
                 transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
                 dst[b] = make_uint4(o0, o1, o2, o3);
+            }
+            if (sums) {                                    // uniform branch: every thread of the block takes it
+                sumx = block_sum(sumx, reinterpret_cast<int*>(red));
+                if (tid == 0) sums[t] = sumx;
             }
         } else {
             uint32_t* dst = reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * K);
@@ -174,7 +184,7 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 
 static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, float* out_f32, int8_t* out_i8,
                        float* scales, int T, int K, float eps, int mode, const float* gate = nullptr,
-                       const int* gamma_sel = nullptr, int perm_kp = 0) {
+                       const int* gamma_sel = nullptr, int perm_kp = 0, int perm_stride = 0, int* sums = nullptr) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(x && T >= 1 && K >= 1, "row helper: bad arguments (T=%d K=%d)", T, K);
     const size_t smem = (size_t)K * sizeof(float);
@@ -190,7 +200,8 @@ static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, flo
                      (!gamma_sel || K % 8 == 0);
     LSPK_REQUIRE(perm_kp == 0 || vec, "row helper: the permuted output needs K %% 4 == 0 and 16-byte aligned buffers");
     LSPK_CUDA(launch(vec ? row_norm_quant_kernel<true> : row_norm_quant_kernel<false>, dim3(T), dim3(kRowThreads), smem,
-                     true, x, gate, gamma, gamma_sel, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode, vec ? perm_kp : 0));
+                     true, x, gate, gamma, gamma_sel, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode, vec ? perm_kp : 0,
+                     perm_stride > 0 ? perm_stride : perm_kp, sums));
     return LSPK_OK;
 }
 
@@ -222,18 +233,23 @@ int norm_quant_rows_selected(const float* x, const void* gamma_bf16, const int* 
     return launch_rows(x, gamma_bf16, 1, nullptr, out, scales, T, K, eps, 3, nullptr, gamma_sel);
 }
 
-// Quantise (mode as in split_row_prologue: QUANT or RMSNORM_QUANT) straight into the GEMM's permuted, padded
-// activation layout.  Returns LSPK_ERR_ARG-free 'not applicable' through *done = 0 when the vector path cannot run.
-int quantize_rows_permuted(const lspk_linear_args* a, int K, int Kp, int8_t* out_perm, float* scales, int* done) {
+// Quantise fp32 rows (QUANT, RMSNORM_QUANT or GATED_RMSNORM_QUANT prologue of `a`) straight into the permuted,
+// padded activation layout of the tensor-core kernels: rows `stride` bytes apart (0: Kp), optionally with the
+// per-row sums of the int8 values.  *done = 0 when the vector path cannot run (shape / alignment).
+int quantize_rows_permuted(const lspk_linear_args* a, int K, int Kp, int8_t* out_perm, float* scales, int* done,
+                           int stride, int* sums) {
     *done = 0;
     auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    if ((K % 4) || !aligned(a->x_f32) || !aligned(a->gamma) || !aligned(out_perm)) return LSPK_OK;
+    if ((K % 4) || !aligned(a->x_f32) || !aligned(a->gamma) || !aligned(out_perm) || !aligned(a->gate_f32) || (stride & 15))
+        return LSPK_OK;
     int mode;
+    const float* gate = nullptr;
     if (a->prologue == LSPK_PRO_QUANT) mode = 2;
     else if (a->prologue == LSPK_PRO_RMSNORM_QUANT) mode = 3;
+    else if (a->prologue == LSPK_PRO_GATED_RMSNORM_QUANT) { mode = 3; gate = a->gate_f32; }
     else return LSPK_OK;
-    if (int rc = launch_rows(a->x_f32, a->gamma, a->gamma_is_bf16, nullptr, out_perm, scales, a->M, K, a->eps, mode, nullptr,
-                             nullptr, Kp))
+    if (int rc = launch_rows(a->x_f32, a->gamma, a->gamma_is_bf16, nullptr, out_perm, scales, a->M, K, a->eps, mode, gate,
+                             nullptr, Kp, stride, sums))
         return rc;
     *done = 1;
     return LSPK_OK;

@@ -258,9 +258,11 @@ static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool
     const DevLayer& L = m->layers[li];
     const int H = c.hidden_size, I = c.intermediate_size;
     const bool bitnet = c.arch == 0;
-    // one row: the linear kernels normalise and quantise themselves; from 32 rows the tensor-core path takes
-    // fp32 rows too and quantises them straight into its own activation layout (one kernel, not two)
-    const bool fused_quant = rows == 1 || rows >= 32;
+    // fp32 rows go to the linear layer as they are: one row is normalised and quantised inside the GEMV;
+    // more rows are quantised once, by one kernel, straight into the activation layout of the kernel that
+    // takes them (eight-row tiles below 32 rows, the tcgen05 GEMM from there).  The library scratch this
+    // uses is sized by the warm-up run that precedes every graph capture.
+    const bool fused_quant = true;
     const float eps = c.rms_norm_eps;
 
     auto linear = [&](int n_mats, const int* which, float* const* outs, const float* src, int8_t* src_q,
