@@ -104,22 +104,32 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
             return word;
         };
         if (perm_kp > 0) {
-            uint4* dst = reinterpret_cast<uint4*>(out_i8 + (size_t)t * perm_stride);
+            // one quarter of a 16-element block per thread (all threads busy); the four lanes of a block
+            // exchange their words and lane q assembles output word q = byte q of the four quarters
+            uint32_t* dst = reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * perm_stride);
+            const int P4 = perm_kp >> 2;
+            const int lane = tid & 31, q = lane & 3, base = lane & ~3;
             int sumx = 0;
-            for (int b = tid; b < perm_kp / 16; b += kRowThreads) {
-                uint32_t a[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    a[q] = (4 * b + q) < K4 ? quant4(4 * b + q) : 0u;
-                    sumx = __dp4a((int)a[q], 0x01010101, sumx);
-                }
-                uint32_t o0, o1, o2, o3;
-                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
-                dst[b] = make_uint4(o0, o1, o2, o3);
+            for (int i0 = 0; i0 < P4; i0 += kRowThreads) {          // uniform trip count: shuffles need whole warps
+                const int i = i0 + tid;
+                const uint32_t mine = i < K4 ? quant4(i) : 0u;
+                sumx = __dp4a((int)mine, 0x01010101, sumx);
+                const uint32_t w0 = __shfl_sync(0xffffffffu, mine, base + 0), w1 = __shfl_sync(0xffffffffu, mine, base + 1);
+                const uint32_t w2 = __shfl_sync(0xffffffffu, mine, base + 2), w3 = __shfl_sync(0xffffffffu, mine, base + 3);
+                const uint32_t sel = 0x4440u + 0x1111u * (uint32_t)q;      // byte q of the first operand, byte q of the second
+                const uint32_t lo = __byte_perm(w0, w1, sel & 0x00ffu), hi = __byte_perm(w2, w3, sel & 0x00ffu);
+                if (i < P4) dst[i] = __byte_perm(lo, hi, 0x5410);
             }
             if (sums) {                                    // uniform branch: every thread of the block takes it
-                sumx = block_sum(sumx, reinterpret_cast<int*>(red));
-                if (tid == 0) sums[t] = sumx;
+                sumx = __reduce_add_sync(0xffffffffu, sumx);
+                int* redi = reinterpret_cast<int*>(red);
+                if (lane == 0) redi[tid >> 5] = sumx;
+                __syncthreads();
+                if (tid == 0) {
+                    int total = 0;
+                    for (int w = 0; w < kRowThreads / 32; ++w) total += redi[w];
+                    sums[t] = total;
+                }
             }
         } else {
             uint32_t* dst = reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * K);
