@@ -246,9 +246,19 @@ def run_sweep(args):
             us = 1000.0 * ms.value / (reps * n_copies)
             nbytes = N * Kd / 4 + 4 * M * Kd + 4 * M * N
             ops = 2.0 * M * N * Kd
-            rows.append({"shape": name, "N": N, "K": Kd, "M": M, "us": us, "GBps": nbytes / us / 1e3,
-                         "frac_hbm": nbytes / us / 1e3 / peak, "TOPS": ops / us / 1e6,
-                         "path": "tcgen05" if M >= 32 else "cuda-core"})
+            row = {"shape": name, "N": N, "K": Kd, "M": M, "us": us, "GBps": nbytes / us / 1e3,
+                   "frac_hbm": nbytes / us / 1e3 / peak, "TOPS": ops / us / 1e6,
+                   "path": "tcgen05" if M >= 32 else ("mma.sync" if M > 1 else "dp4a")}
+            if M == 1:
+                # the same launches as independent graph nodes (8 forked streams): the kernel's amortised
+                # throughput when it is not a link of a dependency chain
+                y8 = dev.DeviceArray((8, N), np.float32)
+                K.check(lib.lspk_bench_linear_copies_independent(handles, n_copies, x.ptr, y8.ptr, 1, reps, 8, ctypes.byref(ms)))
+                ui = 1000.0 * ms.value / (reps * n_copies)
+                row.update({"us_independent": ui, "GBps_independent": nbytes / ui / 1e3,
+                            "frac_hbm_independent": nbytes / ui / 1e3 / peak})
+                y8.free()
+            rows.append(row)
             x.free()
             y.free()
         for c in copies:

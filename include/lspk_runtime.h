@@ -90,6 +90,10 @@ int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32
                              float* ms_out);
 /* Floor cost of a kernel boundary: a graph of n_kernels empty dependent kernels, replayed reps times. */
 int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out);
+/* lspk_bench_linear_copies with the launches of a pass on n_streams forked streams (independent graph nodes):
+ * the amortised throughput of the kernel outside a dependency chain.  y holds n_streams * M * N floats. */
+int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
+                                         int n_streams, float* ms_out);
 
 #ifdef __cplusplus
 }

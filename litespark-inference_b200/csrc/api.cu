@@ -43,7 +43,10 @@ static int g_trace_cap = 0;
 unsigned long long* trace_buffer() { return g_trace; }
 int trace_capacity() { return g_trace_cap; }
 
-cudaStream_t stream() { return g_stream; }
+static cudaStream_t g_stream_override = nullptr;    // measurement aid: launches go here while set
+cudaStream_t stream() { return g_stream_override ? g_stream_override : g_stream; }
+cudaStream_t main_stream() { return g_stream; }
+void set_stream_override(cudaStream_t s) { g_stream_override = s; }
 bool pdl_enabled() { return g_pdl; }
 int sm_count() { return g_sm_count; }
 

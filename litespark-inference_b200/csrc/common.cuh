@@ -14,6 +14,8 @@ namespace lspk {
 void set_error(const char* fmt, ...);
 int  fail(int code, const char* fmt, ...);          // records the message, returns code
 cudaStream_t stream();                              // the library's launch stream
+cudaStream_t main_stream();                         // the same, ignoring a measurement override
+void set_stream_override(cudaStream_t s);           // measurement aid: route launches to another stream (nullptr: off)
 bool pdl_enabled();                                 // programmatic dependent launch on/off
 int  sm_count();
 int  ensure_init();                                 // bind to a GPU on first use

@@ -889,6 +889,78 @@ int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32
     return rc;
 }
 
+// The same product, but the launches of one pass do not depend on one another: they are captured on
+// `n_streams` forked streams (round-robin, one output buffer per stream), so the graph holds independent
+// kernel nodes and the GPU may overlap them.  This is the amortised single-GEMV figure: what the kernel
+// streams when it is not a link in a dependency chain.  y must hold n_streams * N floats.
+int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
+                                         int n_streams, float* ms_out) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_REQUIRE(w && n_w >= 1 && x_f32 && y && M == 1 && reps >= 1 && ms_out && n_streams >= 1 && n_streams <= 16,
+                 "lspk_bench_linear_copies_independent: bad arguments (one row only: more rows share library scratch)");
+    const Weight* w0 = reinterpret_cast<const Weight*>(w[0]);
+    const size_t y_stride = (size_t)M * w0->N;
+    auto one = [&](int i, float* out) -> int {
+        lspk_linear_args a = {};
+        a.w[0] = w[i];
+        a.out[0] = out;
+        a.n_mats = 1;
+        a.M = M;
+        a.prologue = LSPK_PRO_QUANT;
+        a.epilogue = LSPK_EPI_STORE;
+        a.x_f32 = x_f32;
+        return lspk_linear(&a);
+    };
+    if (int rc = one(0, y)) return rc;                    // sets kernel attributes
+    LSPK_CUDA(cudaStreamSynchronize(main_stream()));
+    cudaStream_t side[16] = {};
+    cudaEvent_t fork = nullptr, join[16] = {};
+    int rc = LSPK_OK;
+    cudaError_t e = cudaEventCreateWithFlags(&fork, cudaEventDisableTiming);
+    for (int s = 0; s < n_streams && e == cudaSuccess; ++s) {
+        e = cudaStreamCreateWithFlags(&side[s], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming);
+    }
+    cudaGraph_t g = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (e == cudaSuccess) e = cudaStreamBeginCapture(main_stream(), cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+        cudaEventRecord(fork, main_stream());
+        for (int s = 0; s < n_streams; ++s) cudaStreamWaitEvent(side[s], fork, 0);
+        const bool pdl_was = pdl_enabled();
+        lspk_set_pdl(0);                                  // no programmatic edges: plain independent nodes
+        for (int i = 0; i < n_w && rc == LSPK_OK; ++i) {
+            set_stream_override(side[i % n_streams]);
+            rc = one(i, y + (size_t)(i % n_streams) * y_stride);
+        }
+        set_stream_override(nullptr);
+        lspk_set_pdl(pdl_was ? 1 : 0);
+        for (int s = 0; s < n_streams; ++s) {
+            cudaEventRecord(join[s], side[s]);
+            cudaStreamWaitEvent(main_stream(), join[s], 0);
+        }
+        e = cudaStreamEndCapture(main_stream(), &g);
+    }
+    if (e == cudaSuccess && rc == LSPK_OK) e = cudaGraphInstantiate(&exec, g, 0);
+    if (g) cudaGraphDestroy(g);
+    if (e == cudaSuccess && rc == LSPK_OK) {
+        cudaGraphLaunch(exec, main_stream());
+        rc = lspk_timer_start();
+        for (int i = 0; i < reps && !rc; ++i)
+            if (cudaGraphLaunch(exec, main_stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
+        if (!rc) rc = lspk_timer_stop(ms_out);
+        cudaStreamSynchronize(main_stream());
+    }
+    if (exec) cudaGraphExecDestroy(exec);
+    for (int s = 0; s < n_streams; ++s) {
+        if (join[s]) cudaEventDestroy(join[s]);
+        if (side[s]) cudaStreamDestroy(side[s]);
+    }
+    if (fork) cudaEventDestroy(fork);
+    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "independent-launch benchmark failed: %s", cudaGetErrorString(e));
+    return rc;
+}
+
 // Floor cost of a dependent kernel boundary: replay a graph of `n_kernels` kernels of `grid` CTAs x
 // 256 threads that do no work, each depending on the previous one, and report the time of `reps` replays.
 int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out) {
