@@ -444,6 +444,19 @@ def main():
     K.check(lib.lspk_bench_lm_head(state.handle, 20, ctypes.byref(ms), ctypes.byref(lm_bytes)))
     lm_ms = float(ms.value) / 20
     lm_gbs = lm_bytes.value / (lm_ms * 1e-3) / 1e9
+    # the single GEMV of config 1 (6912 x 2560, fused quantiser) as independent launches: the 30 layers' gate
+    # matrices (133 MB, larger than the L2) on 8 forked streams inside one graph -- what the kernel streams
+    # when it is not a link of a dependency chain
+    from litespark_inference_b200.torchless import device as dev
+    gate_handles = (ctypes.c_void_p * cfg.num_layers)(*[dm.projection(li, "gate_proj") for li in range(cfg.num_layers)])
+    gx = dev.DeviceArray.from_numpy(np.random.default_rng(3).standard_normal((1, cfg.hidden_size)).astype(np.float32))
+    gy = dev.DeviceArray((8, cfg.intermediate_size), np.float32)
+    K.check(lib.lspk_bench_linear_copies_independent(gate_handles, cfg.num_layers, gx.ptr, gy.ptr, 1, 20, 8, ctypes.byref(ms)))
+    gemv_us = 1000.0 * float(ms.value) / (20 * cfg.num_layers)
+    gemv_bytes = cfg.intermediate_size * cfg.hidden_size / 4 + 4 * cfg.hidden_size + 4 * cfg.intermediate_size
+    gemv_gbs = gemv_bytes / gemv_us / 1e3
+    gx.free()
+    gy.free()
     token_ms = total_ms / (args.steps * GEN_LEN)
     kv_bytes = 2 * cfg.num_layers * (PROMPT_LEN + GEN_LEN / 2) * cfg.num_kv_heads * 128 * 2
     token_bytes = lin_bytes.value + lm_bytes.value + kv_bytes
@@ -518,6 +531,10 @@ def main():
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                      "launches_timed": n_launch.value * reps,
                      "how": "CUDA events around graph replays of the 120 linear launches of one token over all 30 layers' weights (521 MB, > L2)"},
+        "roofline_gemv_independent": {"kernel": "ternary_linear_kernel (M=1, 6912x2560, fused quantiser)", "bound": "hbm",
+                                      "achieved": gemv_gbs, "peak": peak, "unit": "GB/s", "frac": gemv_gbs / peak,
+                                      "us_per_launch": gemv_us, "bytes_per_launch": gemv_bytes,
+                                      "how": "the 30 layers' gate matrices as independent graph nodes on 8 forked streams, 20 replays"},
         "roofline_lm_head": {"kernel": "lm_head_kernel<bf16>", "bound": "hbm", "achieved": lm_gbs, "peak": peak,
                              "unit": "GB/s", "frac": lm_gbs / peak, "us_per_launch": 1000.0 * lm_ms},
         "roofline_token": {"bytes_per_token": token_bytes, "us_per_token": 1000.0 * token_ms, "achieved": token_gbs,
