@@ -90,3 +90,19 @@ def test_first_positions_are_exact(shaped, oracle, port):
     for t in prompt:
         got, want = rt.forward_one(dm, st, t), oracle.forward_one(port, m, ost, t)
         assert _rel_l2(got, want) <= 1e-5
+
+
+def test_long_context_at_head_dim_128(shaped, oracle, port):
+    """560 positions with the fp16 cache: the decode kernel's second batch of keys at head size 128 (512 per
+    batch), the prefill kernel's third.  The first decode step after the prefill must track the oracle as
+    closely as the prefill itself does."""
+    cfg, m, dm = shaped
+    n = 560
+    prompt = [int(t) for t in np.random.default_rng(9).integers(0, cfg.vocab_size, n + 2)]
+    st = rt.init_state(dm, n + 4, kv_dtype="fp16")
+    ost = oracle.State(cfg, n + 4, np.float16)
+    e0 = _rel_l2(rt.forward_prefill(dm, st, prompt[:n]), oracle.forward_prefill(port, m, ost, prompt[:n]))
+    assert e0 <= MEDIAN_REL_L2_NO_REF
+    for t in prompt[n:]:
+        e = _rel_l2(rt.forward_one(dm, st, t), oracle.forward_one(port, m, ost, t))
+        assert e <= max(2.0 * e0, 0.1) + 0.05, f"decode step error {e:.3e} vs prefill error {e0:.3e}"

@@ -209,3 +209,22 @@ def _falcon_oracle(oracle, cfg, fm, ids):
         h = kern.rmsnorm_into(x, fm.final_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
         logits = oracle.lm_head(kern, fm, h)
     return logits
+
+
+@pytest.mark.parametrize("kv", ["fp32", "fp16"])
+def test_long_context_beyond_one_key_batch(toy, oracle, port, kv):
+    """More positions than one batch of keys in either attention kernel (512 per batch in the cluster-split
+    decode kernel at this head size with an fp32 cache, 1024 with fp16; 256 in the prefill kernel): chunked
+    prefill of 1100 tokens, then teacher-forced decode steps, logits against the oracle."""
+    cfg, m, dm = toy
+    n = 1100
+    prompt = [int(t) for t in np.random.default_rng(21).integers(0, cfg.vocab_size, n + 4)]
+    st = rt.init_state(dm, n + 8, kv_dtype=kv)
+    ost = oracle.State(cfg, n + 8, np.float32 if kv == "fp32" else np.float16)
+    got = rt.forward_prefill(dm, st, prompt[:n])
+    want = oracle.forward_prefill(port, m, ost, prompt[:n])
+    assert _close(got, want)
+    for t in prompt[n:]:
+        got, want = rt.forward_one(dm, st, t), oracle.forward_one(port, m, ost, t)
+        assert _close(got, want)
+    assert st.pos == n + 4
