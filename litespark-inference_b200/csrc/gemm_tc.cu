@@ -299,19 +299,52 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     if (tid == 0 && abort_flag && p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
 }
 
-// K split: int32 sums of all K ranges -> fp32 outputs (rescale, optional residual add), and the raw
-// accumulators where asked for.
-__global__ void splitk_finish_kernel(const int32_t* __restrict__ ws, float* __restrict__ out, int32_t* __restrict__ acc_out,
-                                     const float* __restrict__ x_scales, float w_scale, int M, int N, int epilogue) {
+// K split: int32 sums of all K ranges -> fp32 outputs (rescale, residual add or the gated pairing), and the
+// raw accumulators where asked for.  Up to three matrices of one call are finished by one launch; for the
+// gated epilogues segment 0 is the gate and segment 1 the up projection (same N), and only out[0] is written.
+struct FinishSeg {
+    const int32_t* ws;
+    float* out;
+    int32_t* acc_out;
+    float w_scale;
+    int N;
+};
+struct FinishParams {
+    FinishSeg seg[3];
+    int n_seg;
+    int M;
+    int epilogue;
+    const float* x_scales;
+};
+
+__global__ void splitk_finish_kernel(const FinishParams p) {
     grid_dependency_launch();
     grid_dependency_wait();
-    const size_t total = (size_t)M * N;
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int t = (int)(i / N);
-        const int a = ws[i];
-        if (acc_out) acc_out[i] = a;
-        const float y = __fmul_rn((float)a, __fmul_rn(x_scales[t], w_scale));
-        out[i] = epilogue == LSPK_EPI_ADD ? __fadd_rn(out[i], y) : y;
+    const bool pair = p.epilogue == LSPK_EPI_RELU2_MUL || p.epilogue == LSPK_EPI_SILU_MUL;
+    const int n_seg = pair ? 1 : p.n_seg;
+    for (int sgi = 0; sgi < n_seg; ++sgi) {
+        const FinishSeg sg = p.seg[sgi];
+        const size_t total = (size_t)p.M * sg.N;
+        for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const int t = (int)(i / sg.N);
+            const int a = sg.ws[i];
+            if (sg.acc_out) sg.acc_out[i] = a;
+            const float xs = p.x_scales[t];
+            const float y = __fmul_rn((float)a, __fmul_rn(xs, sg.w_scale));
+            if (pair) {
+                const int b = p.seg[1].ws[i];
+                if (p.seg[1].acc_out) p.seg[1].acc_out[i] = b;
+                const float u = __fmul_rn((float)b, __fmul_rn(xs, p.seg[1].w_scale));
+                if (p.epilogue == LSPK_EPI_SILU_MUL) {
+                    sg.out[i] = __fmul_rn(__fdiv_rn(y, __fadd_rn(expf(-y), 1.0f)), u);
+                } else {
+                    const float gpos = fmaxf(y, 0.0f);
+                    sg.out[i] = __fmul_rn(__fmul_rn(gpos, gpos), u);
+                }
+            } else {
+                sg.out[i] = p.epilogue == LSPK_EPI_ADD ? __fadd_rn(sg.out[i], y) : y;
+            }
+        }
     }
 }
 
@@ -391,13 +424,16 @@ static cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const
     return launch(kern, grid, dim3(kTcThreads), smem, true, mw, mx, p);
 }
 
-// Tensor-core path.  Handles STORE / ADD epilogues of one or several matrices sharing the input
-// (each matrix is its own launch); the gated pairings stay on the CUDA-core kernel.
+// Tensor-core path.  Handles STORE / ADD epilogues of one or several matrices sharing the input (each matrix is
+// its own GEMM launch) and the gated gate/up pairings (two GEMMs into the int32 workspace, gate applied by the
+// finish kernel).
 int linear_tensor_core(const lspk_linear_args* a, int* handled) {
     *handled = 0;
     static const int min_m = getenv("LSPK_TC_MIN_M") ? atoi(getenv("LSPK_TC_MIN_M")) : 32;
     if (a->M < min_m) return LSPK_OK;
-    if (a->epilogue != LSPK_EPI_STORE && a->epilogue != LSPK_EPI_ADD) return LSPK_OK;
+    const bool pair = a->epilogue == LSPK_EPI_RELU2_MUL || a->epilogue == LSPK_EPI_SILU_MUL;
+    if (a->epilogue != LSPK_EPI_STORE && a->epilogue != LSPK_EPI_ADD && !pair) return LSPK_OK;
+    if (pair && a->n_mats != 2) return LSPK_OK;
     if (a->prologue == LSPK_PRO_GATED_RMSNORM_QUANT) return LSPK_OK;
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return LSPK_OK;
@@ -451,9 +487,48 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(LSPK_ERR_CUDA, "tensor map (activations) failed: %d", (int)r);
     }
+    // ---- per-matrix split decision; the matrices of a call share one workspace, one memset, one finish ----
+    static const int knob_split = getenv("LSPK_TC_SPLITK") ? atoi(getenv("LSPK_TC_SPLITK")) : 1;
+    const int k_blocks = (Kp + kTcBK - 1) / kTcBK;
+    const int m_tiles = (M + TN - 1) / TN;
+    int splits[3] = {1, 1, 1}, kb_per[3] = {k_blocks, k_blocks, k_blocks};
+    size_t ws_off[3] = {0, 0, 0}, ws_total = 0;
+    bool any_split = false;
     for (int i = 0; i < a->n_mats; ++i) {
         const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
-        LSPK_REQUIRE(w && w->K == K && a->out[i], "linear (tensor-core): matrices must share K and have outputs");
+        LSPK_REQUIRE(w && w->K == K && (a->out[i] || (pair && i == 1)),
+                     "linear (tensor-core): matrices must share K and have outputs");
+        LSPK_REQUIRE(!pair || w->N == w0->N, "linear (tensor-core): gate and up must have the same N");
+        const int n_tiles = (w->N + kTcRows - 1) / kTcRows;
+        // K split when the output tiles alone leave most SMs idle: every CTA then streams a fraction of the
+        // bytes and runs a fraction of the K loop; partial sums meet in an int32 workspace (exact).  The gated
+        // pairing always goes through the workspace: its epilogue needs both products of an element.
+        int sp = 1;
+        if (knob_split && n_tiles * m_tiles * 2 <= sm_count()) {
+            sp = sm_count() / (n_tiles * m_tiles);
+            if (sp > 8) sp = 8;
+            if (sp > k_blocks / 2) sp = k_blocks / 2;                   // at least two K blocks per CTA
+            if (sp < 1) sp = 1;
+        }
+        kb_per[i] = (k_blocks + sp - 1) / sp;
+        splits[i] = (k_blocks + kb_per[i] - 1) / kb_per[i];             // no CTA without work
+        if (splits[i] > 1 || pair) {
+            ws_off[i] = ws_total;
+            ws_total += (size_t)M * w->N;
+            any_split = true;
+        }
+    }
+    if (any_split) {
+        if (int rc = grow((void**)&g_tc.split_ws, &g_tc.cap_ws, ws_total * 4)) return rc;
+        LSPK_CUDA(cudaMemsetAsync(g_tc.split_ws, 0, ws_total * 4, stream()));
+    }
+    FinishParams fp = {};
+    fp.M = M;
+    fp.epilogue = a->epilogue;
+    fp.x_scales = xs;
+    size_t finish_elems = 0;
+    for (int i = 0; i < a->n_mats; ++i) {
+        const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
         CUtensorMap mw;
         const cuuint64_t row_words = (cuuint64_t)w->chunks * 64;          // 4-byte units per row group
         const cuuint64_t dims[2] = {row_words, (cuuint64_t)w->groups};
@@ -464,6 +539,7 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(LSPK_ERR_CUDA, "tensor map (weights) failed: %d", (int)r);
+        const bool via_ws = splits[i] > 1 || pair;
         TcParams p = {};
         p.out = a->out[i];
         p.acc_out = a->acc_out[i];
@@ -472,39 +548,29 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
         p.M = M;
         p.N = w->N;
         p.K = K;
-        p.k_blocks = (Kp + kTcBK - 1) / kTcBK;
+        p.k_blocks = k_blocks;
+        p.kb_per_split = kb_per[i];
         p.epilogue = a->epilogue;
         p.error_flag = g_tc.err;
-        const int n_tiles = (w->N + kTcRows - 1) / kTcRows, m_tiles = (M + TN - 1) / TN;
-        // K split when the output tiles alone leave most SMs idle: every CTA then streams a fraction of the
-        // bytes and runs a fraction of the K loop; partial sums meet in an int32 workspace (exact)
-        static const int knob_split = getenv("LSPK_TC_SPLITK") ? atoi(getenv("LSPK_TC_SPLITK")) : 1;
-        int splits = 1;
-        if (knob_split && n_tiles * m_tiles * 2 <= sm_count()) {
-            splits = sm_count() / (n_tiles * m_tiles);
-            if (splits > 8) splits = 8;
-            if (splits > p.k_blocks / 2) splits = p.k_blocks / 2;      // at least two K blocks per CTA
-            if (splits < 1) splits = 1;
-        }
-        p.kb_per_split = (p.k_blocks + splits - 1) / splits;
-        splits = (p.k_blocks + p.kb_per_split - 1) / p.kb_per_split;     // no CTA without work
-        if (splits > 1) {
-            if (int rc = grow((void**)&g_tc.split_ws, &g_tc.cap_ws, (size_t)M * w->N * 4)) return rc;
-            LSPK_CUDA(cudaMemsetAsync(g_tc.split_ws, 0, (size_t)M * w->N * 4, stream()));
-            p.split_ws = g_tc.split_ws;
-        }
-        const dim3 grid(n_tiles, m_tiles, splits);
+        p.split_ws = via_ws ? g_tc.split_ws + ws_off[i] : nullptr;
+        const int n_tiles = (w->N + kTcRows - 1) / kTcRows;
+        const dim3 grid(n_tiles, m_tiles, splits[i]);
         cudaError_t e = TN == 128 ? launch_tc<128>(mw, mx, p, grid)
                        : TN == 64 ? launch_tc<64>(mw, mx, p, grid)
                                   : launch_tc<32>(mw, mx, p, grid);
-        if (e == cudaSuccess && splits > 1) {
-            const size_t total = (size_t)M * w->N;
-            int fgrid = (int)((total + 255) / 256);
-            if (fgrid > sm_count() * 4) fgrid = sm_count() * 4;
-            e = launch(splitk_finish_kernel, dim3(fgrid), dim3(256), 0, true, (const int32_t*)g_tc.split_ws, p.out, p.acc_out,
-                       xs, w->scale, M, w->N, a->epilogue);
-        }
         if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
+        if (via_ws) {
+            fp.seg[fp.n_seg++] = FinishSeg{g_tc.split_ws + ws_off[i], a->out[i], a->acc_out[i], w->scale, w->N};
+            finish_elems += (size_t)M * w->N;
+        }
+    }
+    if (fp.n_seg > 0) {
+        if (pair) finish_elems /= 2;
+        int fgrid = (int)((finish_elems / (size_t)fp.n_seg + 255) / 256);
+        if (fgrid > sm_count() * 4) fgrid = sm_count() * 4;
+        if (fgrid < 1) fgrid = 1;
+        cudaError_t e = launch(splitk_finish_kernel, dim3(fgrid), dim3(256), 0, true, fp);
+        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "tensor-core finish launch failed: %s", cudaGetErrorString(e));
     }
     *handled = 1;
     return LSPK_OK;

@@ -331,14 +331,8 @@ static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool
         if (int rc = linear(1, which, outs, s->attn, s->xq_h, bitnet ? &L.norm[LSPK_NORM_ATTN_SUB] : nullptr, H,
                             LSPK_EPI_ADD)) return rc;
     }
-    // MLP block
-    if (rows >= 32 && bitnet) {
-        // many rows: gate and up as two plain products (they take the tensor-core path), then the gate
-        const int which[2] = {LSPK_PROJ_GATE, LSPK_PROJ_UP};
-        float* outs[2] = {s->inter, s->inter2};
-        if (int rc = linear(2, which, outs, s->x, s->xq_h, &L.norm[LSPK_NORM_POST_ATTN], H, LSPK_EPI_STORE)) return rc;
-        if (int rc = lspk_relu2_mul_rows(s->inter, s->inter2, s->inter, rows, I)) return rc;
-    } else {
+    // MLP block: gate and up as one call with the gate (ReLU^2 or SiLU) as its epilogue at every row count
+    {
         const int which[2] = {LSPK_PROJ_GATE, LSPK_PROJ_UP};
         float* outs[2] = {s->inter, nullptr};
         if (int rc = linear(2, which, outs, s->x, s->xq_h, &L.norm[LSPK_NORM_POST_ATTN], H,

@@ -173,7 +173,7 @@ def test_linear_ragged_shapes(port, N, Kd, M):
     W.free()
 
 
-@pytest.mark.parametrize("M", [1, 4, 8, 20])
+@pytest.mark.parametrize("M", [1, 4, 8, 20, 64, 160])
 def test_linear_fused_qkv_norm_and_epilogues(port, M):
     """Three matrices sharing one input with the RMSNorm+quantiser prologue (q/k/v), the residual
     add epilogue (o/down) and the ReLU^2 / SiLU gates (gate/up)."""
