@@ -644,6 +644,199 @@ __global__ void __launch_bounds__(kAttnThreads) attention_split_kernel(const Att
     tr.end();
 }
 
+// Prefill form: kRows consecutive query rows of one head per CTA (rows of one sequence, already rotated,
+// keys and values already in the cache).  Every key / value row is fetched once for the kRows queries
+// instead of once per query; row r attends keys 0 .. pos0 + t0 + r.  Same lane layout as the one-row
+// kernel (TPK lanes per cache row, halving exchange for the dot products).
+constexpr int kRows = 4;
+
+template <typename KVT, int D>
+__global__ void __launch_bounds__(kAttnThreads) attention_rows_kernel(const AttnParams p) {
+    constexpr int VEC = KvVec<KVT>::N;
+    constexpr int NCH = D / VEC;
+    constexpr int TPK = NCH > 32 ? 32 : NCH;
+    constexpr int CPT = NCH / TPK;
+    constexpr int NG = kAttnThreads / TPK;
+    constexpr int SB = (TPK < 8 ? TPK : 8) / CPT;      // keys per group in flight
+    constexpr int KPB = NG * SB;
+    extern __shared__ __align__(16) float at_smem[];
+    float* qs = at_smem;                           // [kRows][D]
+    float* part = qs + kRows * D;                  // [NG][kRows][D] value partial sums
+    float* sc = part + NG * kRows * D;             // [kRows][n_stride] scores / probabilities
+    __shared__ __align__(16) float red[2][kRows][8];
+    grid_dependency_launch();
+    grid_dependency_wait();
+
+    const int h = blockIdx.x, t0 = blockIdx.y * kRows;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nrows = min(kRows, p.T - t0);
+    const int G = p.Q / p.KV, kvh = h / G;
+    const int pos0 = p.pos_ptr[0] + t0;            // position of this CTA's first row
+    const int n_max = pos0 + nrows;                // keys 0 .. n_max - 1 are needed by some row
+    const int n_stride = (p.t_max + 3) & ~3;
+    const int kd = p.KV * D;
+    const KVT* ck = reinterpret_cast<const KVT*>(p.cache_k) + (size_t)kvh * D;
+    const KVT* cv = reinterpret_cast<const KVT*>(p.cache_v) + (size_t)kvh * D;
+    const int g = tid / TPK, c = tid % TPK;
+
+    for (int i = tid; i < kRows * D; i += kAttnThreads) {
+        const int r = i / D, d = i % D;
+        qs[i] = r < nrows ? p.q[(size_t)(t0 + r) * p.Q * D + (size_t)h * D + d] : 0.0f;
+    }
+    __syncthreads();
+
+    // ---- scores -----------------------------------------------------------------------------------------
+    const float inv_sqrt_d = 1.0f / sqrtf((float)D);
+    float mx[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) mx[r] = -INFINITY;
+    for (int base = 0; base < n_max; base += KPB) {
+        uint4 kbuf[SB][CPT];
+#pragma unroll
+        for (int j = 0; j < SB; ++j) {
+            const int i = base + g + j * NG;
+            if (i < n_max) {
+                const uint4* kp = reinterpret_cast<const uint4*>(ck + (size_t)i * kd);
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) kbuf[j][u] = kp[c + u * TPK];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            float qreg[CPT][VEC];
+#pragma unroll
+            for (int u = 0; u < CPT; ++u)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) qreg[u][e] = qs[r * D + (c + u * TPK) * VEC + e];
+            float dotp[SB];
+#pragma unroll
+            for (int j = 0; j < SB; ++j) {
+                const int i = base + g + j * NG;
+                float d = 0.0f;
+                if (i < n_max) {
+#pragma unroll
+                    for (int u = 0; u < CPT; ++u) {
+                        float f[VEC];
+                        KvVec<KVT>::unpack(kbuf[j][u], f);
+#pragma unroll
+                        for (int e = 0; e < VEC; ++e) d = fmaf(qreg[u][e], f[e], d);
+                    }
+                }
+                dotp[j] = d;
+            }
+#pragma unroll
+            for (int o = TPK / 2; o >= 1; o >>= 1) {
+                if (o >= SB) {
+#pragma unroll
+                    for (int j = 0; j < SB; ++j) dotp[j] += __shfl_xor_sync(0xffffffffu, dotp[j], o);
+                } else {
+                    const bool upper = (c & o) != 0;
+#pragma unroll
+                    for (int k = 0; k < o; ++k) {
+                        const float send = upper ? dotp[k] : dotp[k + o];
+                        const float keep = upper ? dotp[k + o] : dotp[k];
+                        dotp[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                    }
+                }
+            }
+            if (c < SB) {
+                const int i = base + g + c * NG;
+                if (i <= pos0 + r && r < nrows) {            // causal: row r sees keys up to its own position
+                    const float sv = __fmul_rn(dotp[0], inv_sqrt_d);
+                    sc[r * n_stride + i] = sv;
+                    mx[r] = fmaxf(mx[r], sv);
+                }
+            }
+        }
+    }
+    // ---- softmax of every row: one barrier for the kRows maxima, one for the sums ----------------------------
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const uint32_t u = __reduce_max_sync(0xffffffffu, float_to_ordered(mx[r]));
+        if (lane == 0) red[0][r][warp] = ordered_to_float(u);
+    }
+    __syncthreads();
+    float sum[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const float4 a = *reinterpret_cast<const float4*>(red[0][r]), b = *reinterpret_cast<const float4*>(red[0][r] + 4);
+        mx[r] = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+        sum[r] = 0.0f;
+        if (r < nrows) {
+            for (int i = tid; i <= pos0 + r; i += kAttnThreads) {
+                const float e = expf(sc[r * n_stride + i] - mx[r]);
+                sc[r * n_stride + i] = e;
+                sum[r] += e;
+            }
+        }
+        const float ws = warp_sum(sum[r]);
+        if (lane == 0) red[1][r][warp] = ws;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+        const float4 a = *reinterpret_cast<const float4*>(red[1][r]), b = *reinterpret_cast<const float4*>(red[1][r] + 4);
+        const float total = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+        if (r < nrows)
+            for (int i = tid; i <= pos0 + r; i += kAttnThreads) sc[r * n_stride + i] = __fdiv_rn(sc[r * n_stride + i], total);
+    }
+    __syncthreads();
+
+    // ---- weighted sums of values -----------------------------------------------------------------------------
+    float o[kRows][CPT][VEC];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+        for (int u = 0; u < CPT; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o[r][u][e] = 0.0f;
+    constexpr int VB = 8 / CPT;
+    for (int i0 = g; i0 < n_max; i0 += NG * VB) {
+        uint4 buf[VB][CPT];
+#pragma unroll
+        for (int b = 0; b < VB; ++b) {
+            const int i = i0 + b * NG;
+            if (i < n_max) {
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) buf[b][u] = *(reinterpret_cast<const uint4*>(cv + (size_t)i * kd) + c + u * TPK);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < VB; ++b) {
+            const int i = i0 + b * NG;
+            if (i < n_max) {
+#pragma unroll
+                for (int u = 0; u < CPT; ++u) {
+                    float f[VEC];
+                    KvVec<KVT>::unpack(buf[b][u], f);
+#pragma unroll
+                    for (int r = 0; r < kRows; ++r) {
+                        if (i <= pos0 + r) {
+                            const float pi = sc[r * n_stride + i];
+#pragma unroll
+                            for (int e = 0; e < VEC; ++e) o[r][u][e] = fmaf(pi, f[e], o[r][u][e]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+        for (int u = 0; u < CPT; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) part[(g * kRows + r) * D + (c + u * TPK) * VEC + e] = o[r][u][e];
+    __syncthreads();
+    for (int i = tid; i < nrows * D; i += kAttnThreads) {
+        const int r = i / D, d = i % D;
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NG; ++w) acc += part[(w * kRows + r) * D + d];
+        p.out[(size_t)(t0 + r) * p.Q * D + (size_t)h * D + d] = acc;
+    }
+}
+
 template <typename KVT>
 static int attention_launch_t(const AttnParams& p) {
     const int D = p.D;
@@ -665,6 +858,28 @@ static int attention_launch_t(const AttnParams& p) {
     if (!p.fused) {
         const size_t rs = (size_t)(p.Q + p.KV) * D * sizeof(float);
         LSPK_CUDA(launch(rope_store_kernel<KVT>, dim3(p.T), dim3(kAttnThreads), rs, true, p));
+    }
+    static const int knob_rows = getenv("LSPK_ATTN_ROWS") ? atoi(getenv("LSPK_ATTN_ROWS")) : 1;
+    if (knob_rows && !p.fused && !p.pos_per_row && p.T >= 2 * kRows) {
+        // many consecutive rows of one sequence: kRows query rows per CTA share every key / value row they fetch
+        const int nch2 = D / VEC, tpk2 = nch2 > 32 ? 32 : nch2;
+        const size_t sm = (size_t)(kRows * D + (kAttnThreads / tpk2) * kRows * D + kRows * ((p.t_max + 3) & ~3)) * sizeof(float);
+        if (sm <= 200 * 1024) {
+            static bool rows_attr_set = false;
+            if (!rows_attr_set) {
+                LSPK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<KVT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                LSPK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<KVT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                LSPK_CUDA(cudaFuncSetAttribute(attention_rows_kernel<KVT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+                rows_attr_set = true;
+            }
+            const dim3 rgrid(p.Q, (p.T + kRows - 1) / kRows);
+            cudaError_t re;
+            if (D == 64) re = launch(attention_rows_kernel<KVT, 64>, rgrid, dim3(kAttnThreads), sm, true, p);
+            else if (D == 128) re = launch(attention_rows_kernel<KVT, 128>, rgrid, dim3(kAttnThreads), sm, true, p);
+            else re = launch(attention_rows_kernel<KVT, 256>, rgrid, dim3(kAttnThreads), sm, true, p);
+            if (re != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention (rows) launch failed: %s", cudaGetErrorString(re));
+            return LSPK_OK;
+        }
     }
     static const int knob_split = getenv("LSPK_ATTN_SPLIT") ? atoi(getenv("LSPK_ATTN_SPLIT")) : 1;
     if (p.fused && knob_split && p.Q * p.T * kSplit <= 2 * sm_count() + kSplit) {
