@@ -1,6 +1,8 @@
-// Ternary linear layer on CUDA cores: y[m, n] = float(sum_k w[n,k] * xq[m,k]) * (xscale[m] * wscale)
-// for M = 1 .. 8 token rows per CTA, with the activation quantiser (and optionally the RMSNorm
-// in front of it) fused in as a prologue and the residual add / ReLU^2 gate fused as epilogue.
+// Ternary linear layer on CUDA cores: y[m, n] = float(sum_k w[n,k] * xq[m,k]) * (xscale[m] * wscale),
+// with the activation quantiser (and optionally the RMSNorm in front of it) fused in as a prologue and
+// the residual add / ReLU^2 gate fused as epilogue.  The kernel is written for MT token rows per CTA
+// tile; only MT = 1 (the decode GEMV) is instantiated: two and more rows go to the tensor-core kernels
+// (linear_mma.cu, gemm_tc.cu), expert-grouped launches to linear_mma.cu.
 //
 // Replaces matmul_lut_avx512_m1 / _mT (matmul_lut_avx512_extern_c.cpp:150-236, 258-339) and,
 // through the prologue / epilogue switches, quantize_activation (:425-466),
