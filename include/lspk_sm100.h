@@ -110,7 +110,7 @@ typedef struct {
     lspk_weight_t w[3];
     float* out[3];               /* fp32 [M, N_i] row-major (RELU2_MUL: only out[0], [M,N])  */
     int n_mats;
-    int M;                       /* token rows, 1..LSPK_MAX_GEMV_M for lspk_gemv           */
+    int M;                       /* token rows, any M >= 1                                  */
     int prologue, epilogue;
     const float* x_f32;          /* [M,K] for QUANT / RMSNORM_QUANT                         */
     const int8_t* x_i8;          /* [M,K] for INT8                                          */
@@ -127,9 +127,12 @@ typedef struct {
 
 #define LSPK_MAX_GEMV_M 8
 /* Replaces matmul_lut_{tag}_m1 / _mT (matmul_lut_avx512_extern_c.cpp:150-236, 258-339) plus
- * the helpers fused around them.  Any M >= 1: rows are processed in tiles of up to
- * LSPK_MAX_GEMV_M tokens by the CUDA-core kernel; lspk_linear picks the tcgen05 tensor-core
- * GEMM instead when M is large enough and the shape allows it. */
+ * the helpers fused around them.  Any M >= 1.  One row: the dp4a GEMV with the prologue fused in.
+ * 2..31 rows: tiles of LSPK_MAX_GEMV_M rows on the warp-level int8 tensor cores (mma.sync).  From 32
+ * rows: the TMA + tcgen05 GEMM (all four epilogues; the gated prologue stays on the tile kernel).
+ * With more than one row of fp32 input the rows are normalised + quantised once, by a separate kernel,
+ * into library scratch that grows with cudaMalloc: make the first call of a new size outside stream
+ * capture. */
 int lspk_linear(const lspk_linear_args* a);
 int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tcgen05 only */
 /* The tcgen05 kernel bounds every device-side wait; this reads and clears its expiry flag
