@@ -1,4 +1,4 @@
-"""CPU oracle for the two blocks BASELINE's hybrid configuration asks for and the reference does
+"""CPU oracle for the two blocks of the hybrid (Mamba-2 + MoE) configuration that the reference does
 not contain: the packed-expert ternary MoE layer and the Mamba-2 selective-state-update decode
 step.  TEST INFRASTRUCTURE ONLY.
 

@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory from the REFERENCE itself.
 
-Run in a container that has the reference tree (default /root/reference) and its compiled
+Run where the reference tree is present (its location: environment variable LSPK_REFERENCE_ROOT) with its compiled
 kernels under oracle/_ref (``make -C oracle ref``):
 
     python tests/golden/make_golden.py
