@@ -51,6 +51,7 @@ import __graft_entry__ as entry  # noqa: E402
 
 PROMPT_LEN = 128
 GEN_LEN = 128
+N_STREAMS = int(os.environ.get("LSPK_BENCH_STREAMS", "8"))   # forked streams of the independent-launch GEMV measurement
 METRIC = "tg128 decode tok/s at BitNet-2B shape; ternary GEMV GB/s vs B200 HBM peak"
 
 
@@ -219,9 +220,56 @@ def bench_tp_mlp(dist, rank, world, model, lib, K):
             "bytes_gathered_per_block": 4 * (I + H)}
 
 
+def measure_shape(lib, dev, K, synthetic, rng, peak, name, Ms):
+    """One BitNet-2B projection shape at the token counts Ms: fused-quantiser linear launches rotated over
+    enough device copies of the matrix to exceed the L2 (about 300 MB), as a dependency chain; for one token
+    row also as independent graph nodes, in both scheduling modes of the GEMV."""
+    rows = []
+    N, Kd = synthetic.BITNET_2B_SHAPES[name]
+    proj = synthetic.random_projection_fast(rng, N, Kd)
+    n_copies = max(2, int(np.ceil(300e6 / (N * Kd / 4))))
+    copies = [dev.DeviceWeight(proj.w_packed, proj.scale) for _ in range(n_copies)]
+    handles = (ctypes.c_void_p * n_copies)(*[c.handle for c in copies])
+    for M in Ms:
+        x = dev.DeviceArray.from_numpy(rng.standard_normal((M, Kd)).astype(np.float32))
+        y = dev.DeviceArray((M, N), np.float32)
+        ms = ctypes.c_float(0.0)
+        reps = 20 if M <= 8 else 5
+        K.check(lib.lspk_bench_linear_copies(handles, n_copies, x.ptr, y.ptr, M, reps, ctypes.byref(ms)))
+        K.check(lib.lspk_tc_check_error())
+        us = 1000.0 * ms.value / (reps * n_copies)
+        nbytes = N * Kd / 4 + 4 * M * Kd + 4 * M * N
+        ops = 2.0 * M * N * Kd
+        row = {"shape": name, "N": N, "K": Kd, "M": M, "us": us, "GBps": nbytes / us / 1e3,
+               "frac_hbm": nbytes / us / 1e3 / peak, "TOPS": ops / us / 1e6,
+               "path": "tcgen05" if M >= 32 else ("mma.sync" if M > 1 else "dp4a")}
+        if M == 1:
+            # the same launches as independent graph nodes (forked streams): the kernel's amortised
+            # throughput when it is not a link of a dependency chain.  Fused quantiser, then the reference
+            # kernel's own contract (int8 vector + scale in), each in both scheduling modes.
+            y8 = dev.DeviceArray((N_STREAMS, N), np.float32)
+            nb8 = N * Kd / 4 + Kd + 4 * N
+            for mode, mname in ((K.GEMV_LATENCY, "latency"), (K.GEMV_THROUGHPUT, "throughput")):
+                K.check(lib.lspk_set_gemv_mode(mode))
+                for int8_in, tag, nb in ((0, "", nbytes), (1, "_int8", nb8)):
+                    K.check(lib.lspk_bench_linear_copies_independent(handles, None, n_copies, x.ptr, y8.ptr, 1, reps,
+                                                                     N_STREAMS, int8_in, ctypes.byref(ms)))
+                    ui = 1000.0 * ms.value / (reps * n_copies)
+                    key = f"independent{tag}_{mname}"
+                    row.update({f"us_{key}": ui, f"GBps_{key}": nb / ui / 1e3, f"frac_hbm_{key}": nb / ui / 1e3 / peak})
+            K.check(lib.lspk_set_gemv_mode(K.GEMV_LATENCY))
+            K.check(lib.lspk_tc_check_error())
+            y8.free()
+        rows.append(row)
+        x.free()
+        y.free()
+    for c in copies:
+        c.free()
+    return rows
+
+
 def run_sweep(args):
-    """Config 2: the five BitNet-2B projection shapes x token counts; fused-quantiser linear launches
-    rotated over enough device copies of the matrix to exceed the L2 (about 300 MB per shape)."""
+    """The BitNet-2B projection shapes x token counts (M = 1, 8, 32, 128, 512)."""
     entry.load_package()
     from litespark_inference_b200.torchless import device as dev
     from litespark_inference_b200.torchless import kernel as K
@@ -231,39 +279,41 @@ def run_sweep(args):
     rng = np.random.default_rng(0)
     rows = []
     for name in ("q", "k", "gate", "down"):
-        N, Kd = synthetic.BITNET_2B_SHAPES[name]
-        proj = synthetic.random_projection_fast(rng, N, Kd)
-        n_copies = max(2, int(np.ceil(300e6 / (N * Kd / 4))))
-        copies = [dev.DeviceWeight(proj.w_packed, proj.scale) for _ in range(n_copies)]
-        handles = (ctypes.c_void_p * n_copies)(*[c.handle for c in copies])
-        for M in (1, 8, 32, 128, 512):
-            x = dev.DeviceArray.from_numpy(rng.standard_normal((M, Kd)).astype(np.float32))
-            y = dev.DeviceArray((M, N), np.float32)
-            ms = ctypes.c_float(0.0)
-            reps = 20 if M <= 8 else 5
-            K.check(lib.lspk_bench_linear_copies(handles, n_copies, x.ptr, y.ptr, M, reps, ctypes.byref(ms)))
-            K.check(lib.lspk_tc_check_error())
-            us = 1000.0 * ms.value / (reps * n_copies)
-            nbytes = N * Kd / 4 + 4 * M * Kd + 4 * M * N
-            ops = 2.0 * M * N * Kd
-            row = {"shape": name, "N": N, "K": Kd, "M": M, "us": us, "GBps": nbytes / us / 1e3,
-                   "frac_hbm": nbytes / us / 1e3 / peak, "TOPS": ops / us / 1e6,
-                   "path": "tcgen05" if M >= 32 else ("mma.sync" if M > 1 else "dp4a")}
-            if M == 1:
-                # the same launches as independent graph nodes (8 forked streams): the kernel's amortised
-                # throughput when it is not a link of a dependency chain
-                y8 = dev.DeviceArray((8, N), np.float32)
-                K.check(lib.lspk_bench_linear_copies_independent(handles, n_copies, x.ptr, y8.ptr, 1, reps, 8, ctypes.byref(ms)))
-                ui = 1000.0 * ms.value / (reps * n_copies)
-                row.update({"us_independent": ui, "GBps_independent": nbytes / ui / 1e3,
-                            "frac_hbm_independent": nbytes / ui / 1e3 / peak})
-                y8.free()
-            rows.append(row)
-            x.free()
-            y.free()
-        for c in copies:
-            c.free()
+        rows += measure_shape(lib, dev, K, synthetic, rng, peak, name, (1, 8, 32, 128, 512))
     print(json.dumps({"workload": "sweep", "peak_GBps": peak, "peak_kind": peak_kind, "rows": rows}))
+
+
+def run_gemv(args):
+    """The single GEMV y = W x at 6912 x 2560 (the reference's own CPU-runnable kernel case): device figures as
+    in the sweep, and the reference's CPU kernel on one host core (it is single-threaded at one row)."""
+    entry.load_package()
+    from litespark_inference_b200.torchless import device as dev
+    from litespark_inference_b200.torchless import kernel as K
+    from litespark_inference_b200.torchless import synthetic
+    lib = K.load_library(True)
+    peak, peak_kind = load_peaks()
+    rng = np.random.default_rng(0)
+    row = measure_shape(lib, dev, K, synthetic, rng, peak, "gate", (1,))[0]
+    cpu = None
+    if not args.no_cpu_baseline:
+        orc = entry.load_oracle()
+        tier = orc.ref_tier()
+        kern, kind = (orc.Kernels("ref", tier), "reference") if tier is not None else (orc.Kernels("port"), "port")
+        N, Kd = synthetic.BITNET_2B_SHAPES["gate"]
+        proj = synthetic.random_projection_fast(rng, N, Kd)
+        x = rng.standard_normal((1, Kd)).astype(np.float32)
+        xq, xs = np.empty((1, Kd), np.int8), np.empty(1, np.float32)
+        kern.quantize_activation_batched(x, xq, xs)
+        times, out = [], np.empty(N, np.float32)
+        for _ in range(200):
+            t0 = time.perf_counter()
+            kern.matmul_packed_m1(xq[0], proj.w_packed, proj.scale, float(xs[0]), out)
+            times.append(time.perf_counter() - t0)
+        cpu_us = 1e6 * statistics.median(times)
+        cpu = {"value": cpu_us, "unit": "us per GEMV", "cores": 1, "kind": kind,
+               "sample": "median of 200 calls of the one-row kernel on a 6912x2560 matrix, int8 vector in"}
+    print(json.dumps({"workload": "gemv 6912x2560", "peak_GBps": peak, "peak_kind": peak_kind, "row": row,
+                      "cpu_baseline": cpu}))
 
 
 def run_hybrid(args):
@@ -301,9 +351,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="tg128", choices=["tg128", "sweep", "hybrid"],
+    ap.add_argument("--workload", default="tg128", choices=["tg128", "sweep", "gemv", "hybrid"],
                     help="tg128: the headline line; sweep: per-shape x token-count table of the ternary linear "
-                         "kernels; hybrid: Mamba-2 + MoE decode (extra lines, not the headline)")
+                         "kernels; gemv: the single 6912x2560 GEMV; hybrid: Mamba-2 + MoE decode (extra lines, "
+                         "not the headline)")
     ap.add_argument("--seqs-per-gpu", type=int, default=8, help="batch of the extra data-parallel measurement")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompt for profiler captures")
     ap.add_argument("--gen-len", type=int, default=GEN_LEN, help="fewer decode steps for profiler captures")
@@ -317,6 +368,9 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.workload == "sweep":
         run_sweep(args)
+        return
+    if args.workload == "gemv":
+        run_gemv(args)
         return
     if args.workload == "hybrid":
         run_hybrid(args)
@@ -444,17 +498,29 @@ def main():
     K.check(lib.lspk_bench_lm_head(state.handle, 20, ctypes.byref(ms), ctypes.byref(lm_bytes)))
     lm_ms = float(ms.value) / 20
     lm_gbs = lm_bytes.value / (lm_ms * 1e-3) / 1e9
-    # the single GEMV of config 1 (6912 x 2560, fused quantiser) as independent launches: the 30 layers' gate
-    # matrices (133 MB, larger than the L2) on 8 forked streams inside one graph -- what the kernel streams
-    # when it is not a link of a dependency chain
+    # the single GEMV of config 0 (6912 x 2560) as independent launches: the 30 layers' gate matrices (133 MB,
+    # larger than the L2) on 8 forked streams inside one graph -- what the kernel streams when it is not a link
+    # of a dependency chain.  Input: the int8 vector + scale of the reference kernel's contract.  Both scheduling
+    # modes, and the fused gate/up launch (two matrices, ReLU^2 epilogue) in throughput mode.
     from litespark_inference_b200.torchless import device as dev
     gate_handles = (ctypes.c_void_p * cfg.num_layers)(*[dm.projection(li, "gate_proj") for li in range(cfg.num_layers)])
+    up_handles = (ctypes.c_void_p * cfg.num_layers)(*[dm.projection(li, "up_proj") for li in range(cfg.num_layers)])
     gx = dev.DeviceArray.from_numpy(np.random.default_rng(3).standard_normal((1, cfg.hidden_size)).astype(np.float32))
-    gy = dev.DeviceArray((8, cfg.intermediate_size), np.float32)
-    K.check(lib.lspk_bench_linear_copies_independent(gate_handles, cfg.num_layers, gx.ptr, gy.ptr, 1, 20, 8, ctypes.byref(ms)))
-    gemv_us = 1000.0 * float(ms.value) / (20 * cfg.num_layers)
-    gemv_bytes = cfg.intermediate_size * cfg.hidden_size / 4 + 4 * cfg.hidden_size + 4 * cfg.intermediate_size
-    gemv_gbs = gemv_bytes / gemv_us / 1e3
+    gy = dev.DeviceArray((N_STREAMS, cfg.intermediate_size), np.float32)
+    gemv_bytes = cfg.intermediate_size * cfg.hidden_size / 4 + cfg.hidden_size + 4 * cfg.intermediate_size
+    gemv = {}
+    for mode, mname, up in ((K.GEMV_LATENCY, "latency", None), (K.GEMV_THROUGHPUT, "throughput", None),
+                            (K.GEMV_THROUGHPUT, "throughput_gate_up", up_handles)):
+        K.check(lib.lspk_set_gemv_mode(mode))
+        K.check(lib.lspk_bench_linear_copies_independent(gate_handles, up, cfg.num_layers, gx.ptr, gy.ptr, 1, 20, N_STREAMS, 1,
+                                                         ctypes.byref(ms)))
+        us = 1000.0 * float(ms.value) / (20 * cfg.num_layers)
+        nb = gemv_bytes + (cfg.intermediate_size * cfg.hidden_size / 4 if up is not None else 0)
+        gemv[mname] = {"us_per_launch": us, "bytes_per_launch": nb, "achieved": nb / us / 1e3, "frac": nb / us / 1e3 / peak}
+    K.check(lib.lspk_set_gemv_mode(K.GEMV_LATENCY))
+    K.check(lib.lspk_tc_check_error())
+    gemv_us = gemv["throughput"]["us_per_launch"]
+    gemv_gbs = gemv["throughput"]["achieved"]
     gx.free()
     gy.free()
     token_ms = total_ms / (args.steps * GEN_LEN)
@@ -531,10 +597,11 @@ def main():
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                      "launches_timed": n_launch.value * reps,
                      "how": "CUDA events around graph replays of the 120 linear launches of one token over all 30 layers' weights (521 MB, > L2)"},
-        "roofline_gemv_independent": {"kernel": "ternary_linear_kernel (M=1, 6912x2560, fused quantiser)", "bound": "hbm",
-                                      "achieved": gemv_gbs, "peak": peak, "unit": "GB/s", "frac": gemv_gbs / peak,
-                                      "us_per_launch": gemv_us, "bytes_per_launch": gemv_bytes,
-                                      "how": "the 30 layers' gate matrices as independent graph nodes on 8 forked streams, 20 replays"},
+        "roofline_gemv_independent": {"kernel": "ternary_linear_kernel (M=1, 6912x2560, int8 vector in, throughput mode)",
+                                      "bound": "hbm", "achieved": gemv_gbs, "peak": peak, "unit": "GB/s",
+                                      "frac": gemv_gbs / peak, "us_per_launch": gemv_us, "bytes_per_launch": gemv_bytes,
+                                      "modes": gemv,
+                                      "how": "the 30 layers' gate matrices as independent graph nodes on %d forked streams, 20 replays" % N_STREAMS + ""},
         "roofline_lm_head": {"kernel": "lm_head_kernel<bf16>", "bound": "hbm", "achieved": lm_gbs, "peak": peak,
                              "unit": "GB/s", "frac": lm_gbs / peak, "us_per_launch": 1000.0 * lm_ms},
         "roofline_token": {"bytes_per_token": token_bytes, "us_per_token": 1000.0 * token_ms, "achieved": token_gbs,

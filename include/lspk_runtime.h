@@ -91,9 +91,12 @@ int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32
 /* Floor cost of a kernel boundary: a graph of n_kernels empty dependent kernels, replayed reps times. */
 int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out);
 /* lspk_bench_linear_copies with the launches of a pass on n_streams forked streams (independent graph nodes):
- * the amortised throughput of the kernel outside a dependency chain.  y holds n_streams * M * N floats. */
-int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
-                                         int n_streams, float* ms_out);
+ * the amortised throughput of the kernel outside a dependency chain.  y holds n_streams * M * N floats.
+ * int8_input != 0: x is quantised once beforehand and the launches take the int8 vector + scale, which is the
+ * contract of the reference's matmul_lut_*_m1; 0: every launch quantises x itself (fused prologue).
+ * w_up != NULL: launch i is the gated pair (w[i], w_up[i]) with the ReLU^2 epilogue. */
+int lspk_bench_linear_copies_independent(const lspk_weight_t* w, const lspk_weight_t* w_up, int n_w, const float* x_f32,
+                                         float* y, int M, int reps, int n_streams, int int8_input, float* ms_out);
 
 #ifdef __cplusplus
 }

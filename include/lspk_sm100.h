@@ -135,6 +135,17 @@ typedef struct {
  * capture. */
 int lspk_linear(const lspk_linear_args* a);
 int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tcgen05 only */
+/* How the one-row product (M = 1, the reference's matmul_lut_*_m1) is scheduled.
+ *   LSPK_GEMV_LATENCY (default): for a chain of launches in which each consumes the previous one's output
+ *     (a decode step): one CTA per 16-row group, weights requested by per-lane loads before the dependency
+ *     wait.
+ *   LSPK_GEMV_THROUGHPUT: for back-to-back launches that do not depend on one another (the way the
+ *     reference's kernel benchmark calls matmul_lut_*_m1 in a loop): fewer CTAs, each with a ring of up to
+ *     four row groups in shared memory filled by bulk asynchronous copies requested at kernel entry.
+ * Results are bit-identical in both modes.  The mbarrier waits of the second mode are bounded; an expiry is
+ * reported by lspk_tc_check_error. */
+enum { LSPK_GEMV_LATENCY = 0, LSPK_GEMV_THROUGHPUT = 1 };
+int lspk_set_gemv_mode(int mode);
 /* The tcgen05 kernel bounds every device-side wait; this reads and clears its expiry flag
  * (LSPK_ERR_DEVICE_WAIT if a wait ran out since the last call).  Synchronises the stream. */
 int lspk_tc_check_error(void);

@@ -51,6 +51,9 @@ bool pdl_enabled() { return g_pdl; }
 int sm_count() { return g_sm_count; }
 
 // Lazily bind to a device the first time any entry point needs one.
+static int* g_wait_flag = nullptr;
+int* device_wait_flag() { return g_wait_flag; }
+
 int ensure_init() {
     if (g_device >= 0) return LSPK_OK;
     const char* env = getenv("LITESPARK_DEVICE");
@@ -82,6 +85,10 @@ int lspk_init(int device) {
     LSPK_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
     LSPK_CUDA(cudaEventCreate(&g_ev0));
     LSPK_CUDA(cudaEventCreate(&g_ev1));
+    if (!g_wait_flag) {
+        LSPK_CUDA(cudaMalloc((void**)&g_wait_flag, 16));
+        LSPK_CUDA(cudaMemset(g_wait_flag, 0, 16));
+    }
     g_sm_count = prop.multiProcessorCount;
     g_device = device;
     const char* p = getenv("LITESPARK_PDL");

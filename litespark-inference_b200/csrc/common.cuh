@@ -100,6 +100,10 @@ inline cudaError_t launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 // When a trace buffer is installed (lspk_trace_begin), CTA 0 of every traced kernel appends one
 // record of kTraceWords 64-bit words: [kernel id, globaltimer at entry, SM clock at up to 12 phase
 // marks, globaltimer at exit].  Word 0 of the buffer is the record counter.
+// Device int that kernels with bounded waits set to LSPK_ERR_DEVICE_WAIT when a wait runs out (allocated by
+// lspk_init; read and cleared by lspk_tc_check_error).
+int* device_wait_flag();
+
 constexpr int kTraceWords = 16;
 unsigned long long* trace_buffer();       // device pointer or nullptr
 int trace_capacity();                     // records
@@ -140,6 +144,48 @@ struct PhaseTrace {
 
 #ifdef __CUDACC__
 // ---- device helpers --------------------------------------------------------------
+
+// ---- mbarrier / bulk-copy wrappers -----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Contiguous global -> shared copy by the copy engine (both addresses 16-byte aligned, bytes a multiple of
+// 16), completion counted on `bar`; the lines are marked evict-first in L2 (read-once weight stream).
+__device__ __forceinline__ void bulk_load_stream(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
 
 // Wait until the kernels this launch depends on have completed and their writes are
 // visible.  A no-op when the launch carries no programmatic dependency.

@@ -48,29 +48,7 @@ struct TcParams {
     int* error_flag;
 };
 
-// ---- PTX wrappers ------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
+// ---- PTX wrappers (mbarrier and fences: common.cuh) --------------------------------------------
 // Bounded wait.  Returns false (and raises the CTA-wide abort flag) when the limit is reached or
 // another thread already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -87,7 +65,6 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
         : "memory");
 }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -445,10 +422,7 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
     const int8_t* xq = a->x_i8;
     const float* xs = a->x_scales;
     if (int rc = grow((void**)&g_tc.xq_perm, &g_tc.cap_perm, (size_t)M * Kp)) return rc;
-    if (!g_tc.err) {
-        LSPK_CUDA(cudaMalloc((void**)&g_tc.err, 16));
-        LSPK_CUDA(cudaMemset(g_tc.err, 0, 16));
-    }
+    g_tc.err = device_wait_flag();
     int permuted = 0;
     if (a->prologue != LSPK_PRO_INT8) {
         if (int rc = grow((void**)&g_tc.xs, &g_tc.cap_xs, (size_t)M * 4)) return rc;
@@ -578,13 +552,14 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
 
 // Reads (and clears) the device-side wait-expiry flag of the tensor-core kernel.
 int tensor_core_check_error() {
+    g_tc.err = device_wait_flag();
     if (!g_tc.err) return LSPK_OK;
     int v = 0;
     LSPK_CUDA(cudaMemcpyAsync(&v, g_tc.err, 4, cudaMemcpyDeviceToHost, stream()));
     LSPK_CUDA(cudaStreamSynchronize(stream()));
     if (v) {
         cudaMemsetAsync(g_tc.err, 0, 4, stream());
-        return fail(LSPK_ERR_DEVICE_WAIT, "tensor-core GEMM: a bounded device-side wait expired");
+        return fail(LSPK_ERR_DEVICE_WAIT, "a bounded device-side wait expired (tensor-core GEMM or bulk-copy GEMV)");
     }
     return LSPK_OK;
 }

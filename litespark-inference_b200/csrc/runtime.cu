@@ -887,25 +887,47 @@ int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32
 // `n_streams` forked streams (round-robin, one output buffer per stream), so the graph holds independent
 // kernel nodes and the GPU may overlap them.  This is the amortised single-GEMV figure: what the kernel
 // streams when it is not a link in a dependency chain.  y must hold n_streams * N floats.
-int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
-                                         int n_streams, float* ms_out) {
+int lspk_bench_linear_copies_independent(const lspk_weight_t* w, const lspk_weight_t* w_up, int n_w, const float* x_f32,
+                                         float* y, int M, int reps, int n_streams, int int8_input, float* ms_out) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(w && n_w >= 1 && x_f32 && y && M == 1 && reps >= 1 && ms_out && n_streams >= 1 && n_streams <= 16,
                  "lspk_bench_linear_copies_independent: bad arguments (one row only: more rows share library scratch)");
     const Weight* w0 = reinterpret_cast<const Weight*>(w[0]);
     const size_t y_stride = (size_t)M * w0->N;
+    // int8_input: the reference kernel's own contract (matmul_lut_*_m1 takes the quantised vector and its
+    // scale); x is quantised once, outside the timed region
+    int8_t* xq = nullptr;
+    float* xs = nullptr;
+    if (int8_input) {
+        LSPK_CUDA(cudaMalloc((void**)&xq, (size_t)w0->K + 16));
+        LSPK_CUDA(cudaMalloc((void**)&xs, 16));
+        if (int rc = lspk_quantize_rows(x_f32, xq, xs, 1, w0->K)) return rc;
+    }
     auto one = [&](int i, float* out) -> int {
         lspk_linear_args a = {};
         a.w[0] = w[i];
         a.out[0] = out;
         a.n_mats = 1;
         a.M = M;
-        a.prologue = LSPK_PRO_QUANT;
         a.epilogue = LSPK_EPI_STORE;
-        a.x_f32 = x_f32;
+        if (w_up) {                                       // the fused gate/up launch of a feed-forward block
+            a.w[1] = w_up[i];
+            a.n_mats = 2;
+            a.epilogue = LSPK_EPI_RELU2_MUL;
+        }
+        if (int8_input) {
+            a.prologue = LSPK_PRO_INT8;
+            a.x_i8 = xq;
+            a.x_scales = xs;
+        } else {
+            a.prologue = LSPK_PRO_QUANT;
+            a.x_f32 = x_f32;
+        }
         return lspk_linear(&a);
     };
     if (int rc = one(0, y)) return rc;                    // sets kernel attributes
+    // one graph holds several passes over the matrices, so that the fork and join of a replay weigh little
+    const int passes = n_w >= 256 ? 1 : (256 + n_w - 1) / n_w;
     LSPK_CUDA(cudaStreamSynchronize(main_stream()));
     cudaStream_t side[16] = {};
     cudaEvent_t fork = nullptr, join[16] = {};
@@ -923,9 +945,9 @@ int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const 
         for (int s = 0; s < n_streams; ++s) cudaStreamWaitEvent(side[s], fork, 0);
         const bool pdl_was = pdl_enabled();
         lspk_set_pdl(0);                                  // no programmatic edges: plain independent nodes
-        for (int i = 0; i < n_w && rc == LSPK_OK; ++i) {
+        for (int i = 0; i < n_w * passes && rc == LSPK_OK; ++i) {
             set_stream_override(side[i % n_streams]);
-            rc = one(i, y + (size_t)(i % n_streams) * y_stride);
+            rc = one(i % n_w, y + (size_t)(i % n_streams) * y_stride);
         }
         set_stream_override(nullptr);
         lspk_set_pdl(pdl_was ? 1 : 0);
@@ -943,6 +965,7 @@ int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const 
         for (int i = 0; i < reps && !rc; ++i)
             if (cudaGraphLaunch(exec, main_stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
         if (!rc) rc = lspk_timer_stop(ms_out);
+        if (!rc) *ms_out /= (float)passes;                // time of reps passes over the n_w matrices
         cudaStreamSynchronize(main_stream());
     }
     if (exec) cudaGraphExecDestroy(exec);
@@ -951,6 +974,8 @@ int lspk_bench_linear_copies_independent(const lspk_weight_t* w, int n_w, const 
         if (side[s]) cudaStreamDestroy(side[s]);
     }
     if (fork) cudaEventDestroy(fork);
+    if (xq) cudaFree(xq);
+    if (xs) cudaFree(xs);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "independent-launch benchmark failed: %s", cudaGetErrorString(e));
     return rc;
 }

@@ -216,6 +216,65 @@ def test_linear_fused_qkv_norm_and_epilogues(port, M):
     assert np.array_equal(dres.numpy(), res + port.matmul_packed_mT(got_q, got_s, mats["q"], scales["q"]))
 
 
+@pytest.fixture
+def throughput_mode():
+    lib = K.load_library(True)
+    K.check(lib.lspk_set_gemv_mode(K.GEMV_THROUGHPUT))
+    yield lib
+    K.check(lib.lspk_set_gemv_mode(K.GEMV_LATENCY))
+    K.check(lib.lspk_tc_check_error())         # no bounded wait of the bulk-copy kernel ran out
+
+
+@pytest.mark.parametrize("N,Kd", [SHAPES["q"], SHAPES["k"], SHAPES["gate"], SHAPES["down"], (5, 20), (33, 260),
+                                  (1, 8), (48, 12288), (7000, 1000), (16 * 700, 64)])
+def test_gemv_throughput_mode_bit_exact(port, throughput_mode, N, Kd):
+    """The bulk-copy schedule of the one-row product (ring of row groups in shared memory, several groups per
+    CTA, ring refills at N = 11200) gives the same integers and floats as the oracle, for the int8 contract
+    and for the fused quantiser, with ragged K and N."""
+    w, packed, x, ws = _rand_case(N * 3 + Kd, N, Kd, 1)
+    xq, xs = np.empty((1, Kd), np.int8), np.empty(1, np.float32)
+    port.quantize_activation_batched(x, xq, xs)
+    want_acc, want_y = port.acc_int32(xq, packed), port.matmul_packed_mT(xq, xs, packed, ws)
+    W = dev.DeviceWeight(packed, ws)
+    y, acc = dev.DeviceArray((1, N), np.float32), dev.DeviceArray((1, N), np.int32)
+    dev.linear([W], [y], 1, x_i8=dev.DeviceArray.from_numpy(xq), x_scales=dev.DeviceArray.from_numpy(xs), acc_outs=[acc])
+    assert np.array_equal(acc.numpy(), want_acc) and np.array_equal(y.numpy(), want_y)
+    y2, acc2 = dev.DeviceArray((1, N), np.float32), dev.DeviceArray((1, N), np.int32)
+    xq_t = dev.DeviceArray((1, Kd), np.int8)
+    dev.linear([W], [y2], 1, x_f32=dev.DeviceArray.from_numpy(x), acc_outs=[acc2], xq_out=xq_t)
+    assert np.array_equal(xq_t.numpy(), xq)
+    assert np.array_equal(acc2.numpy(), want_acc) and np.array_equal(y2.numpy(), want_y)
+    W.free()
+
+
+def test_gemv_throughput_mode_fused_launches(port, throughput_mode):
+    """q/k/v in one launch behind the RMSNorm prologue, the gated pair and the residual add, throughput mode
+    against latency mode: identical bits."""
+    H, I = 2560, 6912
+    rng = np.random.default_rng(123)
+    mats = {n: _rand_case(150 + i, *SHAPES[n], 1)[1] for i, n in enumerate(["q", "k", "v", "gate", "up", "down"])}
+    dW = {n: dev.DeviceWeight(mats[n], 0.5 + 0.1 * i) for i, n in enumerate(mats)}
+    dx = dev.DeviceArray.from_numpy((rng.standard_normal((1, H)) * 2.0).astype(np.float32))
+    dg = dev.DeviceArray.from_numpy(synthetic.fp32_to_bf16_u16(rng.uniform(0.5, 1.5, H).astype(np.float32)))
+    res0 = rng.standard_normal((1, H)).astype(np.float32)
+
+    def run_all():
+        outs = [dev.DeviceArray((1, SHAPES[n][0]), np.float32) for n in ("q", "k", "v")]
+        dev.linear([dW["q"], dW["k"], dW["v"]], outs, 1, x_f32=dx, gamma=dg)
+        inter = dev.DeviceArray((1, I), np.float32)
+        dev.linear([dW["gate"], dW["up"]], [inter, None], 1, x_f32=dx, gamma=dg, epilogue=K.EPI_RELU2_MUL)
+        res = dev.DeviceArray.from_numpy(res0)
+        dev.linear([dW["down"]], [res], 1, x_f32=inter, epilogue=K.EPI_ADD)
+        return [o.numpy() for o in outs] + [inter.numpy(), res.numpy()]
+
+    got = run_all()
+    K.check(throughput_mode.lspk_set_gemv_mode(K.GEMV_LATENCY))
+    want = run_all()
+    for g, w_ in zip(got, want):
+        assert np.array_equal(g, w_)
+    assert np.isfinite(got[-1]).all() and np.abs(got[-1] - res0).max() > 0
+
+
 def test_linear_is_linear_and_zero_safe(port):
     """Size-independent properties at the full gate/up shape: W(x1 + x2) = W x1 + W x2 on the integer
     accumulators, and an all-zero input gives exactly zero."""
