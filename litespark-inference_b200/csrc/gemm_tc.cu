@@ -35,17 +35,28 @@ constexpr int kTcBK = 128;               // K elements per pipeline block
 constexpr int kTcRows = 128;             // output features per CTA
 constexpr unsigned kSpinLimit = 1u << 22;
 
-struct TcParams {
+// One matrix of a launch: the matrices of a call (q/k/v; gate/up) share the activations and are covered by one
+// grid, matrix i owning the output-feature tiles [tile0, tile0 + ceil(N / 128)) of gridDim.x.
+struct TcSeg {
     float* out;
     int32_t* acc_out;
-    const float* x_scales;
+    int32_t* split_ws;       // K split / gated pairing: this CTA's K range stores its int32 partial sums in slice
+                             // blockIdx.z of this workspace ([splits][M, N]); the finish kernel adds the slices
     float w_scale;
-    int M, N, K;
+    int N;
+    int tile0;
+};
+struct TcParams {
+    TcSeg seg[3];
+    int n_seg;
+    const float* x_scales;
+    int M, K;
     int k_blocks;            // K blocks of the whole product
     int kb_per_split;        // K blocks per CTA along gridDim.z (== k_blocks when K is not split)
-    int32_t* split_ws;       // K split: int32 partial sums are added here ([M, N], zeroed by the host side)
     int epilogue;            // LSPK_EPI_STORE or LSPK_EPI_ADD
     int* error_flag;
+    unsigned long long* trace;   // optional phase trace: one record per role of CTA (0,0,0) (ids 10, 11, 12)
+    int trace_cap;
 };
 
 // ---- PTX wrappers (mbarrier and fences: common.cuh) --------------------------------------------
@@ -82,8 +93,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 
 template <int TN>
 __global__ void __launch_bounds__(kTcThreads)
-ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                       const TcParams p) {
+ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
+                       const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x,
+                       const __grid_constant__ TcParams p) {
     constexpr int kPackedBytes = kTcRows * kTcBK / 4;       // 4096
     constexpr int kATileBytes = kTcRows * kTcBK;            // 16384
     constexpr int kBTileBytes = TN * kTcBK;
@@ -102,7 +114,12 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * kTcRows;
+    int sgi = 0;
+    if (p.n_seg > 1 && (int)blockIdx.x >= p.seg[1].tile0) sgi = 1;
+    if (p.n_seg > 2 && (int)blockIdx.x >= p.seg[2].tile0) sgi = 2;
+    const TcSeg& sg = p.seg[sgi];
+    const CUtensorMap* map_w = sgi == 0 ? &map_w0 : sgi == 1 ? &map_w1 : &map_w2;
+    const int n0 = ((int)blockIdx.x - sg.tile0) * kTcRows;
     const int m0 = blockIdx.y * TN;
     // K split: this CTA's K blocks are [kb0, kb0 + nkb)
     const int kb0 = blockIdx.z * p.kb_per_split;
@@ -140,18 +157,22 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     if (warp == 0) {
         // ---------------- producer ------------------------------------------------------------
         if (lane == 0) {
+            PhaseTrace tr;
+            tr.begin(p.trace, p.trace_cap, 10, 0);
             int issued = 0;
             for (int kb = 0; kb < nkb; ++kb) {
+                if ((kb & 1) == 0) tr.mark();              // before the wait for blocks 0, 2, 4, ...
                 const int s = kb % kTcStages;
                 if (kb >= kTcStages && !mbar_wait(&empty[s], ((kb / kTcStages) - 1) & 1, abortp)) break;
                 if (*abortp) break;
                 mbar_expect_tx(&full_tma[s], kPackedBytes + kBTileBytes);
                 // packed weights: inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes
                 // = 128 units per row group), outer coordinate = row group
-                tma_load_2d(packed(s), &map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_tma[s]);
+                tma_load_2d(packed(s), map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_tma[s]);
                 tma_load_2d(b_tile(s), &map_x, (kb0 + kb) * kTcBK, m0, &full_tma[s]);
                 ++issued;
             }
+            tr.end();
             if (*abortp) {
                 // drain: wait (bounded) for every copy this thread started
                 for (int kb = 0; kb < issued; ++kb) {
@@ -164,8 +185,11 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else if (warp == 1) {
         // ---------------- MMA issuer ------------------------------------------------------------
         if (lane == 0) {
+            PhaseTrace tr;
+            tr.begin(p.trace, p.trace_cap, 11, 32);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
+                if ((kb & 1) == 0) tr.mark();
                 const int s = kb % kTcStages;
                 const uint32_t ph = (kb / kTcStages) & 1;
                 ok = mbar_wait(&full_tma[s], ph, abortp) && mbar_wait(&full_a[s], ph, abortp);
@@ -194,13 +218,17 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                  smem_u32(&acc_ready))
                              : "memory");
+            tr.end();
         }
     } else {
         // ---------------- expand packed weights -> int8 operand tile, then epilogue ---------------
         const int row = tid - 64;                         // 0..127: weight row inside the CTA tile
         const int gi = row >> 4, rr = row & 15;
         bool ok = true;
+        PhaseTrace tr;
+        tr.begin(p.trace, p.trace_cap, 12, 64);
         for (int kb = 0; kb < nkb && ok; ++kb) {
+            if ((kb & 7) == 0 && kb < 24) tr.mark();
             const int s = kb % kTcStages;
             ok = mbar_wait(&full_tma[s], (kb / kTcStages) & 1, abortp);
             if (!ok) break;
@@ -225,7 +253,9 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             mbar_arrive(&full_a[s]);
         }
         // epilogue: TMEM lane = weight row, column = token
+        tr.mark();                                         // all blocks expanded
         if (ok) ok = mbar_wait(&acc_ready, 0, abortp);
+        tr.mark();                                         // accumulators complete
         ok = __all_sync(0xffffffffu, ok);              // the tensor-memory loads below need the whole warp
         if (ok) {
             tc_fence_after();
@@ -234,6 +264,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 #pragma unroll 1
             for (int cb = 0; cb < TN / 32; ++cb) {
                 uint32_t v[32];
+                tr.mark();                                 // previous slab stored
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -247,25 +278,44 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.N) {
+                tr.mark();                                 // a 32-column slab of accumulators is in registers
+                const int t0 = m0 + cb * 32;
+                const int jmax = min(32, p.M - t0);        // token rows of this slab that exist
+                if (n < sg.N && jmax > 0) {
+                    const size_t o0 = (size_t)t0 * sg.N + n;
+                    if (sg.split_ws) {
+                        // partial sums of this K range: exact in int32, slice blockIdx.z of the workspace
+                        int32_t* wsp = sg.split_ws + (size_t)blockIdx.z * p.M * sg.N + o0;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int t = m0 + cb * 32 + j;
-                        if (t < p.M) {
-                            const int a = (int)v[j];
-                            const size_t o = (size_t)t * p.N + n;
-                            if (p.split_ws) {                      // partial sum of this K range: exact in int32
-                                atomicAdd(p.split_ws + o, a);
-                                continue;
-                            }
-                            if (p.acc_out) p.acc_out[o] = a;
-                            const float y = __fmul_rn((float)a, __fmul_rn(p.x_scales[t], p.w_scale));
-                            p.out[o] = p.epilogue == LSPK_EPI_ADD ? __fadd_rn(p.out[o], y) : y;
+                        for (int j = 0; j < 32; ++j)
+                            if (j < jmax) wsp[(size_t)j * sg.N] = (int)v[j];
+                    } else {
+                        float* outp = sg.out + o0;
+                        const float* xsp = p.x_scales + t0;
+                        if (sg.acc_out) {
+                            int32_t* accp = sg.acc_out + o0;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < jmax) accp[(size_t)j * sg.N] = (int)v[j];
+                        }
+                        if (p.epilogue == LSPK_EPI_ADD) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < jmax) {
+                                    const float y = __fmul_rn((float)(int)v[j], __fmul_rn(xsp[j], sg.w_scale));
+                                    outp[(size_t)j * sg.N] = __fadd_rn(outp[(size_t)j * sg.N], y);
+                                }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < jmax)
+                                    outp[(size_t)j * sg.N] = __fmul_rn((float)(int)v[j], __fmul_rn(xsp[j], sg.w_scale));
                         }
                     }
                 }
             }
         }
+        tr.end();
     }
     tc_fence_before();
     __syncthreads();
@@ -280,11 +330,12 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 // raw accumulators where asked for.  Up to three matrices of one call are finished by one launch; for the
 // gated epilogues segment 0 is the gate and segment 1 the up projection (same N), and only out[0] is written.
 struct FinishSeg {
-    const int32_t* ws;
+    const int32_t* ws;       // [splits][M, N]
     float* out;
     int32_t* acc_out;
     float w_scale;
     int N;
+    int splits;
 };
 struct FinishParams {
     FinishSeg seg[3];
@@ -304,12 +355,14 @@ __global__ void splitk_finish_kernel(const FinishParams p) {
         const size_t total = (size_t)p.M * sg.N;
         for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
             const int t = (int)(i / sg.N);
-            const int a = sg.ws[i];
+            int a = sg.ws[i];
+            for (int z = 1; z < sg.splits; ++z) a += sg.ws[(size_t)z * total + i];
             if (sg.acc_out) sg.acc_out[i] = a;
             const float xs = p.x_scales[t];
             const float y = __fmul_rn((float)a, __fmul_rn(xs, sg.w_scale));
             if (pair) {
-                const int b = p.seg[1].ws[i];
+                int b = p.seg[1].ws[i];
+                for (int z = 1; z < p.seg[1].splits; ++z) b += p.seg[1].ws[(size_t)z * total + i];
                 if (p.seg[1].acc_out) p.seg[1].acc_out[i] = b;
                 const float u = __fmul_rn((float)b, __fmul_rn(xs, p.seg[1].w_scale));
                 if (p.epilogue == LSPK_EPI_SILU_MUL) {
@@ -389,7 +442,7 @@ int quant_scratch(size_t M, size_t K, int8_t** q, float** s, int** sums) {
 }
 
 template <int TN>
-static cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid) {
+static cudaError_t launch_tc(const CUtensorMap* mw, const CUtensorMap& mx, const TcParams& p, dim3 grid) {
     constexpr size_t smem = (size_t)kTcStages * (kTcRows * kTcBK / 4 + kTcRows * kTcBK + TN * kTcBK) + 1024;
     static bool attr_set = false;
     auto kern = ternary_gemm_tc_kernel<TN>;
@@ -398,7 +451,7 @@ static cudaError_t launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    return launch(kern, grid, dim3(kTcThreads), smem, true, mw, mx, p);
+    return launch(kern, grid, dim3(kTcThreads), smem, true, mw[0], mw[1], mw[2], mx, p);
 }
 
 // Tensor-core path.  Handles STORE / ADD epilogues of one or several matrices sharing the input (each matrix is
@@ -449,7 +502,24 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
     if (a->xq_out) LSPK_CUDA(cudaMemcpyAsync(a->xq_out, xq, (size_t)M * K, cudaMemcpyDeviceToDevice, stream()));
     if (a->xscale_out) LSPK_CUDA(cudaMemcpyAsync(a->xscale_out, xs, (size_t)M * 4, cudaMemcpyDeviceToDevice, stream()));
 
-    const int TN = M >= 128 ? 128 : M > 32 ? 64 : 32;
+    // ---- one grid for all matrices of the call: output-feature tiles of matrix 0, 1, 2 side by side in grid.x --
+    const int k_blocks = (Kp + kTcBK - 1) / kTcBK;
+    int n_tiles[3] = {0, 0, 0}, total_tiles = 0;
+    for (int i = 0; i < a->n_mats; ++i) {
+        const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
+        LSPK_REQUIRE(w && w->K == K && (a->out[i] || (pair && i == 1)),
+                     "linear (tensor-core): matrices must share K and have outputs");
+        LSPK_REQUIRE(!pair || w->N == w0->N, "linear (tensor-core): gate and up must have the same N");
+        n_tiles[i] = (w->N + kTcRows - 1) / kTcRows;
+        total_tiles += n_tiles[i];
+    }
+    // Token rows per CTA tile.  A K block costs about the same whatever the tile's width (the loop is bound by
+    // its handshakes, not by the tensor pipe), so 256 rows per tile halve the work when the grid still fills
+    // the machine or the K loop is long; otherwise more, narrower tiles win.
+    static const int knob_tn256 = getenv("LSPK_TC_TN256") ? atoi(getenv("LSPK_TC_TN256")) : 1;
+    const bool wide = M > 128 && knob_tn256 && (total_tiles * ((M + 255) / 256) * 2 > sm_count() || k_blocks >= 32);
+    const int TN = wide ? 256 : M > 64 ? 128 : M > 32 ? 64 : 32;
+    const int m_tiles = (M + TN - 1) / TN;
     CUtensorMap mx;
     {
         const cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)M};
@@ -461,82 +531,74 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(LSPK_ERR_CUDA, "tensor map (activations) failed: %d", (int)r);
     }
-    // ---- per-matrix split decision; the matrices of a call share one workspace, one memset, one finish ----
+    // K split when the output tiles alone leave most SMs idle: every CTA then streams a fraction of the bytes and
+    // runs a fraction of the K loop; the partial sums of a K range go to their own slice of an int32 workspace
+    // and the finish kernel adds the slices (exact).  The gated pairing always goes through the workspace: its
+    // epilogue needs both products of an element.
     static const int knob_split = getenv("LSPK_TC_SPLITK") ? atoi(getenv("LSPK_TC_SPLITK")) : 1;
-    const int k_blocks = (Kp + kTcBK - 1) / kTcBK;
-    const int m_tiles = (M + TN - 1) / TN;
-    int splits[3] = {1, 1, 1}, kb_per[3] = {k_blocks, k_blocks, k_blocks};
+    int sp = 1;
+    if (knob_split && total_tiles * m_tiles * 2 <= sm_count()) {
+        sp = sm_count() / (total_tiles * m_tiles);
+        if (sp > 8) sp = 8;
+        if (sp > k_blocks / 2) sp = k_blocks / 2;                       // at least two K blocks per CTA
+        if (sp < 1) sp = 1;
+    }
+    const int kb_per = (k_blocks + sp - 1) / sp;
+    const int splits = (k_blocks + kb_per - 1) / kb_per;                // no CTA without work
+    const bool via_ws = splits > 1 || pair;
     size_t ws_off[3] = {0, 0, 0}, ws_total = 0;
-    bool any_split = false;
-    for (int i = 0; i < a->n_mats; ++i) {
-        const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
-        LSPK_REQUIRE(w && w->K == K && (a->out[i] || (pair && i == 1)),
-                     "linear (tensor-core): matrices must share K and have outputs");
-        LSPK_REQUIRE(!pair || w->N == w0->N, "linear (tensor-core): gate and up must have the same N");
-        const int n_tiles = (w->N + kTcRows - 1) / kTcRows;
-        // K split when the output tiles alone leave most SMs idle: every CTA then streams a fraction of the
-        // bytes and runs a fraction of the K loop; partial sums meet in an int32 workspace (exact).  The gated
-        // pairing always goes through the workspace: its epilogue needs both products of an element.
-        int sp = 1;
-        if (knob_split && n_tiles * m_tiles * 2 <= sm_count()) {
-            sp = sm_count() / (n_tiles * m_tiles);
-            if (sp > 8) sp = 8;
-            if (sp > k_blocks / 2) sp = k_blocks / 2;                   // at least two K blocks per CTA
-            if (sp < 1) sp = 1;
-        }
-        kb_per[i] = (k_blocks + sp - 1) / sp;
-        splits[i] = (k_blocks + kb_per[i] - 1) / kb_per[i];             // no CTA without work
-        if (splits[i] > 1 || pair) {
+    if (via_ws) {
+        for (int i = 0; i < a->n_mats; ++i) {
+            const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
             ws_off[i] = ws_total;
-            ws_total += (size_t)M * w->N;
-            any_split = true;
+            ws_total += (size_t)M * w->N * splits;
         }
-    }
-    if (any_split) {
         if (int rc = grow((void**)&g_tc.split_ws, &g_tc.cap_ws, ws_total * 4)) return rc;
-        LSPK_CUDA(cudaMemsetAsync(g_tc.split_ws, 0, ws_total * 4, stream()));
     }
+    CUtensorMap mw[3];
+    TcParams p = {};
     FinishParams fp = {};
     fp.M = M;
     fp.epilogue = a->epilogue;
     fp.x_scales = xs;
     size_t finish_elems = 0;
+    int tile0 = 0;
     for (int i = 0; i < a->n_mats; ++i) {
         const Weight* w = reinterpret_cast<const Weight*>(a->w[i]);
-        CUtensorMap mw;
         const cuuint64_t row_words = (cuuint64_t)w->chunks * 64;          // 4-byte units per row group
         const cuuint64_t dims[2] = {row_words, (cuuint64_t)w->groups};
         const cuuint64_t strides[1] = {row_words * 4};
         const cuuint32_t box[2] = {128, 8};                               // 512 bytes x 8 row groups
         const cuuint32_t estr[2] = {1, 1};
-        CUresult r = enc(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w->dev, dims, strides, box, estr,
+        CUresult r = enc(&mw[i], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w->dev, dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return fail(LSPK_ERR_CUDA, "tensor map (weights) failed: %d", (int)r);
-        const bool via_ws = splits[i] > 1 || pair;
-        TcParams p = {};
-        p.out = a->out[i];
-        p.acc_out = a->acc_out[i];
-        p.x_scales = xs;
-        p.w_scale = w->scale;
-        p.M = M;
-        p.N = w->N;
-        p.K = K;
-        p.k_blocks = k_blocks;
-        p.kb_per_split = kb_per[i];
-        p.epilogue = a->epilogue;
-        p.error_flag = g_tc.err;
-        p.split_ws = via_ws ? g_tc.split_ws + ws_off[i] : nullptr;
-        const int n_tiles = (w->N + kTcRows - 1) / kTcRows;
-        const dim3 grid(n_tiles, m_tiles, splits[i]);
-        cudaError_t e = TN == 128 ? launch_tc<128>(mw, mx, p, grid)
+        p.seg[i] = TcSeg{a->out[i], a->acc_out[i], via_ws ? g_tc.split_ws + ws_off[i] : nullptr, w->scale, w->N, tile0};
+        tile0 += n_tiles[i];
+        if (via_ws) {
+            fp.seg[fp.n_seg++] = FinishSeg{g_tc.split_ws + ws_off[i], a->out[i], a->acc_out[i], w->scale, w->N, splits};
+            finish_elems += (size_t)M * w->N;
+        }
+    }
+    for (int i = a->n_mats; i < 3; ++i) mw[i] = mw[0];
+    p.n_seg = a->n_mats;
+    p.x_scales = xs;
+    p.M = M;
+    p.K = K;
+    p.k_blocks = k_blocks;
+    p.kb_per_split = kb_per;
+    p.epilogue = a->epilogue;
+    p.error_flag = g_tc.err;
+    p.trace = trace_buffer();
+    p.trace_cap = trace_capacity();
+    {
+        const dim3 grid(total_tiles, m_tiles, splits);
+        cudaError_t e = TN == 256 ? launch_tc<256>(mw, mx, p, grid)
+                       : TN == 128 ? launch_tc<128>(mw, mx, p, grid)
                        : TN == 64 ? launch_tc<64>(mw, mx, p, grid)
                                   : launch_tc<32>(mw, mx, p, grid);
         if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "tensor-core GEMM launch failed: %s", cudaGetErrorString(e));
-        if (via_ws) {
-            fp.seg[fp.n_seg++] = FinishSeg{g_tc.split_ws + ws_off[i], a->out[i], a->acc_out[i], w->scale, w->N};
-            finish_elems += (size_t)M * w->N;
-        }
     }
     if (fp.n_seg > 0) {
         if (pair) finish_elems /= 2;
