@@ -281,6 +281,11 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
                 tr.mark();                                 // a 32-column slab of accumulators is in registers
                 const int t0 = m0 + cb * 32;
                 const int jmax = min(32, p.M - t0);        // token rows of this slab that exist
+                // scale of token row t0 + lane (one coalesced load; handed round by shuffles below)
+                const float my_scale = (!sg.split_ws && lane < jmax) ? __fmul_rn(__ldg(p.x_scales + t0 + lane), sg.w_scale) : 0.0f;
+                float sc[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sc[j] = __shfl_sync(0xffffffffu, my_scale, j);
                 if (n < sg.N && jmax > 0) {
                     const size_t o0 = (size_t)t0 * sg.N + n;
                     if (sg.split_ws) {
@@ -291,25 +296,26 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
                             if (j < jmax) wsp[(size_t)j * sg.N] = (int)v[j];
                     } else {
                         float* outp = sg.out + o0;
-                        const float* xsp = p.x_scales + t0;
                         if (sg.acc_out) {
                             int32_t* accp = sg.acc_out + o0;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
                                 if (j < jmax) accp[(size_t)j * sg.N] = (int)v[j];
                         }
+                        // every load of the slab before its first store: the stores may alias the residual as far
+                        // as the compiler knows, and would otherwise serialise 32 round trips
                         if (p.epilogue == LSPK_EPI_ADD) {
+                            float res[32];
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (j < jmax) {
-                                    const float y = __fmul_rn((float)(int)v[j], __fmul_rn(xsp[j], sg.w_scale));
-                                    outp[(size_t)j * sg.N] = __fadd_rn(outp[(size_t)j * sg.N], y);
-                                }
-                        } else {
+                            for (int j = 0; j < 32; ++j) res[j] = j < jmax ? outp[(size_t)j * sg.N] : 0.0f;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
                                 if (j < jmax)
-                                    outp[(size_t)j * sg.N] = __fmul_rn((float)(int)v[j], __fmul_rn(xsp[j], sg.w_scale));
+                                    outp[(size_t)j * sg.N] = __fadd_rn(res[j], __fmul_rn((float)(int)v[j], sc[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < jmax) outp[(size_t)j * sg.N] = __fmul_rn((float)(int)v[j], sc[j]);
                         }
                     }
                 }
