@@ -43,7 +43,7 @@ template <typename KVT>
 __global__ void __launch_bounds__(kAttnThreads) rope_store_kernel(const AttnParams p) {
     grid_dependency_launch();
     grid_dependency_wait();
-    extern __shared__ __align__(16) float rs_smem[];     // (Q + KV) * D raw q and k of this row
+    extern __shared__ __align__(16) float rs_smem[];     // (Q + KV) * D raw q and k of this row, cos | sin, raw v
     const int t = blockIdx.x, tid = threadIdx.x;
     const int pos = p.pos_per_row ? p.pos_ptr[t] : p.pos_ptr[0] + t;
     const int D = p.D, half = D / 2;
@@ -51,11 +51,21 @@ __global__ void __launch_bounds__(kAttnThreads) rope_store_kernel(const AttnPara
     float* qrow = p.q + (size_t)t * qd;
     const float* krow = p.k_cur + (size_t)t * kd;
     const float* vrow = p.v_cur + (size_t)t * kd;
+    // everything this row reads goes to shared memory first: the stores below may alias the inputs as far as
+    // the compiler knows, and loads interleaved with them would each wait for the store before
+    float* cr = rs_smem + qd + kd;
+    float* sr = cr + half;
+    float* vs = sr + half;
     for (int i = tid; i < qd; i += kAttnThreads) rs_smem[i] = qrow[i];
-    for (int i = tid; i < kd; i += kAttnThreads) rs_smem[qd + i] = krow[i];
+    for (int i = tid; i < kd; i += kAttnThreads) {
+        rs_smem[qd + i] = krow[i];
+        vs[i] = vrow[i];
+    }
+    for (int i = tid; i < half; i += kAttnThreads) {
+        cr[i] = p.rope_cos[(size_t)pos * half + i];
+        sr[i] = p.rope_sin[(size_t)pos * half + i];
+    }
     __syncthreads();
-    const float* cr = p.rope_cos + (size_t)pos * half;
-    const float* sr = p.rope_sin + (size_t)pos * half;
     for (int i = tid; i < qd; i += kAttnThreads) {
         const int hd = i / D, d = i % D;
         qrow[i] = rope_elem(rs_smem + hd * D, d, half, cr, sr);
@@ -65,7 +75,7 @@ __global__ void __launch_bounds__(kAttnThreads) rope_store_kernel(const AttnPara
     for (int i = tid; i < kd; i += kAttnThreads) {
         const int hd = i / D, d = i % D;
         ck[i] = kv_make<KVT>(rope_elem(rs_smem + qd + hd * D, d, half, cr, sr));
-        cv[i] = kv_make<KVT>(vrow[i]);
+        cv[i] = kv_make<KVT>(vs[i]);
     }
 }
 
@@ -856,7 +866,7 @@ static int attention_launch_t(const AttnParams& p) {
         attr_set = true;
     }
     if (!p.fused) {
-        const size_t rs = (size_t)(p.Q + p.KV) * D * sizeof(float);
+        const size_t rs = (size_t)((p.Q + 2 * p.KV) * D + D) * sizeof(float);
         LSPK_CUDA(launch(rope_store_kernel<KVT>, dim3(p.T), dim3(kAttnThreads), rs, true, p));
     }
     static const int knob_rows = getenv("LSPK_ATTN_ROWS") ? atoi(getenv("LSPK_ATTN_ROWS")) : 1;

@@ -351,6 +351,14 @@ struct FinishParams {
     const float* x_scales;
 };
 
+// Sum of one element over the K-range slices (at most 8): all loads issued before the first add.
+__device__ __forceinline__ int sum_slices(const int32_t* first, size_t slice, int splits) {
+    int v[8];
+#pragma unroll
+    for (int z = 0; z < 8; ++z) v[z] = z < splits ? first[(size_t)z * slice] : 0;
+    return ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+}
+
 __global__ void splitk_finish_kernel(const FinishParams p) {
     grid_dependency_launch();
     grid_dependency_wait();
@@ -361,14 +369,12 @@ __global__ void splitk_finish_kernel(const FinishParams p) {
         const size_t total = (size_t)p.M * sg.N;
         for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
             const int t = (int)(i / sg.N);
-            int a = sg.ws[i];
-            for (int z = 1; z < sg.splits; ++z) a += sg.ws[(size_t)z * total + i];
+            const int a = sum_slices(sg.ws + i, total, sg.splits);
             if (sg.acc_out) sg.acc_out[i] = a;
             const float xs = p.x_scales[t];
             const float y = __fmul_rn((float)a, __fmul_rn(xs, sg.w_scale));
             if (pair) {
-                int b = p.seg[1].ws[i];
-                for (int z = 1; z < p.seg[1].splits; ++z) b += p.seg[1].ws[(size_t)z * total + i];
+                const int b = sum_slices(p.seg[1].ws + i, total, p.seg[1].splits);
                 if (p.seg[1].acc_out) p.seg[1].acc_out[i] = b;
                 const float u = __fmul_rn((float)b, __fmul_rn(xs, p.seg[1].w_scale));
                 if (p.epilogue == LSPK_EPI_SILU_MUL) {
