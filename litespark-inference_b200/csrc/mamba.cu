@@ -40,15 +40,26 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     __shared__ float xs_s[ROWS];
     __shared__ __align__(16) float B_s[N];
     __shared__ __align__(16) float C_s[N];
-    grid_dependency_launch();
-    grid_dependency_wait();
     const int b = blockIdx.y, hh = blockIdx.x, head = hh >> 1, p0 = (hh & 1) * ROWS;
     const int tid = threadIdx.x;
+    // This thread's 16 state values are requested before the dependency wait: the state was last written by
+    // this kernel one decode step ago, not by the projection that runs in front of it, and it is the bulk
+    // of the bytes (16 KB per CTA each way against 1.3 KB of projection output).
+    float4 st[4];
+    float4* srow;
+    {
+        float* ssm0 = state + (size_t)b * state_floats + (size_t)conv_dim * 4;
+        srow = reinterpret_cast<float4*>(ssm0 + ((size_t)(head * P + p0 + (tid >> 3)) * N + (tid & 7) * 16));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) st[q] = srow[q];
+    }
+    grid_dependency_launch();
+    grid_dependency_wait();
     const float* zrow = zx + (size_t)b * in_out;
     const float* xbc_raw = zrow + d_inner;
     const float* dt_raw = zrow + d_inner + conv_dim;
     float* ring = state + (size_t)b * state_floats;              // [conv_dim][4]
-    float* ssm = ring + (size_t)conv_dim * 4;                    // [heads][P][N]
+    // behind the ring: the state matrices [heads][P][N] (srow above)
     const int pos = pos_ptr[b];
     const int slot = pos & 3;
 
@@ -78,10 +89,6 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     const int p = tid >> 3, seg = tid & 7;
     const float xv = xs_s[p];
     const float dtx = __fmul_rn(dt, xv);
-    float4* srow = reinterpret_cast<float4*>(ssm + ((size_t)(head * P + p0 + p) * N + seg * 16));
-    float4 st[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) st[q] = srow[q];
     float ysum = 0.0f;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
