@@ -68,7 +68,8 @@ int lspk_timer_stop(float* ms_out);
 /* In-kernel phase trace (measurement aid): after lspk_trace_begin, CTA 0 of each traced kernel
  * appends a record of 16 uint64 words [kernel id, globaltimer ns at entry, SM clock at phase marks
  * ..., globaltimer ns at exit]; lspk_trace_read copies the records out and clears the counter.
- * Kernels captured into a CUDA graph before lspk_trace_begin do not record. */
+ * Kernels captured into a CUDA graph before lspk_trace_begin do not record; a later call with the same or a
+ * smaller max_records keeps the buffer (graphs captured in between stay valid), a larger one replaces it. */
 int lspk_trace_begin(int max_records);
 int lspk_trace_read(unsigned long long* host_out, int max_records, int* n_out);
 

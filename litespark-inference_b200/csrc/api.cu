@@ -196,8 +196,20 @@ int lspk_flush_l2(void) {
 int lspk_trace_begin(int max_records) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE(max_records >= 1, "lspk_trace_begin: max_records must be positive");
-    if (g_trace) cudaFree(g_trace);
+    // A buffer that is large enough is kept (only its counter is cleared): graphs captured while it was
+    // installed hold its address.  A larger one replaces it; such graphs must then be rebuilt by their owner.
+    if (g_trace && max_records <= g_trace_cap) {
+        LSPK_CUDA(cudaDeviceSynchronize());
+        LSPK_CUDA(cudaMemset(g_trace, 0, 8));
+        LSPK_CUDA(cudaDeviceSynchronize());
+        return LSPK_OK;
+    }
+    if (g_trace) {
+        LSPK_CUDA(cudaDeviceSynchronize());
+        cudaFree(g_trace);
+    }
     g_trace = nullptr;
+    g_trace_cap = 0;
     const size_t bytes = (1 + (size_t)max_records * kTraceWords) * 8;
     LSPK_CUDA(cudaMalloc((void**)&g_trace, bytes));
     LSPK_CUDA(cudaMemset(g_trace, 0, bytes));

@@ -40,7 +40,14 @@ __device__ __forceinline__ void mma_u8s8(int c[4], uint32_t a0, uint32_t a1, uin
 // consecutive rows start 64 bytes apart modulo 128, which makes the quarter-warp 16-byte loads (two tokens x
 // four words) conflict-free.
 
-template <bool PAIR, bool GROUPED>
+// BULK: the packed weights of the CTA's row groups arrive in a shared-memory ring by bulk asynchronous copies
+// (one thread requests up to p.bulk_stages groups ahead, each a contiguous block of the device layout) instead of
+// per-lane register loads.  For launches that stream tens of megabytes (the expert-grouped MoE products): the
+// bytes in flight per SM then do not depend on registers or on where the CTA is in its reduction.
+constexpr int kMBulkStages = 4;
+constexpr unsigned kMBulkSpinLimit = 1u << 22;
+
+template <bool PAIR, bool GROUPED, bool BULK>
 __global__ void __launch_bounds__(kMThreads)
 ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -54,6 +61,12 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
     constexpr int kPartInts = kMWarps * kMT * 16 * (PAIR ? 2 : 1);
     float* s_scale = reinterpret_cast<float*>(part + kPartInts);               // [kMT]
     int* s_sumx = reinterpret_cast<int*>(s_scale + kMT);                       // [kMT]
+    unsigned char* ring_base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(s_sumx + kMT) + 127) & ~uintptr_t(127));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_base);                   // [kMBulkStages]
+    uint32_t* ring = reinterpret_cast<uint32_t*>(ring_base + 128);             // [stages][PAIR?2:1][chunks*64 words]
+    const int grp_words = p.chunks * 64;
+    const int stage_words = grp_words * (PAIR ? 2 : 1);
 
     const int z = GROUPED ? blockIdx.z : 0;
     const size_t w_off = GROUPED ? (size_t)z * p.grp_w_stride : 0;
@@ -110,7 +123,7 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
     PhaseTrace tr;
     tr.begin(p.trace, p.trace_cap, 3);
     tr.mark();                                          // 0: entry
-    if (!GROUPED) load_batch(s0, g0, 0, wa, wb);       // weights never depend on the previous kernel
+    if (!GROUPED && !BULK) load_batch(s0, g0, 0, wa, wb);       // weights never depend on the previous kernel
     grid_dependency_launch();
     grid_dependency_wait();
     tr.mark();                                          // 1: predecessor finished
@@ -119,6 +132,34 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
     const int* rows = GROUPED ? p.grp_rows + (size_t)z * p.grp_rows_stride : nullptr;
     const int out_m = tid >> 4, out_r = tid & 15;
     bool first_tile = true;
+
+    // BULK: the CTA's work as one sequence: for every token tile, every row group of this CTA
+    const int ngrp_cta = (int)blockIdx.x < p.total_groups ? (p.total_groups - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int tile_step = (int)gridDim.y * kMT;
+    const int ntile_cta = M_eff > (int)blockIdx.y * kMT ? (M_eff - 1 - (int)blockIdx.y * kMT) / tile_step + 1 : 0;
+    const int total_it = BULK ? ngrp_cta * ntile_cta : 0;
+    auto issue_it = [&](int it_) {                     // one thread: request sequence element it_ into its stage
+        int ss, gg;
+        locate((int)blockIdx.x + (it_ % ngrp_cta) * (int)gridDim.x, ss, gg);
+        const int st = it_ % p.bulk_stages;
+        uint32_t* dst = ring + (size_t)st * stage_words;
+        const uint32_t bytes = (uint32_t)grp_words * 4u;
+        mbar_expect_tx(&bars[st], bytes * (PAIR ? 2u : 1u));
+        const uint4* src_a = p.seg[ss].w + w_off + (size_t)gg * p.chunks * kRowsPerGroup;
+        bulk_load_stream(dst, src_a, bytes, &bars[st]);
+        if (PAIR) bulk_load_stream(dst + grp_words, p.seg[1].w + w_off + (size_t)gg * p.chunks * kRowsPerGroup, bytes, &bars[st]);
+    };
+    int it = 0;
+    int wait_failed = 0;
+    bool give_up = false;                              // CTA-uniform: a bounded wait ran out somewhere in the CTA
+    if (BULK) {
+        if (tid == 0) {
+            for (int st = 0; st < p.bulk_stages; ++st) mbar_init(&bars[st], 1);
+            fence_mbar_init();
+            for (int i = 0; i < p.bulk_stages && i < total_it; ++i) issue_it(i);
+        }
+        // the barriers are used after the __syncthreads that follows the prologue of the first tile
+    }
 
     for (int m0 = blockIdx.y * kMT; m0 < M_eff; m0 += gridDim.y * kMT) {
         const int mt = min(kMT, M_eff - m0);
@@ -131,8 +172,8 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
             if (n >= p.seg[seg_i].N) return 0.0f;
             return p.seg[seg_i].out[(size_t)out_row(out_m) * p.seg[seg_i].N + n];
         };
-        float resid = residual_of(s, g);
-        if (GROUPED || !first_tile) load_batch(s, g, 0, wa, wb);
+        float resid = BULK ? 0.0f : residual_of(s, g);
+        if (!BULK && (GROUPED || !first_tile)) load_batch(s, g, 0, wa, wb);
         first_tile = false;
 
         // ---- prologue: the tile's rows -> permuted int8 rows in shared memory ------------------------------
@@ -158,18 +199,36 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
             } else {
                 const int8_t* src = p.x_i8 + (size_t)in_row(m) * p.K;
                 int sumx = 0;
-#pragma unroll 2
-                for (int b = lane; b < nblk; b += 32) {
-                    uint32_t a[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int k = b * 16 + q * 4;
-                        a[q] = (k < p.K) ? *reinterpret_cast<const uint32_t*>(src + k) : 0u;
-                        sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                if ((p.K & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                    // whole 16-element blocks, 16-byte aligned: one load per block, four blocks in flight per lane
+                    const uint4* src4 = reinterpret_cast<const uint4*>(src);
+                    const int kblk = p.K >> 4;
+#pragma unroll 4
+                    for (int b = lane; b < nblk; b += 32) {
+                        uint4 a = make_uint4(0, 0, 0, 0);
+                        if (b < kblk) a = src4[b];
+                        sumx = __dp4a((int)a.x, 0x01010101, sumx);
+                        sumx = __dp4a((int)a.y, 0x01010101, sumx);
+                        sumx = __dp4a((int)a.z, 0x01010101, sumx);
+                        sumx = __dp4a((int)a.w, 0x01010101, sumx);
+                        uint32_t o0, o1, o2, o3;
+                        transpose4x4_bytes(a.x, a.y, a.z, a.w, o0, o1, o2, o3);
+                        *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
                     }
-                    uint32_t o0, o1, o2, o3;
-                    transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
-                    *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
+                } else {
+#pragma unroll 2
+                    for (int b = lane; b < nblk; b += 32) {
+                        uint32_t a[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int k = b * 16 + q * 4;
+                            a[q] = (k < p.K) ? *reinterpret_cast<const uint32_t*>(src + k) : 0u;
+                            sumx = __dp4a((int)a[q], 0x01010101, sumx);
+                        }
+                        uint32_t o0, o1, o2, o3;
+                        transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                        *reinterpret_cast<uint4*>(xq_row + b * 16) = make_uint4(o0, o1, o2, o3);
+                    }
                 }
                 sumx = warp_sum(sumx);
                 if (lane == 0) { s_scale[m] = p.x_scales[in_row(m)]; s_sumx[m] = sumx; }
@@ -198,6 +257,39 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                     if (PAIR) acc_b[f][c] = 0;
                 }
             const int8_t* xrow = xq + (size_t)gid * rs;            // B operand: token gid
+            if (BULK) {
+                const int st = it % p.bulk_stages;
+                const uint32_t parity = (uint32_t)(it / p.bulk_stages) & 1u;
+                bool arrived = false;
+                for (unsigned i = 0; i < kMBulkSpinLimit && !arrived; ++i) arrived = mbar_try_wait(&bars[st], parity);
+                wait_failed |= arrived ? 0 : 1;
+                const uint32_t* sa = ring + (size_t)st * stage_words + lane;
+#pragma unroll 2
+                for (int pr = warp; pr < pairs; pr += kMWarps) {
+                    const int j0 = 2 * pr;
+                    const bool two = j0 + 1 < p.chunks;
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(xrow + (size_t)(4 * j0 + t4) * 16);
+                    uint4 x1 = make_uint4(0, 0, 0, 0);
+                    if (two) x1 = *reinterpret_cast<const uint4*>(xrow + (size_t)(4 * (j0 + 1) + t4) * 16);
+                    const uint32_t xb0[4] = {x0.x, x0.y, x0.z, x0.w};
+                    const uint32_t xb1[4] = {x1.x, x1.y, x1.z, x1.w};
+                    const uint32_t a0 = sa[j0 * 64], a1 = sa[j0 * 64 + 32];
+                    const uint32_t a2 = two ? sa[(j0 + 1) * 64] : 0x55555555u, a3 = two ? sa[(j0 + 1) * 64 + 32] : 0x55555555u;
+                    uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+                    if (PAIR) {
+                        b0 = sa[grp_words + j0 * 64];
+                        b1 = sa[grp_words + j0 * 64 + 32];
+                        b2 = two ? sa[grp_words + (j0 + 1) * 64] : 0x55555555u;
+                        b3 = two ? sa[grp_words + (j0 + 1) * 64 + 32] : 0x55555555u;
+                    }
+#pragma unroll
+                    for (int f = 0; f < 4; ++f) {
+                        const uint32_t mask = 0x03030303u << (2 * f);
+                        mma_u8s8(acc_a[f], a0 & mask, a1 & mask, a2 & mask, a3 & mask, xb0[f], xb1[f]);
+                        if (PAIR) mma_u8s8(acc_b[f], b0 & mask, b1 & mask, b2 & mask, b3 & mask, xb0[f], xb1[f]);
+                    }
+                }
+            } else
             for (int base = 0;; ) {
 #pragma unroll
                 for (int i = 0; i < kMNI; ++i) {
@@ -226,7 +318,7 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                 load_batch(s, g, base, wa, wb);
             }
             tr.mark();                                             // 4+: MMAs of a row group done
-            if (has_next) load_batch(ns, ng, 0, wa, wb);           // in flight during the reduction below
+            if (!BULK && has_next) load_batch(ns, ng, 0, wa, wb);  // in flight during the reduction below
 
             // masks -> one int; C fragment: c0,c1 = (row gid, tokens 2*t4, 2*t4+1), c2,c3 = (row gid+8, same)
 #pragma unroll
@@ -240,7 +332,27 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                     part[kMWarps * kMT * 16 + (warp * kMT + tok) * 16 + row] = u;
                 }
             }
-            __syncthreads();
+            if (BULK) {
+                // every warp is done with this stage: request the element bulk_stages ahead into it.  A wait that
+                // ran out ends the CTA once its outstanding copies (bounded wait again) have landed.
+                if (__syncthreads_or(wait_failed)) {
+                    if (tid == 0) {
+                        if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+                        for (int k = it + 1; k < it + p.bulk_stages && k < total_it; ++k) {
+                            bool done = false;
+                            for (unsigned i = 0; i < kMBulkSpinLimit && !done; ++i)
+                                done = mbar_try_wait(&bars[k % p.bulk_stages], (uint32_t)(k / p.bulk_stages) & 1u);
+                        }
+                    }
+                    give_up = true;
+                } else {
+                    if (tid == 0 && it + p.bulk_stages < total_it) issue_it(it + p.bulk_stages);
+                    ++it;
+                }
+            } else {
+                __syncthreads();
+            }
+            if (give_up) break;
 
             if (tid < kMT * 16) {
                 const LinearSeg& sg = p.seg[s];
@@ -270,7 +382,7 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                             sg.out[o] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
                         }
                     } else if (p.epilogue == LSPK_EPI_ADD) {
-                        sg.out[o] = __fadd_rn(resid, ya);
+                        sg.out[o] = __fadd_rn(BULK ? sg.out[o] : resid, ya);
                     } else {
                         sg.out[o] = ya;
                     }
@@ -284,15 +396,16 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
             g = ng;
             resid = next_resid;
         }
+        if (give_up) break;
         if (!GROUPED) break;
     }
     tr.end();
 }
 
-template <bool PAIR, bool GROUPED>
+template <bool PAIR, bool GROUPED, bool BULK = false>
 static cudaError_t launch_mma(const LinearParams& p, dim3 grid, size_t smem) {
     static bool attr_set = false;
-    auto kern = ternary_linear_mma_kernel<PAIR, GROUPED>;
+    auto kern = ternary_linear_mma_kernel<PAIR, GROUPED, BULK>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
@@ -307,9 +420,18 @@ int linear_mma_launch(const LinearParams& p, bool pair, bool grouped, int grid_x
     LSPK_REQUIRE(p.prologue == LSPK_PRO_INT8 || (p.prologue == kProInt8Tiled && !grouped),
                  "linear: the eight-row kernel takes int8 rows (prologue %d)", p.prologue);
     const int Kp = p.chunks * kWeightsPerChunk;
-    const size_t smem = (size_t)kMT * mma_row_stride(Kp) + (size_t)kMWarps * kMT * 16 * (pair ? 2 : 1) * 4 + kMT * 8 + 64;
+    size_t smem = (size_t)kMT * mma_row_stride(Kp) + (size_t)kMWarps * kMT * 16 * (pair ? 2 : 1) * 4 + kMT * 8 + 64;
     LSPK_REQUIRE(smem <= 200 * 1024, "linear: K=%d too large for the 8-row activation tile (limit about 24000)", p.K);
     const dim3 grid(grid_x, grid_y, grid_z);
+    if (p.bulk_stages > 0) {
+        // expert-grouped launches only (set by the MoE layer): ring behind the tile
+        LSPK_REQUIRE(grouped && p.bulk_stages <= kMBulkStages, "linear (mma): bulk ring is for expert-grouped launches");
+        smem += 256 + (size_t)p.bulk_stages * p.chunks * 256 * (pair ? 2 : 1);
+        LSPK_REQUIRE(smem <= 200 * 1024, "linear (mma): bulk ring too large");
+        cudaError_t e = pair ? launch_mma<true, true, true>(p, grid, smem) : launch_mma<false, true, true>(p, grid, smem);
+        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear (mma, bulk) launch failed: %s", cudaGetErrorString(e));
+        return LSPK_OK;
+    }
     cudaError_t e = grouped ? (pair ? launch_mma<true, true>(p, grid, smem) : launch_mma<false, true>(p, grid, smem))
                             : (pair ? launch_mma<true, false>(p, grid, smem) : launch_mma<false, false>(p, grid, smem));
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear (mma) launch failed: %s", cudaGetErrorString(e));

@@ -233,9 +233,26 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     // At most min(E, R) experts have rows; CTAs of the others leave at once.  Two resident CTAs per SM
     // over the experts that can be active keeps enough weight bytes in flight.
     const int active = E < R ? E : R;
-    const int ctas = (2 * sm_count() + active - 1) / active;
+    int ctas = (2 * sm_count() + active - 1) / active;
+    // The expert products stream tens of megabytes per launch: the weights go through the bulk-copy ring of the
+    // eight-row kernel (LSPK_MOE_BULK = ring depth, 0 = per-lane loads).  CTAs per SM follow from the ring's size.
+    static const int knob_bulk = getenv("LSPK_MOE_BULK") ? atoi(getenv("LSPK_MOE_BULK")) : 3;
+    auto bulk_ctas = [&](int chunks, bool pair, int Kp, int* stages) -> int {
+        int st = knob_bulk > 4 ? 4 : knob_bulk;
+        const size_t stage = (size_t)chunks * 256 * (pair ? 2 : 1);
+        const size_t base = (size_t)8 * mma_row_stride(Kp) + (size_t)8 * 8 * 16 * (pair ? 2 : 1) * 4 + 8 * 8 + 64 + 256;
+        while (st > 1 && base + st * stage > 110 * 1024) --st;
+        *stages = st;
+        const size_t smem = base + st * stage + 1024;
+        int per_sm = (int)((227 * 1024) / smem);
+        if (per_sm < 1) per_sm = 1;
+        if (per_sm > 3) per_sm = 3;
+        return (per_sm * sm_count() + active - 1) / active;
+    };
     LinearParams p = {};
-    p.trace = nullptr;
+    p.error_flag = device_wait_flag();
+    p.trace = trace_buffer();
+    p.trace_cap = trace_capacity();
     p.prologue = LSPK_PRO_INT8;
     p.stream_weights = 0;
     p.grp_counts = m->counts;
@@ -255,6 +272,7 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     p.x_i8 = m->xq;
     p.x_scales = m->xs;
     p.grp_in_shift = 1;                // routed row 2*token + slot reads token's activations
+    if (knob_bulk > 0) ctas = bulk_ctas(p.chunks, true, p.chunks * kWeightsPerChunk, &p.bulk_stages);
     if (int rc = linear_launch_params(p, 8, true, true, ctas < m->groups_gu ? ctas : m->groups_gu, 1, E)) return rc;
     // SubLN + quantiser per routed row, with the row's expert's norm weights
     if (int rc = norm_quant_rows_selected(m->inter, m->sub_norm, m->sel, m->xq2, m->xs2, R, I, m->eps)) return rc;
@@ -268,6 +286,7 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     p.x_i8 = m->xq2;
     p.x_scales = m->xs2;
     p.grp_in_shift = 0;
+    if (knob_bulk > 0) ctas = bulk_ctas(p.chunks, false, p.chunks * kWeightsPerChunk, &p.bulk_stages);
     if (int rc = linear_launch_params(p, 8, false, true, ctas < m->groups_d ? ctas : m->groups_d, 1, E)) return rc;
     LSPK_CUDA(launch(moe_combine_kernel, dim3(B), dim3(256), 0, true, x, (const float*)m->ydown, (const float*)m->selw, H));
     if (sel_out) LSPK_CUDA(cudaMemcpyAsync(sel_out, m->sel, (size_t)R * 4, cudaMemcpyDeviceToDevice, stream()));
