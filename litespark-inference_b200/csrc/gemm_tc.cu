@@ -106,7 +106,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    __shared__ __align__(8) uint64_t full_tma[kTcStages];
+    __shared__ __align__(8) uint64_t full_w[kTcStages];     // packed weights of the stage have landed
+    __shared__ __align__(8) uint64_t full_tma[kTcStages];   // activation tile of the stage has landed
     __shared__ __align__(8) uint64_t full_a[kTcStages];
     __shared__ __align__(8) uint64_t empty[kTcStages];
     __shared__ __align__(8) uint64_t acc_ready;
@@ -132,6 +133,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(&full_w[s], 1);
             mbar_init(&full_tma[s], 1);
             mbar_init(&full_a[s], 128);
             mbar_init(&empty[s], 1);
@@ -152,29 +154,45 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
     volatile int* abortp = &abort_flag;
 
     grid_dependency_launch();
-    grid_dependency_wait();                 // the activations come from the previous kernel
+    // The packed weights do not depend on the previous kernel: the producer requests the first ring of them, and
+    // the expansion warps turn them into operand tiles, while that kernel is still running.  Whoever touches the
+    // activations, the scales or the outputs waits for it first.
+    auto load_weights = [&](int kb) {
+        const int s = kb % kTcStages;
+        mbar_expect_tx(&full_w[s], kPackedBytes);
+        // inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes = 128 units per row
+        // group), outer coordinate = row group
+        tma_load_2d(packed(s), map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_w[s]);
+    };
 
     if (warp == 0) {
         // ---------------- producer ------------------------------------------------------------
         if (lane == 0) {
             PhaseTrace tr;
             tr.begin(p.trace, p.trace_cap, 10, 0);
+            const int early = min(nkb, kTcStages);
+            for (int kb = 0; kb < early; ++kb) load_weights(kb);
+            grid_dependency_wait();
             int issued = 0;
             for (int kb = 0; kb < nkb; ++kb) {
                 if ((kb & 1) == 0) tr.mark();              // before the wait for blocks 0, 2, 4, ...
                 const int s = kb % kTcStages;
                 if (kb >= kTcStages && !mbar_wait(&empty[s], ((kb / kTcStages) - 1) & 1, abortp)) break;
                 if (*abortp) break;
-                mbar_expect_tx(&full_tma[s], kPackedBytes + kBTileBytes);
-                // packed weights: inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes
-                // = 128 units per row group), outer coordinate = row group
-                tma_load_2d(packed(s), map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_tma[s]);
+                if (kb >= early) load_weights(kb);
+                mbar_expect_tx(&full_tma[s], kBTileBytes);
                 tma_load_2d(b_tile(s), &map_x, (kb0 + kb) * kTcBK, m0, &full_tma[s]);
                 ++issued;
             }
             tr.end();
             if (*abortp) {
                 // drain: wait (bounded) for every copy this thread started
+                const int w_issued = issued > early ? issued : early;
+                for (int kb = 0; kb < w_issued; ++kb) {
+                    const int s = kb % kTcStages;
+                    if (kb + kTcStages >= w_issued)
+                        for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&full_w[s], (kb / kTcStages) & 1); ++i) {}
+                }
                 for (int kb = 0; kb < issued; ++kb) {
                     const int s = kb % kTcStages;
                     if (kb + kTcStages >= issued)
@@ -187,6 +205,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
         if (lane == 0) {
             PhaseTrace tr;
             tr.begin(p.trace, p.trace_cap, 11, 32);
+            grid_dependency_wait();
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 if ((kb & 1) == 0) tr.mark();
@@ -230,7 +249,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
         for (int kb = 0; kb < nkb && ok; ++kb) {
             if ((kb & 7) == 0 && kb < 24) tr.mark();
             const int s = kb % kTcStages;
-            ok = mbar_wait(&full_tma[s], (kb / kTcStages) & 1, abortp);
+            ok = mbar_wait(&full_w[s], (kb / kTcStages) & 1, abortp);
             if (!ok) break;
             const unsigned char* pk = packed(s);
             unsigned char* arow = a_tile(s) + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
@@ -253,6 +272,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
             mbar_arrive(&full_a[s]);
         }
         // epilogue: TMEM lane = weight row, column = token
+        grid_dependency_wait();                            // scales, residual and outputs belong to the chain
         tr.mark();                                         // all blocks expanded
         if (ok) ok = mbar_wait(&acc_ready, 0, abortp);
         tr.mark();                                         // accumulators complete
