@@ -17,6 +17,7 @@ import oracle_blocks as ob  # noqa: E402
 
 hyb = importlib.import_module("litespark_inference_b200.torchless.hybrid")
 dev = importlib.import_module("litespark_inference_b200.torchless.device")
+K = importlib.import_module("litespark_inference_b200.torchless.kernel")
 
 SSM_REL_TOL = 1e-4      # stated tolerance for the fp32 state-space arithmetic
 
@@ -133,6 +134,31 @@ def test_gated_norm_prologue(port):
     assert d.max() <= 1 and (d != 0).mean() < 0.05
     assert np.array_equal(acc.numpy(), port.acc_int32(gq, packed))
     assert np.array_equal(out.numpy(), port.matmul_packed_mT(gq, gs, packed, 0.75))
+
+
+def test_moe_full_shape_expert_with_two_row_tiles(port):
+    """BitNet-2B-sized experts (2560 -> 6912 -> 2560, full-size stages of the weight ring) with ten identical rows, so
+    that two experts receive ten routed rows each (two tiles of eight: the ring is streamed twice), plus two rows
+    of their own."""
+    cfg = _small_cfg(hidden_size=2560, intermediate_size=6912, num_experts=8, num_layers=2)
+    model = hyb.random_hybrid(cfg, seed=11, norm_jitter=0.1, fast=True)
+    layer = next(L for L in model.layers if L.kind == "moe")
+    rng = np.random.default_rng(3)
+    x = np.concatenate([np.tile(rng.standard_normal((1, cfg.hidden_size)), (10, 1)),
+                        rng.standard_normal((2, cfg.hidden_size))]).astype(np.float32)
+    dm = hyb.DeviceMoE(layer, cfg.rms_norm_eps)
+    dx = dev.DeviceArray.from_numpy(x)
+    sel = dev.DeviceArray((12, 2), np.int32)
+    dm.forward(dx, 12, sel)
+    got, gsel = dx.numpy(), sel.numpy()
+    assert all(np.array_equal(got[0], got[i]) for i in range(1, 10))
+    for t in (0, 10, 11):
+        tr = {}
+        want = ob.moe_layer_step(port, layer, x[t], cfg.rms_norm_eps, trace=tr)
+        assert list(gsel[t]) == tr["experts"]
+        assert np.abs(got[t] - want).max() <= 5e-3 * np.abs(want - x[t]).max()
+    dm.free()
+    assert K.load_library(True).lspk_tc_check_error() == 0      # no bounded wait of the weight ring ran out
 
 
 def test_hybrid_greedy_tokens_match_oracle(oracle, port):
