@@ -62,6 +62,10 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     // behind the ring: the state matrices [heads][P][N] (srow above)
     const int pos = pos_ptr[b];
     const int slot = pos & 3;
+    // per-head scalars and this thread's gate input: requested here so that their round trip overlaps the
+    // convolution's (they are used after the barrier below)
+    const float dt_in = dt_raw[head], dt_b = dt_bias[head], a_head = A[head], d_head = Dskip[head];
+    const float z_gate = (tid & 7) == 0 ? zrow[head * P + p0 + (tid >> 3)] : 0.0f;
 
     // depthwise conv step + SiLU for the channels this CTA needs: its 32 x-channels, all of B and C
     for (int idx = tid; idx < ROWS + 2 * N; idx += 256) {
@@ -83,9 +87,9 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     }
     __syncthreads();
 
-    const float dv = __fadd_rn(dt_raw[head], dt_bias[head]);
+    const float dv = __fadd_rn(dt_in, dt_b);
     const float dt = dv > 20.0f ? dv : log1pf(expf(dv));
-    const float dA = expf(__fmul_rn(dt, A[head]));
+    const float dA = expf(__fmul_rn(dt, a_head));
     const int p = tid >> 3, seg = tid & 7;
     const float xv = xs_s[p];
     const float dtx = __fmul_rn(dt, xv);
@@ -109,8 +113,8 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     ysum += __shfl_xor_sync(0xffffffffu, ysum, 1);
     if (seg == 0) {
         const int ch = head * P + p0 + p;
-        const float y = __fadd_rn(ysum, __fmul_rn(Dskip[head], xv));
-        vout[(size_t)b * d_inner + ch] = __fmul_rn(y, silu_f(zrow[ch]));
+        const float y = __fadd_rn(ysum, __fmul_rn(d_head, xv));
+        vout[(size_t)b * d_inner + ch] = __fmul_rn(y, silu_f(z_gate));
     }
 }
 
