@@ -459,9 +459,7 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
                 tr.mark();                           // 9+: round reduced and stored
                 __syncthreads();                     // the partial sums are rewritten by the next round
             }
-            break;                                   // one token row: a single tile
-        }
-
+        } else {
         // ---- loop over this CTA's row groups: integer dot products, reduction, epilogue ----------------
         while (true) {
             const int next_flat = flat + gridDim.x;
@@ -568,6 +566,7 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             } else {
                 load_batch(s, g, 0, wa, wb);
             }
+        }
         }
         if (!GROUPED) break;
     }
