@@ -90,6 +90,10 @@ int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32
                              float* ms_out);
 /* Floor cost of a kernel boundary: a graph of n_kernels empty dependent kernels, replayed reps times. */
 int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out);
+/* Test aid for the bounded device-side waits: launches one thread that polls an mbarrier nothing arrives on
+ * `polls` times (1..65536), gives up, and raises the library's wait flag; the next lspk_tc_check_error then
+ * returns LSPK_ERR_DEVICE_WAIT once and clears it.  Nothing faults and the context stays usable. */
+int lspk_debug_expire_wait(int polls);
 /* lspk_bench_linear_copies with the launches of a pass on n_streams forked streams (independent graph nodes):
  * the amortised throughput of the kernel outside a dependency chain.  y holds n_streams * M * N floats.
  * int8_input != 0: x is quantised once beforehand and the launches take the int8 vector + scale, which is the

@@ -658,6 +658,33 @@ int tensor_core_check_error() {
     return LSPK_OK;
 }
 
+// Exercises the expiry path of the bounded waits without any other kernel's help: one thread polls an mbarrier
+// that nothing will ever arrive on, a given number of times, then raises the wait flag and returns (the context
+// stays usable; lspk_tc_check_error reports LSPK_ERR_DEVICE_WAIT once).
+__global__ void wait_expiry_probe_kernel(int* flag, unsigned polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        fence_mbar_init();
+        bool arrived = false;
+        for (unsigned i = 0; i < polls && !arrived; ++i) arrived = mbar_try_wait(&bar, 0);
+        if (!arrived && flag) atomicExch(flag, LSPK_ERR_DEVICE_WAIT);
+    }
+}
+
+int expire_one_wait(unsigned polls) {
+    int* flag = device_wait_flag();
+    LSPK_REQUIRE(flag, "lspk_debug_expire_wait: library not initialised");
+    LSPK_CUDA(launch(wait_expiry_probe_kernel, dim3(1), dim3(32), 0, false, flag, polls));
+    return LSPK_OK;
+}
+
 }  // namespace lspk
 
 extern "C" int lspk_tc_check_error(void) { return lspk::tensor_core_check_error(); }
+
+extern "C" int lspk_debug_expire_wait(int polls) {
+    if (int rc = lspk::ensure_init()) return rc;
+    LSPK_REQUIRE(polls >= 1 && polls <= (1 << 16), "lspk_debug_expire_wait: polls must be in 1..65536");
+    return lspk::expire_one_wait((unsigned)polls);
+}

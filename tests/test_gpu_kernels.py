@@ -275,6 +275,27 @@ def test_gemv_throughput_mode_fused_launches(port, throughput_mode):
     assert np.isfinite(got[-1]).all() and np.abs(got[-1] - res0).max() > 0
 
 
+def test_bounded_wait_expiry_is_reported_and_clears(port):
+    """A device-side wait that runs out sets the library's flag; the host reads it once as LSPK_ERR_DEVICE_WAIT,
+    and the library keeps working (nothing faults, no kernel is left spinning)."""
+    lib = K.load_library(True)
+    assert lib.lspk_tc_check_error() == 0
+    K.check(lib.lspk_debug_expire_wait(2000))
+    assert lib.lspk_tc_check_error() == 6                   # LSPK_ERR_DEVICE_WAIT
+    assert b"wait expired" in lib.lspk_last_error()
+    lib.lspk_clear_error()
+    assert lib.lspk_tc_check_error() == 0                   # cleared by the read
+    N, Kd = 48, 256
+    w, packed, x, ws = _rand_case(5, N, Kd, 1)
+    xq, xs = np.empty((1, Kd), np.int8), np.empty(1, np.float32)
+    port.quantize_activation_batched(x, xq, xs)
+    W = dev.DeviceWeight(packed, ws)
+    y = dev.DeviceArray((1, N), np.float32)
+    dev.linear([W], [y], 1, x_f32=dev.DeviceArray.from_numpy(x))
+    assert np.array_equal(y.numpy(), port.matmul_packed_mT(xq, xs, packed, ws))
+    W.free()
+
+
 def test_linear_is_linear_and_zero_safe(port):
     """Size-independent properties at the full gate/up shape: W(x1 + x2) = W x1 + W x2 on the integer
     accumulators, and an all-zero input gives exactly zero."""
