@@ -135,7 +135,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
         for (int s = 0; s < kTcStages; ++s) {
             mbar_init(&full_w[s], 1);
             mbar_init(&full_tma[s], 1);
-            mbar_init(&full_a[s], 128);
+            mbar_init(&full_a[s], 4);                      // one arrival per expansion warp
             mbar_init(&empty[s], 1);
         }
         mbar_init(&acc_ready, 1);
@@ -269,7 +269,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
                 }
             }
             fence_async_smem();                            // generic-proxy writes -> visible to the tensor unit
-            mbar_arrive(&full_a[s]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_a[s]);        // 4 arrivals per stage instead of 128
         }
         // epilogue: TMEM lane = weight row, column = token
         grid_dependency_wait();                            // scales, residual and outputs belong to the chain
