@@ -43,6 +43,7 @@ enum {
 /* ------------------------------------------------------------------------------------ */
 int lspk_init(int device);              /* select the GPU for this process; idempotent   */
 int lspk_device_count(void);
+int lspk_mem_info(size_t* free_bytes, size_t* total_bytes);   /* cudaMemGetInfo of the bound GPU */
 int lspk_sm_count(void);
 const char* lspk_last_error(void);      /* last recorded message ("" if none)            */
 int lspk_error_count(void);             /* number of failures recorded so far            */
@@ -218,8 +219,10 @@ int matmul_lut_sm100_max_threads(void);
  * until exit; the call makes no cudaMalloc / cudaFree.  Host pointers in and out, like the drop-in.
  * Returns LSPK_OK, or LSPK_ERR_ARG when the matrix does not fit the array (about N*K/2 + K + 4N
  * bytes are needed: 6912 x 2560 fits, 6912 x 6912 does not).
- * The first call on a device also creates the library's stream and looks up the array's device
- * address: make that first call before any stream capture begins.  Every call reuses the same
+ * If the library is not yet bound to a GPU, the first call binds it (lspk_init: one stream, two events,
+ * no device allocation: the word its bounded waits report through is also part of the library image)
+ * and looks up the array's device address: make that first call before any stream capture begins.  The
+ * call makes the bound GPU current for the calling thread.  Every call reuses the same
  * array, and the array keeps what the previous call left; nothing needs clearing because each call
  * overwrites what it reads.  Calls are serialised on the host and run on one stream; work issued by
  * other means that touched the array at the same time on the GPU would race with them. */

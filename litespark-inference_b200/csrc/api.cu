@@ -43,6 +43,10 @@ static int g_trace_cap = 0;
 unsigned long long* trace_buffer() { return g_trace; }
 int trace_capacity() { return g_trace_cap; }
 
+static unsigned g_scratch_gen = 1;
+unsigned scratch_generation() { return g_scratch_gen; }
+void scratch_moved() { ++g_scratch_gen; }
+
 static cudaStream_t g_stream_override = nullptr;    // measurement aid: launches go here while set
 cudaStream_t stream() { return g_stream_override ? g_stream_override : g_stream; }
 cudaStream_t main_stream() { return g_stream; }
@@ -50,9 +54,14 @@ void set_stream_override(cudaStream_t s) { g_stream_override = s; }
 bool pdl_enabled() { return g_pdl; }
 int sm_count() { return g_sm_count; }
 
-// Lazily bind to a device the first time any entry point needs one.
+// Word that kernels with bounded waits set when a wait runs out.  It is part of the library image (zero when
+// the module is loaded), so binding to a device allocates nothing; its device address is looked up once.
+static __device__ int g_wait_flag_word[4];
 static int* g_wait_flag = nullptr;
 int* device_wait_flag() { return g_wait_flag; }
+int bound_device() { return g_device; }
+
+// Lazily bind to a device the first time any entry point needs one.
 
 int ensure_init() {
     if (g_device >= 0) return LSPK_OK;
@@ -78,21 +87,41 @@ int lspk_init(int device) {
     if (prop.major != 10)
         return fail(LSPK_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only",
                     device, prop.major, prop.minor);
-    LSPK_CUDA(cudaSetDevice(device));
-    if (g_stream && g_device != device) {
+    if (g_device >= 0 && g_device != device)
         return fail(LSPK_ERR_STATE, "library already bound to device %d", g_device);
+    LSPK_CUDA(cudaSetDevice(device));
+    // Nothing below allocates device memory.  Either every object exists and the library is bound, or none
+    // is kept and a later call starts again from a clean state.
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    void* flag = nullptr;
+    e = cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreate(&e0);
+    if (e == cudaSuccess) e = cudaEventCreate(&e1);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&flag, g_wait_flag_word);
+    if (e != cudaSuccess) {
+        if (e1) cudaEventDestroy(e1);
+        if (e0) cudaEventDestroy(e0);
+        if (st) cudaStreamDestroy(st);
+        return fail(LSPK_ERR_CUDA, "lspk_init: binding to device %d failed: %s", device, cudaGetErrorString(e));
     }
-    LSPK_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
-    LSPK_CUDA(cudaEventCreate(&g_ev0));
-    LSPK_CUDA(cudaEventCreate(&g_ev1));
-    if (!g_wait_flag) {
-        LSPK_CUDA(cudaMalloc((void**)&g_wait_flag, 16));
-        LSPK_CUDA(cudaMemset(g_wait_flag, 0, 16));
-    }
+    g_stream = st;
+    g_ev0 = e0;
+    g_ev1 = e1;
+    g_wait_flag = static_cast<int*>(flag);
     g_sm_count = prop.multiProcessorCount;
     g_device = device;
     const char* p = getenv("LITESPARK_PDL");
     if (p) g_pdl = atoi(p) != 0;
+    return LSPK_OK;
+}
+
+int lspk_mem_info(size_t* free_bytes, size_t* total_bytes) {
+    if (int rc = ensure_init()) return rc;
+    size_t f = 0, t = 0;
+    LSPK_CUDA(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
     return LSPK_OK;
 }
 

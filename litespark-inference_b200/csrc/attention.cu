@@ -410,6 +410,9 @@ __global__ void __launch_bounds__(kAttnThreads) attention_split_kernel(const Att
     PhaseTrace tr;
     tr.begin(p.trace, p.trace_cap, 2);
     tr.mark();                                   // 0: entry
+    // Shared memory of another CTA of the cluster may only be touched once that CTA has started: every CTA
+    // announces itself here and the matching wait sits just before the first remote store, off the critical path.
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 
     grid_dependency_launch();
     grid_dependency_wait();
@@ -624,6 +627,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_split_kernel(const Att
         for (int e = 0; e < VEC; ++e) part[g * D + (c + u * TPK) * VEC + e] = o[u][e];
     __syncthreads();
     // ---- hand (maximum, sum, partial output) to rank 0, which merges the kSplit softmax pieces --------------
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // every CTA of the cluster is running
     if (tid < D) {
         float acc = 0.0f;
 #pragma unroll

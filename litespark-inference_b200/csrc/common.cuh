@@ -19,6 +19,12 @@ void set_stream_override(cudaStream_t s);           // measurement aid: route la
 bool pdl_enabled();                                 // programmatic dependent launch on/off
 int  sm_count();
 int  ensure_init();                                 // bind to a GPU on first use
+// Library-owned device scratch (the row quantiser's buffers, the K-split workspace, the per-layer buffers of
+// the MoE and Mamba blocks) grows by free + malloc, which moves it.  A CUDA graph captured earlier holds the
+// old addresses, so whoever moves scratch bumps this counter and every graph owner compares it with the value
+// it recorded at capture and re-captures when they differ.
+unsigned scratch_generation();
+void scratch_moved();
 
 #define LSPK_CUDA(expr)                                                              \
     do {                                                                             \
@@ -100,9 +106,10 @@ inline cudaError_t launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 // When a trace buffer is installed (lspk_trace_begin), CTA 0 of every traced kernel appends one
 // record of kTraceWords 64-bit words: [kernel id, globaltimer at entry, SM clock at up to 12 phase
 // marks, globaltimer at exit].  Word 0 of the buffer is the record counter.
-// Device int that kernels with bounded waits set to LSPK_ERR_DEVICE_WAIT when a wait runs out (allocated by
-// lspk_init; read and cleared by lspk_tc_check_error).
+// Device int that kernels with bounded waits set to LSPK_ERR_DEVICE_WAIT when a wait runs out (a word of the
+// library image whose address lspk_init looks up; read and cleared by lspk_tc_check_error).
 int* device_wait_flag();
+int  bound_device();                                // ordinal of the GPU the library is bound to, -1 before
 
 constexpr int kTraceWords = 16;
 unsigned long long* trace_buffer();       // device pointer or nullptr

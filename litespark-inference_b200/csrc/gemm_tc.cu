@@ -233,10 +233,14 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
                                  smem_u32(&empty[s]))
                              : "memory");
             }
-            if (ok)
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                                 smem_u32(&acc_ready))
-                             : "memory");
+            // On the regular path this tells the epilogue warps that every MMA has completed.  After an abort
+            // nobody waits on it any more (they saw the abort flag), and the same commit + one bounded wait makes
+            // sure that no MMA issued above is still in flight when the tensor memory is freed below.
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_u32(&acc_ready))
+                         : "memory");
+            if (!ok)
+                for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&acc_ready, 0); ++i) {}
             tr.end();
         }
     } else {
@@ -249,7 +253,8 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
         for (int kb = 0; kb < nkb && ok; ++kb) {
             if ((kb & 7) == 0 && kb < 24) tr.mark();
             const int s = kb % kTcStages;
-            ok = mbar_wait(&full_w[s], (kb / kTcStages) & 1, abortp);
+            // warp-uniform: every lane polls with its own counter, and the barrier below needs the whole warp
+            ok = __all_sync(0xffffffffu, mbar_wait(&full_w[s], (kb / kTcStages) & 1, abortp));
             if (!ok) break;
             const unsigned char* pk = packed(s);
             unsigned char* arow = a_tile(s) + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
@@ -275,6 +280,7 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
         // epilogue: TMEM lane = weight row, column = token
         grid_dependency_wait();                            // scales, residual and outputs belong to the chain
         tr.mark();                                         // all blocks expanded
+        __syncwarp();
         if (ok) ok = mbar_wait(&acc_ready, 0, abortp);
         tr.mark();                                         // accumulators complete
         ok = __all_sync(0xffffffffu, ok);              // the tensor-memory loads below need the whole warp
@@ -453,8 +459,12 @@ static TcScratch g_tc;
 
 static int grow(void** p, size_t* cap, size_t need) {
     if (need <= *cap) return LSPK_OK;
+    // cudaFree waits for the device, so no kernel in flight still uses the old buffer; graphs that hold its
+    // address are re-captured by their owners (scratch_generation)
     if (*p) cudaFree(*p);
     *p = nullptr;
+    *cap = 0;
+    scratch_moved();
     LSPK_CUDA(cudaMalloc(p, need + need / 4 + 256));
     *cap = need + need / 4 + 256;
     return LSPK_OK;

@@ -36,6 +36,7 @@ struct HybridState {
     int* h_int = nullptr;
     float* h_logits = nullptr;
     cudaGraphExec_t graph = nullptr;
+    unsigned graph_gen = 0;           // scratch_generation() at capture
     int graph_nodes = 0;
     size_t bytes = 0;
 };
@@ -67,17 +68,27 @@ static int enqueue_hybrid_step(HybridState* s) {
 }
 
 static int hybrid_build_graph(HybridState* s) {
-    if (s->graph) return LSPK_OK;
+    if (s->graph && s->graph_gen == scratch_generation()) return LSPK_OK;
+    // A graph whose scratch addresses went stale (another state made a layer's buffers grow) is captured
+    // again; every buffer is already large enough for this state then, and the kernels' attributes are set.
+    const bool recapture = s->graph != nullptr;
+    if (recapture) {
+        LSPK_CUDA(cudaStreamSynchronize(stream()));
+        cudaGraphExecDestroy(s->graph);
+        s->graph = nullptr;
+    }
     // scratch of every layer is sized before capture (allocation is not allowed while capturing)
     for (auto& L : s->m->layers) {
         if (L.mamba) { if (int rc = mamba_reserve(L.mamba, s->batch)) return rc; }
         else { if (int rc = moe_reserve(L.moe, s->batch)) return rc; }
     }
-    // A plain run first: sets kernel attributes and surfaces launch errors.  It advances the
-    // recurrent state, so it is only done on a freshly reset state, which is reset again afterwards.
-    if (int rc = enqueue_hybrid_step(s)) return rc;
-    LSPK_CUDA(cudaStreamSynchronize(stream()));
-    if (int rc = lspk_hybrid_state_reset(reinterpret_cast<lspk_hybrid_state_t>(s))) return rc;
+    if (!recapture) {
+        // A plain run first: sets kernel attributes, sizes the shared scratch and surfaces launch errors.  It
+        // advances the recurrent state, so it is only done on a freshly reset state, which is reset again afterwards.
+        if (int rc = enqueue_hybrid_step(s)) return rc;
+        LSPK_CUDA(cudaStreamSynchronize(stream()));
+        if (int rc = lspk_hybrid_state_reset(reinterpret_cast<lspk_hybrid_state_t>(s))) return rc;
+    }
     cudaGraph_t g = nullptr;
     LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_hybrid_step(s);
@@ -93,6 +104,7 @@ static int hybrid_build_graph(HybridState* s) {
     e = cudaGraphInstantiate(&s->graph, g, 0);
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "hybrid graph instantiate failed: %s", cudaGetErrorString(e));
+    s->graph_gen = scratch_generation();
     return LSPK_OK;
 }
 

@@ -126,6 +126,11 @@ int mamba_reserve(Mamba* m, int B) {
     cudaFree(m->v);
     cudaFree(m->xq);
     cudaFree(m->xs);
+    m->zx = m->v = nullptr;
+    m->xq = nullptr;
+    m->xs = nullptr;
+    m->cap_B = 0;
+    scratch_moved();
     const size_t qk = (size_t)(m->cfg.hidden > m->d_inner ? m->cfg.hidden : m->d_inner);
     LSPK_CUDA(cudaMalloc((void**)&m->xq, (size_t)B * qk));
     LSPK_CUDA(cudaMalloc((void**)&m->xs, (size_t)B * 4));

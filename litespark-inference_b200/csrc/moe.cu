@@ -195,8 +195,14 @@ static int moe_alloc(void** p, size_t bytes, Moe* m) {
 // Make the per-call scratch large enough for B token rows (allocates; call before any graph capture).
 int moe_reserve(Moe* m, int B) {
     if (B <= m->cap_B) return LSPK_OK;
-    void* old[] = {m->xq, m->xq2, m->xs, m->xs2, m->selw, m->inter, m->ydown, m->sel, m->counts, m->rows};
-    for (void* p : old) cudaFree(p);
+    void** old[] = {(void**)&m->xq, (void**)&m->xq2, (void**)&m->xs, (void**)&m->xs2, (void**)&m->selw,
+                    (void**)&m->inter, (void**)&m->ydown, (void**)&m->sel, (void**)&m->counts, (void**)&m->rows};
+    for (void** p : old) {
+        cudaFree(*p);
+        *p = nullptr;
+    }
+    m->cap_B = 0;               // nothing is held until every buffer below exists
+    scratch_moved();
     const size_t R = 2 * (size_t)B;
     int rc = 0;
     rc |= moe_alloc((void**)&m->xq, (size_t)B * m->H, m);

@@ -18,7 +18,7 @@ namespace lspk {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[LSPK_NOALLOC_SCRATCH_BYTES];
 
 static std::mutex g_noalloc_mu;
-static unsigned char* g_noalloc_dev[64] = {};     // device address of the array, per device ordinal
+static unsigned char* g_noalloc_dev = nullptr;     // device address of the array on the GPU the library is bound to
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -48,17 +48,17 @@ extern "C" int matmul_lut_sm100_m1_noalloc(const int8_t* x, const uint8_t* packe
                     "array holds %zu (use matmul_lut_sm100_m1, which allocates, for larger matrices)",
                     N, K, need, (size_t)LSPK_NOALLOC_SCRATCH_BYTES);
 
-    // The array's name is only a host-side handle here: the device address has to be asked for,
-    // once per device, with that device current.
-    int dev = 0;
-    LSPK_CUDA(cudaGetDevice(&dev));
-    LSPK_REQUIRE(dev >= 0 && dev < 64, "matmul_lut_sm100_m1_noalloc: device ordinal %d not supported", dev);
-    if (!g_noalloc_dev[dev]) {
+    // The array's name is only a host-side handle here: the device address has to be asked for, with
+    // the right device current.  The library's stream lives on the GPU the library is bound to, so that
+    // GPU is made current for the calling thread (which may never have selected one) before the lookup
+    // and for every copy and launch below.
+    LSPK_CUDA(cudaSetDevice(bound_device()));
+    if (!g_noalloc_dev) {
         void* p = nullptr;
         LSPK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
-        g_noalloc_dev[dev] = static_cast<unsigned char*>(p);
+        g_noalloc_dev = static_cast<unsigned char*>(p);
     }
-    unsigned char* base = g_noalloc_dev[dev];
+    unsigned char* base = g_noalloc_dev;
     uint8_t* d_raw = base;
     uint4* d_tiled = reinterpret_cast<uint4*>(base + raw_bytes);
     int8_t* d_x = reinterpret_cast<int8_t*>(base + raw_bytes + tiled_bytes);

@@ -62,6 +62,7 @@ struct State {
     float* h_logits = nullptr;        // pinned staging for logits
     std::vector<int> host_pos;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};   // [0] no logits store, [1] with logits
+    unsigned graph_gen[2] = {0, 0};   // scratch_generation() at capture: a later move of library scratch voids the graph
     int graph_nodes = 0;
     size_t bytes = 0;
     size_t kv_elem() const { return kv_fp16 ? 2 : 4; }
@@ -380,7 +381,14 @@ static int enqueue_step(State* s, bool store_logits) {
 }
 
 static int build_graph(State* s, int variant) {
-    if (s->graph[variant]) return LSPK_OK;
+    if (s->graph[variant] && s->graph_gen[variant] == scratch_generation()) return LSPK_OK;
+    if (s->graph[variant]) {
+        // library scratch whose addresses the graph holds was moved by a later call (a larger prefill, a
+        // state of another batch size): capture again
+        LSPK_CUDA(cudaStreamSynchronize(stream()));
+        cudaGraphExecDestroy(s->graph[variant]);
+        s->graph[variant] = nullptr;
+    }
     // First run the step once outside capture: it sets the kernels' shared-memory attributes
     // (not allowed while capturing) and surfaces launch errors directly.  The warm-up must not
     // change the state: save and restore the control block around it.
@@ -408,6 +416,7 @@ static int build_graph(State* s, int variant) {
     e = cudaGraphInstantiate(&s->graph[variant], g, 0);
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    s->graph_gen[variant] = scratch_generation();
     return LSPK_OK;
 }
 

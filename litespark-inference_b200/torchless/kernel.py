@@ -60,6 +60,7 @@ GEMV_LATENCY, GEMV_THROUGHPUT = 0, 1          # lspk_set_gemv_mode
 _SIGNATURES = {
     "lspk_init": ([_ci], _ci),
     "lspk_device_count": ([], _ci),
+    "lspk_mem_info": ([ctypes.POINTER(_sz), ctypes.POINTER(_sz)], _ci),
     "lspk_sm_count": ([], _ci),
     "lspk_last_error": ([], ctypes.c_char_p),
     "lspk_error_count": ([], _ci),

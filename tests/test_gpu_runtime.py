@@ -113,6 +113,35 @@ def test_batched_sequences_equal_single_sequences(toy):
     assert together == alone
 
 
+def test_decode_graph_survives_scratch_growth(toy, oracle, port):
+    """A batched state's decode graph holds the addresses of library scratch (quantised rows).  A later
+    prefill of more rows makes that scratch grow, i.e. move; the next decode step must notice and capture its
+    graph again instead of replaying stale addresses.  Every step is checked against the oracle, sequence by
+    sequence."""
+    cfg, m, dm = toy
+    B, t_max = 4, 160
+    rng = np.random.default_rng(31)
+    st = rt.init_state(dm, t_max, batch=B, kv_dtype="fp32")
+    osts = [oracle.State(cfg, t_max) for _ in range(B)]
+
+    def step(tokens):
+        _, lg = rt.forward_step(st, tokens, want_logits=True)
+        for b in range(B):
+            assert _close(lg[b], oracle.forward_one(port, m, osts[b], int(tokens[b]))), f"sequence {b}"
+
+    step(rng.integers(0, cfg.vocab_size, B))                      # captures the graph at 4 rows of scratch
+    step(rng.integers(0, cfg.vocab_size, B))
+    long_prompt = [int(t) for t in rng.integers(0, cfg.vocab_size, 128)]
+    got = rt.forward_prefill(dm, st, long_prompt, seq=2)             # 128 rows: the row scratch is reallocated
+    assert _close(got, oracle.forward_prefill(port, m, osts[2], long_prompt))
+    short_prompt = [int(t) for t in rng.integers(0, cfg.vocab_size, 20)]
+    got = rt.forward_prefill(dm, st, short_prompt, seq=0)            # 20 rows: the eight-row kernel's scratch
+    assert _close(got, oracle.forward_prefill(port, m, osts[0], short_prompt))
+    step(rng.integers(0, cfg.vocab_size, B))
+    step(rng.integers(0, cfg.vocab_size, B))
+    assert [st.get_pos(b) for b in range(B)] == [24, 4, 132, 4]
+
+
 def test_state_exhaustion_and_rollback(toy):
     cfg, m, dm = toy
     st = rt.init_state(dm, 6)

@@ -82,7 +82,17 @@ def test_tp_mlp_block_two_gpus(tmp_path):
                    NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    outs = []
+    try:
+        for p in procs:
+            outs.append(p.communicate(timeout=300)[0])
+    finally:
+        # a rank that died before the communicator was formed leaves its peer blocked inside NCCL's
+        # bootstrap: never leave a child behind holding a GPU
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+                p.wait()
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
         assert f"rank {r} ok" in o

@@ -8,6 +8,7 @@ different calls in a row and requires each to equal what ``matmul_lut_sm100_m1``
 same inputs, bit for bit (the two run the same kernel on the same values).  This file sorts last on
 purpose: a run that stops at the first failure has then already been through every other test.
 """
+import ctypes
 import importlib
 
 import numpy as np
@@ -35,6 +36,25 @@ def test_noalloc_matches_allocating_entry_point_twice_in_a_row():
         assert np.array_equal(got, want), f"N={N} K={Kdim}"
         again = K.matmul_packed_m1_noalloc(xq, packed, ws, xs)
         assert np.array_equal(again, want)
+
+
+def _free_bytes(lib):
+    free = ctypes.c_size_t(0)
+    assert lib.lspk_mem_info(ctypes.byref(free), None) == 0
+    return free.value
+
+
+def test_noalloc_call_leaves_free_device_memory_unchanged():
+    """What the entry point promises a host without an allocator: after its first call has bound the
+    library, a call of any accepted size takes no device memory (cudaMemGetInfo before and after)."""
+    lib = K.load_library()
+    packed, xq, ws, xs = _case(6, 2560, 2560)
+    K.matmul_packed_m1_noalloc(xq, packed, ws, xs)       # first call on this device: binds, looks the array up
+    before = _free_bytes(lib)
+    for seed, N, Kdim in ((7, 6912, 2560), (8, 640, 2560)):
+        packed, xq, ws, xs = _case(seed, N, Kdim)
+        K.matmul_packed_m1_noalloc(xq, packed, ws, xs)
+    assert _free_bytes(lib) == before
 
 
 def test_noalloc_rejects_what_does_not_fit():
