@@ -168,8 +168,9 @@ def load_library(require_device: bool = True) -> ctypes.CDLL:
         for neutral, tagged in _ALIASES.items():
             setattr(lib, neutral, getattr(lib, tagged.format(T=_ARCH_TAG)))
         try:
-            from . import _runtime_abi
+            from . import _bench_abi, _runtime_abi
             _runtime_abi.bind(lib)
+            _bench_abi.bind(lib)
         except ImportError:
             pass
         _lib = lib

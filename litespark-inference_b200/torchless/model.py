@@ -86,6 +86,22 @@ class FalconTernaryConfig(BitNetConfig):
 
 
 @dataclass
+class PackedFalconLayer:
+    """One Falcon-E layer (reference model.py:180-189): no sub-norms."""
+    q_proj: PackedProjection
+    k_proj: PackedProjection
+    v_proj: PackedProjection
+    o_proj: PackedProjection
+    gate_proj: PackedProjection
+    up_proj: PackedProjection
+    down_proj: PackedProjection
+    input_norm: np.ndarray
+    post_attn_norm: np.ndarray
+    attn_sub_norm: None = None      # read by the uploader, which treats both families alike
+    ffn_sub_norm: None = None
+
+
+@dataclass
 class PackedFalconModel:
     """Falcon-E family (reference model.py:166-250): SiLU gate, no sub-norms, untied LM head."""
     config: FalconTernaryConfig

@@ -6,7 +6,8 @@ from __future__ import annotations
 
 import numpy as np
 
-from .model import BitNetConfig, PackedBitNetModel, PackedLayer, PackedProjection
+from .model import (BitNetConfig, FalconTernaryConfig, PackedBitNetModel, PackedFalconLayer, PackedFalconModel,
+                    PackedLayer, PackedProjection)
 from .pack import pack_ternary_4_per_byte
 from .quantize import fp32_to_bf16_u16
 
@@ -107,3 +108,65 @@ def random_checkpoint_tensors(cfg: BitNetConfig, seed: int = 0) -> dict:
         for suf, n in norms.items():
             t[f"model.layers.{i}{suf}"] = gamma(n)
     return t
+
+
+# ---- Falcon-E family ------------------------------------------------------------------------------------------
+def toy_falcon_config(hidden=256, layers=2, heads=4, kv_heads=2, inter=512, vocab=1024, eos=(2,)) -> FalconTernaryConfig:
+    return FalconTernaryConfig(hidden_size=hidden, num_layers=layers, num_heads=heads, num_kv_heads=kv_heads,
+                               intermediate_size=inter, vocab_size=vocab, max_position_embeddings=2048,
+                               rms_norm_eps=1e-5, rope_theta=10000.0, eos_token_ids=tuple(eos))
+
+
+def hf_pack_rows(t: np.ndarray) -> np.ndarray:
+    """int8 {-1, 0, +1} [N, K] -> the Hugging Face BitNet packing uint8 [ceil(N / 4), K] that Falcon-E checkpoints
+    store: byte (r, c) = codes of rows r, r + n, r + 2n, r + 3n at column c, two bits each (rows past N: code 1)."""
+    N, K = t.shape
+    n = (N + 3) // 4
+    codes = np.ones((4 * n, K), dtype=np.uint8)
+    codes[:N] = (t.astype(np.int16) + 1).astype(np.uint8)
+    return (codes[0:n] | (codes[n:2 * n] << 2) | (codes[2 * n:3 * n] << 4) | (codes[3 * n:4 * n] << 6)).astype(np.uint8)
+
+
+def random_falcon_checkpoint_tensors(cfg: FalconTernaryConfig, seed: int = 0, untied_head: bool = True) -> dict:
+    """Random Falcon-E checkpoint as ``{name: (array, safetensors dtype tag)}``: ternary projections in the
+    Hugging Face packing with a bf16 ``weight_scale`` (the reciprocal of the per-tensor scale), bf16 norms,
+    bf16 embedding and (optionally) an untied bf16 LM head.  What ``loader.save_falcon_dir`` writes."""
+    rng = np.random.default_rng(seed)
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    kv = cfg.num_kv_heads * (H // cfg.num_heads)
+    t = {"model.embed_tokens.weight": (fp32_to_bf16_u16(rng.standard_normal((cfg.vocab_size, H), dtype=np.float32)), "BF16"),
+         "model.norm.weight": (fp32_to_bf16_u16(rng.uniform(0.9, 1.1, H).astype(np.float32)), "BF16")}
+    if untied_head:
+        t["lm_head.weight"] = (fp32_to_bf16_u16(rng.standard_normal((cfg.vocab_size, H), dtype=np.float32)), "BF16")
+    shapes = {".self_attn.q_proj.weight": (H, H), ".self_attn.k_proj.weight": (kv, H), ".self_attn.v_proj.weight": (kv, H),
+              ".self_attn.o_proj.weight": (H, H), ".mlp.gate_proj.weight": (I, H), ".mlp.up_proj.weight": (I, H),
+              ".mlp.down_proj.weight": (H, I)}
+    for i in range(cfg.num_layers):
+        for suf, (N, K) in shapes.items():
+            w = rng.integers(-1, 2, size=(N, K), dtype=np.int8)
+            t[f"model.layers.{i}{suf}"] = (hf_pack_rows(w), "U8")
+            # stored scale = 1 / w_scale, kept exactly representable in bf16
+            inv = fp32_to_bf16_u16(np.array([rng.uniform(0.7, 2.0)], dtype=np.float32))
+            t[f"model.layers.{i}{suf}_scale"] = (inv, "BF16")
+        for suf in (".input_layernorm.weight", ".post_attention_layernorm.weight"):
+            t[f"model.layers.{i}{suf}"] = (fp32_to_bf16_u16(rng.uniform(0.9, 1.1, H).astype(np.float32)), "BF16")
+    return t
+
+
+def random_falcon_model(cfg: FalconTernaryConfig, seed: int = 0, norm_jitter: float = 0.1) -> PackedFalconModel:
+    """Random-init Falcon-E-shaped host model (SiLU gate, no sub-norms, untied bf16 LM head)."""
+    rng = np.random.default_rng(seed)
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    kv = cfg.num_kv_heads * (H // cfg.num_heads)
+
+    def gamma(n):
+        return fp32_to_bf16_u16((np.ones(n) + rng.uniform(-norm_jitter, norm_jitter, n)).astype(np.float32))
+
+    layers = [PackedFalconLayer(
+        q_proj=random_projection(rng, H, H), k_proj=random_projection(rng, kv, H), v_proj=random_projection(rng, kv, H),
+        o_proj=random_projection(rng, H, H), gate_proj=random_projection(rng, I, H), up_proj=random_projection(rng, I, H),
+        down_proj=random_projection(rng, H, I), input_norm=gamma(H), post_attn_norm=gamma(H))
+        for _ in range(cfg.num_layers)]
+    emb = fp32_to_bf16_u16(rng.standard_normal((cfg.vocab_size, H), dtype=np.float32))
+    head = fp32_to_bf16_u16(rng.standard_normal((cfg.vocab_size, H), dtype=np.float32))
+    return PackedFalconModel(config=cfg, embed_tokens=emb, final_norm=gamma(H), layers=layers, lm_head_tokens=head)

@@ -355,10 +355,27 @@ def _attention_rows(cfg, state: State, li: int, q_rows: np.ndarray, base_pos: in
     return out
 
 
+def silu_mul(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """Falcon's gate, in the reference's operation order (runtime.py:726-732): g / (exp(-g) + 1) * u."""
+    out = np.negative(gate)
+    np.exp(out, out=out)
+    out += np.float32(1.0)
+    np.divide(gate, out, out=out)
+    out *= up
+    return out
+
+
 def lm_head(kern: Kernels, model, h: np.ndarray) -> np.ndarray:
-    """Tied LM head in whichever embedding format the model carries (runtime.py:131-148)."""
+    """LM head in whichever format the model carries: the tied embedding (runtime.py:131-148) or, for the
+    Falcon-E family, its own table (runtime.py:700-706)."""
     V = model.config.vocab_size
     out = np.empty(V, dtype=np.float32)
+    if getattr(model, "lm_head_int4", None) is not None:
+        return kern.lm_head_int4(model.lm_head_int4, model.lm_head_scale, h, out, model.config.hidden_size)
+    if getattr(model, "lm_head_int8", None) is not None:
+        return kern.lm_head_int8(model.lm_head_int8, model.lm_head_scale, h, out)
+    if getattr(model, "lm_head_tokens", None) is not None:
+        return kern.lm_head_bf16(model.lm_head_tokens, h, out)
     if getattr(model, "embed_int4", None) is not None:
         return kern.lm_head_int4(model.embed_int4, model.embed_scale, h, out, model.config.hidden_size)
     if getattr(model, "embed_int8", None) is not None:
@@ -370,7 +387,9 @@ def forward_hidden(kern: Kernels, model, state: State, token_ids, trace: Optiona
     """Layer loop for T >= 1 tokens starting at state.pos; returns the post-final-norm hidden
     rows [T, H] and advances state.pos.  Row by row this is the reference's decode step
     (torchless/runtime.py:171-282); for T > 1 it is its batched prefill (:285-436), which the
-    reference documents (and the survey confirmed) to be identical per row."""
+    reference documents (and the survey confirmed) to be identical per row.  Layers without sub-norms are the
+    Falcon-E family (falcon_forward_one, runtime.py:735-817): the attention output and the gated product
+    are quantised as they are, and the gate is SiLU."""
     c = model.config
     H, I = c.hidden_size, c.intermediate_size
     Q, KV = c.num_heads, c.num_kv_heads
@@ -388,6 +407,9 @@ def forward_hidden(kern: Kernels, model, state: State, token_ids, trace: Optiona
         K = src.shape[1]
         q8 = np.empty((T, K), np.int8)
         sc = np.empty(T, np.float32)
+        if gamma is None:
+            kern.quantize_activation_batched(np.ascontiguousarray(src), q8, sc)
+            return q8, sc
         tmp = np.empty((T, K), np.float32)
         if gamma.dtype == np.uint16:
             kern.rmsnorm_quantize_batched(np.ascontiguousarray(src), gamma, q8, sc, tmp, eps)
@@ -410,14 +432,18 @@ def forward_hidden(kern: Kernels, model, state: State, token_ids, trace: Optiona
             state.cache_k[li, base + t] = apply_rope(k[t].reshape(KV, D), cr, sr)
             state.cache_v[li, base + t] = v[t].reshape(KV, D)
         attn = _attention_rows(c, state, li, q, base)
-        q8, sc = normq(attn, L.attn_sub_norm)
+        falcon = getattr(L, "attn_sub_norm", None) is None
+        q8, sc = normq(attn, None if falcon else L.attn_sub_norm)
         x += proj(q8, sc, L.o_proj)
         q8, sc = normq(x, L.post_attn_norm)
         g = proj(q8, sc, L.gate_proj)
         u = proj(q8, sc, L.up_proj)
-        inter = np.empty((T, I), np.float32)
-        kern.relu2_mul_into_batched(g, u, inter)
-        q8, sc = normq(inter, L.ffn_sub_norm)
+        if falcon:
+            inter = silu_mul(g, u)
+        else:
+            inter = np.empty((T, I), np.float32)
+            kern.relu2_mul_into_batched(g, u, inter)
+        q8, sc = normq(inter, None if falcon else L.ffn_sub_norm)
         x += proj(q8, sc, L.down_proj)
         if trace is not None:
             trace.setdefault("x_after_layer", []).append(x.copy())
@@ -459,6 +485,24 @@ def generate(kern, model, prompt, max_new_tokens: int, state: Optional[State] = 
         toks.append(nxt)
         logits = forward_one(kern, model, state, nxt)
     return (toks, all_logits) if return_logits else toks
+
+
+def falcon_generate(kern, model, prompt, max_new_tokens: int):
+    """Greedy decode that stops before an end-of-sequence id (torchless/runtime.py:826-837); the prompt goes
+    through one token at a time, as falcon_forward_prefill does (:820-824)."""
+    state = State(model.config, len(prompt) + max_new_tokens + 1)
+    logits = None
+    for t in prompt:
+        logits = forward_one(kern, model, state, int(t))
+    eos = set(model.config.eos_token_ids)
+    out = []
+    for _ in range(max_new_tokens):
+        nxt = int(np.argmax(logits))
+        if nxt in eos:
+            break
+        out.append(nxt)
+        logits = forward_one(kern, model, state, nxt)
+    return out
 
 
 def lookup_speculation(context, match_n: int, k: int):

@@ -210,8 +210,66 @@ def gen_runtime(tier: str):
     print(f"runtime_toy_{tier}.npz")
 
 
+def gen_falcon(tier: str):
+    """Falcon-E family through the reference's own runtime (falcon_forward_one / falcon_generate) and loader
+    (_unpack_hf_packed_bitnet / _load_falcon_proj), on a toy model and a toy checkpoint tensor."""
+    kernel, runtime, pack, quantize, ops, refmodel = reference_modules(tier)
+    import importlib
+    loader = importlib.import_module("litespark_inference.torchless.loader")
+    out = {}
+    cfg = synthetic.toy_falcon_config()
+    m = synthetic.random_falcon_model(cfg, seed=41)
+    rcfg = refmodel.FalconTernaryConfig(cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads,
+                                        cfg.intermediate_size, cfg.vocab_size, cfg.max_position_embeddings,
+                                        cfg.rms_norm_eps, cfg.rope_theta, cfg.eos_token_ids)
+
+    def proj(p):
+        return refmodel.PackedProjection(w_packed=p.w_packed, w_sum=np.zeros(p.out_features, np.int32),
+                                         scale=p.scale, in_features=p.in_features, out_features=p.out_features)
+    layers = [refmodel.PackedFalconLayer(proj(L.q_proj), proj(L.k_proj), proj(L.v_proj), proj(L.o_proj),
+                                         proj(L.gate_proj), proj(L.up_proj), proj(L.down_proj),
+                                         L.input_norm, L.post_attn_norm) for L in m.layers]
+    rm = refmodel.PackedFalconModel(config=rcfg, embed_tokens=m.embed_tokens, final_norm=m.final_norm,
+                                    projection_backend="neon", layers=layers, lm_head_tokens=m.lm_head_tokens)
+    prompt = [int(t) for t in np.random.default_rng(42).integers(3, cfg.vocab_size, 14)]
+    out["prompt"] = np.array(prompt, np.int32)
+    st = runtime.init_state(rm, 64)
+    out["logits_stepwise"] = np.stack([runtime.falcon_forward_one(rm, st, t).copy() for t in prompt])
+    out["greedy24"] = np.array(runtime.falcon_generate(rm, prompt, 24), np.int32)
+    # generation that meets an end-of-sequence id: make the first greedy token the EOS id and generate again
+    eos_cfg = refmodel.FalconTernaryConfig(cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads,
+                                           cfg.intermediate_size, cfg.vocab_size, cfg.max_position_embeddings,
+                                           cfg.rms_norm_eps, cfg.rope_theta, (int(out["greedy24"][3]),))
+    rm.config = eos_cfg
+    out["eos_id"] = np.int32(out["greedy24"][3])
+    out["greedy_until_eos"] = np.array(runtime.falcon_generate(rm, prompt, 24), np.int32)
+    # loader: the Hugging Face row-blocked packing, ragged row count (37 rows in 10 byte rows)
+    rng = np.random.default_rng(43)
+    w = rng.integers(-1, 2, (37, 24), dtype=np.int8)
+    hf = synthetic.hf_pack_rows(w)
+    out["hf_packed"] = hf
+    out["hf_unpacked"] = loader._unpack_hf_packed_bitnet(hf, 37)
+    assert np.array_equal(out["hf_unpacked"], w)
+
+    class FakeFile:                     # the two members _load_falcon_proj touches
+        header = {"w": {}, "w_scale": {}}
+
+        @staticmethod
+        def get(key):
+            return (hf, "U8") if key == "w" else (np.array([0x3FC0], np.uint16), "BF16")      # bf16 1.5
+    p = loader._load_falcon_proj(FakeFile, "w", 37, "neon")
+    out["hf_proj_packed"] = p.w_packed
+    out["hf_proj_scale"] = np.float64(p.scale)
+    np.savez_compressed(HERE / f"falcon_toy_{tier}.npz", **out)
+    print(f"falcon_toy_{tier}.npz")
+
+
 if __name__ == "__main__":
+    if "--falcon-only" in sys.argv:
+        gen_falcon("avx512")
+        sys.exit(0)
     gen_host()
     for tier in ("avx512", "avx2"):
         gen_kernels(tier)
     gen_runtime("avx512")
+    gen_falcon("avx512")

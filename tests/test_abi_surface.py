@@ -35,7 +35,9 @@ def test_ctypes_layer_binds_every_declared_symbol():
     rt_abi = importlib.import_module("litespark_inference_b200.torchless._runtime_abi")
     hyb = importlib.import_module("litespark_inference_b200.torchless.hybrid")
     tpm = importlib.import_module("litespark_inference_b200.torchless.tp")
-    bound = set(K._SIGNATURES) | set(rt_abi.SIGNATURES) | set(hyb.SIGNATURES) | set(tpm.SIGNATURES)
+    bench_abi = importlib.import_module("litespark_inference_b200.torchless._bench_abi")
+    bound = set(K._SIGNATURES) | set(rt_abi.SIGNATURES) | set(hyb.SIGNATURES) | set(tpm.SIGNATURES) \
+        | set(bench_abi.SIGNATURES)
     declared = _declared_symbols()
     assert declared - bound == set(), f"declared but not bound in Python: {sorted(declared - bound)}"
     assert bound - declared == set(), f"bound in Python but not declared: {sorted(bound - declared)}"

@@ -182,62 +182,33 @@ def test_int8_and_int4_embeddings(toy, oracle, port):
         assert _close(got, want)
 
 
-def test_falcon_style_model(toy, oracle):
-    """No sub-norms, SiLU gate, untied head: checked against a numpy restatement of
-    falcon_forward_one (reference runtime.py:735-817) built from oracle pieces."""
-    cfg, m, dm = toy
+def test_falcon_family_matches_reference_runtime(golden_dir, oracle, port, tmp_path):
+    """Falcon-E family (no sub-norms, SiLU gate, untied LM head, EOS stop) against the reference's own
+    falcon_forward_one / falcon_generate (fixture generated by tests/golden/make_golden.py), and a synthetic
+    checkpoint in the Hugging Face packing through the loader onto the device."""
+    g = np.load(golden_dir / "falcon_toy_avx512.npz")
+    cfg = synthetic.toy_falcon_config()
+    m = synthetic.random_falcon_model(cfg, seed=41)
+    prompt = [int(t) for t in g["prompt"]]
+    st = rt.init_state(m, 64, kv_dtype="fp32")
+    for i, t in enumerate(prompt):
+        assert _close(rt.falcon_forward_one(m, st, t), g["logits_stepwise"][i]), f"position {i}"
+    assert rt.falcon_generate(m, prompt, 24) == [int(t) for t in g["greedy24"]]
     import copy
-    fm = copy.copy(m)
-    fm._lspk_device = None
-    fm.layers = [copy.copy(L) for L in m.layers]
-    for L in fm.layers:
-        L.attn_sub_norm = None
-        L.ffn_sub_norm = None
-    st = rt.init_state(fm, 16, kv_dtype="fp32")
-    got = rt.forward_prefill(fm, st, [7, 8, 9])
-    assert np.isfinite(got).all() and got.shape == (cfg.vocab_size,)
-    want = _falcon_oracle(oracle, cfg, fm, [7, 8, 9])
+    m2 = copy.copy(m)
+    m2._lspk_device = None
+    m2.config = synthetic.toy_falcon_config(eos=(int(g["eos_id"]),))
+    assert rt.falcon_generate(m2, prompt, 24) == [int(t) for t in g["greedy_until_eos"]]
+    # loader -> device: a checkpoint in the row-blocked packing, int8 tables, against the oracle
+    loader = importlib.import_module("litespark_inference_b200.torchless.loader")
+    loader.save_falcon_dir(tmp_path, cfg, synthetic.random_falcon_checkpoint_tensors(cfg, seed=6))
+    lm = loader.load_falcon_dir(tmp_path, embed_dtype="int8")
+    st = rt.init_state(lm, 16, kv_dtype="fp32")
+    got = rt.falcon_forward_prefill(lm, st, [7, 8, 9])
+    ost = oracle.State(cfg, 16)
+    for t in (7, 8, 9):
+        want = oracle.forward_one(port, lm, ost, t)
     assert _close(got, want)
-
-
-def _falcon_oracle(oracle, cfg, fm, ids):
-    kern = oracle.Kernels("port")
-    H, I, Q, KV = cfg.hidden_size, cfg.intermediate_size, cfg.num_heads, cfg.num_kv_heads
-    D = H // Q
-    st = oracle.State(cfg, 16)
-    logits = None
-    for tok in ids:
-        x = oracle.embed_row(fm, tok)
-        pos = st.pos
-
-        def q_of(v):
-            q8 = np.empty(v.shape[0], np.int8)
-            return q8, kern.quantize_activation(np.ascontiguousarray(v), q8)
-
-        for li, L in enumerate(fm.layers):
-            h = kern.rmsnorm_into(x, L.input_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
-            q8, s = q_of(h)
-            q = kern.matmul_packed_m1(q8, L.q_proj.w_packed, L.q_proj.scale, s)
-            k = kern.matmul_packed_m1(q8, L.k_proj.w_packed, L.k_proj.scale, s)
-            v = kern.matmul_packed_m1(q8, L.v_proj.w_packed, L.v_proj.scale, s)
-            cr, sr = st.rope_cos[pos], st.rope_sin[pos]
-            q = oracle.apply_rope(q.reshape(Q, D), cr, sr).reshape(1, -1)
-            st.cache_k[li, pos] = oracle.apply_rope(k.reshape(KV, D), cr, sr)
-            st.cache_v[li, pos] = v.reshape(KV, D)
-            attn = oracle._attention_rows(cfg, st, li, q, pos)[0]
-            q8, s = q_of(attn)
-            x = x + kern.matmul_packed_m1(q8, L.o_proj.w_packed, L.o_proj.scale, s)
-            h = kern.rmsnorm_into(x, L.post_attn_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
-            q8, s = q_of(h)
-            g = kern.matmul_packed_m1(q8, L.gate_proj.w_packed, L.gate_proj.scale, s)
-            u = kern.matmul_packed_m1(q8, L.up_proj.w_packed, L.up_proj.scale, s)
-            inter = (g / (np.exp(-g) + np.float32(1))) * u
-            q8, s = q_of(inter.astype(np.float32))
-            x = x + kern.matmul_packed_m1(q8, L.down_proj.w_packed, L.down_proj.scale, s)
-        st.pos += 1
-        h = kern.rmsnorm_into(x, fm.final_norm, np.empty(H, np.float32), cfg.rms_norm_eps)
-        logits = oracle.lm_head(kern, fm, h)
-    return logits
 
 
 @pytest.mark.parametrize("kv", ["fp32", "fp16"])

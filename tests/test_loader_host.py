@@ -90,3 +90,42 @@ def test_loader_rejects_bad_input(tmp_path):
     toy_checkpoint(tmp_path)
     with pytest.raises(ValueError):
         loader.load_bitnet_dir(tmp_path, embed_dtype="fp8", device_quantize=False)
+
+
+def test_falcon_packing_and_loader_match_reference(tmp_path, golden_dir):
+    """The Hugging Face row-blocked packing of Falcon-E checkpoints against the reference loader's own outputs
+    (fixture generated from its _unpack_hf_packed_bitnet / _load_falcon_proj), then a whole synthetic checkpoint
+    through load_falcon_dir."""
+    g = np.load(golden_dir / "falcon_toy_avx512.npz")
+    assert np.array_equal(loader.unpack_hf_packed_bitnet(g["hf_packed"], 37), g["hf_unpacked"])
+    assert np.array_equal(synthetic.hf_pack_rows(g["hf_unpacked"]), g["hf_packed"])
+    sio.save_safetensors(tmp_path / "one.safetensors", {"w": (g["hf_packed"], "U8"),
+                                                        "w_scale": (np.array([0x3FC0], np.uint16), "BF16")})
+    sf = sio.open_safetensors(tmp_path / "one.safetensors")
+    p = loader.load_falcon_projection(sf, "w", 37)
+    assert np.array_equal(p.w_packed, g["hf_proj_packed"]) and p.scale == float(g["hf_proj_scale"])
+    assert (p.out_features, p.in_features) == (37, 24)
+    # whole checkpoint: shapes, scales (reciprocal of the stored tensor), untied head, EOS list
+    cfg = synthetic.toy_falcon_config(eos=(2, 7))
+    t = synthetic.random_falcon_checkpoint_tensors(cfg, seed=4)
+    loader.save_falcon_dir(tmp_path / "ckpt", cfg, t)
+    for embed_dtype in ("bf16", "int8", "int4"):
+        m = loader.load_falcon_dir(tmp_path / "ckpt", embed_dtype=embed_dtype)
+        assert m.config == cfg and len(m.layers) == cfg.num_layers
+        L = m.layers[1]
+        raw, _ = t["model.layers.1.mlp.down_proj.weight"]
+        assert np.array_equal(pack.unpack_4_per_byte(L.down_proj.w_packed, cfg.intermediate_size),
+                              loader.unpack_hf_packed_bitnet(raw, cfg.hidden_size))
+        inv = quantize.bf16_u16_to_fp32(t["model.layers.1.mlp.down_proj.weight_scale"][0])[0]
+        assert L.down_proj.scale == float(1.0 / inv)
+        assert L.attn_sub_norm is None and L.ffn_sub_norm is None
+        tables = {"bf16": (m.embed_tokens, m.lm_head_tokens), "int8": (m.embed_int8, m.lm_head_int8),
+                  "int4": (m.embed_int4, m.lm_head_int4)}[embed_dtype]
+        assert tables[0] is not None and tables[1] is not None and not np.array_equal(tables[0], tables[1])
+    # a checkpoint without lm_head.weight ties the head to the embedding
+    t2 = {k: v for k, v in t.items() if k != "lm_head.weight"}
+    loader.save_falcon_dir(tmp_path / "tied", cfg, t2)
+    m = loader.load_falcon_dir(tmp_path / "tied", embed_dtype="bf16")
+    assert m.lm_head_tokens is m.embed_tokens
+    with pytest.raises(FileNotFoundError):
+        loader.load_falcon_dir(tmp_path / "nowhere")

@@ -139,3 +139,21 @@ def test_compiled_reference_agrees_with_port(oracle, port):
     yp = port.matmul_packed_mT(xq_p, xs_p, packed, 0.8125)
     yr = ref.matmul_packed_mT(xq_r, xs_r, packed, 0.8125)
     assert np.array_equal(yp, yr)
+
+
+def test_falcon_restatement_matches_reference_runtime(oracle, port, golden_dir):
+    """The Falcon-E branch of the oracle (no sub-norms, SiLU gate, untied head, EOS stop) against the
+    reference's falcon_forward_one / falcon_generate on the toy Falcon model."""
+    g = np.load(golden_dir / "falcon_toy_avx512.npz")
+    cfg = synthetic.toy_falcon_config()
+    m = synthetic.random_falcon_model(cfg, seed=41)
+    prompt = [int(t) for t in g["prompt"]]
+    st = oracle.State(cfg, 64)
+    step = np.stack([oracle.forward_one(port, m, st, t) for t in prompt])
+    assert np.allclose(step, g["logits_stepwise"], rtol=1e-5, atol=1e-5)
+    assert oracle.falcon_generate(port, m, prompt, 24) == [int(t) for t in g["greedy24"]]
+    import copy
+    m2 = copy.copy(m)
+    m2.config = synthetic.toy_falcon_config(eos=(int(g["eos_id"]),))
+    stopped = oracle.falcon_generate(port, m2, prompt, 24)
+    assert stopped == [int(t) for t in g["greedy_until_eos"]] and len(stopped) == 3
