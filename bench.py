@@ -134,54 +134,121 @@ def host_threads() -> int:
         return os.cpu_count() or 1
 
 
-def cpu_reference_tok_s(model, prompt, n_prompt: int, n_decode: int):
-    """Decode tok/s of the reference's CPU kernels on this host: the compiled reference objects
-    under oracle/_ref when this CPU can run them, else the C restatement.  The host loop is the
-    oracle's numpy restatement of the reference's forward_one."""
+def _set_omp_threads(n: int) -> bool:
+    """Thread count of the OpenMP runtime the compiled reference kernels use (libgomp, already loaded with
+    them).  Returns False when it cannot be set."""
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(int(n))
+        return True
+    except (OSError, AttributeError):
+        return False
+
+
+class CpuReference:
+    """The reference's CPU path on this host: its compiled kernel objects under oracle/_ref when this CPU can
+    run them (else the C restatement), driven by the oracle's numpy restatement of the reference's runtime.py
+    host loop.  One prefill of the prompt (chunks of 64 rows, the reference's limit), then tg passes that roll the
+    position back to the end of the prompt, exactly like the device arm."""
+
+    def __init__(self, model, prompt, tier=None):
+        self.orc = entry.load_oracle()
+        tier = tier or self.orc.ref_tier()
+        if tier is not None:
+            self.kern, self.kind, self.what = self.orc.Kernels("ref", tier), "reference", f"oracle/_ref {tier} build"
+        else:
+            self.kern, self.kind = self.orc.Kernels("port"), "port"
+            self.what = "oracle C restatement (no usable reference object)"
+        self.model, self.prompt = model, list(prompt)
+        self.threads = self.kern.max_threads()
+        self.state = None
+
+    def prefill(self, gen_len: int) -> float:
+        self.state = self.orc.State(self.model.config, len(self.prompt) + gen_len + 1, np.float16)
+        t0 = time.perf_counter()
+        logits = self.orc.forward_prefill(self.kern, self.model, self.state, self.prompt)
+        self.pp_s = time.perf_counter() - t0
+        self.first = int(np.argmax(logits))
+        return self.pp_s
+
+    def tg(self, n_decode: int) -> float:
+        """Seconds for n_decode greedy steps from the end of the prompt."""
+        self.state.pos = len(self.prompt)
+        tok = self.first
+        t0 = time.perf_counter()
+        for _ in range(n_decode):
+            tok = int(np.argmax(self.orc.forward_one(self.kern, self.model, self.state, tok)))
+        return time.perf_counter() - t0
+
+
+def cpu_variants(model, prompt, n_decode: int):
+    """Short samples of the other CPU configurations a user of the reference can run: its AVX2 build and a
+    single OpenMP thread (tok/s over n_decode greedy steps after the full prompt)."""
+    out = {}
     orc = entry.load_oracle()
-    tier = orc.ref_tier()
-    if tier is not None:
-        kern, kind, what = orc.Kernels("ref", tier), "reference", f"oracle/_ref {tier} build"
-    else:
-        kern, kind, what = orc.Kernels("port"), "port", "oracle C restatement (no usable reference object)"
-    st = orc.State(model.config, n_prompt + n_decode + 1, np.float16)
-    logits = orc.forward_prefill(kern, model, st, prompt[:n_prompt])
-    tok = int(np.argmax(logits))
-    t0 = time.perf_counter()
-    for _ in range(n_decode):
-        logits = orc.forward_one(kern, model, st, tok)
-        tok = int(np.argmax(logits))
-    dt = time.perf_counter() - t0
-    return n_decode / dt, kind, what, kern.max_threads()
+    best = orc.ref_tier()
+    for tier in ("avx512", "avx2"):
+        if best is None or (tier == "avx512" and best != "avx512"):
+            continue
+        try:
+            ref = CpuReference(model, prompt, tier)
+            ref.prefill(n_decode)
+            out[f"{tier}_all_threads_tok_s"] = n_decode / ref.tg(n_decode)
+            if _set_omp_threads(1):
+                n1 = max(4, n_decode // 3)
+                out[f"{tier}_1_thread_tok_s"] = n1 / ref.tg(n1)
+                _set_omp_threads(ref.threads)
+        except (RuntimeError, OSError) as ex:
+            out[f"{tier}_error"] = str(ex)[:120]
+    out["sample"] = (f"{n_decode} greedy decode steps ({max(4, n_decode // 3)} on one thread) after the "
+                     f"{len(prompt)}-token prompt, fp16 KV")
+    return out
 
 
 def run_reference_arm(args):
-    """--impl reference: the reference's CPU path on the host cores, rank 0 only."""
+    """--impl reference: the reference's CPU path on the host cores, rank 0 only.  A step is one tg pass of the
+    same workload as the device arm: GEN_LEN greedy steps after the PROMPT_LEN-token prompt, fp16 KV."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cfg, model = build_model()
-    prompt = [int(t) for t in np.random.default_rng(1).integers(0, cfg.vocab_size, PROMPT_LEN)]
-    n_prompt, n_decode = 16, 16
-    vals = []
-    for i in range(args.warmup + args.steps):
-        v, kind, what, threads = cpu_reference_tok_s(model, prompt, n_prompt, n_decode)
-        if i >= args.warmup:
-            vals.append(v)
-    value = statistics.mean(vals)
-    sample = (f"{what}; {n_decode} greedy decode steps after a {n_prompt}-token prompt per step "
-              f"(bounded sample of pp128+tg128), fp16 KV, OMP threads={threads}")
+    prompt = [int(t) for t in np.random.default_rng(100).integers(0, cfg.vocab_size, PROMPT_LEN)]
+    ref = CpuReference(model, prompt)
+    ref.prefill(GEN_LEN)
+    # the whole run has to end within a few minutes: at most 12 tg passes are timed (about 3 s each); a request
+    # for more steps re-uses their mean
+    n_timed = min(args.steps, 12)
+    n_warm = min(args.warmup, 2)
+    for _ in range(n_warm):
+        ref.tg(GEN_LEN)
+    secs = [ref.tg(GEN_LEN) for _ in range(n_timed)]
+    value = GEN_LEN * len(secs) / sum(secs)
+    sample = (f"{ref.what}; every step = {GEN_LEN} greedy decode steps after the {PROMPT_LEN}-token prompt (prefilled "
+              f"once, in two 64-row chunks, {ref.pp_s * 1e3:.0f} ms), fp16 KV, OMP threads={ref.threads}; "
+              f"{n_timed} of the {args.steps} steps timed after {n_warm} warm-up passes")
+    extra = {} if args.skip_extras else cpu_variants(model, prompt, 32)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * n_decode / value,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * sum(secs) / len(secs),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
-        "config": {"workload": "BitNet-2B-shaped decoder, pp128+tg128 batch 1 (bounded CPU sample)",
-                   "l2": "inputs larger than L2"},
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind, "sample": sample},
+        "config": workload_config(1),
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": ref.threads, "kind": ref.kind, "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "prefill": {"tokens": PROMPT_LEN, "ms": ref.pp_s * 1e3, "tok_s": PROMPT_LEN / ref.pp_s},
+        "cpu_variants": extra,
     }
     print(json.dumps(line))
+
+
+def workload_config(world: int) -> dict:
+    """The `config` object of the JSON line, shared by both arms so that they name the same workload."""
+    return {"workload": "BitNet-2B-shaped decoder (30 layers, H=2560, I=6912, 20/5 heads, V=128256, "
+                        f"bf16 tied embedding), {PROMPT_LEN}-token random prompt + {GEN_LEN} greedy steps, "
+                        "batch 1 per GPU, fp16 KV",
+            "parallelism": f"dp{world} (independent sequence per GPU, no collective)",
+            "l2": "inputs larger than L2 (1.18 GB of weights streamed per token)",
+            "step": "one tg128 pass = 128 chained decode steps",
+            "arithmetic": "int8 activations x ternary (2-bit packed) weights -> int32, fp32 rescale"}
 
 
 def bench_tp_mlp(dist, rank, world, model, lib, K):
@@ -214,8 +281,19 @@ def bench_tp_mlp(dist, rank, world, model, lib, K):
     t = torch.tensor([ms.value], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     tp_us = 1000.0 * float(t.item()) / (reps * n_blocks)
+    # correctness: layer 0's block through the split path against the same block unsplit on this GPU
+    group.mlp_block(sl[0][0], sl[1][0], sl[2][0], x, norm, sub, 1e-5, i_s, i_f, d_s, y_f)
+    y_split = y_f.numpy()
+    L0 = model.layers[0]
+    full = [W(getattr(L0, n)) for n in ("gate_proj", "up_proj", "down_proj")]
+    y_one = dev.DeviceArray((H,), np.float32)
+    dev.linear(full[:2], [i_f, None], 1, x_f32=x, gamma=norm, epilogue=K.EPI_RELU2_MUL)
+    dev.linear(full[2:], [y_one], 1, x_f32=i_f, gamma=sub)
+    same = bool(np.array_equal(y_split, y_one.numpy()))
+    flag = torch.tensor([1 if same else 0], device="cuda", dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     group.close()
-    return {"degree": world, "us_per_mlp_block": tp_us,
+    return {"degree": world, "us_per_mlp_block": tp_us, "bit_identical": bool(flag.item()),
             "how": "row-split gate/up/down slices + 2 NCCL all-gathers per block, graph of 30 blocks, max over ranks",
             "bytes_gathered_per_block": 4 * (I + H)}
 
@@ -480,6 +558,69 @@ def main():
         except Exception as ex:
             tp_info = {"error": str(ex)[:200]}
 
+    # ---- the data-parallel serving configuration: seqs_per_gpu independent sequences per GPU in lock step, every
+    #      rank its own sequences (64 sequences over 8 GPUs at the defaults), no inter-GPU traffic.  Device time,
+    #      max over ranks; every sequence's tokens are then checked against the same sequence decoded alone
+    #      (batch 1) on rank 0's GPU. ---------------------------------------------------------------------------
+    extra = {}
+    try:
+        if args.skip_extras:
+            raise RuntimeError("skipped (--skip-extras)")
+        B = args.seqs_per_gpu
+        seq_prompt = lambda g: np.ascontiguousarray(
+            np.random.default_rng(500 + g).integers(0, cfg.vocab_size, PROMPT_LEN), dtype=np.int32)
+        bstate = rt.init_state(dm, t_max, batch=B, kv_dtype="fp16")
+        firsts = np.empty(B, np.int32)
+        one = np.empty(1, np.int32)
+        for b in range(B):
+            pb = seq_prompt(rank * B + b)
+            K.check(lib.lspk_forward_prefill(bstate.handle, b, pb.ctypes.data, PROMPT_LEN, None, None, one.ctypes.data))
+            firsts[b] = one[0]
+        btoks = np.empty((GEN_LEN, B), np.int32)
+
+        def tg128_batch():
+            for b in range(B):
+                bstate.set_pos(b, PROMPT_LEN)
+            K.check(lib.lspk_timer_start())
+            K.check(lib.lspk_decode_greedy(bstate.handle, firsts.ctypes.data, GEN_LEN, btoks.ctypes.data))
+            K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
+            return float(ms.value)
+
+        tg128_batch()
+        barrier()
+        bms = min(tg128_batch() for _ in range(3))
+        all_first, all_toks = [firsts.copy()], [btoks.copy()]
+        if dist is not None:
+            import torch
+            t = torch.tensor([bms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            bms = float(t.item())
+            mine = torch.tensor(np.concatenate([firsts[None, :], btoks]), device="cuda", dtype=torch.int32)
+            gathered = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(gathered, mine)
+            all_first = [g[0].cpu().numpy() for g in gathered]
+            all_toks = [g[1:].cpu().numpy() for g in gathered]
+        extra["batch8_tok_s_per_gpu"] = B * GEN_LEN / (bms / 1000.0)
+        extra["config4_aggregate_tok_s"] = world * B * GEN_LEN / (bms / 1000.0)
+        extra["config4"] = (f"{world * B} sequences, {B} per GPU in lock step, {PROMPT_LEN}-token prompts + {GEN_LEN} "
+                            "greedy steps, device time, max over ranks")
+        extra["batch8_step_kernels"] = bstate.step_kernel_count
+        bstate.close()
+        if rank == 0:
+            same, checked = True, 0
+            for r in range(world):
+                for b in range(B):
+                    pb = seq_prompt(r * B + b)
+                    state.pos = 0
+                    K.check(lib.lspk_forward_prefill(state.handle, 0, pb.ctypes.data, PROMPT_LEN, None, None, one.ctypes.data))
+                    K.check(lib.lspk_decode_greedy(state.handle, one.ctypes.data, GEN_LEN, toks.ctypes.data))
+                    same = same and int(one[0]) == int(all_first[r][b]) and bool(np.array_equal(toks, all_toks[r][:, b]))
+                    checked += 1
+            extra["dp_tokens_identical"] = same
+            extra["dp_sequences_checked"] = checked
+    except Exception as ex:  # the headline line must still be printed
+        extra["batch8_error"] = str(ex)[:200]
+
     if rank != 0:
         if dist is not None:
             dist.barrier()
@@ -528,56 +669,23 @@ def main():
     token_bytes = lin_bytes.value + lm_bytes.value + kv_bytes
     token_gbs = token_bytes / (token_ms * 1e-3) / 1e9
 
-    # ---- extra: 8 independent sequences per GPU in lock step (small-batch GEMV rows) -----------------
-    extra = {}
-    try:
-        if args.skip_extras:
-            raise RuntimeError("skipped (--skip-extras)")
-        B = args.seqs_per_gpu
-        bstate = rt.init_state(dm, t_max, batch=B, kv_dtype="fp16")
-        firsts = np.empty(B, np.int32)
-        one = np.empty(1, np.int32)
-        for b in range(B):
-            pb = np.ascontiguousarray(np.random.default_rng(500 + b).integers(0, cfg.vocab_size, PROMPT_LEN), dtype=np.int32)
-            K.check(lib.lspk_forward_prefill(bstate.handle, b, pb.ctypes.data, PROMPT_LEN, None, None, one.ctypes.data))
-            firsts[b] = one[0]
-        btoks = np.empty((GEN_LEN, B), np.int32)
-
-        def tg128_batch():
-            for b in range(B):
-                bstate.set_pos(b, PROMPT_LEN)
-            K.check(lib.lspk_timer_start())
-            K.check(lib.lspk_decode_greedy(bstate.handle, firsts.ctypes.data, GEN_LEN, btoks.ctypes.data))
-            K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
-            return float(ms.value)
-
-        tg128_batch()
-        bms = min(tg128_batch() for _ in range(3))
-        extra["batch8_tok_s_per_gpu"] = B * GEN_LEN / (bms / 1000.0)
-        extra["batch8_step_kernels"] = bstate.step_kernel_count
-        bstate.close()
-    except Exception as ex:  # the headline line must still be printed
-        extra["batch8_error"] = str(ex)[:200]
-
     # ---- CPU baseline: the reference's kernels on this host's cores, bounded sample ------------------
     cpu = None
     if not args.no_cpu_baseline:
-        v, kind, what, threads = cpu_reference_tok_s(model, prompt, 16, 24)
-        cpu = {"value": v, "unit": "tok/s", "cores": threads, "kind": kind,
-               "sample": f"{what}; 24 greedy decode steps after a 16-token prompt of the same model, fp16 KV"}
+        ref = CpuReference(model, prompt)
+        ref.prefill(GEN_LEN)
+        n_cpu = 3
+        secs = [ref.tg(GEN_LEN) for _ in range(n_cpu)]
+        cpu = {"value": GEN_LEN * n_cpu / sum(secs), "unit": "tok/s", "cores": ref.threads, "kind": ref.kind,
+               "sample": f"{ref.what}; {n_cpu} passes of {GEN_LEN} greedy decode steps after the {PROMPT_LEN}-token prompt "
+                         f"of the same model (prefill {ref.pp_s * 1e3:.0f} ms, two 64-row chunks), fp16 KV, OMP threads={ref.threads}"}
 
     line = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
-        "config": {"workload": "BitNet-2B-shaped decoder (30 layers, H=2560, I=6912, 20/5 heads, V=128256, "
-                               f"bf16 tied embedding), {PROMPT_LEN}-token random prompt + {GEN_LEN} greedy steps, "
-                               "batch 1 per GPU, fp16 KV",
-                   "parallelism": f"dp{world} (independent sequence per GPU, no collective)",
-                   "l2": "inputs larger than L2 (1.18 GB of weights streamed per token)",
-                   "step": "one tg128 pass = 128 chained decode steps",
-                   "arithmetic": "int8 activations x ternary (2-bit packed) weights -> int32, fp32 rescale"},
+        "config": workload_config(world),
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * GEN_LEN,
                 "d2h_bytes_per_step": 4 * GEN_LEN,
