@@ -298,6 +298,41 @@ def bench_tp_mlp(dist, rank, world, model, lib, K):
             "bytes_gathered_per_block": 4 * (I + H)}
 
 
+def time_linear_batch(lib, K, dev, gate_handles, up_handles, x_f32, N, reps, per_call=90):
+    """Microseconds per product through lspk_linear_batch: the products (one matrix each, or gate + up pairs with
+    the ReLU^2 epilogue) share one quantised activation vector and write distinct outputs; calls of up to
+    `per_call` products, CUDA events around `reps` passes over all of them."""
+    n = len(gate_handles)
+    Kd = x_f32.shape[-1]
+    xq, xs = dev.DeviceArray((1, Kd), np.int8), dev.DeviceArray((1,), np.float32)
+    K.check(lib.lspk_quantize_rows(x_f32.ptr, xq.ptr, xs.ptr, 1, Kd))
+    outs = dev.DeviceArray((n, N), np.float32)
+    arr = (K.LinearArgs * n)()
+    for i, a in enumerate(arr):
+        a.w[0] = gate_handles[i]
+        a.n_mats, a.epilogue = 1, K.EPI_STORE
+        if up_handles is not None:
+            a.w[1] = up_handles[i]
+            a.n_mats, a.epilogue = 2, K.EPI_RELU2_MUL
+        a.out[0] = outs.ptr + 4 * N * i
+        a.M, a.prologue, a.x_i8, a.x_scales = 1, K.PRO_INT8, xq.ptr, xs.ptr
+    calls = [(i, min(per_call, n - i)) for i in range(0, n, per_call)]
+
+    def one_pass():
+        for i0, cnt in calls:
+            K.check(lib.lspk_linear_batch(ctypes.byref(arr[i0]), cnt))
+
+    one_pass()
+    ms = ctypes.c_float(0.0)
+    K.check(lib.lspk_timer_start())
+    for _ in range(reps):
+        one_pass()
+    K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
+    for d in (xq, xs, outs):
+        d.free()
+    return 1000.0 * float(ms.value) / (reps * n)
+
+
 def measure_shape(lib, dev, K, synthetic, rng, peak, name, Ms):
     """One BitNet-2B projection shape at the token counts Ms: fused-quantiser linear launches rotated over
     enough device copies of the matrix to exceed the L2 (about 300 MB), as a dependency chain; for one token
@@ -327,15 +362,15 @@ def measure_shape(lib, dev, K, synthetic, rng, peak, name, Ms):
             # kernel's own contract (int8 vector + scale in), each in both scheduling modes.
             y8 = dev.DeviceArray((N_STREAMS, N), np.float32)
             nb8 = N * Kd / 4 + Kd + 4 * N
-            for mode, mname in ((K.GEMV_LATENCY, "latency"), (K.GEMV_THROUGHPUT, "throughput")):
-                K.check(lib.lspk_set_gemv_mode(mode))
-                for int8_in, tag, nb in ((0, "", nbytes), (1, "_int8", nb8)):
-                    K.check(lib.lspk_bench_linear_copies_independent(handles, None, n_copies, x.ptr, y8.ptr, 1, reps,
-                                                                     N_STREAMS, int8_in, ctypes.byref(ms)))
-                    ui = 1000.0 * ms.value / (reps * n_copies)
-                    key = f"independent{tag}_{mname}"
-                    row.update({f"us_{key}": ui, f"GBps_{key}": nb / ui / 1e3, f"frac_hbm_{key}": nb / ui / 1e3 / peak})
-            K.check(lib.lspk_set_gemv_mode(K.GEMV_LATENCY))
+            for int8_in, tag, nb in ((0, "", nbytes), (1, "_int8", nb8)):
+                K.check(lib.lspk_bench_linear_copies_independent(handles, None, n_copies, x.ptr, y8.ptr, 1, reps,
+                                                                 N_STREAMS, int8_in, ctypes.byref(ms)))
+                ui = 1000.0 * ms.value / (reps * n_copies)
+                key = f"independent{tag}_launches"
+                row.update({f"us_{key}": ui, f"GBps_{key}": nb / ui / 1e3, f"frac_hbm_{key}": nb / ui / 1e3 / peak})
+            # the same products through the batched entry point: all copies of the matrix in one launch
+            ub = time_linear_batch(lib, K, dev, [c.handle for c in copies], None, x, N, reps)
+            row.update({"us_batched": ub, "GBps_batched": nb8 / ub / 1e3, "frac_hbm_batched": nb8 / ub / 1e3 / peak})
             K.check(lib.lspk_tc_check_error())
             y8.free()
         rows.append(row)
@@ -650,18 +685,20 @@ def main():
     gy = dev.DeviceArray((N_STREAMS, cfg.intermediate_size), np.float32)
     gemv_bytes = cfg.intermediate_size * cfg.hidden_size / 4 + cfg.hidden_size + 4 * cfg.intermediate_size
     gemv = {}
-    for mode, mname, up in ((K.GEMV_LATENCY, "latency", None), (K.GEMV_THROUGHPUT, "throughput", None),
-                            (K.GEMV_THROUGHPUT, "throughput_gate_up", up_handles)):
-        K.check(lib.lspk_set_gemv_mode(mode))
-        K.check(lib.lspk_bench_linear_copies_independent(gate_handles, up, cfg.num_layers, gx.ptr, gy.ptr, 1, 20, N_STREAMS, 1,
-                                                         ctypes.byref(ms)))
-        us = 1000.0 * float(ms.value) / (20 * cfg.num_layers)
+    K.check(lib.lspk_bench_linear_copies_independent(gate_handles, None, cfg.num_layers, gx.ptr, gy.ptr, 1, 20, N_STREAMS, 1,
+                                                     ctypes.byref(ms)))
+    us = 1000.0 * float(ms.value) / (20 * cfg.num_layers)
+    gemv["launch_per_matrix"] = {"us_per_product": us, "bytes_per_product": gemv_bytes, "achieved": gemv_bytes / us / 1e3,
+                                 "frac": gemv_bytes / us / 1e3 / peak,
+                                 "how": f"lspk_linear per matrix, independent graph nodes on {N_STREAMS} forked streams"}
+    for mname, up in (("batched", None), ("batched_gate_up", up_handles)):
+        us = time_linear_batch(lib, K, dev, list(gate_handles), list(up) if up is not None else None, gx,
+                               cfg.intermediate_size, 20)
         nb = gemv_bytes + (cfg.intermediate_size * cfg.hidden_size / 4 if up is not None else 0)
-        gemv[mname] = {"us_per_launch": us, "bytes_per_launch": nb, "achieved": nb / us / 1e3, "frac": nb / us / 1e3 / peak}
-    K.check(lib.lspk_set_gemv_mode(K.GEMV_LATENCY))
+        gemv[mname] = {"us_per_product": us, "bytes_per_product": nb, "achieved": nb / us / 1e3, "frac": nb / us / 1e3 / peak}
     K.check(lib.lspk_tc_check_error())
-    gemv_us = gemv["throughput"]["us_per_launch"]
-    gemv_gbs = gemv["throughput"]["achieved"]
+    gemv_us = gemv["batched"]["us_per_product"]
+    gemv_gbs = gemv["batched"]["achieved"]
     gx.free()
     gy.free()
     token_ms = total_ms / (args.steps * GEN_LEN)
@@ -705,11 +742,12 @@ def main():
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                      "launches_timed": n_launch.value * reps,
                      "how": "CUDA events around graph replays of the 120 linear launches of one token over all 30 layers' weights (521 MB, > L2)"},
-        "roofline_gemv_independent": {"kernel": "ternary_linear_kernel (M=1, 6912x2560, int8 vector in, throughput mode)",
+        "roofline_gemv_independent": {"kernel": "ternary_gemv_stream_kernel (lspk_linear_batch: one-row products, 6912x2560, int8 vector in)",
                                       "bound": "hbm", "achieved": gemv_gbs, "peak": peak, "unit": "GB/s",
-                                      "frac": gemv_gbs / peak, "us_per_launch": gemv_us, "bytes_per_launch": gemv_bytes,
-                                      "modes": gemv,
-                                      "how": "the 30 layers' gate matrices as independent graph nodes on %d forked streams, 20 replays" % N_STREAMS + ""},
+                                      "frac": gemv_gbs / peak, "us_per_product": gemv_us, "bytes_per_product": gemv_bytes,
+                                      "variants": gemv,
+                                      "how": "the 30 layers' gate matrices (133 MB, larger than the L2) as ONE call of the batched "
+                                             "entry point, CUDA events around 20 calls"},
         "roofline_lm_head": {"kernel": "lm_head_kernel<bf16>", "bound": "hbm", "achieved": lm_gbs, "peak": peak,
                              "unit": "GB/s", "frac": lm_gbs / peak, "us_per_launch": 1000.0 * lm_ms},
         "roofline_token": {"bytes_per_token": token_bytes, "us_per_token": 1000.0 * token_ms, "achieved": token_gbs,

@@ -137,17 +137,16 @@ typedef struct {
  * capture. */
 int lspk_linear(const lspk_linear_args* a);
 int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tcgen05 only */
-/* How the one-row product (M = 1, the reference's matmul_lut_*_m1) is scheduled.
- *   LSPK_GEMV_LATENCY (default): for a chain of launches in which each consumes the previous one's output
- *     (a decode step): one CTA per 16-row group, weights requested by per-lane loads before the dependency
- *     wait.
- *   LSPK_GEMV_THROUGHPUT: for back-to-back launches that do not depend on one another (the way the
- *     reference's kernel benchmark calls matmul_lut_*_m1 in a loop): fewer CTAs, each with a ring of up to
- *     four row groups in shared memory filled by bulk asynchronous copies requested at kernel entry.
- * Results are bit-identical in both modes.  The mbarrier waits of the second mode are bounded; an expiry is
- * reported by lspk_tc_check_error. */
-enum { LSPK_GEMV_LATENCY = 0, LSPK_GEMV_THROUGHPUT = 1 };
-int lspk_set_gemv_mode(int mode);
+/* n independent one-row products in ONE launch: product i is args[i], which must have M == 1 and the int8
+ * prologue (x_i8 + x_scales: the contract of the reference's matmul_lut_{tag}_m1, matmul_lut_avx512_extern_c.cpp:
+ * 150-236; quantise fp32 rows first with lspk_quantize_rows / lspk_rmsnorm_quantize_rows), one matrix with the
+ * STORE / ADD epilogue or a gate + up pair with a gated epilogue, up to 96 products, K up to 8192.  For callers
+ * that loop over matrices which do not depend on one another (the reference's kernel benchmark does; so do the
+ * experts of a mixture layer): the row groups of all products form one stream that a persistent grid, one CTA
+ * per SM, pulls through per-warp rings of bulk asynchronous copies, so that no product pays a kernel's fill and
+ * drain.  The outputs must not be inputs of other products of the same call.  Results are bit-identical to
+ * lspk_linear.  Every device-side wait is bounded; an expiry is reported by lspk_tc_check_error. */
+int lspk_linear_batch(const lspk_linear_args* args, int n);
 /* The tcgen05 kernel bounds every device-side wait; this reads and clears its expiry flag
  * (LSPK_ERR_DEVICE_WAIT if a wait ran out since the last call).  Synchronises the stream. */
 int lspk_tc_check_error(void);

@@ -873,8 +873,7 @@ static int attention_launch_t(const AttnParams& p) {
         const size_t rs = (size_t)((p.Q + 2 * p.KV) * D + D) * sizeof(float);
         LSPK_CUDA(launch(rope_store_kernel<KVT>, dim3(p.T), dim3(kAttnThreads), rs, true, p));
     }
-    static const int knob_rows = getenv("LSPK_ATTN_ROWS") ? atoi(getenv("LSPK_ATTN_ROWS")) : 1;
-    if (knob_rows && !p.fused && !p.pos_per_row && p.T >= 2 * kRows) {
+    if (!p.fused && !p.pos_per_row && p.T >= 2 * kRows) {
         // many consecutive rows of one sequence: kRows query rows per CTA share every key / value row they fetch
         const int nch2 = D / VEC, tpk2 = nch2 > 32 ? 32 : nch2;
         const size_t sm = (size_t)(kRows * D + (kAttnThreads / tpk2) * kRows * D + kRows * ((p.t_max + 3) & ~3)) * sizeof(float);
@@ -895,9 +894,10 @@ static int attention_launch_t(const AttnParams& p) {
             return LSPK_OK;
         }
     }
-    static const int knob_split = getenv("LSPK_ATTN_SPLIT") ? atoi(getenv("LSPK_ATTN_SPLIT")) : 1;
-    if (p.fused && knob_split && p.Q * p.T * kSplit <= 2 * sm_count() + kSplit) {
-        // decode rows: keys split over a cluster of kSplit CTAs
+    if (p.fused) {
+        // decode rows: keys split over a cluster of kSplit CTAs.  Every decode launch takes this kernel, whatever
+        // the number of sequences, so that a sequence's attention sums are formed in the same order alone and in a
+        // batch (its tokens do not depend on what it is batched with).
         const int nch = D / VEC, tpk = nch > 32 ? 32 : nch;
         const int local_keys = (p.t_max + kSplit - 1) / kSplit + 1;
         const size_t sm = (size_t)(5 * D + (kAttnThreads / tpk) * D + kSplit * D + local_keys) * sizeof(float);

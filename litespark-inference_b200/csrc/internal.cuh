@@ -42,7 +42,7 @@ struct LinearParams {
     int8_t* xq_out;
     float* xscale_out;
     int stream_weights;    // 1: weights are read once by this launch -> evict-first loads
-    int bulk_stages;       // > 0: bulk-copy variant of the one-row kernel with a weight ring of this many stages
+    int bulk_stages;       // > 0 (expert-grouped launches of the eight-row kernel): weight ring of this many stages
     int* error_flag;       // set to LSPK_ERR_DEVICE_WAIT when a bounded wait of that variant runs out
     unsigned long long* trace;
     int trace_cap;
@@ -73,7 +73,6 @@ __host__ __device__ inline int mma_row_stride(int Kp) { return (Kp % 128 == 0) ?
 // Launch the CUDA-core kernel with fully prepared parameters.  mt: rows per CTA tile (1, 2, 4 or 8).
 int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z);
 
-int set_gemv_mode(int mode);
 // linear.cu: validate + launch the CUDA-core ternary linear kernel on the library stream.
 int linear_cuda_core(const lspk_linear_args* a);
 

@@ -25,9 +25,6 @@ namespace lspk {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kBulkBatch = 8;                   // row groups a CTA of the bulk-copy variant handles per round
-constexpr int kBulkPartBytes = 2 * kBulkBatch * 8 * 16 * 4;
-constexpr unsigned kBulkSpinLimit = 1u << 22;   // polls of an mbarrier before a CTA gives up (seconds)
 
 // Reductions over the eight warps of a CTA.  One barrier each: the result is read back from `slot`
 // (8 floats, 16-byte aligned) by every thread, so two consecutive reductions need two slots.
@@ -54,10 +51,7 @@ __device__ __forceinline__ float cta8_max_nonneg(float v, float* slot) {
 // PAIR    gate/up pairing (two weight streams, gated epilogue)
 // GROUPED expert-grouped launch: blockIdx.z is the expert; its row list and row count are read from
 //         device arrays, its weights and scales are found by stride (packed-expert MoE GEMV)
-// BULK    the packed weights of a row group arrive in shared memory by bulk copies that one thread issues at
-//         kernel entry (all of the CTA's first groups at once, a ring of p.bulk_stages) instead of through
-//         per-lane register loads: more bytes in flight per SM, none of them held in registers
-template <int MT, int NI, int NB, bool PAIR, bool GROUPED, bool BULK>
+template <int MT, int NI, int NB, bool PAIR, bool GROUPED>
 #ifdef LSPK_LINEAR_MIN_BLOCKS
 __global__ void __launch_bounds__(kThreads, LSPK_LINEAR_MIN_BLOCKS)
 #else
@@ -75,15 +69,6 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     float* redf = reinterpret_cast<float*>(part + kPartInts);          // [32] reduction scratch
     float* s_scale = redf + 32;                                        // [MT]
     int* s_sumx = reinterpret_cast<int*>(s_scale + MT);                // [MT][warps] partial sums of x
-    // BULK: mbarriers and the weight ring behind everything else, on a 128-byte boundary
-    unsigned char* ring_base = reinterpret_cast<unsigned char*>(
-        (reinterpret_cast<uintptr_t>(s_sumx + MT * kWarps) + 127) & ~uintptr_t(127));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_base);           // [kBulkBatch]
-    int* bpart = reinterpret_cast<int*>(ring_base + 128);              // [PAIR?2:1][kBulkBatch][warps][16]
-    uint4* ring = reinterpret_cast<uint4*>(ring_base + 128 + kBulkPartBytes);   // [stages][PAIR?2:1][chunks*16]
-    const int grp_u4 = p.chunks * kRowsPerGroup;
-    const int stage_u4 = grp_u4 * (PAIR ? 2 : 1);
-
     const int z = GROUPED ? blockIdx.z : 0;
     const size_t w_off = GROUPED ? (size_t)z * p.grp_w_stride : 0;
 
@@ -117,32 +102,9 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             }
         }
     };
-    // BULK: request row group number `it_` of this CTA into its ring stage (one thread)
-    auto issue_group = [&](int it_) {
-        int ss, gg;
-        locate((int)blockIdx.x + it_ * (int)gridDim.x, ss, gg);
-        const int st = it_ % p.bulk_stages;
-        uint4* dst = ring + (size_t)st * stage_u4;
-        const uint32_t bytes = (uint32_t)grp_u4 * 16u;
-        mbar_expect_tx(&bars[st], bytes * (PAIR ? 2u : 1u));
-        const uint4* src_a = p.seg[ss].w + (size_t)gg * grp_u4;
-        if (p.stream_weights) {
-            bulk_load_stream(dst, src_a, bytes, &bars[st]);
-            if (PAIR) bulk_load_stream(dst + grp_u4, p.seg[1].w + (size_t)gg * grp_u4, bytes, &bars[st]);
-        } else {
-            bulk_load(dst, src_a, bytes, &bars[st]);
-            if (PAIR) bulk_load(dst + grp_u4, p.seg[1].w + (size_t)gg * grp_u4, bytes, &bars[st]);
-        }
-    };
     PhaseTrace tr;
     tr.begin(p.trace, p.trace_cap, 1);
     tr.mark();                                   // 0: entry
-    if (BULK && tid == 0) {
-        for (int st = 0; st < p.bulk_stages; ++st) mbar_init(&bars[st], 1);
-        fence_mbar_init();
-        for (int it_ = 0; it_ < p.bulk_stages && (int)blockIdx.x + it_ * (int)gridDim.x < p.total_groups; ++it_)
-            issue_group(it_);
-    }
     const int pairs = (p.chunks + 1) / 2;
     const bool one_batch = kWarps * NI >= pairs;     // a row group's weights fit one register batch
     const bool fp32_in = p.prologue != LSPK_PRO_INT8;
@@ -156,7 +118,7 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
     //      An expert-grouped launch cannot: whether this expert has any row is device data. ----
     uint4 wa[NI], wb[PAIR ? NI : 1];
     uint4 na[NI], nb_[PAIR ? NI : 1];                // the next row group's first batch
-    if (!GROUPED && !BULK) load_batch(s0, g0, 0, wa, wb);
+    if (!GROUPED) load_batch(s0, g0, 0, wa, wb);
     float gm[NB][16];
     if (normed) {
 #pragma unroll
@@ -209,8 +171,8 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
             if (n >= p.seg[seg_i].N) return 0.0f;
             return p.seg[seg_i].out[(size_t)out_row(out_m) * p.seg[seg_i].N + n];
         };
-        float resid = BULK ? 0.0f : residual_of(s, g);
-        if (!BULK && (GROUPED || !first_tile)) load_batch(s, g, 0, wa, wb);
+        float resid = residual_of(s, g);
+        if (GROUPED || !first_tile) load_batch(s, g, 0, wa, wb);
         first_tile = false;
 
         // ---- prologue: this tile's activations -> permuted int8 rows in shared memory ---------------
@@ -367,99 +329,6 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
         __syncthreads();
         tr.mark();                                   // 7: activations visible to all warps
 
-        // ---- bulk-copy variant: the CTA's row groups in rounds of up to bulk_stages groups.  A round waits for
-        //      its stages, forms the partial sums of all its groups, and reduces and stores them behind a single
-        //      barrier; only then are the stages requested again. ------------------------------------------------
-        if constexpr (BULK) {
-            const int S = p.bulk_stages;
-            int wait_failed = 0;
-            for (int it0 = 0; (int)blockIdx.x + it0 * (int)gridDim.x < p.total_groups; it0 += S) {
-                int n_here = 1;
-                while (n_here < S && (int)blockIdx.x + (it0 + n_here) * (int)gridDim.x < p.total_groups) ++n_here;
-                const uint32_t parity = (uint32_t)(it0 / S) & 1u;
-                // output element of this thread in the round: group tid / 16, row tid % 16
-                int es = 0, eg = 0;
-                float eres = 0.0f;
-                const bool e_on = tid < 16 * n_here;
-                if (e_on) {
-                    locate((int)blockIdx.x + (it0 + out_m) * (int)gridDim.x, es, eg);
-                    if (p.epilogue == LSPK_EPI_ADD && eg * kRowsPerGroup + out_r < p.seg[es].N)
-                        eres = p.seg[es].out[(size_t)eg * kRowsPerGroup + out_r];
-                }
-#pragma unroll
-                for (int gi = 0; gi < kBulkBatch; ++gi) {
-                    if (gi < n_here) {
-                        bool arrived = false;
-                        for (unsigned i = 0; i < kBulkSpinLimit && !arrived; ++i) arrived = mbar_try_wait(&bars[gi], parity);
-                        wait_failed |= arrived ? 0 : 1;
-                        int acc_a[4] = {0, 0, 0, 0}, acc_b[4] = {0, 0, 0, 0};
-                        const uint4* sa = ring + (size_t)gi * stage_u4 + r;
-#pragma unroll 2
-                        for (int j = 2 * warp + h; j < p.chunks; j += 2 * kWarps) {
-                            const int4* xp = reinterpret_cast<const int4*>(xq + (size_t)j * 64);
-                            chunk_dot(sa[j * kRowsPerGroup], xp, acc_a);
-                            if (PAIR) chunk_dot(sa[grp_u4 + j * kRowsPerGroup], xp, acc_b);
-                        }
-                        int v = acc_a[0] + (acc_a[1] >> 2) + (acc_a[2] >> 4) + (acc_a[3] >> 6);
-                        v += __shfl_down_sync(0xffffffffu, v, 16);
-                        if (h == 0) bpart[(gi * kWarps + warp) * 16 + r] = v;
-                        if (PAIR) {
-                            int u = acc_b[0] + (acc_b[1] >> 2) + (acc_b[2] >> 4) + (acc_b[3] >> 6);
-                            u += __shfl_down_sync(0xffffffffu, u, 16);
-                            if (h == 0) bpart[(kBulkBatch + gi) * kWarps * 16 + warp * 16 + r] = u;
-                        }
-                    }
-                }
-                tr.mark();                           // 8+: dot products of a round done
-                if (__syncthreads_or(wait_failed)) {
-                    // a wait ran out: flag it, give this round's copies one more bounded wait, leave
-                    if (tid == 0) {
-                        if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
-                        for (int gi = 0; gi < n_here; ++gi) {
-                            bool done = false;
-                            for (unsigned i = 0; i < kBulkSpinLimit && !done; ++i) done = mbar_try_wait(&bars[gi], parity);
-                        }
-                    }
-                    break;
-                }
-                if (tid == 0)
-                    for (int gi = 0; gi < S && (int)blockIdx.x + (it0 + S + gi) * (int)gridDim.x < p.total_groups; ++gi)
-                        issue_group(it0 + S + gi);
-                if (e_on) {
-                    const LinearSeg& sg = p.seg[es];
-                    const int n = eg * kRowsPerGroup + out_r;
-                    if (n < sg.N) {
-                        int va = 0, vb = 0, sx = 0;
-#pragma unroll
-                        for (int w = 0; w < kWarps; ++w) {
-                            va += bpart[(out_m * kWarps + w) * 16 + out_r];
-                            if (PAIR) vb += bpart[(kBulkBatch + out_m) * kWarps * 16 + w * 16 + out_r];
-                            sx += s_sumx[w];
-                        }
-                        va -= sx;
-                        if (sg.acc_out) sg.acc_out[n] = va;
-                        const float ya = __fmul_rn((float)va, __fmul_rn(s_scale[0], sg.w_scale));
-                        if (PAIR) {
-                            vb -= sx;
-                            if (p.seg[1].acc_out) p.seg[1].acc_out[n] = vb;
-                            const float yb = __fmul_rn((float)vb, __fmul_rn(s_scale[0], p.seg[1].w_scale));
-                            if (p.epilogue == LSPK_EPI_SILU_MUL) {
-                                sg.out[n] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
-                            } else {
-                                const float gpos = fmaxf(ya, 0.0f);
-                                sg.out[n] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
-                            }
-                        } else if (p.epilogue == LSPK_EPI_ADD) {
-                            sg.out[n] = __fadd_rn(eres, ya);
-                        } else {
-                            sg.out[n] = ya;
-                        }
-                    }
-                }
-                tr.mark();                           // 9+: round reduced and stored
-                __syncthreads();                     // the partial sums are rewritten by the next round
-            }
-        } else {
         // ---- loop over this CTA's row groups: integer dot products, reduction, epilogue ----------------
         while (true) {
             const int next_flat = flat + gridDim.x;
@@ -567,7 +436,6 @@ ternary_linear_kernel(const __grid_constant__ LinearParams p) {
                 load_batch(s, g, 0, wa, wb);
             }
         }
-        }
         if (!GROUPED) break;
     }
     tr.end();
@@ -579,15 +447,10 @@ static size_t linear_smem_bytes(int MT, int Kp, bool pair) {
     b += 32 * 4 + MT * 4 + MT * kWarps * 4;
     return b;
 }
-// with the weight ring of the bulk-copy variant (alignment slack, barriers, stages)
-static size_t linear_bulk_smem_bytes(int Kp, bool pair, int chunks, int stages) {
-    return linear_smem_bytes(1, Kp, pair) + 128 + 128 + kBulkPartBytes + (size_t)stages * chunks * 256 * (pair ? 2 : 1);
-}
-
-template <int MT, int NI, int NB, bool PAIR, bool GROUPED, bool BULK = false>
+template <int MT, int NI, int NB, bool PAIR, bool GROUPED>
 static cudaError_t launch_linear(const LinearParams& p, dim3 grid, size_t smem) {
     static bool attr_set = false;
-    auto kern = ternary_linear_kernel<MT, NI, NB, PAIR, GROUPED, BULK>;
+    auto kern = ternary_linear_kernel<MT, NI, NB, PAIR, GROUPED>;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return e;
@@ -605,31 +468,15 @@ static cudaError_t launch_linear_mt(const LinearParams& p, dim3 grid, bool pair,
     return pair ? launch_linear<MT, 8, 8, true, false>(p, grid, smem) : launch_linear<MT, 8, 8, false, false>(p, grid, smem);
 }
 
-static cudaError_t launch_linear_bulk(const LinearParams& p, dim3 grid, bool pair, size_t smem) {
-    if (p.chunks <= 64)
-        return pair ? launch_linear<1, 4, 1, true, false, true>(p, grid, smem) : launch_linear<1, 4, 1, false, false, true>(p, grid, smem);
-    if (p.chunks <= 128)
-        return pair ? launch_linear<1, 8, 2, true, false, true>(p, grid, smem) : launch_linear<1, 8, 2, false, false, true>(p, grid, smem);
-    return pair ? launch_linear<1, 8, 8, true, false, true>(p, grid, smem) : launch_linear<1, 8, 8, false, false, true>(p, grid, smem);
-}
-
 int linear_launch_params(const LinearParams& p, int mt, bool pair, bool grouped, int grid_x, int grid_y, int grid_z) {
     // more than one token row per tile (and every expert-grouped launch): the eight-row mma kernel
     if (mt > 1 || grouped) return linear_mma_launch(p, pair, grouped, grid_x, grid_y, grid_z);
     const int Kp = p.chunks * kWeightsPerChunk;
-    const size_t smem = p.bulk_stages > 0 ? linear_bulk_smem_bytes(Kp, pair, p.chunks, p.bulk_stages)
-                                          : linear_smem_bytes(1, Kp, pair);
+    const size_t smem = linear_smem_bytes(1, Kp, pair);
     LSPK_REQUIRE(smem <= 200 * 1024 && p.chunks <= 512, "linear: K=%d too large (limit 32768)", p.K);
     const dim3 grid(grid_x, grid_y, grid_z);
-    const cudaError_t e = p.bulk_stages > 0 ? launch_linear_bulk(p, grid, pair, smem) : launch_linear_mt<1>(p, grid, pair, smem);
+    const cudaError_t e = launch_linear_mt<1>(p, grid, pair, smem);
     if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "linear launch failed: %s", cudaGetErrorString(e));
-    return LSPK_OK;
-}
-
-static int g_gemv_mode = LSPK_GEMV_LATENCY;
-int set_gemv_mode(int mode) {
-    LSPK_REQUIRE(mode == LSPK_GEMV_LATENCY || mode == LSPK_GEMV_THROUGHPUT, "lspk_set_gemv_mode: unknown mode %d", mode);
-    g_gemv_mode = mode;
     return LSPK_OK;
 }
 
@@ -737,33 +584,10 @@ int linear_cuda_core(const lspk_linear_args* a) {
     // runs once per CTA, which then loops over its row groups).  With several token tiles the grid's
     // second dimension already fills the machine.
     const int tiles = (a->M + MT - 1) / MT;
-    static const int knob_stream = getenv("LSPK_STREAM_WEIGHTS") ? atoi(getenv("LSPK_STREAM_WEIGHTS")) : 1;
-    static const int knob_ctas_per_sm = getenv("LSPK_LINEAR_CTAS_PER_SM") ? atoi(getenv("LSPK_LINEAR_CTAS_PER_SM")) : 2;
-    p.stream_weights = (tiles == 1 && knob_stream) ? 1 : 0;
+    p.stream_weights = tiles == 1 ? 1 : 0;
     int ctas = groups;
-    if (knob_ctas_per_sm > 0) {
-        const int per_wave = tiles == 1 ? knob_ctas_per_sm * sm_count()
-                                        : (2 * sm_count() + tiles - 1) / tiles;
-        if (ctas > per_wave) ctas = per_wave > 0 ? per_wave : 1;
-    }
-    // One token row in throughput mode: the bulk-copy variant.  A CTA takes g row groups, all requested at
-    // kernel entry into a ring of g stages; g grows with the size of the launch so that about half an SM count
-    // of CTAs remain (measured best for back-to-back independent launches), bounded by the ring's size.
-    // LSPK_LINEAR_BULK = g forces a depth of up to eight (0: never).
-    static const int knob_bulk = getenv("LSPK_LINEAR_BULK") ? atoi(getenv("LSPK_LINEAR_BULK")) : -1;
-    if (tiles == 1 && (knob_bulk > 0 || (knob_bulk < 0 && g_gemv_mode == LSPK_GEMV_THROUGHPUT))) {
-        const size_t stage = (size_t)p.chunks * 256 * (pair ? 2 : 1);
-        const int half_sms = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
-        int g = knob_bulk > 0 ? knob_bulk : (groups + half_sms - 1) / half_sms;
-        if (g > 4 && knob_bulk <= 0) g = 4;
-        if (g > kBulkBatch) g = kBulkBatch;
-        while (g > 1 && (size_t)g * stage > 96 * 1024) --g;
-        if (stage <= 96 * 1024) {
-            p.bulk_stages = g;
-            p.error_flag = device_wait_flag();
-            ctas = (groups + g - 1) / g;
-        }
-    }
+    const int per_wave = tiles == 1 ? 2 * sm_count() : (2 * sm_count() + tiles - 1) / tiles;
+    if (ctas > per_wave) ctas = per_wave > 0 ? per_wave : 1;
     return linear_launch_params(p, MT, pair, false, ctas, tiles, 1);
 }
 
@@ -772,8 +596,6 @@ int linear_cuda_core(const lspk_linear_args* a) {
 using namespace lspk;
 
 static int g_force_path = 0;   // 0 auto, 1 CUDA-core only, 2 tensor-core only
-
-extern "C" int lspk_set_gemv_mode(int mode) { return set_gemv_mode(mode); }
 
 extern "C" int lspk_linear_force_path(int path) {
     LSPK_REQUIRE(path >= 0 && path <= 2, "lspk_linear_force_path: path must be 0, 1 or 2");

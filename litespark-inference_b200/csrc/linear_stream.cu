@@ -1,0 +1,325 @@
+// Many independent one-row ternary products in ONE launch (lspk_linear_batch).
+//
+// The reference's kernel benchmark calls matmul_lut_*_m1 in a loop over matrices that do not depend on one
+// another (benchmark_kernel.py, the per-shape timing loops; kernel matmul_lut_avx512_m1,
+// matmul_lut_avx512_extern_c.cpp:150-236).  On the GPU a launch per matrix pays a ramp every time: a 4.4 MB
+// matrix is 0.7 us of HBM time, shorter than the fill and drain of a kernel.  Here the whole list is one
+// stream of bytes: the row groups of all products form one flat sequence of units, dealt round-robin to every
+// warp of a persistent grid (one CTA per SM), and each warp keeps a private ring of bulk copies
+// (cp.async.bulk + mbarrier) running ahead of its arithmetic, across product boundaries.
+//
+//   unit   = 16 output rows of one product (both matrices of a gated gate/up pair), cut along K into stages of
+//            at most 10 KB; a warp accumulates a unit's stages in registers and stores its 16 results itself:
+//            no CTA-wide barrier per unit, only one per product (when the next activation vector is installed)
+//   vector = the int8 activations of product i + 1 are fetched into registers while product i is computed, then
+//            byte-transposed into the other of two shared-memory slots
+// The arithmetic per row is the one-row kernel's (masked dp4a fields, exact shifts, sum(x) subtracted once), so
+// results are bit-identical to lspk_linear.  Every mbarrier wait is bounded: on expiry the warp raises the
+// library's wait flag, stops computing and only keeps the CTA's barriers company until the kernel ends.
+#include "internal.cuh"
+#include "ternary_core.cuh"
+
+namespace lspk {
+
+constexpr int kSWarps = 8;                       // warps per CTA
+constexpr int kSRing = 2;                        // ring stages per warp
+constexpr int kSStageChunks = 40;                // 16-row x 16-byte chunks per stage (all matrices of a unit)
+constexpr int kSStageBytes = kSStageChunks * kRowsPerGroup * 16;   // 10240
+constexpr int kSMaxItems = 96;
+constexpr int kSMaxKp = 8192;                    // longest row (K rounded up to 64)
+constexpr unsigned kSSpinLimit = 1u << 22;
+
+struct StreamItem {
+    const uint4* w[2];
+    float* out;
+    int32_t* acc[2];
+    const int8_t* x;
+    const float* xs;
+    float ws[2];
+    int N, K, chunks, groups;
+    int nm;            // matrices per unit: 1, or 2 for the gated pairing
+    int epilogue;
+    int unit0;         // flat index of this product's first unit
+    int cps;           // chunks per stage and matrix
+    int sub;           // stages per unit
+};
+struct StreamParams {
+    StreamItem it[kSMaxItems];
+    int n;
+    int total_units;
+    int* error_flag;
+};
+
+struct StreamCursor {      // position in one warp's sequence of stages
+    int item, unit, s;
+};
+
+__global__ void __launch_bounds__(kSWarps * 32, 1)
+ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint4* ring = reinterpret_cast<uint4*>(smem_raw);                                   // [warps][ring][stage]
+    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw + (size_t)kSWarps * kSRing * kSStageBytes);   // [2][kSMaxKp]
+    __shared__ __align__(8) uint64_t bars[kSWarps][kSRing];
+    __shared__ int s_sumx[2][kSWarps];
+    __shared__ float s_scale[2];
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = lane & 15, h = lane >> 4;
+    const int TW = gridDim.x * kSWarps;
+    const int gw = blockIdx.x * kSWarps + warp;
+    uint4* my_ring = ring + (size_t)warp * kSRing * (kSStageBytes / 16);
+
+    auto settle = [&](StreamCursor& c) {          // move c.item to the product that holds c.unit
+        while (c.item < p.n && c.unit >= p.it[c.item].unit0 + p.it[c.item].groups) ++c.item;
+    };
+    auto advance = [&](StreamCursor& c) {
+        if (++c.s >= p.it[c.item].sub) {
+            c.s = 0;
+            c.unit += TW;
+            settle(c);
+        }
+    };
+    auto issue = [&](const StreamCursor& c, int slot) {       // one lane: request a stage into ring slot `slot`
+        const StreamItem& it = p.it[c.item];
+        const int g = c.unit - it.unit0;
+        const int c0 = c.s * it.cps, c1 = min(c0 + it.cps, it.chunks);
+        const uint32_t bytes = (uint32_t)(c1 - c0) * kRowsPerGroup * 16u;
+        uint4* dst = my_ring + (size_t)slot * (kSStageBytes / 16);
+        mbar_expect_tx(&bars[warp][slot], bytes * (uint32_t)it.nm);
+        for (int m = 0; m < it.nm; ++m)
+            bulk_load_stream(dst + (size_t)m * (c1 - c0) * kRowsPerGroup,
+                             it.w[m] + ((size_t)g * it.chunks + c0) * kRowsPerGroup, bytes, &bars[warp][slot]);
+    };
+
+    if (tid == 0) s_abort = 0;
+    if (lane == 0) {
+        for (int s = 0; s < kSRing; ++s) mbar_init(&bars[warp][s], 1);
+        fence_mbar_init();
+    }
+    __syncwarp();
+    grid_dependency_launch();
+    // the weights do not depend on whatever ran before: fill the ring first
+    StreamCursor prod = {0, gw, 0}, cons = {0, gw, 0};
+    settle(prod);
+    settle(cons);
+    int issued = 0, consumed = 0;
+    if (lane == 0) {
+        while (issued < kSRing && prod.item < p.n) {
+            issue(prod, issued % kSRing);
+            advance(prod);
+            ++issued;
+        }
+    }
+    issued = __shfl_sync(0xffffffffu, issued, 0);
+    prod.item = __shfl_sync(0xffffffffu, prod.item, 0);
+    prod.unit = __shfl_sync(0xffffffffu, prod.unit, 0);
+    prod.s = __shfl_sync(0xffffffffu, prod.s, 0);
+    grid_dependency_wait();
+
+    // activation vector of product `i`: this thread's 16-byte blocks (at most two), raw, into registers
+    uint32_t raw[2][4];
+    auto fetch_x = [&](int i) {
+        const StreamItem& it = p.it[i];
+        const int Kp = it.chunks * kWeightsPerChunk;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int k0 = (tid + u * kSWarps * 32) * 16;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int k = k0 + q * 4;
+                raw[u][q] = (k0 < Kp && k < it.K) ? __ldg(reinterpret_cast<const uint32_t*>(it.x + k)) : 0u;
+            }
+        }
+    };
+    auto install_x = [&](int i) {                 // registers -> transposed int8 row in slot i & 1, partial sum(x)
+        const StreamItem& it = p.it[i];
+        const int Kp = it.chunks * kWeightsPerChunk;
+        int8_t* dst = xq + (size_t)(i & 1) * kSMaxKp;
+        int sumx = 0;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int k0 = (tid + u * kSWarps * 32) * 16;
+            if (k0 < Kp) {
+                uint32_t o0, o1, o2, o3;
+                transpose4x4_bytes(raw[u][0], raw[u][1], raw[u][2], raw[u][3], o0, o1, o2, o3);
+                sumx = __dp4a((int)o0, 0x01010101, sumx);
+                sumx = __dp4a((int)o1, 0x01010101, sumx);
+                sumx = __dp4a((int)o2, 0x01010101, sumx);
+                sumx = __dp4a((int)o3, 0x01010101, sumx);
+                *reinterpret_cast<uint4*>(dst + k0) = make_uint4(o0, o1, o2, o3);
+            }
+        }
+        sumx = __reduce_add_sync(0xffffffffu, sumx);
+        if (lane == 0) s_sumx[i & 1][warp] = sumx;
+        if (tid == 0) s_scale[i & 1] = it.xs[0];
+    };
+    fetch_x(0);
+    install_x(0);
+    __syncthreads();
+
+    bool dead = false;                           // this warp gave up (a wait ran out here or elsewhere in the CTA)
+    for (int i = 0; i < p.n; ++i) {
+        if (i + 1 < p.n) fetch_x(i + 1);         // in flight while product i is computed
+        const StreamItem& it = p.it[i];
+        const int8_t* xrow = xq + (size_t)(i & 1) * kSMaxKp;
+        int sx = 0;
+#pragma unroll
+        for (int w = 0; w < kSWarps; ++w) sx += s_sumx[i & 1][w];
+        const float xscale = s_scale[i & 1];
+        int acc_a[4] = {0, 0, 0, 0}, acc_b[4] = {0, 0, 0, 0};
+        while (!dead && cons.item == i) {
+            const int slot = consumed % kSRing;
+            const uint32_t parity = (uint32_t)(consumed / kSRing) & 1u;
+            bool arrived = false;
+            for (unsigned spin = 0; spin < kSSpinLimit && !arrived; ++spin) {
+                arrived = mbar_try_wait(&bars[warp][slot], parity);
+                if (!arrived && (spin & 1023u) == 1023u && *(volatile int*)&s_abort) break;
+            }
+            if (!__all_sync(0xffffffffu, arrived)) {
+                dead = true;
+                if (lane == 0) {
+                    s_abort = 1;
+                    if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+                }
+                break;
+            }
+            const int g = cons.unit - it.unit0;
+            const int c0 = cons.s * it.cps, c1 = min(c0 + it.cps, it.chunks);
+            const uint4* sa = my_ring + (size_t)slot * (kSStageBytes / 16);
+            const uint4* sb = sa + (size_t)(c1 - c0) * kRowsPerGroup;
+            if (cons.s == 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc_a[c] = acc_b[c] = 0;
+            }
+#pragma unroll 2
+            for (int j = c0 + h; j < c1; j += 2) {
+                const int4* xp = reinterpret_cast<const int4*>(xrow + (size_t)j * 64);
+                chunk_dot(sa[(j - c0) * kRowsPerGroup + r], xp, acc_a);
+                if (it.nm == 2) chunk_dot(sb[(j - c0) * kRowsPerGroup + r], xp, acc_b);
+            }
+            const bool last = cons.s == it.sub - 1;
+            ++consumed;
+            advance(cons);
+            // hand the slot back: everyone has read it; then one lane requests the stage kSRing ahead
+            __syncwarp();
+            if (lane == 0 && prod.item < p.n) {
+                issue(prod, slot);
+                advance(prod);
+                ++issued;
+            }
+            if (last) {
+                int va = acc_a[0] + (acc_a[1] >> 2) + (acc_a[2] >> 4) + (acc_a[3] >> 6);
+                va += __shfl_down_sync(0xffffffffu, va, 16);
+                int vb = 0;
+                if (it.nm == 2) {
+                    vb = acc_b[0] + (acc_b[1] >> 2) + (acc_b[2] >> 4) + (acc_b[3] >> 6);
+                    vb += __shfl_down_sync(0xffffffffu, vb, 16);
+                }
+                const int n = g * kRowsPerGroup + r;
+                if (h == 0 && n < it.N) {
+                    va -= sx;
+                    if (it.acc[0]) it.acc[0][n] = va;
+                    const float ya = __fmul_rn((float)va, __fmul_rn(xscale, it.ws[0]));
+                    if (it.nm == 2) {
+                        vb -= sx;
+                        if (it.acc[1]) it.acc[1][n] = vb;
+                        const float yb = __fmul_rn((float)vb, __fmul_rn(xscale, it.ws[1]));
+                        if (it.epilogue == LSPK_EPI_SILU_MUL) {
+                            it.out[n] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
+                        } else {
+                            const float gpos = fmaxf(ya, 0.0f);
+                            it.out[n] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                        }
+                    } else if (it.epilogue == LSPK_EPI_ADD) {
+                        it.out[n] = __fadd_rn(it.out[n], ya);
+                    } else {
+                        it.out[n] = ya;
+                    }
+                }
+            }
+            // lane 0 advanced the producer cursor: share it
+            prod.item = __shfl_sync(0xffffffffu, prod.item, 0);
+            prod.unit = __shfl_sync(0xffffffffu, prod.unit, 0);
+            prod.s = __shfl_sync(0xffffffffu, prod.s, 0);
+            issued = __shfl_sync(0xffffffffu, issued, 0);
+        }
+        if (i + 1 < p.n) install_x(i + 1);
+        __syncthreads();
+        if (*(volatile int*)&s_abort) dead = true;
+    }
+    // A warp that stopped early may still have copies in flight into its ring: give each one bounded wait so that
+    // nothing lands in shared memory after the CTA has gone.
+    if (dead && lane == 0) {
+        for (int k = consumed; k < issued; ++k) {
+            const int slot = k % kSRing;
+            const uint32_t parity = (uint32_t)(k / kSRing) & 1u;
+            for (unsigned spin = 0; spin < kSSpinLimit && !mbar_try_wait(&bars[warp][slot], parity); ++spin) {}
+        }
+    }
+}
+
+static size_t stream_smem_bytes() { return (size_t)kSWarps * kSRing * kSStageBytes + 2 * (size_t)kSMaxKp; }
+
+}  // namespace lspk
+
+using namespace lspk;
+
+extern "C" int lspk_linear_batch(const lspk_linear_args* args, int n) {
+    if (int rc = ensure_init()) return rc;
+    LSPK_REQUIRE(args && n >= 1 && n <= kSMaxItems, "lspk_linear_batch: 1..%d products per call (got %d)", kSMaxItems, n);
+    static StreamParams p;                        // 10 KB: kept off the stack; calls are serialised by the caller
+    p.n = n;
+    p.error_flag = device_wait_flag();
+    int unit0 = 0;
+    for (int i = 0; i < n; ++i) {
+        const lspk_linear_args& a = args[i];
+        const bool pair = a.epilogue == LSPK_EPI_RELU2_MUL || a.epilogue == LSPK_EPI_SILU_MUL;
+        LSPK_REQUIRE(a.M == 1, "lspk_linear_batch: product %d has %d rows (one-row products only)", i, a.M);
+        LSPK_REQUIRE(a.prologue == LSPK_PRO_INT8 && a.x_i8 && a.x_scales,
+                     "lspk_linear_batch: product %d: int8 activations + scale in (quantise fp32 rows first with "
+                     "lspk_quantize_rows / lspk_rmsnorm_quantize_rows)", i);
+        LSPK_REQUIRE(((uintptr_t)a.x_i8 & 3) == 0, "lspk_linear_batch: product %d: x_i8 must be 4-byte aligned", i);
+        LSPK_REQUIRE(a.epilogue >= 0 && a.epilogue <= 3, "lspk_linear_batch: product %d: unknown epilogue", i);
+        LSPK_REQUIRE(a.n_mats == (pair ? 2 : 1), "lspk_linear_batch: product %d: one matrix, or gate + up for a gated epilogue", i);
+        const Weight* w0 = reinterpret_cast<const Weight*>(a.w[0]);
+        LSPK_REQUIRE(w0 && a.out[0], "lspk_linear_batch: product %d: null weight or output", i);
+        LSPK_REQUIRE(w0->chunks * kWeightsPerChunk <= kSMaxKp, "lspk_linear_batch: product %d: K=%d too long (limit %d)", i, w0->K, kSMaxKp);
+        StreamItem& it = p.it[i];
+        it = StreamItem{};
+        it.w[0] = w0->dev;
+        it.ws[0] = w0->scale;
+        it.acc[0] = a.acc_out[0];
+        it.nm = pair ? 2 : 1;
+        if (pair) {
+            const Weight* w1 = reinterpret_cast<const Weight*>(a.w[1]);
+            LSPK_REQUIRE(w1 && w1->K == w0->K && w1->N == w0->N, "lspk_linear_batch: product %d: gate and up must have the same shape", i);
+            it.w[1] = w1->dev;
+            it.ws[1] = w1->scale;
+            it.acc[1] = a.acc_out[1];
+        }
+        it.out = a.out[0];
+        it.x = a.x_i8;
+        it.xs = a.x_scales;
+        it.N = w0->N;
+        it.K = w0->K;
+        it.chunks = w0->chunks;
+        it.groups = w0->groups;
+        it.epilogue = a.epilogue;
+        it.unit0 = unit0;
+        it.cps = kSStageChunks / it.nm;
+        it.sub = (it.chunks + it.cps - 1) / it.cps;
+        unit0 += it.groups;
+    }
+    p.total_units = unit0;
+    static bool attr_set = false;
+    const size_t smem = stream_smem_bytes();
+    if (!attr_set) {
+        LSPK_CUDA(cudaFuncSetAttribute(ternary_gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    int ctas = (unit0 + kSWarps - 1) / kSWarps;
+    if (ctas > sm_count()) ctas = sm_count();
+    LSPK_CUDA(launch(ternary_gemv_stream_kernel, dim3(ctas), dim3(kSWarps * 32), smem, true, p));
+    return LSPK_OK;
+}

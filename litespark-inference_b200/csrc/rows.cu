@@ -10,13 +10,25 @@
 
 namespace lspk {
 
-constexpr int kRowThreads = 512;
+constexpr int kRowThreads = 256;     // eight warps: the lanes of the canonical sum-of-squares order
 
 __device__ __forceinline__ float silu_gate(float z) { return __fdiv_rn(z, __fadd_rn(expf(-z), 1.0f)); }
 
 __device__ __forceinline__ float gamma_at(const void* gamma, int is_bf16, int k) {
     return is_bf16 ? bf16_bits_to_f32(reinterpret_cast<const uint16_t*>(gamma)[k])
                    : reinterpret_cast<const float*>(gamma)[k];
+}
+
+// Combines the threads' canonical sum-of-squares values (ternary_core.cuh: thread = lane of the 256-lane group)
+// over the CTA.  Two barriers: `red` can be reused right after.
+__device__ __forceinline__ float row_ssq_combine(float lane_value, float* red) {
+    static_assert(kRowThreads == 256, "the canonical order has 256 lanes");
+    const float v = warp_sum(lane_value);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    const float total = canonical_ssq_combine(red);
+    __syncthreads();
+    return total;
 }
 
 // mode bit 0: apply RMSNorm first; bit 1: quantise (else write fp32 rows to out_f32).
@@ -50,25 +62,34 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
         const int K4 = K >> 2;
         const float4* src4 = reinterpret_cast<const float4*>(src);
         float4* xs4 = reinterpret_cast<float4*>(xs);
-        float ssq = 0.0f, amax = 0.0f;
-        for (int i = tid; i < K4; i += kRowThreads) {
-            float4 v = src4[i];
-            if (gsrc) {
-                const float4 gz = reinterpret_cast<const float4*>(gsrc)[i];
-                v.x = __fmul_rn(v.x, silu_gate(gz.x));
-                v.y = __fmul_rn(v.y, silu_gate(gz.y));
-                v.z = __fmul_rn(v.z, silu_gate(gz.z));
-                v.w = __fmul_rn(v.w, silu_gate(gz.w));
+        // first pass in the canonical order of the sum of squares: thread = lane, 16-element blocks tid, tid + 256,
+        // ...; element e of a block goes into partial e % 4 (a float4's .x/.y/.z/.w are e % 4 = 0..3)
+        float amax = 0.0f;
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int b4 = tid * 4; b4 < K4; b4 += kRowThreads * 4) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int i = b4 + q;
+                if (i < K4) {
+                    float4 v = src4[i];
+                    if (gsrc) {
+                        const float4 gz = reinterpret_cast<const float4*>(gsrc)[i];
+                        v.x = __fmul_rn(v.x, silu_gate(gz.x));
+                        v.y = __fmul_rn(v.y, silu_gate(gz.y));
+                        v.z = __fmul_rn(v.z, silu_gate(gz.z));
+                        v.w = __fmul_rn(v.w, silu_gate(gz.w));
+                    }
+                    xs4[i] = v;
+                    ss[0] = fmaf(v.x, v.x, ss[0]);
+                    ss[1] = fmaf(v.y, v.y, ss[1]);
+                    ss[2] = fmaf(v.z, v.z, ss[2]);
+                    ss[3] = fmaf(v.w, v.w, ss[3]);
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                }
             }
-            xs4[i] = v;
-            ssq = fmaf(v.x, v.x, ssq);
-            ssq = fmaf(v.y, v.y, ssq);
-            ssq = fmaf(v.z, v.z, ssq);
-            ssq = fmaf(v.w, v.w, ssq);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
         }
         if (norm) {
-            ssq = block_sum(ssq, red);
+            const float ssq = row_ssq_combine((ss[0] + ss[1]) + (ss[2] + ss[3]), red);
             const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)K), eps)));
             amax = 0.0f;
             for (int i = tid; i < K4; i += kRowThreads) {
@@ -139,16 +160,15 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
         return;
     }
 
-    float ssq = 0.0f;
     for (int k = tid; k < K; k += kRowThreads) {
         float v = src[k];
         if (gsrc) v = __fmul_rn(v, silu_gate(gsrc[k]));
         xs[k] = v;
-        ssq = fmaf(v, v, ssq);
     }
     float amax = 0.0f;
     if (norm) {
-        ssq = block_sum(ssq, red);
+        __syncthreads();
+        const float ssq = row_ssq_combine(canonical_ssq_lane(xs, K, tid), red);
         const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)K), eps)));
         for (int k = tid; k < K; k += kRowThreads) {
             const float v = __fmul_rn(__fmul_rn(xs[k], rrms), gamma_at(gamma, gamma_is_bf16, k));

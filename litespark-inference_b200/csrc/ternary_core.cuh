@@ -28,6 +28,31 @@ __device__ __forceinline__ void chunk_dot(const uint4& wv, const int4* __restric
     }
 }
 
+// Sum of squares of a row in the ONE summation order every kernel of the library uses, so that a row normalised
+// by the fused prologue of the one-row GEMV, by the row kernel in front of the many-row products or by a prefill
+// comes out bit-identical (a sum that rounds differently flips int8 activations, and a deep network amplifies
+// that into different tokens).  The order: the row is cut into 16-element blocks; block b belongs to lane
+// b % 256 of a 256-lane group; a lane walks its blocks in increasing order and, inside a block, adds element e
+// into partial e % 4 with a fused multiply-add; the lane's value is (p0 + p1) + (p2 + p3); lanes combine through
+// the xor-shuffle tree of warp_sum and the eight warps as ((w0 + w1) + (w2 + w3)) + ((w4 + w5) + (w6 + w7)).
+// canonical_ssq_lane returns the value of lane `lane256` for a row of K floats readable at `row` (shared or
+// global memory; elements at and beyond K count as zero).
+__device__ __forceinline__ float canonical_ssq_lane(const float* __restrict__ row, int K, int lane256) {
+    float ss[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = lane256 * 16; k0 < K; k0 += 256 * 16) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float v = (k0 + e < K) ? row[k0 + e] : 0.0f;
+            ss[e & 3] = fmaf(v, v, ss[e & 3]);
+        }
+    }
+    return (ss[0] + ss[1]) + (ss[2] + ss[3]);
+}
+// Combines the eight warp sums (warp w's value at slot[w]) in the canonical order.
+__device__ __forceinline__ float canonical_ssq_combine(const float* slot) {
+    return ((slot[0] + slot[1]) + (slot[2] + slot[3])) + ((slot[4] + slot[5]) + (slot[6] + slot[7]));
+}
+
 // fp32 -> int8 with round-half-even and saturation to [-128, 127] in one instruction: the pair
 // _mm512_cvtps_epi32 + _mm512_cvtsepi32_epi8 of the reference quantiser.
 __device__ __forceinline__ uint32_t quant_rne_sat(float v) {

@@ -54,7 +54,6 @@ class LinearArgs(ctypes.Structure):
 
 PRO_INT8, PRO_QUANT, PRO_RMSNORM_QUANT, PRO_GATED_RMSNORM_QUANT = 0, 1, 2, 3
 EPI_STORE, EPI_ADD, EPI_RELU2_MUL, EPI_SILU_MUL = 0, 1, 2, 3
-GEMV_LATENCY, GEMV_THROUGHPUT = 0, 1          # lspk_set_gemv_mode
 
 # name -> (argtypes, restype) of every symbol declared in include/lspk_sm100.h
 _SIGNATURES = {
@@ -89,7 +88,7 @@ _SIGNATURES = {
                            ctypes.POINTER(_sz)], _ci),
     "lspk_linear": ([ctypes.POINTER(LinearArgs)], _ci),
     "lspk_linear_force_path": ([_ci], _ci),
-    "lspk_set_gemv_mode": ([_ci], _ci),
+    "lspk_linear_batch": ([ctypes.POINTER(LinearArgs), _ci], _ci),
     "lspk_tc_check_error": ([], _ci),
     "lspk_quantize_rows": ([_vp, _vp, _vp, _ci, _ci], _ci),
     "lspk_rmsnorm_rows": ([_vp, _vp, _ci, _vp, _ci, _ci, _cf], _ci),

@@ -216,63 +216,94 @@ def test_linear_fused_qkv_norm_and_epilogues(port, M):
     assert np.array_equal(dres.numpy(), res + port.matmul_packed_mT(got_q, got_s, mats["q"], scales["q"]))
 
 
-@pytest.fixture
-def throughput_mode():
+def _batch_args(items):
+    """ctypes array of lspk_linear_args for lspk_linear_batch: items = [(weights, out, xq, xs, epilogue, accs)]."""
+    arr = (K.LinearArgs * len(items))()
+    for a, (ws_, out, xq, xs, epi, accs) in zip(arr, items):
+        for i, w in enumerate(ws_):
+            a.w[i] = w.handle
+        for i, acc in enumerate(accs):
+            a.acc_out[i] = acc.ptr
+        a.out[0] = out.ptr
+        a.n_mats, a.M, a.prologue, a.epilogue = len(ws_), 1, K.PRO_INT8, epi
+        a.x_i8, a.x_scales = xq.ptr, xs.ptr
+    return arr
+
+
+def test_linear_batch_bit_exact_over_shapes(port):
+    """One launch over independent one-row products of every kind the stream kernel distinguishes: the model's
+    shapes, ragged K and N, a K long enough for three stages per unit, a matrix with fewer row groups than the
+    grid has warps and one with many times more, each with its own activation vector; integers and floats
+    against the oracle."""
     lib = K.load_library(True)
-    K.check(lib.lspk_set_gemv_mode(K.GEMV_THROUGHPUT))
-    yield lib
-    K.check(lib.lspk_set_gemv_mode(K.GEMV_LATENCY))
-    K.check(lib.lspk_tc_check_error())         # no bounded wait of the bulk-copy kernel ran out
+    shapes = [SHAPES["q"], SHAPES["k"], SHAPES["gate"], SHAPES["down"], (5, 20), (33, 260), (1, 8), (48, 8192),
+              (7000, 1000), (16 * 1300, 64)]
+    items, wants, keep = [], [], []
+    for ci, (N, Kd) in enumerate(shapes):
+        w, packed, x, ws = _rand_case(N * 3 + Kd, N, Kd, 1)
+        xq, xs = np.empty((1, Kd), np.int8), np.empty(1, np.float32)
+        port.quantize_activation_batched(x, xq, xs)
+        wants.append((port.acc_int32(xq, packed), port.matmul_packed_mT(xq, xs, packed, ws)))
+        W = dev.DeviceWeight(packed, ws)
+        y, acc = dev.DeviceArray((1, N), np.float32), dev.DeviceArray((1, N), np.int32)
+        dxq, dxs = dev.DeviceArray.from_numpy(xq), dev.DeviceArray.from_numpy(xs)
+        keep.append((W, y, acc, dxq, dxs))
+        items.append(([W], y, dxq, dxs, K.EPI_STORE, [acc]))
+    K.check(lib.lspk_linear_batch(_batch_args(items), len(items)))
+    for (W, y, acc, _, _), (want_acc, want_y), shp in zip(keep, wants, shapes):
+        assert np.array_equal(acc.numpy(), want_acc), shp
+        assert np.array_equal(y.numpy(), want_y), shp
+    K.check(lib.lspk_tc_check_error())                     # no bounded wait of the copy rings ran out
+    for W, *_ in keep:
+        W.free()
 
 
-@pytest.mark.parametrize("N,Kd", [SHAPES["q"], SHAPES["k"], SHAPES["gate"], SHAPES["down"], (5, 20), (33, 260),
-                                  (1, 8), (48, 12288), (7000, 1000), (16 * 700, 64)])
-def test_gemv_throughput_mode_bit_exact(port, throughput_mode, N, Kd):
-    """The bulk-copy schedule of the one-row product (ring of row groups in shared memory, several groups per
-    CTA, ring refills at N = 11200) gives the same integers and floats as the oracle, for the int8 contract
-    and for the fused quantiser, with ragged K and N."""
-    w, packed, x, ws = _rand_case(N * 3 + Kd, N, Kd, 1)
-    xq, xs = np.empty((1, Kd), np.int8), np.empty(1, np.float32)
-    port.quantize_activation_batched(x, xq, xs)
-    want_acc, want_y = port.acc_int32(xq, packed), port.matmul_packed_mT(xq, xs, packed, ws)
-    W = dev.DeviceWeight(packed, ws)
-    y, acc = dev.DeviceArray((1, N), np.float32), dev.DeviceArray((1, N), np.int32)
-    dev.linear([W], [y], 1, x_i8=dev.DeviceArray.from_numpy(xq), x_scales=dev.DeviceArray.from_numpy(xs), acc_outs=[acc])
-    assert np.array_equal(acc.numpy(), want_acc) and np.array_equal(y.numpy(), want_y)
-    y2, acc2 = dev.DeviceArray((1, N), np.float32), dev.DeviceArray((1, N), np.int32)
-    xq_t = dev.DeviceArray((1, Kd), np.int8)
-    dev.linear([W], [y2], 1, x_f32=dev.DeviceArray.from_numpy(x), acc_outs=[acc2], xq_out=xq_t)
-    assert np.array_equal(xq_t.numpy(), xq)
-    assert np.array_equal(acc2.numpy(), want_acc) and np.array_equal(y2.numpy(), want_y)
-    W.free()
-
-
-def test_gemv_throughput_mode_fused_launches(port, throughput_mode):
-    """q/k/v in one launch behind the RMSNorm prologue, the gated pair and the residual add, throughput mode
-    against latency mode: identical bits."""
+def test_linear_batch_epilogues_and_argument_errors(port):
+    """Gated gate/up pairs (ReLU^2 and SiLU), the residual add and plain stores mixed in one launch, against the
+    one-product entry point; then what the entry point has to refuse."""
+    lib = K.load_library(True)
     H, I = 2560, 6912
-    rng = np.random.default_rng(123)
-    mats = {n: _rand_case(150 + i, *SHAPES[n], 1)[1] for i, n in enumerate(["q", "k", "v", "gate", "up", "down"])}
+    rng = np.random.default_rng(321)
+    mats = {n: _rand_case(250 + i, *SHAPES[n], 1)[1] for i, n in enumerate(["q", "gate", "up", "down"])}
     dW = {n: dev.DeviceWeight(mats[n], 0.5 + 0.1 * i) for i, n in enumerate(mats)}
-    dx = dev.DeviceArray.from_numpy((rng.standard_normal((1, H)) * 2.0).astype(np.float32))
-    dg = dev.DeviceArray.from_numpy(synthetic.fp32_to_bf16_u16(rng.uniform(0.5, 1.5, H).astype(np.float32)))
+    xh = (rng.standard_normal((1, H)) * 2.0).astype(np.float32)
+    xi = rng.standard_normal((1, I)).astype(np.float32)
+    qh, sh, qi, si = np.empty((1, H), np.int8), np.empty(1, np.float32), np.empty((1, I), np.int8), np.empty(1, np.float32)
+    port.quantize_activation_batched(xh, qh, sh)
+    port.quantize_activation_batched(xi, qi, si)
+    dqh, dsh, dqi, dsi = (dev.DeviceArray.from_numpy(a) for a in (qh, sh, qi, si))
     res0 = rng.standard_normal((1, H)).astype(np.float32)
 
-    def run_all():
-        outs = [dev.DeviceArray((1, SHAPES[n][0]), np.float32) for n in ("q", "k", "v")]
-        dev.linear([dW["q"], dW["k"], dW["v"]], outs, 1, x_f32=dx, gamma=dg)
-        inter = dev.DeviceArray((1, I), np.float32)
-        dev.linear([dW["gate"], dW["up"]], [inter, None], 1, x_f32=dx, gamma=dg, epilogue=K.EPI_RELU2_MUL)
-        res = dev.DeviceArray.from_numpy(res0)
-        dev.linear([dW["down"]], [res], 1, x_f32=inter, epilogue=K.EPI_ADD)
-        return [o.numpy() for o in outs] + [inter.numpy(), res.numpy()]
+    def outputs():
+        return (dev.DeviceArray((1, I), np.float32), dev.DeviceArray((1, I), np.float32),
+                dev.DeviceArray.from_numpy(res0), dev.DeviceArray((1, H), np.float32))
 
-    got = run_all()
-    K.check(throughput_mode.lspk_set_gemv_mode(K.GEMV_LATENCY))
-    want = run_all()
-    for g, w_ in zip(got, want):
-        assert np.array_equal(g, w_)
-    assert np.isfinite(got[-1]).all() and np.abs(got[-1] - res0).max() > 0
+    relu, silu, res, plain = outputs()
+    items = [([dW["gate"], dW["up"]], relu, dqh, dsh, K.EPI_RELU2_MUL, []),
+             ([dW["down"]], res, dqi, dsi, K.EPI_ADD, []),
+             ([dW["gate"], dW["up"]], silu, dqh, dsh, K.EPI_SILU_MUL, []),
+             ([dW["q"]], plain, dqh, dsh, K.EPI_STORE, [])]
+    K.check(lib.lspk_linear_batch(_batch_args(items), len(items)))
+    relu1, silu1, res1, plain1 = outputs()
+    dev.linear([dW["gate"], dW["up"]], [relu1, None], 1, x_i8=dqh, x_scales=dsh, epilogue=K.EPI_RELU2_MUL)
+    dev.linear([dW["down"]], [res1], 1, x_i8=dqi, x_scales=dsi, epilogue=K.EPI_ADD)
+    dev.linear([dW["gate"], dW["up"]], [silu1, None], 1, x_i8=dqh, x_scales=dsh, epilogue=K.EPI_SILU_MUL)
+    dev.linear([dW["q"]], [plain1], 1, x_i8=dqh, x_scales=dsh)
+    for got, want in ((relu, relu1), (silu, silu1), (res, res1), (plain, plain1)):
+        assert np.array_equal(got.numpy(), want.numpy())
+    assert np.abs(res.numpy() - res0).max() > 0
+    K.check(lib.lspk_tc_check_error())
+    # refused: more than one row, an fp32 prologue, too many products, a gated epilogue with one matrix
+    lib.lspk_clear_error()
+    bad = _batch_args([([dW["q"]], plain, dqh, dsh, K.EPI_STORE, [])])
+    bad[0].M = 2
+    assert lib.lspk_linear_batch(bad, 1) == 1 and b"one-row" in lib.lspk_last_error()
+    bad[0].M, bad[0].prologue = 1, K.PRO_QUANT
+    assert lib.lspk_linear_batch(bad, 1) == 1 and b"int8 activations" in lib.lspk_last_error()
+    bad[0].prologue, bad[0].epilogue = K.PRO_INT8, K.EPI_RELU2_MUL
+    assert lib.lspk_linear_batch(bad, 1) == 1
+    assert lib.lspk_linear_batch(bad, 0) == 1 and lib.lspk_linear_batch(bad, 1000) == 1
+    lib.lspk_clear_error()
 
 
 def test_bounded_wait_expiry_is_reported_and_clears(port):
