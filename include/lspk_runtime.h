@@ -80,28 +80,10 @@ int lspk_decode_greedy(lspk_state_t s, const int* first_tokens_host, int n_steps
 /* Number of kernel launches contained in one decode step (graph nodes), for reporting. */
 int lspk_state_step_kernel_count(lspk_state_t s);
 
-/* Measurement helpers (single-sequence states).  lspk_bench_linears replays a graph of just the
- * ternary linear launches of one decode step (4 per layer) `reps` times; lspk_bench_lm_head times the
- * LM-head kernel alone.  Both report CUDA-event milliseconds and the algorithmic bytes of ONE pass. */
-int lspk_bench_linears(lspk_state_t s, int reps, float* ms_out, int* launches_out, double* bytes_out);
-int lspk_bench_lm_head(lspk_state_t s, int reps, float* ms_out, double* bytes_out);
-/* Time y = W_i (quant x) over n_w device copies of one matrix visited round-robin (reps passes). */
-int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
-                             float* ms_out);
-/* Floor cost of a kernel boundary: a graph of n_kernels empty dependent kernels, replayed reps times. */
-int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out);
 /* Test aid for the bounded device-side waits: launches one thread that polls an mbarrier nothing arrives on
  * `polls` times (1..65536), gives up, and raises the library's wait flag; the next lspk_tc_check_error then
  * returns LSPK_ERR_DEVICE_WAIT once and clears it.  Nothing faults and the context stays usable. */
 int lspk_debug_expire_wait(int polls);
-/* lspk_bench_linear_copies with the launches of a pass on n_streams forked streams (independent graph nodes):
- * the amortised throughput of the kernel outside a dependency chain.  y holds n_streams * M * N floats.
- * int8_input != 0: x is quantised once beforehand and the launches take the int8 vector + scale, which is the
- * contract of the reference's matmul_lut_*_m1; 0: every launch quantises x itself (fused prologue).
- * w_up != NULL: launch i is the gated pair (w[i], w_up[i]) with the ReLU^2 epilogue. */
-int lspk_bench_linear_copies_independent(const lspk_weight_t* w, const lspk_weight_t* w_up, int n_w, const float* x_f32,
-                                         float* y, int M, int reps, int n_streams, int int8_input, float* ms_out);
-
 #ifdef __cplusplus
 }
 #endif

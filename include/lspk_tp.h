@@ -26,11 +26,6 @@ int lspk_tp_finalize(void);
 int lspk_tp_mlp_block(lspk_weight_t gate_r, lspk_weight_t up_r, lspk_weight_t down_r, const float* x_dev,
                       const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps, float* inter_slice,
                       float* inter_full, float* down_slice, float* y_full);
-/* CUDA-event time of `reps` replays of a graph of n_blocks MLP blocks over distinct weight triples. */
-int lspk_tp_bench_mlp(const lspk_weight_t* gate_r, const lspk_weight_t* up_r, const lspk_weight_t* down_r, int n_blocks,
-                      const float* x_dev, const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps,
-                      float* inter_slice, float* inter_full, float* down_slice, float* y_full, int reps, float* ms_out);
-
 #ifdef __cplusplus
 }
 #endif

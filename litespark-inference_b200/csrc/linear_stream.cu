@@ -4,9 +4,10 @@
 // another (benchmark_kernel.py, the per-shape timing loops; kernel matmul_lut_avx512_m1,
 // matmul_lut_avx512_extern_c.cpp:150-236).  On the GPU a launch per matrix pays a ramp every time: a 4.4 MB
 // matrix is 0.7 us of HBM time, shorter than the fill and drain of a kernel.  Here the whole list is one
-// stream of bytes: the row groups of all products form one flat sequence of units, dealt round-robin to every
-// warp of a persistent grid (one CTA per SM), and each warp keeps a private ring of bulk copies
-// (cp.async.bulk + mbarrier) running ahead of its arithmetic, across product boundaries.
+// stream of bytes: the row groups of all products form one flat sequence of units; every CTA of a persistent
+// grid (one per SM) takes a contiguous range of it, deals the units of its range round-robin to its warps, and
+// each warp keeps a private ring of bulk copies (cp.async.bulk + mbarrier) running ahead of its arithmetic,
+// across product boundaries.  A range touches one or two products, so a CTA installs one or two vectors.
 //
 //   unit   = 16 output rows of one product (both matrices of a gated gate/up pair), cut along K into stages of
 //            at most 10 KB; a warp accumulates a unit's stages in registers and stores its 16 results itself:
@@ -66,17 +67,19 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r = lane & 15, h = lane >> 4;
-    const int TW = gridDim.x * kSWarps;
-    const int gw = blockIdx.x * kSWarps + warp;
+    // this CTA's range of units [u_lo, u_hi) and the products it touches [i_lo, i_hi]
+    const int per_cta = (p.total_units + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int u_lo = min((int)blockIdx.x * per_cta, p.total_units), u_hi = min(u_lo + per_cta, p.total_units);
     uint4* my_ring = ring + (size_t)warp * kSRing * (kSStageBytes / 16);
 
-    auto settle = [&](StreamCursor& c) {          // move c.item to the product that holds c.unit
+    auto settle = [&](StreamCursor& c) {          // move c.item to the product that holds c.unit (p.n: past the range)
+        if (c.unit >= u_hi) c.item = p.n;
         while (c.item < p.n && c.unit >= p.it[c.item].unit0 + p.it[c.item].groups) ++c.item;
     };
     auto advance = [&](StreamCursor& c) {
         if (++c.s >= p.it[c.item].sub) {
             c.s = 0;
-            c.unit += TW;
+            c.unit += kSWarps;
             settle(c);
         }
     };
@@ -100,9 +103,15 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     __syncwarp();
     grid_dependency_launch();
     // the weights do not depend on whatever ran before: fill the ring first
-    StreamCursor prod = {0, gw, 0}, cons = {0, gw, 0};
+    StreamCursor prod = {0, u_lo + warp, 0}, cons = {0, u_lo + warp, 0};
     settle(prod);
     settle(cons);
+    int i_lo = 0, i_hi = -1;
+    if (u_lo < u_hi) {
+        while (u_lo >= p.it[i_lo].unit0 + p.it[i_lo].groups) ++i_lo;
+        i_hi = i_lo;
+        while (u_hi - 1 >= p.it[i_hi].unit0 + p.it[i_hi].groups) ++i_hi;
+    }
     int issued = 0, consumed = 0;
     if (lane == 0) {
         while (issued < kSRing && prod.item < p.n) {
@@ -128,7 +137,7 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int k = k0 + q * 4;
-                raw[u][q] = (k0 < Kp && k < it.K) ? __ldg(reinterpret_cast<const uint32_t*>(it.x + k)) : 0u;
+                raw[u][q] = (k0 < Kp && k < it.K) ? *reinterpret_cast<const uint32_t*>(it.x + k) : 0u;
             }
         }
     };
@@ -154,13 +163,15 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         if (lane == 0) s_sumx[i & 1][warp] = sumx;
         if (tid == 0) s_scale[i & 1] = it.xs[0];
     };
-    fetch_x(0);
-    install_x(0);
+    if (i_hi >= i_lo) {
+        fetch_x(i_lo);
+        install_x(i_lo);
+    }
     __syncthreads();
 
     bool dead = false;                           // this warp gave up (a wait ran out here or elsewhere in the CTA)
-    for (int i = 0; i < p.n; ++i) {
-        if (i + 1 < p.n) fetch_x(i + 1);         // in flight while product i is computed
+    for (int i = i_lo; i <= i_hi; ++i) {
+        if (i < i_hi) fetch_x(i + 1);            // in flight while product i is computed
         const StreamItem& it = p.it[i];
         const int8_t* xrow = xq + (size_t)(i & 1) * kSMaxKp;
         int sx = 0;
@@ -244,7 +255,7 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             prod.s = __shfl_sync(0xffffffffu, prod.s, 0);
             issued = __shfl_sync(0xffffffffu, issued, 0);
         }
-        if (i + 1 < p.n) install_x(i + 1);
+        if (i < i_hi) install_x(i + 1);
         __syncthreads();
         if (*(volatile int*)&s_abort) dead = true;
     }

@@ -8,67 +8,9 @@
 #include <string.h>
 #include <vector>
 
-#include "internal.cuh"
-#include "../../include/lspk_runtime.h"
+#include "runtime_internal.cuh"
 
 namespace lspk {
-
-struct DevNorm {
-    void* g = nullptr;
-    int is_bf16 = 0;
-    int K = 0;
-};
-
-struct DevLayer {
-    lspk_weight_t proj[7] = {};
-    DevNorm norm[4];
-};
-
-struct DevTable {
-    int kind = -1;
-    void* data = nullptr;
-    float* scale = nullptr;
-};
-
-struct Model {
-    lspk_model_config cfg;
-    std::vector<DevLayer> layers;
-    DevNorm final_norm;
-    DevTable emb, head;
-    bool finalized = false;
-    size_t bytes = 0;
-    int D() const { return cfg.hidden_size / cfg.num_heads; }
-    int kv_dim() const { return cfg.num_kv_heads * D(); }
-};
-
-struct State {
-    Model* m = nullptr;
-    int t_max = 0, batch = 1, kv_fp16 = 1;
-    int cap_rows = 0;                 // rows the scratch buffers hold
-    void *cache_k = nullptr, *cache_v = nullptr;
-    float *rope_cos = nullptr, *rope_sin = nullptr;
-    float* rope_cur = nullptr;        // [batch][D]: cos | sin rows of each sequence's current position (decode step)
-    bool rope_cur_valid = false;      // true while the kernels of a decode step are being enqueued
-    int* ctl = nullptr;               // device: pos[batch], token[batch], step
-    unsigned long long* best = nullptr;   // device: argmax keys [batch]
-    int* tokens_out = nullptr;        // device: [t_max * batch]
-    float *x = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *attn = nullptr, *inter = nullptr, *inter2 = nullptr;
-    float *logits = nullptr;          // [max(batch, 8), V]
-    int logits_rows = 0;
-    int8_t *xq_h = nullptr, *xq_i = nullptr;
-    float* xs = nullptr;
-    int* tok_rows = nullptr;          // device token ids for a prefill chunk
-    int* h_int = nullptr;             // pinned staging for ints
-    float* h_logits = nullptr;        // pinned staging for logits
-    std::vector<int> host_pos;
-    cudaGraphExec_t graph[2] = {nullptr, nullptr};   // [0] no logits store, [1] with logits
-    unsigned graph_gen[2] = {0, 0};   // scratch_generation() at capture: a later move of library scratch voids the graph
-    int graph_nodes = 0;
-    size_t bytes = 0;
-    size_t kv_elem() const { return kv_fp16 ? 2 : 4; }
-    size_t layer_stride() const { return (size_t)t_max * m->kv_dim(); }            // elements
-    size_t seq_stride() const { return layer_stride() * m->cfg.num_layers; }       // elements
-};
 
 // ---- small kernels of the forward pass ---------------------------------------------------
 
@@ -157,48 +99,6 @@ __global__ void finish_step_kernel(int* __restrict__ ctl, unsigned long long* __
     if (b == 0) ctl[2 * batch] += 1;
 }
 
-// Takes part in a dependency chain and does what a decode kernel does at its boundaries: every CTA
-// reads a 10 KB vector the previous kernel wrote (16 floats per thread, 160 threads), reduces over
-// the CTA, and writes its 64-float slice of the next vector.  Measures the floor cost of a kernel
-// boundary plus the first read of freshly written data (see lspk_bench_launch_floor).
-//   mode bit 0: trigger dependents early; bits 1-2: load flavour (0 plain, 1 .cg, 2 volatile);
-//   bit 3: store flavour (0 plain, 1 .cg); bit 4: skip the vector traffic (empty kernel)
-__global__ void chain_probe_kernel(int* __restrict__ sink, const float* __restrict__ vin, float* __restrict__ vout,
-                                   int mode, unsigned long long* trace, int trace_cap) {
-    __shared__ float red[32];
-    PhaseTrace tr;
-    tr.begin(trace, trace_cap, 5);
-    tr.mark();
-    if (mode & 1) grid_dependency_launch();
-    grid_dependency_wait();
-    tr.mark();                                   // 1: predecessor finished
-    if (!(mode & 16)) {
-        const int tid = threadIdx.x, lf = (mode >> 1) & 3;
-        float acc = 0.0f;
-        if (tid < 160) {
-            const float4* src = reinterpret_cast<const float4*>(vin) + tid * 4;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float4 v;
-                if (lf == 1) v = __ldcg(src + q);
-                else if (lf == 2) asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src + q));
-                else v = src[q];
-                acc += (v.x + v.y) + (v.z + v.w);
-            }
-        }
-        tr.mark();                               // 2: this thread's 64 bytes arrived
-        acc = block_sum(acc, red);
-        tr.mark();                               // 3: all warps' data arrived and reduced
-        if (tid < 64 && blockIdx.x < 160) {
-            const float o = acc * 1e-3f + (float)tid;
-            float* dst = vout + blockIdx.x * 64 + tid;
-            if (mode & 8) __stcg(dst, o); else *dst = o;
-        }
-    }
-    if (sink && threadIdx.x == 0 && blockIdx.x == 0) sink[0] += 1;
-    tr.end();
-}
-
 __global__ void advance_pos_kernel(int* __restrict__ ctl, int seq, int by) {
     grid_dependency_launch();
     grid_dependency_wait();
@@ -229,7 +129,7 @@ static int dev_alloc(void** p, size_t bytes, size_t* tally) {
     return LSPK_OK;
 }
 
-static size_t table_bytes(int kind, int V, int H) {
+size_t table_bytes(int kind, int V, int H) {
     return kind == 0 ? (size_t)V * H * 2 : kind == 1 ? (size_t)V * H : (size_t)V * (H / 2);
 }
 
@@ -253,7 +153,7 @@ static int upload_table(DevTable& t, int kind, const void* host, const float* sc
 //   otherwise rows go through the batched norm+quantise kernel once and the linear kernels (eight-row
 //   tensor-core tiles below 32 rows, the tcgen05 GEMM from there) take the int8 prologue.
 //   per_row_seq: rows are different sequences (batched decode) instead of consecutive positions.
-static int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool skip_attention = false) {
+int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool skip_attention) {
     Model* m = s->m;
     const lspk_model_config& c = m->cfg;
     const DevLayer& L = m->layers[li];
@@ -777,257 +677,6 @@ int lspk_forward_prefill(lspk_state_t h, int seq, const int* tokens_host, int T,
         }
     }
     return LSPK_OK;
-}
-
-// ---- measurement helpers ------------------------------------------------------------------------
-// Replay, `reps` times, a graph holding only the ternary linear launches of one decode step of a
-// single-sequence state (4 per layer: q/k/v, o, gate/up, down -- the attention kernel left out),
-// and report the CUDA-event time, the number of linear launches and the algorithmic bytes they
-// move (packed weights + fp32 input + fp32 output per launch).
-int lspk_bench_linears(lspk_state_t h, int reps, float* ms_out, int* launches_out, double* bytes_out) {
-    State* s = reinterpret_cast<State*>(h);
-    LSPK_REQUIRE(s && s->batch == 1 && reps >= 1 && ms_out, "lspk_bench_linears: needs a single-sequence state");
-    Model* m = s->m;
-    const lspk_model_config& c = m->cfg;
-    static cudaGraphExec_t exec = nullptr;
-    static State* exec_for = nullptr;
-    auto enqueue = [&]() -> int {
-        if (int rc = launch_embed(s->ctl + 1, 1, m->emb.kind, m->emb.data, m->emb.scale, s->x, c.hidden_size, c.vocab_size))
-            return rc;
-        for (int li = 0; li < c.num_layers; ++li)
-            if (int rc = run_layer(s, li, 1, false, 0, true)) return rc;
-        return LSPK_OK;
-    };
-    if (!exec || exec_for != s) {
-        if (exec) cudaGraphExecDestroy(exec);
-        exec = nullptr;
-        if (int rc = enqueue()) return rc;
-        LSPK_CUDA(cudaStreamSynchronize(stream()));
-        cudaGraph_t g = nullptr;
-        LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
-        int rc = enqueue();
-        cudaError_t e = cudaStreamEndCapture(stream(), &g);
-        if (rc) return rc;
-        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
-        e = cudaGraphInstantiate(&exec, g, 0);
-        cudaGraphDestroy(g);
-        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
-        exec_for = s;
-    }
-    LSPK_CUDA(cudaGraphLaunch(exec, stream()));          // warm
-    if (int rc = lspk_timer_start()) return rc;
-    for (int i = 0; i < reps; ++i) LSPK_CUDA(cudaGraphLaunch(exec, stream()));
-    if (int rc = lspk_timer_stop(ms_out)) return rc;
-    const double H = c.hidden_size, I = c.intermediate_size, KV = m->kv_dim();
-    const double per_layer = (H * H / 4 + 2 * KV * H / 4 + 4 * H + 4 * (H + 2 * KV))      // q/k/v
-                           + (H * H / 4 + 4 * H + 4 * H)                                   // o
-                           + (2 * I * H / 4 + 4 * H + 4 * I)                               // gate/up
-                           + (H * I / 4 + 4 * I + 4 * H);                                  // down
-    if (launches_out) *launches_out = 4 * c.num_layers;
-    if (bytes_out) *bytes_out = per_layer * c.num_layers;
-    return LSPK_OK;
-}
-
-// Time `reps` LM-head launches (final norm + argmax fused, no logits store) of a single-sequence state.
-int lspk_bench_lm_head(lspk_state_t h, int reps, float* ms_out, double* bytes_out) {
-    State* s = reinterpret_cast<State*>(h);
-    LSPK_REQUIRE(s && s->batch == 1 && reps >= 1 && ms_out, "lspk_bench_lm_head: needs a single-sequence state");
-    Model* m = s->m;
-    const lspk_model_config& c = m->cfg;
-    const DevTable& head = m->head.data ? m->head : m->emb;
-    auto once = [&]() -> int {
-        return lm_head_launch(head.kind, head.data, head.scale, s->x, nullptr, 1, c.vocab_size, c.hidden_size,
-                              m->final_norm.g, m->final_norm.is_bf16, c.rms_norm_eps, s->best);
-    };
-    if (int rc = once()) return rc;
-    if (int rc = lspk_timer_start()) return rc;
-    for (int i = 0; i < reps; ++i)
-        if (int rc = once()) return rc;
-    if (int rc = lspk_timer_stop(ms_out)) return rc;
-    LSPK_CUDA(cudaMemsetAsync(s->best, 0, 8, stream()));
-    if (bytes_out) *bytes_out = (double)table_bytes(head.kind, c.vocab_size, c.hidden_size) + 4.0 * c.hidden_size;
-    return LSPK_OK;
-}
-
-// Time the fused-quantiser linear product y = W_i (quant x) over `n_w` device copies of a matrix,
-// visited round-robin so that consecutive launches read different HBM (defeats the L2 when the
-// copies together exceed it).  One pass over all copies is captured into a graph and replayed.
-int lspk_bench_linear_copies(const lspk_weight_t* w, int n_w, const float* x_f32, float* y, int M, int reps,
-                             float* ms_out) {
-    if (int rc = ensure_init()) return rc;
-    LSPK_REQUIRE(w && n_w >= 1 && x_f32 && y && M >= 1 && reps >= 1 && ms_out, "lspk_bench_linear_copies: bad arguments");
-    auto enqueue = [&]() -> int {
-        for (int i = 0; i < n_w; ++i) {
-            lspk_linear_args a = {};
-            a.w[0] = w[i];
-            a.out[0] = y;
-            a.n_mats = 1;
-            a.M = M;
-            a.prologue = LSPK_PRO_QUANT;
-            a.epilogue = LSPK_EPI_STORE;
-            a.x_f32 = x_f32;
-            if (int rc = lspk_linear(&a)) return rc;
-        }
-        return LSPK_OK;
-    };
-    if (int rc = enqueue()) return rc;                   // sizes scratch, sets kernel attributes
-    LSPK_CUDA(cudaStreamSynchronize(stream()));
-    cudaGraph_t g = nullptr;
-    cudaGraphExec_t exec = nullptr;
-    LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue();
-    cudaError_t e = cudaStreamEndCapture(stream(), &g);
-    if (rc) return rc;
-    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
-    e = cudaGraphInstantiate(&exec, g, 0);
-    cudaGraphDestroy(g);
-    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
-    cudaGraphLaunch(exec, stream());
-    rc = lspk_timer_start();
-    for (int i = 0; i < reps && !rc; ++i)
-        if (cudaGraphLaunch(exec, stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
-    if (!rc) rc = lspk_timer_stop(ms_out);
-    cudaStreamSynchronize(stream());
-    cudaGraphExecDestroy(exec);
-    return rc;
-}
-
-// The same product, but the launches of one pass do not depend on one another: they are captured on
-// `n_streams` forked streams (round-robin, one output buffer per stream), so the graph holds independent
-// kernel nodes and the GPU may overlap them.  This is the amortised single-GEMV figure: what the kernel
-// streams when it is not a link in a dependency chain.  y must hold n_streams * N floats.
-int lspk_bench_linear_copies_independent(const lspk_weight_t* w, const lspk_weight_t* w_up, int n_w, const float* x_f32,
-                                         float* y, int M, int reps, int n_streams, int int8_input, float* ms_out) {
-    if (int rc = ensure_init()) return rc;
-    LSPK_REQUIRE(w && n_w >= 1 && x_f32 && y && M == 1 && reps >= 1 && ms_out && n_streams >= 1 && n_streams <= 16,
-                 "lspk_bench_linear_copies_independent: bad arguments (one row only: more rows share library scratch)");
-    const Weight* w0 = reinterpret_cast<const Weight*>(w[0]);
-    const size_t y_stride = (size_t)M * w0->N;
-    // int8_input: the reference kernel's own contract (matmul_lut_*_m1 takes the quantised vector and its
-    // scale); x is quantised once, outside the timed region
-    int8_t* xq = nullptr;
-    float* xs = nullptr;
-    if (int8_input) {
-        LSPK_CUDA(cudaMalloc((void**)&xq, (size_t)w0->K + 16));
-        LSPK_CUDA(cudaMalloc((void**)&xs, 16));
-        if (int rc = lspk_quantize_rows(x_f32, xq, xs, 1, w0->K)) return rc;
-    }
-    auto one = [&](int i, float* out) -> int {
-        lspk_linear_args a = {};
-        a.w[0] = w[i];
-        a.out[0] = out;
-        a.n_mats = 1;
-        a.M = M;
-        a.epilogue = LSPK_EPI_STORE;
-        if (w_up) {                                       // the fused gate/up launch of a feed-forward block
-            a.w[1] = w_up[i];
-            a.n_mats = 2;
-            a.epilogue = LSPK_EPI_RELU2_MUL;
-        }
-        if (int8_input) {
-            a.prologue = LSPK_PRO_INT8;
-            a.x_i8 = xq;
-            a.x_scales = xs;
-        } else {
-            a.prologue = LSPK_PRO_QUANT;
-            a.x_f32 = x_f32;
-        }
-        return lspk_linear(&a);
-    };
-    if (int rc = one(0, y)) return rc;                    // sets kernel attributes
-    // one graph holds several passes over the matrices, so that the fork and join of a replay weigh little
-    const int passes = n_w >= 256 ? 1 : (256 + n_w - 1) / n_w;
-    LSPK_CUDA(cudaStreamSynchronize(main_stream()));
-    cudaStream_t side[16] = {};
-    cudaEvent_t fork = nullptr, join[16] = {};
-    int rc = LSPK_OK;
-    cudaError_t e = cudaEventCreateWithFlags(&fork, cudaEventDisableTiming);
-    for (int s = 0; s < n_streams && e == cudaSuccess; ++s) {
-        e = cudaStreamCreateWithFlags(&side[s], cudaStreamNonBlocking);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&join[s], cudaEventDisableTiming);
-    }
-    cudaGraph_t g = nullptr;
-    cudaGraphExec_t exec = nullptr;
-    if (e == cudaSuccess) e = cudaStreamBeginCapture(main_stream(), cudaStreamCaptureModeThreadLocal);
-    if (e == cudaSuccess) {
-        cudaEventRecord(fork, main_stream());
-        for (int s = 0; s < n_streams; ++s) cudaStreamWaitEvent(side[s], fork, 0);
-        const bool pdl_was = pdl_enabled();
-        lspk_set_pdl(0);                                  // no programmatic edges: plain independent nodes
-        for (int i = 0; i < n_w * passes && rc == LSPK_OK; ++i) {
-            set_stream_override(side[i % n_streams]);
-            rc = one(i % n_w, y + (size_t)(i % n_streams) * y_stride);
-        }
-        set_stream_override(nullptr);
-        lspk_set_pdl(pdl_was ? 1 : 0);
-        for (int s = 0; s < n_streams; ++s) {
-            cudaEventRecord(join[s], side[s]);
-            cudaStreamWaitEvent(main_stream(), join[s], 0);
-        }
-        e = cudaStreamEndCapture(main_stream(), &g);
-    }
-    if (e == cudaSuccess && rc == LSPK_OK) e = cudaGraphInstantiate(&exec, g, 0);
-    if (g) cudaGraphDestroy(g);
-    if (e == cudaSuccess && rc == LSPK_OK) {
-        cudaGraphLaunch(exec, main_stream());
-        rc = lspk_timer_start();
-        for (int i = 0; i < reps && !rc; ++i)
-            if (cudaGraphLaunch(exec, main_stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
-        if (!rc) rc = lspk_timer_stop(ms_out);
-        if (!rc) *ms_out /= (float)passes;                // time of reps passes over the n_w matrices
-        cudaStreamSynchronize(main_stream());
-    }
-    if (exec) cudaGraphExecDestroy(exec);
-    for (int s = 0; s < n_streams; ++s) {
-        if (join[s]) cudaEventDestroy(join[s]);
-        if (side[s]) cudaStreamDestroy(side[s]);
-    }
-    if (fork) cudaEventDestroy(fork);
-    if (xq) cudaFree(xq);
-    if (xs) cudaFree(xs);
-    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "independent-launch benchmark failed: %s", cudaGetErrorString(e));
-    return rc;
-}
-
-// Floor cost of a dependent kernel boundary: replay a graph of `n_kernels` kernels of `grid` CTAs x
-// 256 threads that do no work, each depending on the previous one, and report the time of `reps` replays.
-int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out) {
-    if (int rc = ensure_init()) return rc;
-    LSPK_REQUIRE(n_kernels >= 1 && grid >= 1 && reps >= 1 && ms_out, "lspk_bench_launch_floor: bad arguments");
-    int* sink = nullptr;
-    LSPK_CUDA(cudaMalloc(&sink, 16 + 2 * 10240 * 4));
-    LSPK_CUDA(cudaMemset(sink, 0, 16 + 2 * 10240 * 4));
-    float* va = reinterpret_cast<float*>(sink + 4);
-    float* vb = va + 10240;
-    static const int mode = getenv("LSPK_PROBE_MODE") ? atoi(getenv("LSPK_PROBE_MODE")) : 17;   // empty kernels, early trigger
-    LSPK_CUDA(cudaDeviceSynchronize());
-    cudaGraph_t g = nullptr;
-    cudaGraphExec_t exec = nullptr;
-    LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
-    cudaError_t le = cudaSuccess;
-    for (int i = 0; i < n_kernels && le == cudaSuccess; ++i)
-        le = launch(chain_probe_kernel, dim3(grid), dim3(256), 0, true, sink, (const float*)((i & 1) ? vb : va), (i & 1) ? va : vb, mode,
-                    trace_buffer(), trace_capacity());
-    cudaError_t e = cudaStreamEndCapture(stream(), &g);
-    if (le != cudaSuccess || e != cudaSuccess) {
-        cudaFree(sink);
-        return fail(LSPK_ERR_CUDA, "launch-floor capture failed: %s", cudaGetErrorString(le != cudaSuccess ? le : e));
-    }
-    e = cudaGraphInstantiate(&exec, g, 0);
-    cudaGraphDestroy(g);
-    if (e != cudaSuccess) {
-        cudaFree(sink);
-        return fail(LSPK_ERR_CUDA, "launch-floor instantiate failed: %s", cudaGetErrorString(e));
-    }
-    cudaGraphLaunch(exec, stream());
-    int rc = lspk_timer_start();
-    for (int i = 0; i < reps && !rc; ++i)
-        if (cudaGraphLaunch(exec, stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
-    if (!rc) rc = lspk_timer_stop(ms_out);
-    cudaStreamSynchronize(stream());
-    cudaGraphExecDestroy(exec);
-    cudaFree(sink);
-    return rc;
 }
 
 int lspk_state_step_kernel_count(lspk_state_t h) {

@@ -150,37 +150,4 @@ int lspk_tp_mlp_block(lspk_weight_t gate_r, lspk_weight_t up_r, lspk_weight_t do
     return lspk_tp_allgather_f32(down_slice, y_full, (size_t)wd->N);
 }
 
-// Time `reps` replays of a graph holding `n_blocks` such MLP blocks over distinct weight triples.
-int lspk_tp_bench_mlp(const lspk_weight_t* gate_r, const lspk_weight_t* up_r, const lspk_weight_t* down_r, int n_blocks,
-                      const float* x_dev, const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps,
-                      float* inter_slice, float* inter_full, float* down_slice, float* y_full, int reps, float* ms_out) {
-    LSPK_REQUIRE(gate_r && up_r && down_r && n_blocks >= 1 && reps >= 1 && ms_out, "lspk_tp_bench_mlp: bad arguments");
-    auto enqueue = [&]() -> int {
-        for (int i = 0; i < n_blocks; ++i)
-            if (int rc = lspk_tp_mlp_block(gate_r[i], up_r[i], down_r[i], x_dev, norm_gamma_bf16, sub_norm_gamma_bf16, eps,
-                                           inter_slice, inter_full, down_slice, y_full)) return rc;
-        return LSPK_OK;
-    };
-    if (int rc = enqueue()) return rc;
-    LSPK_CUDA(cudaStreamSynchronize(stream()));
-    cudaGraph_t g = nullptr;
-    cudaGraphExec_t exec = nullptr;
-    LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue();
-    cudaError_t e = cudaStreamEndCapture(stream(), &g);
-    if (rc) return rc;
-    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
-    e = cudaGraphInstantiate(&exec, g, 0);
-    cudaGraphDestroy(g);
-    if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
-    cudaGraphLaunch(exec, stream());
-    rc = lspk_timer_start();
-    for (int i = 0; i < reps && !rc; ++i)
-        if (cudaGraphLaunch(exec, stream()) != cudaSuccess) rc = fail(LSPK_ERR_CUDA, "graph launch failed");
-    if (!rc) rc = lspk_timer_stop(ms_out);
-    cudaStreamSynchronize(stream());
-    cudaGraphExecDestroy(exec);
-    return rc;
-}
-
 }  // extern "C"

@@ -31,12 +31,7 @@ SIGNATURES = {
     "lspk_forward_prefill": ([_vp, _ci, _vp, _ci, _vp, _vp, _vp], _ci),
     "lspk_decode_greedy": ([_vp, _vp, _ci, _vp], _ci),
     "lspk_state_step_kernel_count": ([_vp], _ci),
-    "lspk_bench_linears": ([_vp, _ci, ctypes.POINTER(_cf), ctypes.POINTER(_ci), ctypes.POINTER(ctypes.c_double)], _ci),
-    "lspk_bench_linear_copies": ([_vp, _ci, _vp, _vp, _ci, _ci, ctypes.POINTER(_cf)], _ci),
-    "lspk_bench_launch_floor": ([_ci, _ci, _ci, ctypes.POINTER(_cf)], _ci),
     "lspk_debug_expire_wait": ([_ci], _ci),
-    "lspk_bench_linear_copies_independent": ([_vp, _vp, _ci, _vp, _vp, _ci, _ci, _ci, _ci, ctypes.POINTER(_cf)], _ci),
-    "lspk_bench_lm_head": ([_vp, _ci, ctypes.POINTER(_cf), ctypes.POINTER(ctypes.c_double)], _ci),
 }
 
 

@@ -31,7 +31,6 @@ SIGNATURES = {
     "lspk_tp_allgather_f32": ([_vp, _vp, _sz], _ci),
     "lspk_tp_finalize": ([], _ci),
     "lspk_tp_mlp_block": ([_vp, _vp, _vp, _vp, _vp, _vp, _cf, _vp, _vp, _vp, _vp], _ci),
-    "lspk_tp_bench_mlp": ([_vp, _vp, _vp, _ci, _vp, _vp, _vp, _cf, _vp, _vp, _vp, _vp, _ci, ctypes.POINTER(_cf)], _ci),
 }
 
 

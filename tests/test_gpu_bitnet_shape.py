@@ -104,7 +104,9 @@ def test_long_context_at_head_dim_128(shaped, oracle, port):
     st = rt.init_state(dm, n + 4, kv_dtype="fp16")
     ost = oracle.State(cfg, n + 4, np.float16)
     e0 = _rel_l2(rt.forward_prefill(dm, st, prompt[:n]), oracle.forward_prefill(port, m, ost, prompt[:n]))
-    assert e0 <= MEDIAN_REL_L2_NO_REF
+    # a single position's error is one draw from the distribution whose median the band test measures
+    # (0.26-0.29 between the reference's own builds); single draws reach about twice that
+    assert e0 <= 2 * MEDIAN_REL_L2_NO_REF
     for t in prompt[n:]:
         e = _rel_l2(rt.forward_one(dm, st, t), oracle.forward_one(port, m, ost, t))
         assert e <= max(2.0 * e0, 0.1) + 0.05, f"decode step error {e:.3e} vs prefill error {e0:.3e}"
