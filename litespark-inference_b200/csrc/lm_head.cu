@@ -378,8 +378,7 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     const int cap = sm_count() * 4;
     if (grid > cap) grid = cap;
     const uint4* e4 = reinterpret_cast<const uint4*>(emb);
-    static const int knob_mma = getenv("LSPK_LM_MMA") ? atoi(getenv("LSPK_LM_MMA")) : 1;
-    if (knob_mma && kind == 0 && T > 1 && H % 32 == 0 && (logits || best_key)) {
+    if (kind == 0 && T > 1 && H % 32 == 0 && (logits || best_key)) {
         // several rows against the bf16 table: tensor-core kernel, up to sixteen rows per pass
         // sixteen rows per pass where their three bf16 terms fit the shared memory (H <= 2100), else eight
         const int per_pass = ((size_t)3 * 16 * (H + 32) * 2 <= 200 * 1024 && T > 8) ? 16 : 8;

@@ -241,8 +241,8 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     const int active = E < R ? E : R;
     int ctas = (2 * sm_count() + active - 1) / active;
     // The expert products stream tens of megabytes per launch: the weights go through the bulk-copy ring of the
-    // eight-row kernel (LSPK_MOE_BULK = ring depth, 0 = per-lane loads).  CTAs per SM follow from the ring's size.
-    static const int knob_bulk = getenv("LSPK_MOE_BULK") ? atoi(getenv("LSPK_MOE_BULK")) : 3;
+    // eight-row kernel, three stages deep where they fit.  CTAs per SM follow from the ring's size.
+    const int knob_bulk = 3;
     auto bulk_ctas = [&](int chunks, bool pair, int Kp, int* stages) -> int {
         int st = knob_bulk > 4 ? 4 : knob_bulk;
         const size_t stage = (size_t)chunks * 256 * (pair ? 2 : 1);

@@ -195,6 +195,157 @@ row_norm_quant_kernel(const float* __restrict__ x, const float* __restrict__ gat
     if (tid == 0) scales[t] = scale;
 }
 
+// Row quantiser for rows of up to 4096 * NB elements, everything in registers: a thread owns the 16-element blocks
+// tid, tid + 256 (the lanes of the canonical sum-of-squares order), loads them once, and -- having whole blocks --
+// writes the permuted layout of the tensor-core kernels without any exchange between lanes.  The norm weights
+// do not depend on the previous kernel and are requested before the dependency wait (unless they are selected
+// per row by device data).  Same arithmetic, step for step, as the fused prologue of the one-row GEMV.
+//   norm      apply RMSNorm (gamma, eps) before the quantiser
+//   perm_kp   > 0: write perm_kp bytes per row (K rounded up to 64, zero padded) in the permuted layout, rows
+//             perm_stride bytes apart, and optionally the sum of the row's int8 values; 0: natural order [T, K]
+template <int NB>
+__global__ void __launch_bounds__(kRowThreads)
+row_quant_regs_kernel(const float* __restrict__ x, const float* __restrict__ gate, const void* __restrict__ gamma_base,
+                      const int* __restrict__ gamma_sel, int gamma_is_bf16, int8_t* __restrict__ out_i8,
+                      float* __restrict__ scales, int K, float eps, int norm, int perm_kp, int perm_stride,
+                      int* __restrict__ sums) {
+    __shared__ __align__(16) float red[32];
+    const int t = blockIdx.x, tid = threadIdx.x;
+    float gm[NB][16];
+    auto load_gamma = [&](const void* gamma) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int k0 = (tid + nb * kRowThreads) * 16;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int k = k0 + q * 4;
+                float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k < K) {
+                    if (gamma_is_bf16) {
+                        const uint2 gb = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(gamma) + k));
+                        gv.x = __uint_as_float(gb.x << 16);
+                        gv.y = __uint_as_float(gb.x & 0xffff0000u);
+                        gv.z = __uint_as_float(gb.y << 16);
+                        gv.w = __uint_as_float(gb.y & 0xffff0000u);
+                    } else {
+                        gv = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(gamma) + k));
+                    }
+                }
+                gm[nb][q * 4 + 0] = gv.x;
+                gm[nb][q * 4 + 1] = gv.y;
+                gm[nb][q * 4 + 2] = gv.z;
+                gm[nb][q * 4 + 3] = gv.w;
+            }
+        }
+    };
+    if (norm && !gamma_sel) load_gamma(gamma_base);
+    grid_dependency_launch();
+    grid_dependency_wait();
+    if (norm && gamma_sel)
+        load_gamma(reinterpret_cast<const char*>(gamma_base) + (size_t)gamma_sel[t] * K * (gamma_is_bf16 ? 2 : 4));
+
+    const float* src = x + (size_t)t * K;
+    float v[NB][16];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        const int k0 = (tid + nb * kRowThreads) * 16;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + q * 4 < K) t4 = *reinterpret_cast<const float4*>(src + k0 + q * 4);
+            v[nb][q * 4 + 0] = t4.x;
+            v[nb][q * 4 + 1] = t4.y;
+            v[nb][q * 4 + 2] = t4.z;
+            v[nb][q * 4 + 3] = t4.w;
+        }
+    }
+    if (gate) {
+        const float* gsrc = gate + (size_t)t * K;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int k0 = (tid + nb * kRowThreads) * 16;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k0 + q * 4 < K) t4 = *reinterpret_cast<const float4*>(gsrc + k0 + q * 4);
+                v[nb][q * 4 + 0] = __fmul_rn(v[nb][q * 4 + 0], silu_gate(t4.x));
+                v[nb][q * 4 + 1] = __fmul_rn(v[nb][q * 4 + 1], silu_gate(t4.y));
+                v[nb][q * 4 + 2] = __fmul_rn(v[nb][q * 4 + 2], silu_gate(t4.z));
+                v[nb][q * 4 + 3] = __fmul_rn(v[nb][q * 4 + 3], silu_gate(t4.w));
+            }
+        }
+    }
+    if (norm) {
+        float ss[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int e = 0; e < 16; ++e) ss[e & 3] = fmaf(v[nb][e], v[nb][e], ss[e & 3]);
+        const float ssq = row_ssq_combine((ss[0] + ss[1]) + (ss[2] + ss[3]), red);
+        const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, (float)K), eps)));
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int e = 0; e < 16; ++e) v[nb][e] = __fmul_rn(__fmul_rn(v[nb][e], rrms), gm[nb][e]);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[nb][e]));
+    amax = block_max(amax, red);
+    const float scale = quant_scale_from_absmax(amax);
+    const float inv = __fdiv_rn(1.0f, scale);
+    const int tail_start = K & ~15;
+    const int limit = perm_kp > 0 ? perm_kp : K;
+    int sumx = 0;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        const int k0 = (tid + nb * kRowThreads) * 16;
+        if (k0 < limit) {
+            uint32_t a[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int k = k0 + q * 4 + e;
+                    int qv = 0;
+                    if (k < tail_start) {
+                        qv = quant_one(v[nb][q * 4 + e], inv);
+                    } else if (k < K) {
+                        qv = max(-127, min(127, (int)roundf(__fmul_rn(v[nb][q * 4 + e], inv))));
+                    }
+                    word |= ((uint32_t)qv & 0xffu) << (8 * e);
+                }
+                a[q] = word;
+                sumx = __dp4a((int)word, 0x01010101, sumx);
+            }
+            if (perm_kp > 0) {
+                uint32_t o0, o1, o2, o3;
+                transpose4x4_bytes(a[0], a[1], a[2], a[3], o0, o1, o2, o3);
+                *reinterpret_cast<uint4*>(out_i8 + (size_t)t * perm_stride + k0) = make_uint4(o0, o1, o2, o3);
+            } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (k0 + q * 4 < K) *reinterpret_cast<uint32_t*>(out_i8 + (size_t)t * K + k0 + q * 4) = a[q];
+            }
+        }
+    }
+    if (sums) {                                        // uniform branch
+        sumx = __reduce_add_sync(0xffffffffu, sumx);
+        int* redi = reinterpret_cast<int*>(red);
+        if ((tid & 31) == 0) redi[tid >> 5] = sumx;
+        __syncthreads();
+        if (tid == 0) {
+            int total = 0;
+            for (int w = 0; w < kRowThreads / 32; ++w) total += redi[w];
+            sums[t] = total;
+        }
+    }
+    if (tid == 0) scales[t] = scale;
+}
+
 // `out` may alias `gate` (in-place gating): no restrict qualifiers.
 __global__ void relu2_mul_kernel(const float* gate, const float* up, float* out, size_t n) {
     grid_dependency_launch();
@@ -229,6 +380,17 @@ static int launch_rows(const float* x, const void* gamma, int gamma_is_bf16, flo
     const bool vec = (K % 4 == 0) && aligned(x) && aligned(out_f32) && aligned(out_i8) && aligned(gamma) && aligned(gate) &&
                      (!gamma_sel || K % 8 == 0);
     LSPK_REQUIRE(perm_kp == 0 || vec, "row helper: the permuted output needs K %% 4 == 0 and 16-byte aligned buffers");
+    // quantising rows of up to 8192 elements: the register-resident kernel
+    if (vec && (mode & 2) && K <= 8192 && (perm_kp == 0 || perm_kp <= 8192)) {
+        const int pstride = perm_stride > 0 ? perm_stride : perm_kp;
+        const cudaError_t e = K <= 4096 && perm_kp <= 4096
+            ? launch(row_quant_regs_kernel<1>, dim3(T), dim3(kRowThreads), 0, true, x, gate, gamma, gamma_sel, gamma_is_bf16,
+                     out_i8, scales, K, eps, mode & 1, perm_kp, pstride, sums)
+            : launch(row_quant_regs_kernel<2>, dim3(T), dim3(kRowThreads), 0, true, x, gate, gamma, gamma_sel, gamma_is_bf16,
+                     out_i8, scales, K, eps, mode & 1, perm_kp, pstride, sums);
+        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "row quantiser launch failed: %s", cudaGetErrorString(e));
+        return LSPK_OK;
+    }
     LSPK_CUDA(launch(vec ? row_norm_quant_kernel<true> : row_norm_quant_kernel<false>, dim3(T), dim3(kRowThreads), smem,
                      true, x, gate, gamma, gamma_sel, gamma_is_bf16, out_f32, out_i8, scales, K, eps, mode, vec ? perm_kp : 0,
                      perm_stride > 0 ? perm_stride : perm_kp, sums));

@@ -43,12 +43,13 @@ _ci, _cf = ctypes.c_int, ctypes.c_float
 REF_MAX_T = 64
 
 
-def build(force: bool = False) -> None:
-    """Run oracle/Makefile (C restatement always; reference objects when the tree exists)."""
+def build(force: bool = False, reference_root: Optional[str] = None) -> None:
+    """Run oracle/Makefile: the C restatement always; the reference's own kernel objects when a checkout of
+    the reference is named (argument, or the environment variable LSPK_REFERENCE_ROOT)."""
     if force or not _PORT_SO.exists():
         subprocess.run(["make", "-C", str(_HERE), "oracle"], check=True, capture_output=True)
-    ref = os.environ.get("LSPK_REFERENCE_ROOT", "/root/reference")
-    if Path(ref, "litespark_inference").is_dir():
+    ref = reference_root or os.environ.get("LSPK_REFERENCE_ROOT", "")
+    if ref and Path(ref, "litespark_inference").is_dir():
         subprocess.run(["make", "-C", str(_HERE), "ref", f"REF={ref}"], check=True,
                        capture_output=True)
 

@@ -21,9 +21,7 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(os.environ.get("LSPK_REFERENCE_ROOT", "/root/reference"))
 sys.path.insert(0, str(ROOT))
-sys.path.insert(0, str(REF))
 
 import __graft_entry__ as entry  # noqa: E402
 
@@ -33,6 +31,11 @@ from litespark_inference_b200.torchless import synthetic  # noqa: E402
 
 def reference_modules(tier: str):
     """Import the reference's torchless modules, bound to oracle/_ref/_matmul_lut_<tier>.so."""
+    if not os.environ.get("LSPK_REFERENCE_ROOT"):
+        sys.exit("set LSPK_REFERENCE_ROOT to a checkout of the reference (its Python package is imported from there)")
+    ref = str(Path(os.environ["LSPK_REFERENCE_ROOT"]))
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
     os.environ["LITESPARK_KERNEL_TIER"] = tier
     for m in [m for m in sys.modules if m.startswith("litespark_inference.")]:
         del sys.modules[m]
