@@ -281,6 +281,23 @@ def bench_tp_mlp(dist, rank, world, model, lib, K):
     t = torch.tensor([ms.value], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     tp_us = 1000.0 * float(t.item()) / (reps * n_blocks)
+    # the same graph with both gathers of every block through CUDA-IPC peer windows (plain stores + bounded waits)
+    peer_us, peer_same = None, None
+    try:
+        handle = group.create_window(I, H)
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        group.open_windows([bytes(g.cpu().tolist()) for g in gathered])
+        dist.barrier()
+        K.check(lib.lspk_tp_bench_mlp(arr(sl[0]), arr(sl[1]), arr(sl[2]), n_blocks, x.ptr, norm.ptr, sub.ptr, 1e-5,
+                                      i_s.ptr, None, d_s.ptr, None, reps, ctypes.byref(ms)))
+        t = torch.tensor([ms.value], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        peer_us = 1000.0 * float(t.item()) / (reps * n_blocks)
+        K.check(lib.lspk_tc_check_error())
+    except Exception as ex:
+        peer_us = {"error": str(ex)[:200]}
     # correctness: layer 0's block through the split path against the same block unsplit on this GPU
     group.mlp_block(sl[0][0], sl[1][0], sl[2][0], x, norm, sub, 1e-5, i_s, i_f, d_s, y_f)
     y_split = y_f.numpy()
@@ -290,11 +307,19 @@ def bench_tp_mlp(dist, rank, world, model, lib, K):
     dev.linear(full[:2], [i_f, None], 1, x_f32=x, gamma=norm, epilogue=K.EPI_RELU2_MUL)
     dev.linear(full[2:], [y_one], 1, x_f32=i_f, gamma=sub)
     same = bool(np.array_equal(y_split, y_one.numpy()))
+    if not isinstance(peer_us, dict):
+        y_peer = group.mlp_block_peer(sl[0][0], sl[1][0], sl[2][0], x, norm, sub, 1e-5, i_s, d_s)
+        peer_same = bool(np.array_equal(y_peer, y_one.numpy().reshape(-1)))
+        same = same and peer_same
     flag = torch.tensor([1 if same else 0], device="cuda", dtype=torch.int32)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.barrier()
     group.close()
-    return {"degree": world, "us_per_mlp_block": tp_us, "bit_identical": bool(flag.item()),
-            "how": "row-split gate/up/down slices + 2 NCCL all-gathers per block, graph of 30 blocks, max over ranks",
+    return {"degree": world, "us_per_mlp_block": peer_us if not isinstance(peer_us, dict) else tp_us,
+            "us_per_mlp_block_nccl": tp_us, "us_per_mlp_block_peer_windows": peer_us,
+            "bit_identical": bool(flag.item()),
+            "how": "row-split gate/up/down slices, the two gathers of a block by plain stores into CUDA-IPC peer windows "
+                   "(and, for comparison, by 2 NCCL all-gathers); graph of 30 blocks, device time, max over ranks",
             "bytes_gathered_per_block": 4 * (I + H)}
 
 
@@ -429,8 +454,35 @@ def run_gemv(args):
                       "cpu_baseline": cpu}))
 
 
-def run_hybrid(args):
-    """Config 5: 24-layer Mamba-2 + MoE decoder, 128 greedy steps after a 128-token prompt at batch 1 and 16."""
+def run_probes(args):
+    """What a decode step would gain from other ways of synchronising its ~150 stages (measurement-only kernels of
+    bench_probes.cu): the kernel boundary with programmatic dependent launch, a persistent cooperative kernel with
+    tagged packets or a counter barrier, and a single thread-block cluster (per-SM streaming rate, exchange cost)."""
+    entry.load_package()
+    from litespark_inference_b200.torchless import kernel as K
+    lib = K.load_library(True)
+    out = {"workload": "probes"}
+    ms = ctypes.c_float(0.0)
+    K.check(lib.lspk_bench_launch_floor(120, 296, 50, ctypes.byref(ms)))
+    out["pdl_chain_empty_kernel_us"] = 1000.0 * ms.value / (120 * 50)
+    us, cyc = ctypes.c_float(0.0), ctypes.c_double(0.0)
+    for mode, name in ((0, "tagged_packets"), (1, "counter_barrier")):
+        for grid in (160, 240, 296):
+            K.check(lib.lspk_bench_handoff(grid, 2000, mode, ctypes.byref(us), ctypes.byref(cyc)))
+            out[f"persistent_{name}_grid{grid}"] = {"us_per_round": us.value, "sm_cycles_per_round": cyc.value}
+    for cs, nc, stages in ((1, 1, 2000), (16, 1, 2000), (16, 9, 400), (1, 148, 400)):
+        K.check(lib.lspk_bench_cluster(cs, nc, stages, 1, 1, 0, ctypes.byref(ms)))
+        gb = cs * nc * stages * 16384 / 1e9
+        out[f"stream_{nc}_clusters_of_{cs}"] = {"GBps_total": gb / (ms.value / 1e3), "GBps_per_sm": gb / (ms.value / 1e3) / (cs * nc)}
+    for cs in (2, 4, 8, 16):
+        K.check(lib.lspk_bench_cluster(cs, 1, 1, 2000, 1, 1, ctypes.byref(ms)))
+        out[f"cluster_exchange_{cs}_ctas_us"] = 1000.0 * ms.value / 2000
+    print(json.dumps(out))
+
+
+def measure_hybrid(passes: int):
+    """Config 5: 24-layer Mamba-2 + MoE decoder, 128 greedy steps after a 128-token prompt at batch 1 and 16
+    (device time of the chained decode graph, best of `passes` + 1)."""
     entry.load_package()
     from litespark_inference_b200.torchless import hybrid as hyb
     from litespark_inference_b200.torchless import kernel as K
@@ -438,14 +490,16 @@ def run_hybrid(args):
     cfg = hyb.HybridConfig()
     model = hyb.random_hybrid(cfg, seed=0, fast=True)
     d = hyb.DeviceHybrid(model)
-    out = {"workload": "hybrid", "device_bytes": d.device_bytes, "batches": []}
+    out = {"workload": "hybrid Mamba-2 + ternary MoE decoder (24 layers, hidden 2560, 80 x 64 heads, d_state 128, 8 experts "
+                       "of FFN 6912, top-2), 128-token random prompt + 128 greedy steps",
+           "device_bytes": d.device_bytes, "batches": []}
     ms = ctypes.c_float(0.0)
     for B in (1, 16):
         st = hyb.HybridState(d, batch=B, max_steps=GEN_LEN)
         prompts = np.random.default_rng(7).integers(0, cfg.vocab_size, (PROMPT_LEN, B)).astype(np.int32)
         first = st.prefill(prompts)
         best = None
-        for _ in range(max(args.steps, 1) + 1):
+        for _ in range(max(passes, 1) + 1):
             K.check(lib.lspk_timer_start())
             st.decode_greedy(first, GEN_LEN)
             K.check(lib.lspk_timer_stop(ctypes.byref(ms)))
@@ -453,7 +507,12 @@ def run_hybrid(args):
         out["batches"].append({"batch": B, "tok_s": B * GEN_LEN / (best / 1000.0), "ms_per_step": best / GEN_LEN,
                                "kernels_per_step": st.step_kernel_count})
         st.close()
-    print(json.dumps(out))
+    d.close()
+    return out
+
+
+def run_hybrid(args):
+    print(json.dumps(measure_hybrid(args.steps)))
 
 
 def main():
@@ -464,7 +523,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="tg128", choices=["tg128", "sweep", "gemv", "hybrid"],
+    ap.add_argument("--no-hybrid", action="store_true", help="skip the hybrid (Mamba-2 + MoE) extra measurement")
+    ap.add_argument("--workload", default="tg128", choices=["tg128", "sweep", "gemv", "hybrid", "probes"],
                     help="tg128: the headline line; sweep: per-shape x token-count table of the ternary linear "
                          "kernels; gemv: the single 6912x2560 GEMV; hybrid: Mamba-2 + MoE decode (extra lines, "
                          "not the headline)")
@@ -487,6 +547,9 @@ def main():
         return
     if args.workload == "hybrid":
         run_hybrid(args)
+        return
+    if args.workload == "probes":
+        run_probes(args)
         return
 
     rank = int(os.environ.get("RANK", "0"))
@@ -717,6 +780,16 @@ def main():
                "sample": f"{ref.what}; {n_cpu} passes of {GEN_LEN} greedy decode steps after the {PROMPT_LEN}-token prompt "
                          f"of the same model (prefill {ref.pp_s * 1e3:.0f} ms, two 64-row chunks), fp16 KV, OMP threads={ref.threads}"}
 
+    # ---- the hybrid configuration (extra lines, not the headline): rank 0's GPU, after the headline numbers ------
+    hybrid = None
+    if not args.skip_extras and not args.no_hybrid:
+        try:
+            state.close()
+            dm.close()
+            hybrid = measure_hybrid(1)
+        except Exception as ex:
+            hybrid = {"error": str(ex)[:200]}
+
     line = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
@@ -755,6 +828,7 @@ def main():
                            "frac_of_nominal_8TBs": token_gbs / 8000.0},
         "cpu_baseline": cpu,
         "extra": extra,
+        "hybrid": hybrid,
         "tp_mlp": tp_info,
     }
     print(json.dumps(line))

@@ -48,7 +48,8 @@ int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out);
 int lspk_bench_linear_copies_independent(const lspk_weight_t* w, const lspk_weight_t* w_up, int n_w, const float* x_f32,
                                          float* y, int M, int reps, int n_streams, int int8_input, float* ms_out);
 
-/* CUDA-event time of `reps` replays of a graph of n_blocks MLP blocks over distinct weight triples. */
+/* CUDA-event time of `reps` replays of a graph of n_blocks MLP blocks over distinct weight triples.
+ * inter_full == NULL: the two gathers of every block go through the peer windows instead of NCCL. */
 int lspk_tp_bench_mlp(const lspk_weight_t* gate_r, const lspk_weight_t* up_r, const lspk_weight_t* down_r, int n_blocks,
                       const float* x_dev, const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps,
                       float* inter_slice, float* inter_full, float* down_slice, float* y_full, int reps, float* ms_out);

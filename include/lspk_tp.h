@@ -26,6 +26,27 @@ int lspk_tp_finalize(void);
 int lspk_tp_mlp_block(lspk_weight_t gate_r, lspk_weight_t up_r, lspk_weight_t down_r, const float* x_dev,
                       const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps, float* inter_slice,
                       float* inter_full, float* down_slice, float* y_full);
+
+/* The same exchange over peer memory (csrc/tp_peer.cu): every rank creates one window (a device buffer holding the
+ * gathered gate product [I], the gathered down product [H] and arrival counters), hands its 64-byte CUDA IPC
+ * handle to the other ranks of the node by any host channel, and opens theirs.  lspk_tp_exchange stores this
+ * rank's slice (which = 0: I / world floats of the gate product, 1: H / world floats of the down product) into
+ * every window with plain stores, then waits, with a bound, until every rank's slice has arrived in its own.
+ * When the bound runs out the library's wait flag is raised (lspk_tc_check_error returns LSPK_ERR_DEVICE_WAIT)
+ * and the stream carries on: a rank that never arrives costs an error code, not a hang. */
+int lspk_tp_window_create(int rank, int world, int I, int H, void* ipc_handle64_out);
+int lspk_tp_window_open(int rank, const void* ipc_handle64);
+int lspk_tp_window_close(void);
+int lspk_tp_window_set_poll_limit(unsigned polls);          /* polls of the arrival counter before a wait gives up */
+/* Test aid for the bounded wait: the next lspk_tp_exchange stores nothing, as if this rank's peers were gone, so
+ * its wait polls a counter that nothing advances, gives up and raises the wait flag.  Nothing faults. */
+int lspk_tp_debug_drop_next_arrival(void);
+const float* lspk_tp_window_vector(int which);              /* device pointer of a gathered vector in the local window */
+int lspk_tp_exchange(const float* slice_dev, int which);
+/* lspk_tp_mlp_block with both gathers through the windows; the gathered down product stays in the window. */
+int lspk_tp_mlp_block_peer(lspk_weight_t gate_r, lspk_weight_t up_r, lspk_weight_t down_r, const float* x_dev,
+                           const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps, float* inter_slice,
+                           float* down_slice);
 #ifdef __cplusplus
 }
 #endif

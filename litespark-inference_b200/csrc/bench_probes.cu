@@ -640,14 +640,20 @@ int lspk_bench_launch_floor(int n_kernels, int grid, int reps, float* ms_out) {
 }
 
 // Time `reps` replays of a graph holding `n_blocks` such MLP blocks over distinct weight triples.
+// inter_full == NULL: the gathers go through the peer windows (lspk_tp_mlp_block_peer) instead of NCCL.
 int lspk_tp_bench_mlp(const lspk_weight_t* gate_r, const lspk_weight_t* up_r, const lspk_weight_t* down_r, int n_blocks,
                       const float* x_dev, const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps,
                       float* inter_slice, float* inter_full, float* down_slice, float* y_full, int reps, float* ms_out) {
     LSPK_REQUIRE(gate_r && up_r && down_r && n_blocks >= 1 && reps >= 1 && ms_out, "lspk_tp_bench_mlp: bad arguments");
     auto enqueue = [&]() -> int {
-        for (int i = 0; i < n_blocks; ++i)
-            if (int rc = lspk_tp_mlp_block(gate_r[i], up_r[i], down_r[i], x_dev, norm_gamma_bf16, sub_norm_gamma_bf16, eps,
-                                           inter_slice, inter_full, down_slice, y_full)) return rc;
+        for (int i = 0; i < n_blocks; ++i) {
+            const int rc = inter_full
+                ? lspk_tp_mlp_block(gate_r[i], up_r[i], down_r[i], x_dev, norm_gamma_bf16, sub_norm_gamma_bf16, eps,
+                                    inter_slice, inter_full, down_slice, y_full)
+                : lspk_tp_mlp_block_peer(gate_r[i], up_r[i], down_r[i], x_dev, norm_gamma_bf16, sub_norm_gamma_bf16, eps,
+                                         inter_slice, down_slice);
+            if (rc) return rc;
+        }
         return LSPK_OK;
     };
     if (int rc = enqueue()) return rc;

@@ -7,18 +7,16 @@
 // (matmul_lut_avx512_mT, matmul_lut_avx512_extern_c.cpp:258-339) and, as the tensor-unit analogue,
 // its AMX tile GEMM (matmul_amx_int8_mT_v2, :819-933).
 //
-// One CTA owns 128 output features (the MMA's M side: one TMEM lane per feature) and up to 512 token rows (the
-// MMA's N side: one TMEM column per token, tiles of TN <= 256).  Per 128-wide K block, through three rings:
-//   warp 0      TMA: 4 KB of packed 2-bit weights (128 rows x 32 bytes of the device chunk layout), six blocks
-//               ahead; it starts before the previous kernel has finished (weights do not depend on it)
-//   warp 1      TMA: the TN x 128-byte tiles of int8 activations (128-byte swizzle), one per (K block, token tile)
-//   warps 3-10  expand the packed rows to signed int8 {-1,0,+1} in the canonical K-major, 128-byte-swizzled
-//               operand layout (thread = weight row x 64-weight half; one packed word -> 16 bytes), ONCE per K
-//               block whatever the number of token tiles
-//   warp 2      one thread issues 4 x tcgen05.mma.kind::i8 (M=128, N=TN, K=32) per (K block, token tile), commits
-//               the activation tile back to its producer after each tile and the weight tile after the last
-// then warps 3-10 read the accumulators with tcgen05.ld (two warps per TMEM lane quarter, alternate 32-column
-// slabs) and write fp32 (and, if asked, the int32).
+// One CTA owns 128 output features (the MMA's M side: one TMEM lane per feature) and TN token rows
+// (the MMA's N side: one TMEM column per token).  Per 128-wide K block, through a 4-stage ring:
+//   warp 0      TMA: 4 KB of packed 2-bit weights (128 rows x 32 bytes of the device chunk layout)
+//               and the TN x 128-byte tile of int8 activations (128-byte swizzle) -> shared memory
+//   warps 2-5   expand the packed rows to signed int8 {-1,0,+1} in the canonical K-major,
+//               128-byte-swizzled operand layout (thread = weight row; one packed word -> 16 bytes)
+//   warp 1      one thread issues 4 x tcgen05.mma.kind::i8 (M=128, N=TN, K=32) per block and
+//               commits the stage back to the producer
+// then warps 2-9 read the accumulators with tcgen05.ld (two warps per quarter of the TMEM lanes, alternate
+// 32-column slabs; warps 6-9 exist only for this) and write fp32 (and, if asked, the int32).
 // The activations are stored with the 4x4 index transpose inside every 16-element block that the
 // masked decode of a packed word implies (same trick as the CUDA-core kernel), so a packed word
 // expands with 4 x (shift, and, byte-subtract) and lands as one aligned 16-byte chunk.
@@ -32,14 +30,9 @@
 
 namespace lspk {
 
-constexpr int kTcExpandWarps = 8;
-constexpr int kTcThreads = 96 + 32 * kTcExpandWarps;   // 11 warps: weight TMA, activation TMA, MMA, 8 x expand/epilogue
-constexpr int kTcWStages = 6;            // ring of packed weight blocks (4 KB each)
-constexpr int kTcAStages = 3;            // ring of expanded weight tiles (16 KB each)
+constexpr int kTcThreads = 320;          // 10 warps: TMA, MMA, 4 x expand + epilogue, 4 x epilogue only
+constexpr int kTcStages = 4;
 constexpr int kTcBK = 128;               // K elements per pipeline block
-constexpr int kTcMaxTokens = 512;        // token rows per CTA (all their accumulators live in tensor memory)
-// ring of activation tiles (TN x 128 bytes each): what fits beside the other two rings
-__host__ __device__ constexpr int tc_b_stages(int TN) { return TN >= 256 ? 4 : TN >= 128 ? 6 : 8; }
 constexpr int kTcRows = 128;             // output features per CTA
 constexpr unsigned kSpinLimit = 1u << 22;
 
@@ -60,7 +53,6 @@ struct TcParams {
     const float* x_scales;
     int M, K;
     int k_blocks;            // K blocks of the whole product
-    int tokens_per_cta;      // token rows per CTA along gridDim.y (a multiple of the tile width, at most 512)
     int kb_per_split;        // K blocks per CTA along gridDim.z (== k_blocks when K is not split)
     int epilogue;            // LSPK_EPI_STORE or LSPK_EPI_ADD
     int* error_flag;
@@ -101,25 +93,24 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 }
 
 template <int TN>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads)
 ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                        const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x,
                        const __grid_constant__ TcParams p) {
     constexpr int kPackedBytes = kTcRows * kTcBK / 4;       // 4096
     constexpr int kATileBytes = kTcRows * kTcBK;            // 16384
     constexpr int kBTileBytes = TN * kTcBK;
-    constexpr int kBStages = tc_b_stages(TN);
+    constexpr int kStageBytes = kPackedBytes + kATileBytes + kBTileBytes;
+    constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;       // power of two >= 32
     // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = TN, M = 128
     constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((128u >> 4) << 24);
 
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    unsigned char* a_ring = smem;                                        // [kTcAStages][16 KB] expanded weights
-    unsigned char* b_ring = a_ring + (size_t)kTcAStages * kATileBytes;   // [kBStages][TN x 128 B] activations
-    unsigned char* w_ring = b_ring + (size_t)kBStages * kBTileBytes;     // [kTcWStages][4 KB] packed weights
-    __shared__ __align__(8) uint64_t full_w[kTcWStages], empty_w[kTcWStages];
-    __shared__ __align__(8) uint64_t full_a[kTcAStages], empty_a[kTcAStages];
-    __shared__ __align__(8) uint64_t full_b[kBStages], empty_b[kBStages];
+    __shared__ __align__(8) uint64_t full_w[kTcStages];     // packed weights of the stage have landed
+    __shared__ __align__(8) uint64_t full_tma[kTcStages];   // activation tile of the stage has landed
+    __shared__ __align__(8) uint64_t full_a[kTcStages];
+    __shared__ __align__(8) uint64_t empty[kTcStages];
     __shared__ __align__(8) uint64_t acc_ready;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
@@ -131,35 +122,29 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
     const TcSeg& sg = p.seg[sgi];
     const CUtensorMap* map_w = sgi == 0 ? &map_w0 : sgi == 1 ? &map_w1 : &map_w2;
     const int n0 = ((int)blockIdx.x - sg.tile0) * kTcRows;
-    // token rows of this CTA: [m0, m0 + n_tiles * TN), every tile with its own TN accumulator columns
-    const int m0 = blockIdx.y * p.tokens_per_cta;
-    const int n_tiles = (min(p.tokens_per_cta, p.M - m0) + TN - 1) / TN;
-    uint32_t tmem_cols = 32;
-    while (tmem_cols < (uint32_t)(n_tiles * TN)) tmem_cols <<= 1;
+    const int m0 = blockIdx.y * TN;
     // K split: this CTA's K blocks are [kb0, kb0 + nkb)
     const int kb0 = blockIdx.z * p.kb_per_split;
     const int nkb = min(p.kb_per_split, p.k_blocks - kb0);
 
+    auto a_tile = [&](int s) { return smem + (size_t)s * kStageBytes; };
+    auto b_tile = [&](int s) { return smem + (size_t)s * kStageBytes + kATileBytes; };
+    auto packed = [&](int s) { return smem + (size_t)s * kStageBytes + kATileBytes + kBTileBytes; };
+
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < kTcWStages; ++s) {
+        for (int s = 0; s < kTcStages; ++s) {
             mbar_init(&full_w[s], 1);
-            mbar_init(&empty_w[s], kTcExpandWarps);         // one arrival per expansion warp
-        }
-        for (int s = 0; s < kTcAStages; ++s) {
-            mbar_init(&full_a[s], kTcExpandWarps);
-            mbar_init(&empty_a[s], 1);
-        }
-        for (int s = 0; s < kBStages; ++s) {
-            mbar_init(&full_b[s], 1);
-            mbar_init(&empty_b[s], 1);
+            mbar_init(&full_tma[s], 1);
+            mbar_init(&full_a[s], 4);                      // one arrival per expansion warp
+            mbar_init(&empty[s], 1);
         }
         mbar_init(&acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 2) {
+    if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                     "r"(tmem_cols)
+                     "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -170,86 +155,83 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
     volatile int* abortp = &abort_flag;
 
     grid_dependency_launch();
+    // The packed weights do not depend on the previous kernel: the producer requests the first ring of them, and
+    // the expansion warps turn them into operand tiles, while that kernel is still running.  Whoever touches the
+    // activations, the scales or the outputs waits for it first.
+    auto load_weights = [&](int kb) {
+        const int s = kb % kTcStages;
+        mbar_expect_tx(&full_w[s], kPackedBytes);
+        // inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes = 128 units per row
+        // group), outer coordinate = row group
+        tma_load_2d(packed(s), map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_w[s]);
+    };
+
     if (warp == 0) {
-        // ---------------- producer of the packed weights: runs ahead of everything, also of the previous kernel ----
-        if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % kTcWStages;
-                if (kb >= kTcWStages && !mbar_wait(&empty_w[s], ((kb / kTcWStages) - 1) & 1, abortp)) break;
-                if (*abortp) break;
-                mbar_expect_tx(&full_w[s], kPackedBytes);
-                // inner coordinate in 4-byte units (a K block is 2 chunks x 16 rows x 16 bytes = 128 units per row
-                // group), outer coordinate = row group
-                tma_load_2d(w_ring + (size_t)s * kPackedBytes, map_w, (kb0 + kb) * 128, n0 / kRowsPerGroup, &full_w[s]);
-                ++issued;
-            }
-            if (*abortp)             // drain: bounded wait for the copies of the last ring's worth of stages
-                for (int kb = max(0, issued - kTcWStages); kb < issued; ++kb)
-                    for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&full_w[kb % kTcWStages], (kb / kTcWStages) & 1); ++i) {}
-        }
-    } else if (warp == 1) {
-        // ---------------- producer of the activation tiles: (K block, token tile) pairs in the MMA's order ---------
+        // ---------------- producer ------------------------------------------------------------
         if (lane == 0) {
             PhaseTrace tr;
-            tr.begin(p.trace, p.trace_cap, 10, 32);
+            tr.begin(p.trace, p.trace_cap, 10, 0);
+            const int early = min(nkb, kTcStages);
+            for (int kb = 0; kb < early; ++kb) load_weights(kb);
             grid_dependency_wait();
-            const int total = nkb * n_tiles;
             int issued = 0;
-            for (int it = 0; it < total; ++it) {
-                if ((it & 7) == 0) tr.mark();
-                const int s = it % kBStages;
-                if (it >= kBStages && !mbar_wait(&empty_b[s], ((it / kBStages) - 1) & 1, abortp)) break;
+            for (int kb = 0; kb < nkb; ++kb) {
+                if ((kb & 1) == 0) tr.mark();              // before the wait for blocks 0, 2, 4, ...
+                const int s = kb % kTcStages;
+                if (kb >= kTcStages && !mbar_wait(&empty[s], ((kb / kTcStages) - 1) & 1, abortp)) break;
                 if (*abortp) break;
-                const int kb = it / n_tiles, j = it % n_tiles;
-                mbar_expect_tx(&full_b[s], kBTileBytes);
-                tma_load_2d(b_ring + (size_t)s * kBTileBytes, &map_x, (kb0 + kb) * kTcBK, m0 + j * TN, &full_b[s]);
+                if (kb >= early) load_weights(kb);
+                mbar_expect_tx(&full_tma[s], kBTileBytes);
+                tma_load_2d(b_tile(s), &map_x, (kb0 + kb) * kTcBK, m0, &full_tma[s]);
                 ++issued;
             }
             tr.end();
-            if (*abortp)
-                for (int it = max(0, issued - kBStages); it < issued; ++it)
-                    for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&full_b[it % kBStages], (it / kBStages) & 1); ++i) {}
+            if (*abortp) {
+                // drain: wait (bounded) for every copy this thread started
+                const int w_issued = issued > early ? issued : early;
+                for (int kb = 0; kb < w_issued; ++kb) {
+                    const int s = kb % kTcStages;
+                    if (kb + kTcStages >= w_issued)
+                        for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&full_w[s], (kb / kTcStages) & 1); ++i) {}
+                }
+                for (int kb = 0; kb < issued; ++kb) {
+                    const int s = kb % kTcStages;
+                    if (kb + kTcStages >= issued)
+                        for (unsigned i = 0; i < kSpinLimit && !mbar_try_wait(&full_tma[s], (kb / kTcStages) & 1); ++i) {}
+                }
+            }
         }
-    } else if (warp == 2) {
+    } else if (warp == 1) {
         // ---------------- MMA issuer ------------------------------------------------------------
         if (lane == 0) {
             PhaseTrace tr;
-            tr.begin(p.trace, p.trace_cap, 11, 64);
+            tr.begin(p.trace, p.trace_cap, 11, 32);
+            grid_dependency_wait();
             bool ok = true;
-            int it = 0;
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 if ((kb & 1) == 0) tr.mark();
-                const int sa = kb % kTcAStages;
-                ok = mbar_wait(&full_a[sa], (kb / kTcAStages) & 1, abortp);
+                const int s = kb % kTcStages;
+                const uint32_t ph = (kb / kTcStages) & 1;
+                ok = mbar_wait(&full_tma[s], ph, abortp) && mbar_wait(&full_a[s], ph, abortp);
                 if (!ok) break;
-                const uint64_t da = umma_desc_sw128(smem_u32(a_ring + (size_t)sa * kATileBytes));
-                for (int j = 0; j < n_tiles && ok; ++j, ++it) {
-                    const int sb = it % kBStages;
-                    ok = mbar_wait(&full_b[sb], (it / kBStages) & 1, abortp);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint64_t db = umma_desc_sw128(smem_u32(b_ring + (size_t)sb * kBTileBytes));
+                tc_fence_after();
+                const uint64_t da = umma_desc_sw128(smem_u32(a_tile(s)));
+                const uint64_t db = umma_desc_sw128(smem_u32(b_tile(s)));
 #pragma unroll
-                    for (int k4 = 0; k4 < kTcBK / 32; ++k4) {
-                        const uint32_t accumulate = (kb | k4) ? 1u : 0u;
-                        // advancing 32 int8 along K = 32 bytes = 2 descriptor address units
-                        asm volatile(
-                            "{\n\t.reg .pred p;\n\t"
-                            "setp.ne.b32 p, %4, 0;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-                            ::"r"(tmem_base + (uint32_t)(j * TN)), "l"(da + (uint64_t)(k4 * 2)), "l"(db + (uint64_t)(k4 * 2)),
-                            "r"(kIdesc), "r"(accumulate)
-                            : "memory");
-                    }
-                    // frees the activation tile once the MMAs above have read it
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                                     smem_u32(&empty_b[sb]))
-                                 : "memory");
+                for (int k4 = 0; k4 < kTcBK / 32; ++k4) {
+                    const uint32_t accumulate = (kb | k4) ? 1u : 0u;
+                    // advancing 32 int8 along K = 32 bytes = 2 descriptor address units
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem_base), "l"(da + (uint64_t)(k4 * 2)), "l"(db + (uint64_t)(k4 * 2)), "r"(kIdesc),
+                        "r"(accumulate)
+                        : "memory");
                 }
-                // frees the expanded weight tile once every token tile has been multiplied with it
+                // frees the stage for the producer once the MMAs above have read it
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                                 smem_u32(&empty_a[sa]))
+                                 smem_u32(&empty[s]))
                              : "memory");
             }
             // On the regular path this tells the epilogue warps that every MMA has completed.  After an abort
@@ -264,41 +246,38 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
         }
     } else {
         // ---------------- expand packed weights -> int8 operand tile, then epilogue ---------------
-        const int e = tid - 96;                           // 0..255
-        const int row = e & 127, c = e >> 7;              // weight row inside the CTA tile, 64-weight chunk of the K block
+        const int row = tid - 64;                         // 0..127: weight row inside the CTA tile
         const int gi = row >> 4, rr = row & 15;
-        const int ew = warp - 3;                          // expansion warp 0..7
         bool ok = true;
         PhaseTrace tr;
-        tr.begin(p.trace, p.trace_cap, 12, 96);
-        for (int kb = 0; kb < nkb && ok; ++kb) {
+        tr.begin(p.trace, p.trace_cap, 12, 64);
+        // warps 6-9 take no part in the expansion: they double the warps that drain the accumulators afterwards
+        for (int kb = 0; kb < (warp < 6 ? nkb : 0) && ok; ++kb) {
             if ((kb & 7) == 0 && kb < 24) tr.mark();
-            const int sw = kb % kTcWStages, sa = kb % kTcAStages;
-            // warp-uniform: every lane polls with its own counter, and the barriers below need the whole warp
-            ok = __all_sync(0xffffffffu, mbar_wait(&full_w[sw], (kb / kTcWStages) & 1, abortp));
-            if (ok && kb >= kTcAStages)
-                ok = __all_sync(0xffffffffu, mbar_wait(&empty_a[sa], ((kb / kTcAStages) - 1) & 1, abortp));
+            const int s = kb % kTcStages;
+            // warp-uniform: every lane polls with its own counter, and the barrier below needs the whole warp
+            ok = __all_sync(0xffffffffu, mbar_wait(&full_w[s], (kb / kTcStages) & 1, abortp));
             if (!ok) break;
-            const unsigned char* pk = w_ring + (size_t)sw * kPackedBytes;
-            unsigned char* arow = a_ring + (size_t)sa * kATileBytes + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
-            const uint4 w = *reinterpret_cast<const uint4*>(pk + gi * 512 + c * 256 + rr * 16);
-            const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+            const unsigned char* pk = packed(s);
+            unsigned char* arow = a_tile(s) + (size_t)(row >> 3) * 1024 + (size_t)(row & 7) * 128;
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                uint4 o;
-                o.x = __vsub4(words[m] & 0x03030303u, 0x01010101u);
-                o.y = __vsub4((words[m] >> 2) & 0x03030303u, 0x01010101u);
-                o.z = __vsub4((words[m] >> 4) & 0x03030303u, 0x01010101u);
-                o.w = __vsub4((words[m] >> 6) & 0x03030303u, 0x01010101u);
-                const int chunk = c * 4 + m;               // 16-byte chunk index inside the 128-byte row
-                *reinterpret_cast<uint4*>(arow + ((chunk ^ (row & 7)) << 4)) = o;
+            for (int c = 0; c < 2; ++c) {                  // the two 64-weight chunks of this K block
+                const uint4 w = *reinterpret_cast<const uint4*>(pk + gi * 512 + c * 256 + rr * 16);
+                const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    uint4 o;
+                    o.x = __vsub4(words[m] & 0x03030303u, 0x01010101u);
+                    o.y = __vsub4((words[m] >> 2) & 0x03030303u, 0x01010101u);
+                    o.z = __vsub4((words[m] >> 4) & 0x03030303u, 0x01010101u);
+                    o.w = __vsub4((words[m] >> 6) & 0x03030303u, 0x01010101u);
+                    const int chunk = c * 4 + m;           // 16-byte chunk index inside the 128-byte row
+                    *reinterpret_cast<uint4*>(arow + ((chunk ^ (row & 7)) << 4)) = o;
+                }
             }
             fence_async_smem();                            // generic-proxy writes -> visible to the tensor unit
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&full_a[sa]);                  // 8 arrivals per stage instead of 256
-                mbar_arrive(&empty_w[sw]);                 // the packed bytes have been read
-            }
+            if (lane == 0) mbar_arrive(&full_a[s]);        // 4 arrivals per stage instead of 128
         }
         // epilogue: TMEM lane = weight row, column = token
         grid_dependency_wait();                            // scales, residual and outputs belong to the chain
@@ -311,10 +290,9 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
             tc_fence_after();
             const int quarter = warp & 3;                  // TMEM lanes this warp may read
             const int n = n0 + quarter * 32 + lane;
-            const int slabs = n_tiles * TN / 32;
-            // two warps share a lane quarter: they take alternate 32-column slabs
 #pragma unroll 1
-            for (int cb = ew >> 2; cb < slabs; cb += 2) {
+            // two warps share a quarter of the TMEM lanes: they take alternate 32-column slabs
+            for (int cb = warp < 6 ? 0 : 1; cb < TN / 32; cb += 2) {
                 uint32_t v[32];
                 tr.mark();                                 // previous slab stored
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(cb * 32);
@@ -377,9 +355,9 @@ ternary_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 2) {
+    if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
     if (tid == 0 && abort_flag && p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
 }
@@ -511,8 +489,7 @@ int quant_scratch(size_t M, size_t K, int8_t** q, float** s, int** sums) {
 
 template <int TN>
 static cudaError_t launch_tc(const CUtensorMap* mw, const CUtensorMap& mx, const TcParams& p, dim3 grid) {
-    constexpr size_t smem = (size_t)kTcWStages * (kTcRows * kTcBK / 4) + (size_t)kTcAStages * kTcRows * kTcBK +
-                            (size_t)tc_b_stages(TN) * TN * kTcBK + 1024;
+    constexpr size_t smem = (size_t)kTcStages * (kTcRows * kTcBK / 4 + kTcRows * kTcBK + TN * kTcBK) + 1024;
     static bool attr_set = false;
     auto kern = ternary_gemm_tc_kernel<TN>;
     if (!attr_set) {
@@ -581,12 +558,12 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
         n_tiles[i] = (w->N + kTcRows - 1) / kTcRows;
         total_tiles += n_tiles[i];
     }
-    // Token rows per tile (the MMA's N) and per CTA: a CTA keeps the accumulators of up to 512 token rows of its 128
-    // features in tensor memory (two tiles of 256), so that a packed K block is fetched and expanded once for
-    // all of them.
-    const int TN = M > 128 ? 256 : M > 64 ? 128 : M > 32 ? 64 : 32;
-    const int tokens_per_cta = M > kTcMaxTokens ? kTcMaxTokens : ((M + TN - 1) / TN) * TN;
-    const int m_tiles = (M + tokens_per_cta - 1) / tokens_per_cta;       // token groups along grid.y
+    // Token rows per CTA tile.  A K block costs about the same whatever the tile's width (the loop is bound by
+    // its handshakes, not by the tensor pipe), so 256 rows per tile halve the work when the grid still fills
+    // the machine or the K loop is long; otherwise more, narrower tiles win.
+    const bool wide = M > 128 && (total_tiles * ((M + 255) / 256) * 2 > sm_count() || k_blocks >= 32);
+    const int TN = wide ? 256 : M > 64 ? 128 : M > 32 ? 64 : 32;
+    const int m_tiles = (M + TN - 1) / TN;
     CUtensorMap mx;
     {
         const cuuint64_t dims[2] = {(cuuint64_t)Kp, (cuuint64_t)M};
@@ -653,7 +630,6 @@ int linear_tensor_core(const lspk_linear_args* a, int* handled) {
     p.M = M;
     p.K = K;
     p.k_blocks = k_blocks;
-    p.tokens_per_cta = tokens_per_cta;
     p.kb_per_split = kb_per;
     p.epilogue = a->epilogue;
     p.error_flag = g_tc.err;

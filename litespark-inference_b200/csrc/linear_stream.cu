@@ -5,30 +5,34 @@
 // matmul_lut_avx512_extern_c.cpp:150-236).  On the GPU a launch per matrix pays a ramp every time: a 4.4 MB
 // matrix is 0.7 us of HBM time, shorter than the fill and drain of a kernel.  Here the whole list is one
 // stream of bytes: the row groups of all products form one flat sequence of units; every CTA of a persistent
-// grid (one per SM) takes a contiguous range of it, deals the units of its range round-robin to its warps, and
-// each warp keeps a private ring of bulk copies (cp.async.bulk + mbarrier) running ahead of its arithmetic,
-// across product boundaries.  A range touches one or two products, so a CTA installs one or two vectors.
+// grid (one per SM) takes a contiguous range of it.  One warp of the CTA does nothing but request the range's
+// stages, in order, into a ring of eighteen 10 KB slots in shared memory (cp.async.bulk + mbarrier, across product
+// boundaries); twelve consumer warps take the units round-robin, each computing its unit alone.  A range touches
+// one or two products, so a CTA installs one or two vectors.
 //
 //   unit   = 16 output rows of one product (both matrices of a gated gate/up pair), cut along K into stages of
 //            at most 10 KB; a warp accumulates a unit's stages in registers and stores its 16 results itself:
 //            no CTA-wide barrier per unit, only one per product (when the next activation vector is installed)
 //   vector = the int8 activations of product i + 1 are fetched into registers while product i is computed, then
 //            byte-transposed into the other of two shared-memory slots
-// The arithmetic per row is the one-row kernel's (masked dp4a fields, exact shifts, sum(x) subtracted once), so
-// results are bit-identical to lspk_linear.  Every mbarrier wait is bounded: on expiry the warp raises the
-// library's wait flag, stops computing and only keeps the CTA's barriers company until the kernel ends.
+// The arithmetic per row is integer throughout and equal to the one-row kernel's (masked 2-bit fields at their bit
+// offset, dp4a, exact shifts, sum(x) subtracted once), so results are bit-identical to lspk_linear.  Every wait is
+// bounded by one deadline in SM cycles (about a second for the whole CTA): on expiry the warp raises the
+// library's wait flag and leaves its ring alone; the other warps stop computing but keep waiting for the copies
+// already requested for them, and all keep the CTA's barriers company until the kernel ends.
 #include "internal.cuh"
 #include "ternary_core.cuh"
 
 namespace lspk {
 
-constexpr int kSWarps = 8;                       // warps per CTA
-constexpr int kSRing = 2;                        // ring stages per warp
+constexpr int kSConsumers = 12;                  // warps that compute; one more warp only requests copies
+constexpr int kSThreads = 32 * (kSConsumers + 1);
+constexpr int kSSlots = 18;                      // stages of the CTA's ring (shared by all consumer warps)
 constexpr int kSStageChunks = 40;                // 16-row x 16-byte chunks per stage (all matrices of a unit)
-constexpr int kSStageBytes = kSStageChunks * kRowsPerGroup * 16;   // 10240
+constexpr int kSStageBytes = kSStageChunks * kRowsPerGroup * 16;   // 10240: 180 KB of ring per SM
 constexpr int kSMaxItems = 96;
 constexpr int kSMaxKp = 8192;                    // longest row (K rounded up to 64)
-constexpr unsigned kSSpinLimit = 1u << 22;
+constexpr long long kSBudgetCycles = 1ll << 31;  // SM cycles (about a second) after which every wait of a CTA gives up
 
 struct StreamItem {
     const uint4* w[2];
@@ -41,6 +45,7 @@ struct StreamItem {
     int nm;            // matrices per unit: 1, or 2 for the gated pairing
     int epilogue;
     int unit0;         // flat index of this product's first unit
+    int q0;            // flat index of this product's first stage
     int cps;           // chunks per stage and matrix
     int sub;           // stages per unit
 };
@@ -51,89 +56,115 @@ struct StreamParams {
     int* error_flag;
 };
 
-struct StreamCursor {      // position in one warp's sequence of stages
-    int item, unit, s;
-};
+__device__ __forceinline__ void consumer_barrier() {      // the consumer warps only (the producer warp never joins)
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kSConsumers) : "memory");
+}
 
-__global__ void __launch_bounds__(kSWarps * 32, 1)
+__global__ void __launch_bounds__(kSThreads, 1)
 ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    uint4* ring = reinterpret_cast<uint4*>(smem_raw);                                   // [warps][ring][stage]
-    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw + (size_t)kSWarps * kSRing * kSStageBytes);   // [2][kSMaxKp]
-    __shared__ __align__(8) uint64_t bars[kSWarps][kSRing];
-    __shared__ int s_sumx[2][kSWarps];
+    uint4* ring = reinterpret_cast<uint4*>(smem_raw);                                   // [slots][stage]
+    int8_t* xq = reinterpret_cast<int8_t*>(smem_raw + (size_t)kSSlots * kSStageBytes);  // [2][kSMaxKp]
+    __shared__ __align__(8) uint64_t full[kSSlots], empty[kSSlots];
+    __shared__ int s_issued;                     // stages requested so far (written by the producer, read by consumers)
+    __shared__ int s_sumx[2][kSConsumers];
     __shared__ float s_scale[2];
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = lane & 15, h = lane >> 4;
     // this CTA's range of units [u_lo, u_hi) and the products it touches [i_lo, i_hi]
     const int per_cta = (p.total_units + (int)gridDim.x - 1) / (int)gridDim.x;
     const int u_lo = min((int)blockIdx.x * per_cta, p.total_units), u_hi = min(u_lo + per_cta, p.total_units);
-    uint4* my_ring = ring + (size_t)warp * kSRing * (kSStageBytes / 16);
-
-    auto settle = [&](StreamCursor& c) {          // move c.item to the product that holds c.unit (p.n: past the range)
-        if (c.unit >= u_hi) c.item = p.n;
-        while (c.item < p.n && c.unit >= p.it[c.item].unit0 + p.it[c.item].groups) ++c.item;
-    };
-    auto advance = [&](StreamCursor& c) {
-        if (++c.s >= p.it[c.item].sub) {
-            c.s = 0;
-            c.unit += kSWarps;
-            settle(c);
-        }
-    };
-    auto issue = [&](const StreamCursor& c, int slot) {       // one lane: request a stage into ring slot `slot`
-        const StreamItem& it = p.it[c.item];
-        const int g = c.unit - it.unit0;
-        const int c0 = c.s * it.cps, c1 = min(c0 + it.cps, it.chunks);
-        const uint32_t bytes = (uint32_t)(c1 - c0) * kRowsPerGroup * 16u;
-        uint4* dst = my_ring + (size_t)slot * (kSStageBytes / 16);
-        mbar_expect_tx(&bars[warp][slot], bytes * (uint32_t)it.nm);
-        for (int m = 0; m < it.nm; ++m)
-            bulk_load_stream(dst + (size_t)m * (c1 - c0) * kRowsPerGroup,
-                             it.w[m] + ((size_t)g * it.chunks + c0) * kRowsPerGroup, bytes, &bars[warp][slot]);
-    };
-
-    if (tid == 0) s_abort = 0;
-    if (lane == 0) {
-        for (int s = 0; s < kSRing; ++s) mbar_init(&bars[warp][s], 1);
-        fence_mbar_init();
-    }
-    __syncwarp();
-    grid_dependency_launch();
-    // the weights do not depend on whatever ran before: fill the ring first
-    StreamCursor prod = {0, u_lo + warp, 0}, cons = {0, u_lo + warp, 0};
-    settle(prod);
-    settle(cons);
     int i_lo = 0, i_hi = -1;
     if (u_lo < u_hi) {
         while (u_lo >= p.it[i_lo].unit0 + p.it[i_lo].groups) ++i_lo;
         i_hi = i_lo;
         while (u_hi - 1 >= p.it[i_hi].unit0 + p.it[i_hi].groups) ++i_hi;
     }
-    int issued = 0, consumed = 0;
-    if (lane == 0) {
-        while (issued < kSRing && prod.item < p.n) {
-            issue(prod, issued % kSRing);
-            advance(prod);
-            ++issued;
+    // stage number (over the whole call) of the first stage of this CTA's first unit
+    const int q_lo = i_hi >= i_lo ? p.it[i_lo].q0 + (u_lo - p.it[i_lo].unit0) * p.it[i_lo].sub : 0;
+
+    // Every wait below is bounded by one deadline for the whole CTA, in SM cycles: whatever goes wrong, the kernel
+    // is over about a second later.
+    const long long deadline = clock64() + kSBudgetCycles;
+    auto expired = [&]() { return clock64() > deadline || *(volatile int*)&s_abort != 0; };
+    if (tid == 0) {
+        s_abort = 0;
+        s_issued = 0;
+        for (int s = 0; s < kSSlots; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
         }
+        fence_mbar_init();
     }
-    issued = __shfl_sync(0xffffffffu, issued, 0);
-    prod.item = __shfl_sync(0xffffffffu, prod.item, 0);
-    prod.unit = __shfl_sync(0xffffffffu, prod.unit, 0);
-    prod.s = __shfl_sync(0xffffffffu, prod.s, 0);
+    __syncthreads();
+    grid_dependency_launch();
+
+    if (warp == kSConsumers) {
+        // ---------------- producer: one thread requests the CTA's stages in order, as slots come free --------------
+        // (the weights do not depend on whatever ran before, so this starts at once)
+        if (lane == 0 && i_hi >= i_lo) {
+            uint64_t policy;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+            int q = 0;
+            bool ok = true;
+            for (int i = i_lo; i <= i_hi && ok; ++i) {
+                const StreamItem& it = p.it[i];
+                const int g_first = max(u_lo, it.unit0) - it.unit0, g_end = min(u_hi, it.unit0 + it.groups) - it.unit0;
+                const int nm = it.nm, chunks = it.chunks, cps = it.cps, sub = it.sub;
+                const uint4* ua = it.w[0] + (size_t)g_first * chunks * kRowsPerGroup;
+                const uint4* ub = nm == 2 ? it.w[1] + (size_t)g_first * chunks * kRowsPerGroup : nullptr;
+                for (int g = g_first; g < g_end && ok; ++g) {
+                    for (int s = 0; s < sub; ++s, ++q) {
+                        const int slot = q % kSSlots;
+                        if (q >= kSSlots) {          // the slot's previous occupant has to be consumed first
+                            const uint32_t parity = (uint32_t)(q / kSSlots - 1) & 1u;
+                            bool freed = mbar_try_wait(&empty[slot], parity);
+                            while (!freed && !expired()) freed = mbar_try_wait(&empty[slot], parity);
+                            if (!freed) {
+                                ok = false;
+                                break;
+                            }
+                        }
+                        const int c0 = s * cps, c1 = min(c0 + cps, chunks);
+                        const uint32_t bytes = (uint32_t)(c1 - c0) * kRowsPerGroup * 16u;
+                        uint4* dst = ring + (size_t)slot * (kSStageBytes / 16);
+                        mbar_expect_tx(&full[slot], bytes * (uint32_t)nm);
+                        bulk_load_policy(dst, ua + (size_t)c0 * kRowsPerGroup, bytes, &full[slot], policy);
+                        if (nm == 2)
+                            bulk_load_policy(dst + (size_t)(c1 - c0) * kRowsPerGroup, ub + (size_t)c0 * kRowsPerGroup, bytes,
+                                             &full[slot], policy);
+                        // Tell the consumers that stage q's phase of full[slot] is now the current one.  A consumer
+                        // must not test a phase parity before the previous use of the slot has completed (the test
+                        // would succeed at once on the stale phase); the release observed above implies that it has.
+                        __threadfence_block();
+                        *(volatile int*)&s_issued = q + 1;
+                    }
+                    ua += (size_t)chunks * kRowsPerGroup;
+                    if (nm == 2) ub += (size_t)chunks * kRowsPerGroup;
+                }
+            }
+            if (!ok && !*(volatile int*)&s_abort) {               // a consumer did not free its slot in time
+                s_abort = 1;
+                if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+            }
+        }
+        return;      // consumers wait for everything that was requested
+    }
+
+    // ---------------- consumers: warp w takes units u_lo + w, u_lo + w + 12, ... ----------------------------------
+    const int r = lane & 15, h = lane >> 4;
     grid_dependency_wait();
 
     // activation vector of product `i`: this thread's 16-byte blocks (at most two), raw, into registers
-    uint32_t raw[2][4];
+    constexpr int kXB = (kSMaxKp / 16 + 32 * kSConsumers - 1) / (32 * kSConsumers);
+    uint32_t raw[kXB][4];
     auto fetch_x = [&](int i) {
         const StreamItem& it = p.it[i];
         const int Kp = it.chunks * kWeightsPerChunk;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int k0 = (tid + u * kSWarps * 32) * 16;
+        for (int u = 0; u < kXB; ++u) {
+            const int k0 = (tid + u * 32 * kSConsumers) * 16;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int k = k0 + q * 4;
@@ -147,8 +178,8 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         int8_t* dst = xq + (size_t)(i & 1) * kSMaxKp;
         int sumx = 0;
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-            const int k0 = (tid + u * kSWarps * 32) * 16;
+        for (int u = 0; u < kXB; ++u) {
+            const int k0 = (tid + u * 32 * kSConsumers) * 16;
             if (k0 < Kp) {
                 uint32_t o0, o1, o2, o3;
                 transpose4x4_bytes(raw[u][0], raw[u][1], raw[u][2], raw[u][3], o0, o1, o2, o3);
@@ -167,110 +198,94 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
         fetch_x(i_lo);
         install_x(i_lo);
     }
-    __syncthreads();
+    consumer_barrier();
 
-    bool dead = false;                           // this warp gave up (a wait ran out here or elsewhere in the CTA)
+    bool dead = false;                           // a wait of this warp ran out: it leaves the ring alone from here on
+    bool skip = false;                           // another warp gave up: keep draining the ring, compute nothing
+    int unit = u_lo + warp;
     for (int i = i_lo; i <= i_hi; ++i) {
         if (i < i_hi) fetch_x(i + 1);            // in flight while product i is computed
         const StreamItem& it = p.it[i];
         const int8_t* xrow = xq + (size_t)(i & 1) * kSMaxKp;
         int sx = 0;
 #pragma unroll
-        for (int w = 0; w < kSWarps; ++w) sx += s_sumx[i & 1][w];
+        for (int w = 0; w < kSConsumers; ++w) sx += s_sumx[i & 1][w];
         const float xscale = s_scale[i & 1];
-        int acc_a[4] = {0, 0, 0, 0}, acc_b[4] = {0, 0, 0, 0};
-        while (!dead && cons.item == i) {
-            const int slot = consumed % kSRing;
-            const uint32_t parity = (uint32_t)(consumed / kSRing) & 1u;
-            bool arrived = false;
-            for (unsigned spin = 0; spin < kSSpinLimit && !arrived; ++spin) {
-                arrived = mbar_try_wait(&bars[warp][slot], parity);
-                if (!arrived && (spin & 1023u) == 1023u && *(volatile int*)&s_abort) break;
-            }
-            if (!__all_sync(0xffffffffu, arrived)) {
-                dead = true;
-                if (lane == 0) {
-                    s_abort = 1;
-                    if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+        const int unit_end = min(u_hi, it.unit0 + it.groups);
+        for (; !dead && unit < unit_end; unit += kSConsumers) {
+            const int g = unit - it.unit0;
+            int acc_a[4] = {0, 0, 0, 0}, acc_b[4] = {0, 0, 0, 0};
+            for (int s = 0; s < it.sub; ++s) {
+                const int q = it.q0 + g * it.sub + s - q_lo;       // this stage's number in the CTA's sequence
+                const int slot = q % kSSlots;
+                const uint32_t parity = (uint32_t)(q / kSSlots) & 1u;
+                // first the request (see the producer), then the data
+                bool arrived = *(volatile int*)&s_issued > q;
+                while (!arrived && !(clock64() > deadline)) arrived = *(volatile int*)&s_issued > q;
+                if (arrived) {
+                    arrived = mbar_try_wait(&full[slot], parity);
+                    while (!arrived && !(clock64() > deadline)) arrived = mbar_try_wait(&full[slot], parity);
                 }
-                break;
-            }
-            const int g = cons.unit - it.unit0;
-            const int c0 = cons.s * it.cps, c1 = min(c0 + it.cps, it.chunks);
-            const uint4* sa = my_ring + (size_t)slot * (kSStageBytes / 16);
-            const uint4* sb = sa + (size_t)(c1 - c0) * kRowsPerGroup;
-            if (cons.s == 0) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc_a[c] = acc_b[c] = 0;
-            }
-#pragma unroll 2
-            for (int j = c0 + h; j < c1; j += 2) {
-                const int4* xp = reinterpret_cast<const int4*>(xrow + (size_t)j * 64);
-                chunk_dot(sa[(j - c0) * kRowsPerGroup + r], xp, acc_a);
-                if (it.nm == 2) chunk_dot(sb[(j - c0) * kRowsPerGroup + r], xp, acc_b);
-            }
-            const bool last = cons.s == it.sub - 1;
-            ++consumed;
-            advance(cons);
-            // hand the slot back: everyone has read it; then one lane requests the stage kSRing ahead
-            __syncwarp();
-            if (lane == 0 && prod.item < p.n) {
-                issue(prod, slot);
-                advance(prod);
-                ++issued;
-            }
-            if (last) {
-                int va = acc_a[0] + (acc_a[1] >> 2) + (acc_a[2] >> 4) + (acc_a[3] >> 6);
-                va += __shfl_down_sync(0xffffffffu, va, 16);
-                int vb = 0;
-                if (it.nm == 2) {
-                    vb = acc_b[0] + (acc_b[1] >> 2) + (acc_b[2] >> 4) + (acc_b[3] >> 6);
-                    vb += __shfl_down_sync(0xffffffffu, vb, 16);
-                }
-                const int n = g * kRowsPerGroup + r;
-                if (h == 0 && n < it.N) {
-                    va -= sx;
-                    if (it.acc[0]) it.acc[0][n] = va;
-                    const float ya = __fmul_rn((float)va, __fmul_rn(xscale, it.ws[0]));
-                    if (it.nm == 2) {
-                        vb -= sx;
-                        if (it.acc[1]) it.acc[1][n] = vb;
-                        const float yb = __fmul_rn((float)vb, __fmul_rn(xscale, it.ws[1]));
-                        if (it.epilogue == LSPK_EPI_SILU_MUL) {
-                            it.out[n] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
-                        } else {
-                            const float gpos = fmaxf(ya, 0.0f);
-                            it.out[n] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
-                        }
-                    } else if (it.epilogue == LSPK_EPI_ADD) {
-                        it.out[n] = __fadd_rn(it.out[n], ya);
-                    } else {
-                        it.out[n] = ya;
+                if (!__all_sync(0xffffffffu, arrived)) {
+                    dead = true;
+                    if (lane == 0) {
+                        s_abort = 1;
+                        if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
                     }
+                    break;
+                }
+                const int c0 = s * it.cps, c1 = min(c0 + it.cps, it.chunks);
+                const uint4* sa = ring + (size_t)slot * (kSStageBytes / 16);
+                const uint4* sb = sa + (size_t)(c1 - c0) * kRowsPerGroup;
+#pragma unroll 2
+                for (int j = c0 + h; j < (skip ? 0 : c1); j += 2) {
+                    const int4* xp = reinterpret_cast<const int4*>(xrow + (size_t)j * 64);
+                    chunk_dot(sa[(j - c0) * kRowsPerGroup + r], xp, acc_a);
+                    if (it.nm == 2) chunk_dot(sb[(j - c0) * kRowsPerGroup + r], xp, acc_b);
+                }
+                // hand the slot back to the producer: every lane has read it
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+            }
+            if (dead || skip) continue;
+            int va = acc_a[0] + (acc_a[1] >> 2) + (acc_a[2] >> 4) + (acc_a[3] >> 6);
+            va += __shfl_down_sync(0xffffffffu, va, 16);
+            int vb = 0;
+            if (it.nm == 2) {
+                vb = acc_b[0] + (acc_b[1] >> 2) + (acc_b[2] >> 4) + (acc_b[3] >> 6);
+                vb += __shfl_down_sync(0xffffffffu, vb, 16);
+            }
+            const int n = g * kRowsPerGroup + r;
+            if (h == 0 && n < it.N) {
+                va -= sx;
+                if (it.acc[0]) it.acc[0][n] = va;
+                const float ya = __fmul_rn((float)va, __fmul_rn(xscale, it.ws[0]));
+                if (it.nm == 2) {
+                    vb -= sx;
+                    if (it.acc[1]) it.acc[1][n] = vb;
+                    const float yb = __fmul_rn((float)vb, __fmul_rn(xscale, it.ws[1]));
+                    if (it.epilogue == LSPK_EPI_SILU_MUL) {
+                        it.out[n] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
+                    } else {
+                        const float gpos = fmaxf(ya, 0.0f);
+                        it.out[n] = __fmul_rn(__fmul_rn(gpos, gpos), yb);
+                    }
+                } else if (it.epilogue == LSPK_EPI_ADD) {
+                    it.out[n] = __fadd_rn(it.out[n], ya);
+                } else {
+                    it.out[n] = ya;
                 }
             }
-            // lane 0 advanced the producer cursor: share it
-            prod.item = __shfl_sync(0xffffffffu, prod.item, 0);
-            prod.unit = __shfl_sync(0xffffffffu, prod.unit, 0);
-            prod.s = __shfl_sync(0xffffffffu, prod.s, 0);
-            issued = __shfl_sync(0xffffffffu, issued, 0);
         }
         if (i < i_hi) install_x(i + 1);
-        __syncthreads();
-        if (*(volatile int*)&s_abort) dead = true;
-    }
-    // A warp that stopped early may still have copies in flight into its ring: give each one bounded wait so that
-    // nothing lands in shared memory after the CTA has gone.
-    if (dead && lane == 0) {
-        for (int k = consumed; k < issued; ++k) {
-            const int slot = k % kSRing;
-            const uint32_t parity = (uint32_t)(k / kSRing) & 1u;
-            for (unsigned spin = 0; spin < kSSpinLimit && !mbar_try_wait(&bars[warp][slot], parity); ++spin) {}
-        }
+        consumer_barrier();
+        // After an abort elsewhere in the CTA this warp still waits for (and releases) every stage requested for it,
+        // so that no copy lands in shared memory after the CTA has gone; it only stops computing.
+        if (*(volatile int*)&s_abort) skip = true;
     }
 }
 
-static size_t stream_smem_bytes() { return (size_t)kSWarps * kSRing * kSStageBytes + 2 * (size_t)kSMaxKp; }
+static size_t stream_smem_bytes() { return (size_t)kSSlots * kSStageBytes + 2 * (size_t)kSMaxKp; }
 
 }  // namespace lspk
 
@@ -282,7 +297,7 @@ extern "C" int lspk_linear_batch(const lspk_linear_args* args, int n) {
     static StreamParams p;                        // 10 KB: kept off the stack; calls are serialised by the caller
     p.n = n;
     p.error_flag = device_wait_flag();
-    int unit0 = 0;
+    int unit0 = 0, q0 = 0;
     for (int i = 0; i < n; ++i) {
         const lspk_linear_args& a = args[i];
         const bool pair = a.epilogue == LSPK_EPI_RELU2_MUL || a.epilogue == LSPK_EPI_SILU_MUL;
@@ -318,9 +333,11 @@ extern "C" int lspk_linear_batch(const lspk_linear_args* args, int n) {
         it.groups = w0->groups;
         it.epilogue = a.epilogue;
         it.unit0 = unit0;
+        it.q0 = q0;
         it.cps = kSStageChunks / it.nm;
         it.sub = (it.chunks + it.cps - 1) / it.cps;
         unit0 += it.groups;
+        q0 += it.groups * it.sub;
     }
     p.total_units = unit0;
     static bool attr_set = false;
@@ -329,8 +346,8 @@ extern "C" int lspk_linear_batch(const lspk_linear_args* args, int n) {
         LSPK_CUDA(cudaFuncSetAttribute(ternary_gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set = true;
     }
-    int ctas = (unit0 + kSWarps - 1) / kSWarps;
+    int ctas = (unit0 + kSConsumers - 1) / kSConsumers;
     if (ctas > sm_count()) ctas = sm_count();
-    LSPK_CUDA(launch(ternary_gemv_stream_kernel, dim3(ctas), dim3(kSWarps * 32), smem, true, p));
+    LSPK_CUDA(launch(ternary_gemv_stream_kernel, dim3(ctas), dim3(kSThreads), smem, true, p));
     return LSPK_OK;
 }

@@ -30,6 +30,14 @@ SIGNATURES = {
     "lspk_tp_world": ([], _ci),
     "lspk_tp_allgather_f32": ([_vp, _vp, _sz], _ci),
     "lspk_tp_finalize": ([], _ci),
+    "lspk_tp_window_create": ([_ci, _ci, _ci, _ci, _vp], _ci),
+    "lspk_tp_window_open": ([_ci, _vp], _ci),
+    "lspk_tp_window_close": ([], _ci),
+    "lspk_tp_window_set_poll_limit": ([ctypes.c_uint], _ci),
+    "lspk_tp_window_vector": ([_ci], _vp),
+    "lspk_tp_debug_drop_next_arrival": ([], _ci),
+    "lspk_tp_exchange": ([_vp, _ci], _ci),
+    "lspk_tp_mlp_block_peer": ([_vp, _vp, _vp, _vp, _vp, _vp, _cf, _vp, _vp], _ci),
     "lspk_tp_mlp_block": ([_vp, _vp, _vp, _vp, _vp, _vp, _cf, _vp, _vp, _vp, _vp], _ci),
 }
 
@@ -92,5 +100,36 @@ class DeviceTP:
         _k.check(self.lib.lspk_tp_mlp_block(gate_r.handle, up_r.handle, down_r.handle, x.ptr, norm.ptr, sub_norm.ptr,
                                             eps, inter_slice.ptr, inter_full.ptr, down_slice.ptr, y_full.ptr))
 
+    # ---- exchange over peer memory (CUDA IPC windows) instead of NCCL -------------------------------------------
+    def create_window(self, I: int, H: int) -> bytes:
+        """Allocate this rank's window for gathered vectors of I and H floats; returns its 64-byte IPC handle,
+        which the caller passes to every other rank (any host channel)."""
+        buf = ctypes.create_string_buffer(64)
+        _k.check(self.lib.lspk_tp_window_create(self.rank, self.world, I, H, buf))
+        self._window = (I, H)
+        return buf.raw
+
+    def open_windows(self, handles) -> None:
+        """handles[r] = the 64-byte handle rank r created (this rank's own entry is ignored)."""
+        for r, h in enumerate(handles):
+            if r != self.rank:
+                _k.check(self.lib.lspk_tp_window_open(r, ctypes.create_string_buffer(bytes(h), 64)))
+
+    def mlp_block_peer(self, gate_r, up_r, down_r, x, norm, sub_norm, eps, inter_slice, down_slice) -> np.ndarray:
+        """The row-split MLP block with both gathers through the windows; returns the gathered down product."""
+        _k.check(self.lib.lspk_tp_mlp_block_peer(gate_r.handle, up_r.handle, down_r.handle, x.ptr, norm.ptr, sub_norm.ptr,
+                                                 eps, inter_slice.ptr, down_slice.ptr))
+        return self.window_vector(1)
+
+    def window_vector(self, which: int) -> np.ndarray:
+        n = self._window[which]
+        out = np.empty(n, np.float32)
+        _k.check(self.lib.lspk_d2h(out.ctypes.data, self.lib.lspk_tp_window_vector(which), out.nbytes))
+        return out
+
+    def close_window(self) -> None:
+        self.lib.lspk_tp_window_close()
+
     def close(self):
+        self.lib.lspk_tp_window_close()
         self.lib.lspk_tp_finalize()

@@ -1,6 +1,7 @@
-"""Two-GPU check of the tensor-parallel MLP block: NCCL all-gather of row slices must give, on every
-rank, exactly the unsplit product.  Needs two GPUs; skipped otherwise.  Runs as two child processes
-(one per GPU) that meet through an NCCL id passed in a file."""
+"""Tensor-parallel MLP block.  On two GPUs (two child processes that meet through files): the row slices gathered
+by NCCL, and then by plain stores into CUDA-IPC peer windows, must give on every rank exactly the unsplit
+product.  On one GPU: the bounded wait of the peer exchange, made to run out (a one-rank group told to expect
+a second rank that does not exist), reports an error code and leaves the library usable; nothing hangs."""
 import os
 import subprocess
 import sys
@@ -58,6 +59,27 @@ want = dev.DeviceArray((1, 2560), np.float32)
 dev.linear([W(down)], [want], 1, x_f32=inter, gamma=ds)
 assert np.array_equal(i_f.numpy(), inter.numpy()), "gathered gate/up slice differs"
 assert np.array_equal(got, want.numpy()), "gathered down slice differs"
+
+# the same block with both gathers through peer windows (CUDA IPC, plain stores, bounded waits): handles travel by file
+handle = group.create_window(6912, 2560)
+hfile = idfile + ".win%d" % rank
+with open(hfile + ".tmp", "wb") as f:
+    f.write(handle)
+os.replace(hfile + ".tmp", hfile)
+handles = []
+for r in range(world):
+    other = idfile + ".win%d" % r
+    for _ in range(600):
+        if os.path.exists(other):
+            break
+        time.sleep(0.05)
+    handles.append(open(other, "rb").read())
+group.open_windows(handles)
+for _ in range(3):          # several exchanges: the counters only grow, epochs must keep matching
+    got_peer = group.mlp_block_peer(g_r, u_r, d_r, dx, dn, ds, 1e-5, i_s, d_s)
+    assert np.array_equal(got_peer, want.numpy().reshape(-1)), "peer-window result differs from the unsplit block"
+    assert np.array_equal(group.window_vector(0), inter.numpy().reshape(-1)), "gathered gate product differs"
+assert K.load_library(True).lspk_tc_check_error() == 0
 group.close()
 print("rank", rank, "ok")
 '''
@@ -96,3 +118,45 @@ def test_tp_mlp_block_two_gpus(tmp_path):
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{o[-3000:]}"
         assert f"rank {r} ok" in o
+
+
+def test_peer_wait_runs_out_and_reports():
+    """The failure path of the peer exchange without a failing GPU: a window that expects two ranks' arrivals is
+    created by a process that is alone, so nobody ever supplies rank 1's share.  The wait kernel gives up after
+    its poll limit, the library's wait flag turns into LSPK_ERR_DEVICE_WAIT exactly once, the stream keeps
+    working, and an exchange of a complete (one-rank) group afterwards succeeds."""
+    import ctypes
+    import importlib
+    import numpy as np
+    K = importlib.import_module("litespark_inference_b200.torchless.kernel")
+    dev = importlib.import_module("litespark_inference_b200.torchless.device")
+    tp = importlib.import_module("litespark_inference_b200.torchless.tp")
+    lib = tp._lib()
+    assert lib.lspk_tc_check_error() == 0
+    buf = ctypes.create_string_buffer(64)
+    sl = dev.DeviceArray.from_numpy(np.arange(32, dtype=np.float32))
+    # a group of two whose second window was never mapped: the exchange refuses before launching anything
+    K.check(lib.lspk_tp_window_create(0, 2, 64, 32, buf))
+    lib.lspk_clear_error()
+    assert lib.lspk_tp_exchange(sl.ptr, 0) == 1 and b"has not been opened" in lib.lspk_last_error()
+    lib.lspk_clear_error()
+    K.check(lib.lspk_tp_window_close())
+    # a slice that never arrives: the test hook drops the store side of the next exchange, so its wait polls a
+    # counter that nothing advances
+    K.check(lib.lspk_tp_window_create(0, 1, 64, 32, buf))
+    K.check(lib.lspk_tp_window_set_poll_limit(2000))
+    K.check(lib.lspk_tp_debug_drop_next_arrival())
+    K.check(lib.lspk_tp_exchange(sl.ptr, 1))
+    assert lib.lspk_tc_check_error() == 6                               # LSPK_ERR_DEVICE_WAIT, reported once
+    lib.lspk_clear_error()
+    assert lib.lspk_tc_check_error() == 0
+    # The lost slice leaves the counter one exchange behind for good, as a lost rank would: a fresh window works.
+    K.check(lib.lspk_tp_window_close())
+    K.check(lib.lspk_tp_window_create(0, 1, 64, 32, buf))
+    full = dev.DeviceArray.from_numpy(np.arange(64, dtype=np.float32) * 0.5)
+    K.check(lib.lspk_tp_exchange(full.ptr, 0))
+    out = np.empty(64, np.float32)
+    K.check(lib.lspk_d2h(out.ctypes.data, lib.lspk_tp_window_vector(0), out.nbytes))
+    assert np.array_equal(out, np.arange(64, dtype=np.float32) * 0.5)
+    assert lib.lspk_tc_check_error() == 0
+    K.check(lib.lspk_tp_window_close())
