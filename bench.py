@@ -358,14 +358,14 @@ def time_linear_batch(lib, K, dev, gate_handles, up_handles, x_f32, N, reps, per
     return 1000.0 * float(ms.value) / (reps * n)
 
 
-def measure_shape(lib, dev, K, synthetic, rng, peak, name, Ms):
+def measure_shape(lib, dev, K, synthetic, rng, peak, name, Ms, copies_mb=300.0):
     """One BitNet-2B projection shape at the token counts Ms: fused-quantiser linear launches rotated over
     enough device copies of the matrix to exceed the L2 (about 300 MB), as a dependency chain; for one token
     row also as independent graph nodes, in both scheduling modes of the GEMV."""
     rows = []
     N, Kd = synthetic.BITNET_2B_SHAPES[name]
     proj = synthetic.random_projection_fast(rng, N, Kd)
-    n_copies = max(2, int(np.ceil(300e6 / (N * Kd / 4))))
+    n_copies = max(2, int(np.ceil(copies_mb * 1e6 / (N * Kd / 4))))
     copies = [dev.DeviceWeight(proj.w_packed, proj.scale) for _ in range(n_copies)]
     handles = (ctypes.c_void_p * n_copies)(*[c.handle for c in copies])
     for M in Ms:
@@ -416,8 +416,10 @@ def run_sweep(args):
     peak, peak_kind = load_peaks()
     rng = np.random.default_rng(0)
     rows = []
-    for name in ("q", "k", "gate", "down"):
-        rows += measure_shape(lib, dev, K, synthetic, rng, peak, name, (1, 8, 32, 128, 512))
+    shapes = [t for t in args.sweep_shapes.split(",") if t]
+    ms = tuple(int(t) for t in args.sweep_m.split(",") if t)
+    for name in shapes:
+        rows += measure_shape(lib, dev, K, synthetic, rng, peak, name, ms, args.sweep_mb)
     print(json.dumps({"workload": "sweep", "peak_GBps": peak, "peak_kind": peak_kind, "rows": rows}))
 
 
@@ -470,10 +472,12 @@ def run_probes(args):
         for grid in (160, 240, 296):
             K.check(lib.lspk_bench_handoff(grid, 2000, mode, ctypes.byref(us), ctypes.byref(cyc)))
             out[f"persistent_{name}_grid{grid}"] = {"us_per_round": us.value, "sm_cycles_per_round": cyc.value}
-    for cs, nc, stages in ((1, 1, 2000), (16, 1, 2000), (16, 9, 400), (1, 148, 400)):
-        K.check(lib.lspk_bench_cluster(cs, nc, stages, 1, 1, 0, ctypes.byref(ms)))
-        gb = cs * nc * stages * 16384 / 1e9
-        out[f"stream_{nc}_clusters_of_{cs}"] = {"GBps_total": gb / (ms.value / 1e3), "GBps_per_sm": gb / (ms.value / 1e3) / (cs * nc)}
+    for issuers, mode in ((1, 0), (4, 4)):          # one requesting thread per CTA, or four warps a quarter of a stage each
+        for cs, nc, stages in ((1, 1, 2000), (16, 1, 2000), (16, 9, 400), (1, 148, 400)):
+            K.check(lib.lspk_bench_cluster(cs, nc, stages, 1, 1, mode, ctypes.byref(ms)))
+            gb = cs * nc * stages * 16384 / 1e9
+            out[f"stream_{nc}_clusters_of_{cs}_{issuers}_issuers"] = {"GBps_total": gb / (ms.value / 1e3),
+                                                                       "GBps_per_sm": gb / (ms.value / 1e3) / (cs * nc)}
     for cs in (2, 4, 8, 16):
         K.check(lib.lspk_bench_cluster(cs, 1, 1, 2000, 1, 1, ctypes.byref(ms)))
         out[f"cluster_exchange_{cs}_ctas_us"] = 1000.0 * ms.value / 2000
@@ -528,6 +532,11 @@ def main():
                     help="tg128: the headline line; sweep: per-shape x token-count table of the ternary linear "
                          "kernels; gemv: the single 6912x2560 GEMV; hybrid: Mamba-2 + MoE decode (extra lines, "
                          "not the headline)")
+    ap.add_argument("--sweep-shapes", default="q,k,gate,down", help="projection shapes of --workload sweep")
+    ap.add_argument("--sweep-m", default="1,8,32,128,512", help="token counts of --workload sweep")
+    ap.add_argument("--sweep-mb", type=float, default=300.0,
+                    help="megabytes of device copies a shape is rotated over (more than the L2 by default; "
+                         "smaller for profiler captures)")
     ap.add_argument("--seqs-per-gpu", type=int, default=8, help="batch of the extra data-parallel measurement")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="shorter prompt for profiler captures")
     ap.add_argument("--gen-len", type=int, default=GEN_LEN, help="fewer decode steps for profiler captures")
@@ -811,7 +820,7 @@ def main():
                      "peak_kind": f"of {peak_kind}",
                      # dram read + write per launch from the ncu capture summarised in
                      # profiles/ternary_linear_kernel_m1_bitnet2b.md (mean of the four launches of a layer)
-                     "traffic": (2514432 + 1705472 + 8908032 + 4539648) / 4.0,
+                     "traffic": (2514944 + 1706240 + 8908800 + 4540416) / 4.0,
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch,
                      "launches_timed": n_launch.value * reps,
                      "how": "CUDA events around graph replays of the 120 linear launches of one token over all 30 layers' weights (521 MB, > L2)"},

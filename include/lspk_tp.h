@@ -27,19 +27,20 @@ int lspk_tp_mlp_block(lspk_weight_t gate_r, lspk_weight_t up_r, lspk_weight_t do
                       const void* norm_gamma_bf16, const void* sub_norm_gamma_bf16, float eps, float* inter_slice,
                       float* inter_full, float* down_slice, float* y_full);
 
-/* The same exchange over peer memory (csrc/tp_peer.cu): every rank creates one window (a device buffer holding the
- * gathered gate product [I], the gathered down product [H] and arrival counters), hands its 64-byte CUDA IPC
- * handle to the other ranks of the node by any host channel, and opens theirs.  lspk_tp_exchange stores this
- * rank's slice (which = 0: I / world floats of the gate product, 1: H / world floats of the down product) into
- * every window with plain stores, then waits, with a bound, until every rank's slice has arrived in its own.
- * When the bound runs out the library's wait flag is raised (lspk_tc_check_error returns LSPK_ERR_DEVICE_WAIT)
- * and the stream carries on: a rank that never arrives costs an error code, not a hang. */
+/* The same exchange over peer memory (csrc/tp_peer.cu): every rank creates one window (a device buffer holding
+ * the gathered gate product [I] and the gathered down product [H] as 64-bit packets, value | exchange number),
+ * hands its 64-byte CUDA IPC handle to the other ranks of the node by any host channel, and opens theirs.
+ * lspk_tp_exchange stores this rank's slice (which = 0: I / world floats of the gate product, 1: H / world floats
+ * of the down product) into every window, one 8-byte store per element, then polls, with a bound, the packets of
+ * its own window until every rank's slice of this exchange is there and writes the plain fp32 vector.  When the
+ * bound runs out the library's wait flag is raised (lspk_tc_check_error returns LSPK_ERR_DEVICE_WAIT) and the
+ * stream carries on: a rank that never arrives costs an error code, not a hang. */
 int lspk_tp_window_create(int rank, int world, int I, int H, void* ipc_handle64_out);
 int lspk_tp_window_open(int rank, const void* ipc_handle64);
 int lspk_tp_window_close(void);
-int lspk_tp_window_set_poll_limit(unsigned polls);          /* polls of the arrival counter before a wait gives up */
+int lspk_tp_window_set_poll_limit(unsigned polls);          /* loads of a packet before the wait for it gives up */
 /* Test aid for the bounded wait: the next lspk_tp_exchange stores nothing, as if this rank's peers were gone, so
- * its wait polls a counter that nothing advances, gives up and raises the wait flag.  Nothing faults. */
+ * its wait polls packets that nothing renews, gives up and raises the wait flag.  Nothing faults. */
 int lspk_tp_debug_drop_next_arrival(void);
 const float* lspk_tp_window_vector(int which);              /* device pointer of a gathered vector in the local window */
 int lspk_tp_exchange(const float* slice_dev, int which);

@@ -385,8 +385,11 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
 // shared memory, the cache rows are written by the CTA that owns position `pos` (head h % G == 0).
 constexpr int kSplit = 8;
 
-template <typename KVT, int D>
-__global__ void __launch_bounds__(kAttnThreads) attention_split_kernel(const AttnParams p) {
+// MINB: CTAs per SM the register budget is held to.  Launches over several sequences have far more clusters than
+// the machine holds at once, so their instantiation trades registers for a fourth resident CTA; the arithmetic
+// (and so every result bit) is the same in both.
+template <typename KVT, int D, int MINB = 1>
+__global__ void __launch_bounds__(kAttnThreads, MINB) attention_split_kernel(const AttnParams p) {
     namespace cg = cooperative_groups;
     constexpr int VEC = KvVec<KVT>::N;
     constexpr int NCH = D / VEC;
@@ -905,6 +908,7 @@ static int attention_launch_t(const AttnParams& p) {
         if (!split_attr_set) {
             LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             split_attr_set = true;
         }
@@ -912,6 +916,7 @@ static int attention_launch_t(const AttnParams& p) {
         const dim3 sgrid(p.Q, p.T, kSplit), cl(1, 1, kSplit);
         cudaError_t se;
         if (D == 64) se = launch_cluster(attention_split_kernel<KVT, 64>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
+        else if (D == 128 && p.T >= 4) se = launch_cluster(attention_split_kernel<KVT, 128, 4>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
         else if (D == 128) se = launch_cluster(attention_split_kernel<KVT, 128>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
         else se = launch_cluster(attention_split_kernel<KVT, 256>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
         if (se != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention (split) launch failed: %s", cudaGetErrorString(se));

@@ -223,6 +223,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 // mode 0: stream `stages_per_cta` stages of 16 KB per CTA through the ring, no exchange
 // mode 1: `rounds` exchanges of a 2560-float vector (slices by rank), no streaming
 // mode 2: both: an exchange after every `stages_per_round` stages
+// + 4: every stage is requested as four 4 KB copies by lane 0 of four warps instead of one 16 KB copy by one thread
 __global__ void __launch_bounds__(256, 1)
 cluster_probe_kernel(const unsigned char* __restrict__ src, size_t src_bytes, int stages_per_cta, int rounds,
                      int stages_per_round, int mode, int* error_word, float* sink) {
@@ -234,22 +235,26 @@ cluster_probe_kernel(const unsigned char* __restrict__ src, size_t src_bytes, in
     const int tid = threadIdx.x;
     const uint32_t rank = cluster_ctarank(), nrank = cluster_nctarank();
     const size_t cta_lin = blockIdx.x;
+    const int issuers = (mode & 4) ? 4 : 1;
+    mode &= 3;
     if (tid == 0) {
         s_fail = 0;
-        for (int s = 0; s < kCpStages; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < kCpStages; ++s) mbar_init(&bars[s], issuers);
         fence_mbar_init();
     }
     __syncthreads();
     cluster_sync_all();                                              // every CTA of the cluster has started
     const int n_stages = mode == 1 ? 0 : stages_per_cta;
     const size_t base = (cta_lin * (size_t)stages_per_cta * kCpStage) % (src_bytes - (size_t)stages_per_cta * kCpStage);
-    auto issue = [&](int k) {
+    auto issue = [&](int k, int part) {                                // part: which of `issuers` equal pieces
         const int s = k % kCpStages;
-        mbar_expect_tx(&bars[s], kCpStage);
-        bulk_load_stream(ring + (size_t)s * kCpStage, src + ((base + (size_t)k * kCpStage) & ~(size_t)15), kCpStage, &bars[s]);
+        const uint32_t bytes = kCpStage / issuers;
+        mbar_expect_tx(&bars[s], bytes);
+        bulk_load_stream(ring + (size_t)s * kCpStage + (size_t)part * bytes,
+                         src + ((base + (size_t)k * kCpStage) & ~(size_t)15) + (size_t)part * bytes, bytes, &bars[s]);
     };
-    if (tid == 0)
-        for (int k = 0; k < kCpStages && k < n_stages; ++k) issue(k);
+    if ((tid & 31) == 0 && (tid >> 5) < issuers)
+        for (int k = 0; k < kCpStages && k < n_stages; ++k) issue(k, tid >> 5);
     float acc = 0.0f;
     int done_rounds = 0;
     const int slice = 2560 / (int)nrank;                              // floats of the vector this CTA produces
@@ -283,7 +288,7 @@ cluster_probe_kernel(const unsigned char* __restrict__ src, size_t src_bytes, in
         }
         __syncthreads();
         if (s_fail) break;
-        if (tid == 0 && k + kCpStages < n_stages) issue(k + kCpStages);
+        if ((tid & 31) == 0 && (tid >> 5) < issuers && k + kCpStages < n_stages) issue(k + kCpStages, tid >> 5);
         if (mode == 2 && (k + 1) % stages_per_round == 0) exchange();
     }
     if (mode == 1)
@@ -303,7 +308,7 @@ extern "C" int lspk_bench_cluster(int cluster_size, int n_clusters, int stages_p
                                   int mode, float* ms_out) {
     if (int rc = ensure_init()) return rc;
     LSPK_REQUIRE((cluster_size == 1 || cluster_size == 2 || cluster_size == 4 || cluster_size == 8 || cluster_size == 16) &&
-                     n_clusters >= 1 && cluster_size * n_clusters <= sm_count() && mode >= 0 && mode <= 2 && ms_out &&
+                     n_clusters >= 1 && cluster_size * n_clusters <= sm_count() && mode >= 0 && (mode & 3) <= 2 && mode <= 6 && ms_out &&
                      stages_per_cta >= 1 && stages_per_cta <= 65536 && rounds >= 1 && stages_per_round >= 1,
                  "lspk_bench_cluster: bad arguments");
     const size_t src_bytes = 1ull << 30;

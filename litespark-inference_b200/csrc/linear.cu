@@ -559,6 +559,7 @@ int linear_cuda_core(const lspk_linear_args* a) {
     p.xscale_out = a->xscale_out;
     p.trace = trace_buffer();
     p.trace_cap = trace_capacity();
+    p.error_flag = device_wait_flag();
     switch (a->prologue) {
         case kProInt8Tiled:                      // set above, never by a caller
             LSPK_REQUIRE(tiled_sums != nullptr, "linear: unknown prologue %d", a->prologue);

@@ -45,7 +45,15 @@ __device__ __forceinline__ void mma_u8s8(int c[4], uint32_t a0, uint32_t a1, uin
 // per-lane register loads.  For launches that stream tens of megabytes (the expert-grouped MoE products): the
 // bytes in flight per SM then do not depend on registers or on where the CTA is in its reduction.
 constexpr int kMBulkStages = 4;
+constexpr int kMIssuers = 4;                          // warps whose lane 0 requests a quarter of each stage
 constexpr unsigned kMBulkSpinLimit = 1u << 22;
+// Pre-tiled int8 rows (the row quantiser's output, already in the tile's layout) arrive by bulk copies in
+// segments of 16 chunks along K, one mbarrier per segment, so the MMAs of the first segment start while the
+// later ones are still on their way; every wait on a segment ends at a clock deadline.
+constexpr int kMXSegChunks = 16;                     // chunks per segment = what the 8 warps consume per step
+constexpr int kMXSegMax = 24;                        // covers K up to 24576
+constexpr long long kMXWaitCycles = 1ll << 31;
+static_assert(kMWarps == kMT && kMXSegMax <= 32, "row staging maps warp -> row and lane -> segment");
 
 template <bool PAIR, bool GROUPED, bool BULK>
 __global__ void __launch_bounds__(kMThreads)
@@ -124,6 +132,18 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
     tr.begin(p.trace, p.trace_cap, 3);
     tr.mark();                                          // 0: entry
     if (!GROUPED && !BULK) load_batch(s0, g0, 0, wa, wb);       // weights never depend on the previous kernel
+    __shared__ __align__(8) uint64_t xbars[kMXSegMax];
+    const int nxseg = (p.chunks + kMXSegChunks - 1) / kMXSegChunks;
+    // CTA-uniform: a full tile of pre-tiled rows, one token tile per CTA
+    const bool x_async = !GROUPED && !BULK && p.prologue == kProInt8Tiled && nxseg <= kMXSegMax &&
+                         p.M - (int)blockIdx.y * kMT >= kMT;
+    if (x_async) {
+        if (tid < nxseg) {
+            mbar_init(&xbars[tid], kMT);
+            fence_mbar_init();
+        }
+        __syncthreads();
+    }
     grid_dependency_launch();
     grid_dependency_wait();
     tr.mark();                                          // 1: predecessor finished
@@ -138,25 +158,32 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
     const int tile_step = (int)gridDim.y * kMT;
     const int ntile_cta = M_eff > (int)blockIdx.y * kMT ? (M_eff - 1 - (int)blockIdx.y * kMT) / tile_step + 1 : 0;
     const int total_it = BULK ? ngrp_cta * ntile_cta : 0;
-    auto issue_it = [&](int it_) {                     // one thread: request sequence element it_ into its stage
+    // Request part `part` (of kMIssuers equal pieces) of sequence element it_ into its stage.  The pieces of a stage
+    // are requested by different warps: one thread gets a bulk copy out only every few hundred cycles, which would
+    // otherwise sit on the CTA's critical path once per row group.
+    auto issue_it = [&](int it_, int part) {
         int ss, gg;
         locate((int)blockIdx.x + (it_ % ngrp_cta) * (int)gridDim.x, ss, gg);
         const int st = it_ % p.bulk_stages;
-        uint32_t* dst = ring + (size_t)st * stage_words;
-        const uint32_t bytes = (uint32_t)grp_words * 4u;
+        const uint32_t bytes = (uint32_t)grp_words * 4u / kMIssuers;             // chunks * 64: a multiple of 16
+        uint32_t* dst = ring + (size_t)st * stage_words + (size_t)part * (bytes / 4u);
         mbar_expect_tx(&bars[st], bytes * (PAIR ? 2u : 1u));
-        const uint4* src_a = p.seg[ss].w + w_off + (size_t)gg * p.chunks * kRowsPerGroup;
+        const uint4* src_a = p.seg[ss].w + w_off + (size_t)gg * p.chunks * kRowsPerGroup + (size_t)part * (bytes / 16u);
         bulk_load_stream(dst, src_a, bytes, &bars[st]);
-        if (PAIR) bulk_load_stream(dst + grp_words, p.seg[1].w + w_off + (size_t)gg * p.chunks * kRowsPerGroup, bytes, &bars[st]);
+        if (PAIR)
+            bulk_load_stream(dst + grp_words,
+                             p.seg[1].w + w_off + (size_t)gg * p.chunks * kRowsPerGroup + (size_t)part * (bytes / 16u), bytes,
+                             &bars[st]);
     };
     int it = 0;
     int wait_failed = 0;
     bool give_up = false;                              // CTA-uniform: a bounded wait ran out somewhere in the CTA
     if (BULK) {
         if (tid == 0) {
-            for (int st = 0; st < p.bulk_stages; ++st) mbar_init(&bars[st], 1);
+            for (int st = 0; st < p.bulk_stages; ++st) mbar_init(&bars[st], kMIssuers);
             fence_mbar_init();
-            for (int i = 0; i < p.bulk_stages && i < total_it; ++i) issue_it(i);
+            for (int i = 0; i < p.bulk_stages && i < total_it; ++i)
+                for (int part = 0; part < kMIssuers; ++part) issue_it(i, part);
         }
         // the barriers are used after the __syncthreads that follows the prologue of the first tile
     }
@@ -177,7 +204,21 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
         first_tile = false;
 
         // ---- prologue: the tile's rows -> permuted int8 rows in shared memory ------------------------------
-        if (p.prologue == kProInt8Tiled) {
+        if (x_async) {
+            // lane s of warp m requests segment s of row m (a contiguous run of the pre-tiled buffer): the eight
+            // warps issue side by side, a thread's own copies go out one after the other, nearest segment first
+            if (lane < nxseg) {
+                const int c0 = lane * kMXSegChunks;
+                const uint32_t bytes = (uint32_t)(min(p.chunks, c0 + kMXSegChunks) - c0) * 64u;
+                const size_t off = (size_t)warp * rs + (size_t)c0 * 64;            // kMWarps == kMT: warp = row
+                mbar_expect_tx(&xbars[lane], bytes);
+                bulk_load(xq + off, p.x_i8 + (size_t)m0 * rs + off, bytes, &xbars[lane]);
+            }
+            if (tid < kMT) {
+                s_scale[tid] = p.x_scales[m0 + tid];
+                s_sumx[tid] = p.x_sums[m0 + tid];
+            }
+        } else if (p.prologue == kProInt8Tiled) {
             // rows already permuted and spaced like the shared-memory tile: a plain 16-byte copy
             const int chunks_per_row = rs / 16;
             const uint4* src = reinterpret_cast<const uint4*>(p.x_i8 + (size_t)m0 * rs);
@@ -234,9 +275,11 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                 if (lane == 0) { s_scale[m] = p.x_scales[in_row(m)]; s_sumx[m] = sumx; }
             }
         }
-        tr.mark();                                                 // 2: rows staged
-        __syncthreads();
+        tr.mark();                                                 // 2: rows staged (or requested)
+        if (!x_async) __syncthreads();
         tr.mark();                                                 // 3: activations visible
+        bool x_pending = x_async;                                  // the first row group waits segment by segment
+        const long long x_deadline = x_async ? clock64() + kMXWaitCycles : 0;
 
         // ---- row groups of this CTA ---------------------------------------------------------------------
         while (true) {
@@ -296,6 +339,14 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                     const int pr = warp + kMWarps * (base + i);
                     if (pr < pairs) {
                         const int j0 = 2 * pr;
+                        if (x_pending) {                           // segment base+i holds chunks j0, j0+1
+                            while (!mbar_try_wait(&xbars[base + i], 0)) {
+                                if (clock64() > x_deadline) {
+                                    wait_failed = 1;
+                                    break;
+                                }
+                            }
+                        }
                         // four masks' B registers of chunk j0 and of chunk j0+1 (zeros past the last chunk)
                         const uint4 x0 = *reinterpret_cast<const uint4*>(xrow + (size_t)(4 * j0 + t4) * 16);
                         uint4 x1 = make_uint4(0, 0, 0, 0);
@@ -346,8 +397,20 @@ ternary_linear_mma_kernel(const __grid_constant__ LinearParams p) {
                     }
                     give_up = true;
                 } else {
-                    if (tid == 0 && it + p.bulk_stages < total_it) issue_it(it + p.bulk_stages);
+                    if (lane == 0 && warp < kMIssuers && it + p.bulk_stages < total_it) issue_it(it + p.bulk_stages, warp);
                     ++it;
+                }
+            } else if (x_pending) {
+                x_pending = false;
+                if (__syncthreads_or(wait_failed)) {
+                    // a segment never arrived: report, give the copies in flight one more bounded wait, leave
+                    if (tid == 0) {
+                        if (p.error_flag) atomicExch(p.error_flag, LSPK_ERR_DEVICE_WAIT);
+                        const long long dl = clock64() + kMXWaitCycles;
+                        for (int k = 0; k < nxseg; ++k)
+                            while (!mbar_try_wait(&xbars[k], 0) && clock64() <= dl) {}
+                    }
+                    give_up = true;
                 }
             } else {
                 __syncthreads();

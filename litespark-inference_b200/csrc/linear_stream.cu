@@ -5,9 +5,9 @@
 // matmul_lut_avx512_extern_c.cpp:150-236).  On the GPU a launch per matrix pays a ramp every time: a 4.4 MB
 // matrix is 0.7 us of HBM time, shorter than the fill and drain of a kernel.  Here the whole list is one
 // stream of bytes: the row groups of all products form one flat sequence of units; every CTA of a persistent
-// grid (one per SM) takes a contiguous range of it.  One warp of the CTA does nothing but request the range's
-// stages, in order, into a ring of eighteen 10 KB slots in shared memory (cp.async.bulk + mbarrier, across product
-// boundaries); twelve consumer warps take the units round-robin, each computing its unit alone.  A range touches
+// grid (one per SM) takes a contiguous range of it.  Six warps of the CTA do nothing but request the range's
+// stages, in order (stage q by warp q % 6), into a ring of eighteen 10 KB slots in shared memory (cp.async.bulk +
+// mbarrier, across product boundaries); twelve consumer warps take the units round-robin, each computing its unit alone.  A range touches
 // one or two products, so a CTA installs one or two vectors.
 //
 //   unit   = 16 output rows of one product (both matrices of a gated gate/up pair), cut along K into stages of
@@ -25,8 +25,12 @@
 
 namespace lspk {
 
-constexpr int kSConsumers = 12;                  // warps that compute; one more warp only requests copies
-constexpr int kSThreads = 32 * (kSConsumers + 1);
+constexpr int kSConsumers = 12;                  // warps that compute
+// Warps that only request copies (one lane each; stage q belongs to warp q % kSProducers).  One thread gets a
+// bulk copy out every ~500 cycles, i.e. 20 bytes per cycle and SM with 10 KB stages: measured on the gate shape,
+// 1 / 2 / 4 / 6 requesting warps reach 0.60 / 0.75 / 0.87 / 0.93 of the measured HBM copy rate.
+constexpr int kSProducers = 6;
+constexpr int kSThreads = 32 * (kSConsumers + kSProducers);
 constexpr int kSSlots = 18;                      // stages of the CTA's ring (shared by all consumer warps)
 constexpr int kSStageChunks = 40;                // 16-row x 16-byte chunks per stage (all matrices of a unit)
 constexpr int kSStageBytes = kSStageChunks * kRowsPerGroup * 16;   // 10240: 180 KB of ring per SM
@@ -56,7 +60,7 @@ struct StreamParams {
     int* error_flag;
 };
 
-__device__ __forceinline__ void consumer_barrier() {      // the consumer warps only (the producer warp never joins)
+__device__ __forceinline__ void consumer_barrier() {      // the consumer warps only (the requesting warps never join)
     asm volatile("bar.sync 1, %0;" ::"n"(32 * kSConsumers) : "memory");
 }
 
@@ -66,7 +70,7 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     uint4* ring = reinterpret_cast<uint4*>(smem_raw);                                   // [slots][stage]
     int8_t* xq = reinterpret_cast<int8_t*>(smem_raw + (size_t)kSSlots * kSStageBytes);  // [2][kSMaxKp]
     __shared__ __align__(8) uint64_t full[kSSlots], empty[kSSlots];
-    __shared__ int s_issued;                     // stages requested so far (written by the producer, read by consumers)
+    __shared__ int s_seq[kSSlots];               // 1 + the number of the last stage requested into each slot (0: none yet)
     __shared__ int s_sumx[2][kSConsumers];
     __shared__ float s_scale[2];
     __shared__ int s_abort;
@@ -90,8 +94,8 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     auto expired = [&]() { return clock64() > deadline || *(volatile int*)&s_abort != 0; };
     if (tid == 0) {
         s_abort = 0;
-        s_issued = 0;
         for (int s = 0; s < kSSlots; ++s) {
+            s_seq[s] = 0;
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -100,8 +104,9 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     __syncthreads();
     grid_dependency_launch();
 
-    if (warp == kSConsumers) {
-        // ---------------- producer: one thread requests the CTA's stages in order, as slots come free --------------
+    if (warp >= kSConsumers) {
+        const int pw = warp - kSConsumers;
+        // ---------------- producers: lane 0 of warp pw requests stages pw, pw + kSProducers, ... as slots come free --
         // (the weights do not depend on whatever ran before, so this starts at once)
         if (lane == 0 && i_hi >= i_lo) {
             uint64_t policy;
@@ -116,6 +121,7 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 const uint4* ub = nm == 2 ? it.w[1] + (size_t)g_first * chunks * kRowsPerGroup : nullptr;
                 for (int g = g_first; g < g_end && ok; ++g) {
                     for (int s = 0; s < sub; ++s, ++q) {
+                        if (q % kSProducers != pw) continue;
                         const int slot = q % kSSlots;
                         if (q >= kSSlots) {          // the slot's previous occupant has to be consumed first
                             const uint32_t parity = (uint32_t)(q / kSSlots - 1) & 1u;
@@ -138,7 +144,7 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                         // must not test a phase parity before the previous use of the slot has completed (the test
                         // would succeed at once on the stale phase); the release observed above implies that it has.
                         __threadfence_block();
-                        *(volatile int*)&s_issued = q + 1;
+                        *(volatile int*)&s_seq[slot] = q + 1;
                     }
                     ua += (size_t)chunks * kRowsPerGroup;
                     if (nm == 2) ub += (size_t)chunks * kRowsPerGroup;
@@ -220,8 +226,8 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 const int slot = q % kSSlots;
                 const uint32_t parity = (uint32_t)(q / kSSlots) & 1u;
                 // first the request (see the producer), then the data
-                bool arrived = *(volatile int*)&s_issued > q;
-                while (!arrived && !(clock64() > deadline)) arrived = *(volatile int*)&s_issued > q;
+                bool arrived = *(volatile int*)&s_seq[slot] > q;
+                while (!arrived && !(clock64() > deadline)) arrived = *(volatile int*)&s_seq[slot] > q;
                 if (arrived) {
                     arrived = mbar_try_wait(&full[slot], parity);
                     while (!arrived && !(clock64() > deadline)) arrived = mbar_try_wait(&full[slot], parity);
@@ -237,11 +243,21 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 const int c0 = s * it.cps, c1 = min(c0 + it.cps, it.chunks);
                 const uint4* sa = ring + (size_t)slot * (kSStageBytes / 16);
                 const uint4* sb = sa + (size_t)(c1 - c0) * kRowsPerGroup;
-#pragma unroll 2
-                for (int j = c0 + h; j < (skip ? 0 : c1); j += 2) {
-                    const int4* xp = reinterpret_cast<const int4*>(xrow + (size_t)j * 64);
-                    chunk_dot(sa[(j - c0) * kRowsPerGroup + r], xp, acc_a);
-                    if (it.nm == 2) chunk_dot(sb[(j - c0) * kRowsPerGroup + r], xp, acc_b);
+                // this half-warp's chunks c0 + h, c0 + h + 2, ...: constant strides from here on (32 uint4 of weights,
+                // 128 bytes of activations per step), so the unrolled loop addresses everything by immediates
+                const int nit = skip ? 0 : (c1 - c0 - h + 1) >> 1;
+                const uint4* wp = sa + h * kRowsPerGroup + r;
+                const int4* xp = reinterpret_cast<const int4*>(xrow + (size_t)(c0 + h) * 64);
+                if (it.nm == 2) {
+                    const uint4* wq = sb + h * kRowsPerGroup + r;
+#pragma unroll 4
+                    for (int t = 0; t < nit; ++t) {
+                        chunk_dot(wp[t * 2 * kRowsPerGroup], xp + t * 8, acc_a);
+                        chunk_dot(wq[t * 2 * kRowsPerGroup], xp + t * 8, acc_b);
+                    }
+                } else {
+#pragma unroll 4
+                    for (int t = 0; t < nit; ++t) chunk_dot(wp[t * 2 * kRowsPerGroup], xp + t * 8, acc_a);
                 }
                 // hand the slot back to the producer: every lane has read it
                 __syncwarp();

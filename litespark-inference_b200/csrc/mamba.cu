@@ -22,8 +22,6 @@ struct Mamba {
     uint16_t *norm = nullptr, *gnorm = nullptr;
     int cap_B = 0;
     float *zx = nullptr, *v = nullptr;      // [B][in_out], [B][d_inner]
-    int8_t* xq = nullptr;                   // [B][max(hidden, d_inner)] quantised rows (B > 1)
-    float* xs = nullptr;                    // [B] their scales
     size_t bytes = 0;
     size_t state_floats() const { return (size_t)conv_dim * 4 + (size_t)cfg.nheads * cfg.headdim * cfg.d_state; }
 };
@@ -124,16 +122,9 @@ int mamba_reserve(Mamba* m, int B) {
     if (B <= m->cap_B) return LSPK_OK;
     cudaFree(m->zx);
     cudaFree(m->v);
-    cudaFree(m->xq);
-    cudaFree(m->xs);
     m->zx = m->v = nullptr;
-    m->xq = nullptr;
-    m->xs = nullptr;
     m->cap_B = 0;
     scratch_moved();
-    const size_t qk = (size_t)(m->cfg.hidden > m->d_inner ? m->cfg.hidden : m->d_inner);
-    LSPK_CUDA(cudaMalloc((void**)&m->xq, (size_t)B * qk));
-    LSPK_CUDA(cudaMalloc((void**)&m->xs, (size_t)B * 4));
     LSPK_CUDA(cudaMalloc((void**)&m->zx, (size_t)B * m->in_out * 4));
     LSPK_CUDA(cudaMalloc((void**)&m->v, (size_t)B * m->d_inner * 4));
     m->bytes += (size_t)B * (m->in_out + m->d_inner) * 4;
@@ -155,7 +146,7 @@ int mamba_step(Mamba* m, float* x, float* state, const int* pos, int B) {
     a.gamma = m->norm;
     a.gamma_is_bf16 = 1;
     a.eps = m->cfg.eps;
-    if (int rc = split_row_prologue(&a, m->cfg.hidden, m->xq, m->xs)) return rc;
+    // several rows: linear_cuda_core quantises them once, straight into the eight-row kernel's tile layout
     if (int rc = linear_cuda_core(&a)) return rc;
     LSPK_CUDA(launch(mamba2_ssu_kernel, dim3(m->cfg.nheads * 2, B), dim3(256), 0, true, (const float*)m->zx, state, pos,
                      (const float*)m->conv_w, (const float*)m->conv_b, (const float*)m->A, (const float*)m->dt_bias,
@@ -171,7 +162,6 @@ int mamba_step(Mamba* m, float* x, float* state, const int* pos, int B) {
     o.gamma = m->gnorm;
     o.gamma_is_bf16 = 1;
     o.eps = m->cfg.eps;
-    if (int rc = split_row_prologue(&o, m->d_inner, m->xq, m->xs)) return rc;
     return linear_cuda_core(&o);
 }
 

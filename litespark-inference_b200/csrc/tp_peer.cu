@@ -2,17 +2,18 @@
 //
 // The NCCL all-gather of tp.cu moves 27.6 KB and 10.2 KB per MLP block: pure latency (a collective launch per
 // message).  Here every rank owns a WINDOW -- one device buffer that all other ranks of the node map through
-// CUDA IPC -- holding the two gathered vectors and two arrival counters.  After a projection a small kernel
-// stores this rank's slice into every rank's window with plain stores through the mapped pointers, fences at
-// system scope and adds one to each rank's counter; before the next projection a one-thread kernel waits until
-// its own counter shows that every rank's slice has arrived.  The wait is bounded: when it runs out it raises the
-// library's wait flag (lspk_tc_check_error -> LSPK_ERR_DEVICE_WAIT) and returns, so a rank that never arrives
-// costs its peers an error code, not a hang.  No collective library, no multicast, nothing but stores, one
-// atomic per peer and loads of local memory.
+// CUDA IPC.  After a projection a small kernel stores this rank's slice into every rank's window as 64-bit
+// packets (fp32 value | number of this exchange << 32), each with one 8-byte store through the mapped pointer:
+// no fence, no atomic, no flag, because the value and the evidence that it is new travel in the same store.
+// One more CTA of the same launch polls the packets of its own window until every one carries the current
+// exchange number and writes the plain fp32 vector the next projection reads.  The polling is bounded: when
+// it runs out the kernel raises the library's wait flag (lspk_tc_check_error -> LSPK_ERR_DEVICE_WAIT) and
+// returns, so a rank that never arrives costs its peers an error code, not a hang.  No collective library, no
+// multicast: plain stores to peer memory and loads of local memory.
 //
-// Window layout (floats): [0, I) gathered gate product, [I, I + H) gathered down product, then two 64-bit
-// arrival counters and two 64-bit epoch words (which exchange of its kind this is: the counters only grow, so
-// the same graph can be replayed).
+// Window layout: [I packets: gathered gate product][H packets: gathered down product] (written by every rank),
+// then, used locally only, the two plain fp32 vectors and the two exchange counters (how many exchanges of each
+// kind are complete; kept on the device so that the same CUDA graph can be replayed).
 #include <string.h>
 
 #include "internal.cuh"
@@ -22,6 +23,7 @@ namespace lspk {
 
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpScatterCtas = 4;
+constexpr int kTpUnpackThreads = 1024;
 
 struct PeerWindow {
     void* local = nullptr;                 // this rank's window (cudaMalloc)
@@ -29,67 +31,91 @@ struct PeerWindow {
     bool opened[kTpMaxWorld] = {};
     size_t bytes = 0;
     int I = 0, H = 0, rank = 0, world = 1;
-    unsigned poll_limit = 1u << 22;
+    unsigned poll_limit = 1u << 20;
 };
 static PeerWindow g_win;
 static bool g_drop_next = false;           // test hook: the next exchange stores nothing (its wait must run out)
 
 struct PeerPtrs {
-    float* data[kTpMaxWorld];
-    unsigned long long* counter[kTpMaxWorld];
+    unsigned long long* dst[kTpMaxWorld];  // this rank's segment of the packet vector in every rank's window
 };
 
-// Store `n` floats of this rank's slice at `offset` floats into every rank's window, then tell every rank.
-__global__ void __launch_bounds__(256) tp_scatter_kernel(const float* __restrict__ slice, int n, PeerPtrs peers, int world) {
+// One launch per exchange.  CTAs 0 .. kTpScatterCtas-1 store `n` floats of this rank's slice into every rank's window
+// as (value, exchange number) packets; the last CTA waits until every packet of this window's vector carries the
+// current exchange number, writes the plain vector and counts the exchange as done.  The waiting CTA depends on
+// the storing CTAs of the OTHER ranks' launches and on those of its own launch, which wait for nobody, so the
+// launch cannot block itself.  The count is advanced only after every packet of this rank has arrived, i.e.
+// after every storing thread has read it.
+__global__ void __launch_bounds__(kTpUnpackThreads)
+tp_exchange_kernel(const float* __restrict__ slice, int n, PeerPtrs peers, int world, int scatter_on,
+                   const unsigned long long* __restrict__ packets, float* __restrict__ plain, int total,
+                   unsigned* done_count, unsigned poll_limit, int* error_flag) {
     grid_dependency_launch();
     grid_dependency_wait();
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        const float v = slice[i];
-        for (int r = 0; r < world; ++r) peers.data[r][i] = v;
-    }
-    __threadfence_system();                // this thread's stores are visible to every GPU before the count below
-    __syncthreads();
-    if (threadIdx.x == 0)
-        for (int r = 0; r < world; ++r) atomicAdd_system(peers.counter[r], 1ull);
-}
-
-// One thread: this is exchange number ++epoch of its kind; wait until all arrivals of that many exchanges are in.
-__global__ void tp_wait_kernel(unsigned long long* counter, unsigned long long* epoch, unsigned long long per_exchange,
-                               unsigned poll_limit, int* error_flag) {
-    grid_dependency_launch();
-    grid_dependency_wait();
-    if (threadIdx.x == 0) {
-        const unsigned long long target = (*epoch += 1ull) * per_exchange;
-        bool ok = false;
-        for (unsigned i = 0; i < poll_limit && !ok; ++i) {
-            unsigned long long v;
-            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(counter) : "memory");
-            ok = v >= target;
+    const unsigned want = *reinterpret_cast<volatile unsigned*>(done_count) + 1u;
+    if (blockIdx.x < kTpScatterCtas) {
+        if (!scatter_on) return;
+        const unsigned long long tag = (unsigned long long)want << 32;
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += kTpScatterCtas * blockDim.x) {
+            const unsigned long long pkt = tag | (unsigned long long)__float_as_uint(slice[i]);
+            for (int r = 0; r < world; ++r)
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(peers.dst[r] + i), "l"(pkt) : "memory");
         }
-        if (!ok && error_flag) atomicExch(error_flag, LSPK_ERR_DEVICE_WAIT);
+        return;
+    }
+    __syncthreads();                       // every thread has read the count before thread 0 advances it below
+    bool ok = true;
+    // eight packets per thread and round: all their loads are in flight together, so a round costs one trip to
+    // memory, and only the packets that have not arrived yet are asked for again
+    for (int base = threadIdx.x; base < total; base += 8 * blockDim.x) {
+        unsigned long long pkt[8];
+        unsigned missing = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (base + k * (int)blockDim.x < total) missing |= 1u << k;
+        for (unsigned poll = 0; poll < poll_limit && missing; ++poll) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (missing & (1u << k))
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(pkt[k]) : "l"(packets + base + k * (int)blockDim.x) : "memory");
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if ((missing & (1u << k)) && (unsigned)(pkt[k] >> 32) == want) missing &= ~(1u << k);
+        }
+        ok = ok && missing == 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (base + k * (int)blockDim.x < total) plain[base + k * (int)blockDim.x] = __uint_as_float((unsigned)pkt[k]);
+    }
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    if (threadIdx.x == 0) {
+        if (!all_ok && error_flag) atomicExch(error_flag, LSPK_ERR_DEVICE_WAIT);
+        *done_count = want;
     }
 }
 
-static size_t window_floats(int I, int H) { return (size_t)I + H; }
-static unsigned long long* counter_of(void* base, int I, int H, int which) {
-    return reinterpret_cast<unsigned long long*>(reinterpret_cast<float*>(base) + ((window_floats(I, H) + 3) & ~(size_t)3)) + which;
-}
-static unsigned long long* epoch_of(void* base, int I, int H, int which) { return counter_of(base, I, H, 2 + which); }
+// byte offsets inside a window
+static size_t off_packets(int I, int which) { return which == 0 ? 0 : (size_t)I * 8; }
+static size_t off_plain(int I, int H, int which) { return (size_t)(I + H) * 8 + (which == 0 ? 0 : (size_t)I * 4); }
+static size_t off_counts(int I, int H) { return ((size_t)(I + H) * 12 + 15) & ~(size_t)15; }
+static size_t window_bytes(int I, int H) { return off_counts(I, H) + 16; }
 
-// which: 0 = gate product (offset 0, I floats in all), 1 = down product (offset I, H floats in all)
+// which: 0 = gate product (I floats in all), 1 = down product (H floats in all)
 static int exchange(const float* slice, int which) {
     const PeerWindow& w = g_win;
     const int total = which == 0 ? w.I : w.H, n = total / w.world;
+    char* base = static_cast<char*>(w.local);
+    unsigned* done = reinterpret_cast<unsigned*>(base + off_counts(w.I, w.H)) + which;
     PeerPtrs pp = {};
     for (int r = 0; r < w.world; ++r) {
         LSPK_REQUIRE(w.peer[r], "tensor-parallel window of rank %d has not been opened", r);
-        pp.data[r] = reinterpret_cast<float*>(w.peer[r]) + (which == 0 ? 0 : w.I) + (size_t)w.rank * n;
-        pp.counter[r] = counter_of(w.peer[r], w.I, w.H, which);
+        pp.dst[r] = reinterpret_cast<unsigned long long*>(static_cast<char*>(w.peer[r]) + off_packets(w.I, which)) + (size_t)w.rank * n;
     }
-    if (g_drop_next) g_drop_next = false;
-    else LSPK_CUDA(launch(tp_scatter_kernel, dim3(kTpScatterCtas), dim3(256), 0, true, slice, n, pp, w.world));
-    LSPK_CUDA(launch(tp_wait_kernel, dim3(1), dim3(32), 0, true, counter_of(w.local, w.I, w.H, which),
-                     epoch_of(w.local, w.I, w.H, which), (unsigned long long)w.world * kTpScatterCtas, w.poll_limit,
+    const int scatter_on = g_drop_next ? 0 : 1;
+    g_drop_next = false;
+    LSPK_CUDA(launch(tp_exchange_kernel, dim3(kTpScatterCtas + 1), dim3(kTpUnpackThreads), 0, true, slice, n, pp, w.world,
+                     scatter_on, (const unsigned long long*)(base + off_packets(w.I, which)),
+                     reinterpret_cast<float*>(base + off_plain(w.I, w.H, which)), total, done, w.poll_limit,
                      device_wait_flag()));
     return LSPK_OK;
 }
@@ -107,7 +133,7 @@ int lspk_tp_window_create(int rank, int world, int I, int H, void* ipc_handle64_
                  "lspk_tp_window_create: bad arguments (world 1..%d, I and H divisible by it)", kTpMaxWorld);
     LSPK_REQUIRE(!g_win.local, "lspk_tp_window_create: a window already exists (close it first)");
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handles are expected to be 64 bytes");
-    const size_t bytes = ((window_floats(I, H) + 3) & ~(size_t)3) * 4 + 4 * 8;
+    const size_t bytes = window_bytes(I, H);
     void* p = nullptr;
     LSPK_CUDA(cudaMalloc(&p, bytes));
     LSPK_CUDA(cudaMemset(p, 0, bytes));
@@ -166,7 +192,7 @@ int lspk_tp_debug_drop_next_arrival(void) {
 
 const float* lspk_tp_window_vector(int which) {
     if (!g_win.local || which < 0 || which > 1) return nullptr;
-    return reinterpret_cast<const float*>(g_win.local) + (which == 0 ? 0 : g_win.I);
+    return reinterpret_cast<const float*>(static_cast<char*>(g_win.local) + off_plain(g_win.I, g_win.H, which));
 }
 
 int lspk_tp_exchange(const float* slice_dev, int which) {

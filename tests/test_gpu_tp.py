@@ -121,10 +121,10 @@ def test_tp_mlp_block_two_gpus(tmp_path):
 
 
 def test_peer_wait_runs_out_and_reports():
-    """The failure path of the peer exchange without a failing GPU: a window that expects two ranks' arrivals is
-    created by a process that is alone, so nobody ever supplies rank 1's share.  The wait kernel gives up after
-    its poll limit, the library's wait flag turns into LSPK_ERR_DEVICE_WAIT exactly once, the stream keeps
-    working, and an exchange of a complete (one-rank) group afterwards succeeds."""
+    """The failure path of the peer exchange without a failing GPU: the store side of one exchange is dropped (a
+    test hook), so the wait polls packets that nothing renews.  It gives up after its poll limit, the library's
+    wait flag turns into LSPK_ERR_DEVICE_WAIT exactly once, the stream keeps working, and the next exchange on
+    the same window succeeds.  A group whose peer window was never mapped is refused before anything launches."""
     import ctypes
     import importlib
     import numpy as np
@@ -141,8 +141,8 @@ def test_peer_wait_runs_out_and_reports():
     assert lib.lspk_tp_exchange(sl.ptr, 0) == 1 and b"has not been opened" in lib.lspk_last_error()
     lib.lspk_clear_error()
     K.check(lib.lspk_tp_window_close())
-    # a slice that never arrives: the test hook drops the store side of the next exchange, so its wait polls a
-    # counter that nothing advances
+    # a slice that never arrives: the test hook drops the store side of the next exchange, so its wait polls
+    # packets that still carry an old exchange number
     K.check(lib.lspk_tp_window_create(0, 1, 64, 32, buf))
     K.check(lib.lspk_tp_window_set_poll_limit(2000))
     K.check(lib.lspk_tp_debug_drop_next_arrival())
@@ -150,10 +150,12 @@ def test_peer_wait_runs_out_and_reports():
     assert lib.lspk_tc_check_error() == 6                               # LSPK_ERR_DEVICE_WAIT, reported once
     lib.lspk_clear_error()
     assert lib.lspk_tc_check_error() == 0
-    # The lost slice leaves the counter one exchange behind for good, as a lost rank would: a fresh window works.
-    K.check(lib.lspk_tp_window_close())
-    K.check(lib.lspk_tp_window_create(0, 1, 64, 32, buf))
+    # the exchange after the lost one carries the next number: the same window works again
     full = dev.DeviceArray.from_numpy(np.arange(64, dtype=np.float32) * 0.5)
+    K.check(lib.lspk_tp_exchange(sl.ptr, 1))                       # kind 1 again: the number after the lost one
+    got1 = np.empty(32, np.float32)
+    K.check(lib.lspk_d2h(got1.ctypes.data, lib.lspk_tp_window_vector(1), got1.nbytes))
+    assert np.array_equal(got1, np.arange(32, dtype=np.float32))
     K.check(lib.lspk_tp_exchange(full.ptr, 0))
     out = np.empty(64, np.float32)
     K.check(lib.lspk_d2h(out.ctypes.data, lib.lspk_tp_window_vector(0), out.nbytes))
