@@ -472,7 +472,7 @@ def run_probes(args):
         for grid in (160, 240, 296):
             K.check(lib.lspk_bench_handoff(grid, 2000, mode, ctypes.byref(us), ctypes.byref(cyc)))
             out[f"persistent_{name}_grid{grid}"] = {"us_per_round": us.value, "sm_cycles_per_round": cyc.value}
-    for issuers, mode in ((1, 0), (4, 4)):          # one requesting thread per CTA, or four warps a quarter of a stage each
+    for issuers, mode in ((1, 0), (4, 4)):          # one requesting thread per CTA, or four warps taking turns
         for cs, nc, stages in ((1, 1, 2000), (16, 1, 2000), (16, 9, 400), (1, 148, 400)):
             K.check(lib.lspk_bench_cluster(cs, nc, stages, 1, 1, mode, ctypes.byref(ms)))
             gb = cs * nc * stages * 16384 / 1e9

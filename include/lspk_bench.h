@@ -26,8 +26,8 @@ int lspk_bench_handoff(int grid, int iters, int mode, float* us_per_round_out, d
  * CTAs (one CTA per SM, 1..16 per cluster) run side by side.  mode 0: each CTA pulls `stages_per_cta` stages of
  * 16 KB from a 1 GB buffer through a ring of eight bulk copies; mode 1: `rounds` exchanges of a 2560-float
  * vector (every CTA stores its slice into every peer's shared memory, one cluster barrier, every CTA reduces the
- * vector); mode 2: an exchange after every `stages_per_round` stages; + 4: every stage is requested as four 4 KB
- * copies by four warps instead of one copy by one thread.  Reports CUDA-event milliseconds. */
+ * vector); mode 2: an exchange after every `stages_per_round` stages; + 4: four warps take turns
+ * requesting the stages instead of one thread requesting all of them.  Reports CUDA-event milliseconds. */
 int lspk_bench_cluster(int cluster_size, int n_clusters, int stages_per_cta, int rounds, int stages_per_round, int mode,
                        float* ms_out);
 

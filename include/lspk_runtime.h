@@ -64,7 +64,10 @@ int lspk_state_read_kv(lspk_state_t s, int seq, int layer, int n_pos, float* k_h
 
 /* One decode step for every sequence of the state: tokens_host[batch] in, optionally
  * logits_host[batch, V] and next_tokens_host[batch] (greedy argmax, first maximum) out.
- * Returns LSPK_ERR_STATE when a cache is full (the reference raises RuntimeError, runtime.py:183). */
+ * Returns LSPK_ERR_STATE when a cache is full (the reference raises RuntimeError, runtime.py:183).
+ * With one sequence and no logits requested the step runs without copy operations: the token is read by the
+ * step's first kernel from mapped pinned memory and the next token comes back in one 8-byte store that the call
+ * polls for (no stream synchronisation). */
 int lspk_forward_step(lspk_state_t s, const int* tokens_host, float* logits_host, int* next_tokens_host);
 
 /* Feed T tokens of sequence `seq` at once (any T >= 1; processed in row chunks).  Outputs, each

@@ -143,8 +143,8 @@ int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tc
  * STORE / ADD epilogue or a gate + up pair with a gated epilogue, up to 96 products, K up to 8192.  For callers
  * that loop over matrices which do not depend on one another (the reference's kernel benchmark does; so do the
  * experts of a mixture layer): the row groups of all products form one stream that a persistent grid, one CTA
- * per SM, pulls through per-warp rings of bulk asynchronous copies, so that no product pays a kernel's fill and
- * drain.  The outputs must not be inputs of other products of the same call.  Results are bit-identical to
+ * per SM, pulls through a shared-memory ring of bulk asynchronous copies (six requesting warps, twelve computing
+ * warps), so that no product pays a kernel's fill and drain.  The outputs must not be inputs of other products of the same call.  Results are bit-identical to
  * lspk_linear.  Every device-side wait is bounded; an expiry is reported by lspk_tc_check_error. */
 int lspk_linear_batch(const lspk_linear_args* args, int n);
 /* The tcgen05 kernel bounds every device-side wait; this reads and clears its expiry flag

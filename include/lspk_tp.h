@@ -30,9 +30,10 @@ int lspk_tp_mlp_block(lspk_weight_t gate_r, lspk_weight_t up_r, lspk_weight_t do
 /* The same exchange over peer memory (csrc/tp_peer.cu): every rank creates one window (a device buffer holding
  * the gathered gate product [I] and the gathered down product [H] as 64-bit packets, value | exchange number),
  * hands its 64-byte CUDA IPC handle to the other ranks of the node by any host channel, and opens theirs.
- * lspk_tp_exchange stores this rank's slice (which = 0: I / world floats of the gate product, 1: H / world floats
- * of the down product) into every window, one 8-byte store per element, then polls, with a bound, the packets of
- * its own window until every rank's slice of this exchange is there and writes the plain fp32 vector.  When the
+ * lspk_tp_exchange is one launch: four CTAs store this rank's slice (which = 0: I / world floats of the gate
+ * product, 1: H / world floats of the down product) into every window, one 8-byte store per element, and a fifth
+ * polls, with a bound, the packets of its own window until every rank's slice of this exchange is there and
+ * writes the plain fp32 vector.  When the
  * bound runs out the library's wait flag is raised (lspk_tc_check_error returns LSPK_ERR_DEVICE_WAIT) and the
  * stream carries on: a rank that never arrives costs an error code, not a hang. */
 int lspk_tp_window_create(int rank, int world, int I, int H, void* ipc_handle64_out);

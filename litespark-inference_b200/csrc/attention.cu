@@ -385,26 +385,33 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
 // shared memory, the cache rows are written by the CTA that owns position `pos` (head h % G == 0).
 constexpr int kSplit = 8;
 
-// MINB: CTAs per SM the register budget is held to.  Launches over several sequences have far more clusters than
-// the machine holds at once, so their instantiation trades registers for a fourth resident CTA; the arithmetic
-// (and so every result bit) is the same in both.
-template <typename KVT, int D, int MINB = 1>
-__global__ void __launch_bounds__(kAttnThreads, MINB) attention_split_kernel(const AttnParams p) {
+// The order of every floating-point sum is defined for kAttnThreads (256) threads: key groups of TPK lanes, one
+// partial output per group, exponentials summed per thread, warp and eight-warp tree.  NT: threads the CTA really
+// has.  Launches over several sequences have far more clusters than the machine holds at once; their instantiation
+// runs 128 threads per CTA (twice the CTAs per SM), each thread group standing in for two of the defined groups
+// with an accumulator apiece, each thread for two of the defined threads in the sum of exponentials: every result
+// bit is the same, so a sequence's tokens do not depend on what it is batched with.  MINB: CTAs per SM the
+// register budget is held to.
+template <typename KVT, int D, int NT = kAttnThreads, int MINB = 1>
+__global__ void __launch_bounds__(NT, MINB) attention_split_kernel(const AttnParams p) {
     namespace cg = cooperative_groups;
     constexpr int VEC = KvVec<KVT>::N;
     constexpr int NCH = D / VEC;
     constexpr int TPK = NCH > 32 ? 32 : NCH;    // lanes per key
     constexpr int CPT = NCH / TPK;              // chunks per lane
-    constexpr int NG = kAttnThreads / TPK;      // key groups
+    constexpr int VG = kAttnThreads / TPK;      // key groups the sums are defined over
+    constexpr int NG = NT / TPK;                // key groups this CTA has
+    constexpr int ACC = VG / NG;                // defined groups per real group (1 or 2): slot j belongs to g + NG * (j % ACC)
     constexpr int SB = 4 / CPT;                 // keys per group in flight (requested before pos is known)
     constexpr int KPB = NG * SB;                // local keys per batch
+    static_assert(NT == kAttnThreads || (NT * 2 == kAttnThreads && NT >= D && SB % 2 == 0), "half-size CTAs: D <= NT, even SB");
     extern __shared__ __align__(16) float at_smem[];
     float* qs = at_smem;                  // [D] rotated query
     float* ks = qs + D;                   // [D] rotated current key
     float* vs = ks + D;                   // [D] current value
     float* raw = vs + D;                  // [2*D] raw q and k before rotation
-    float* part = raw + 2 * D;            // [NG][D] value partial sums of this CTA
-    float* fin = part + NG * D;           // [kSplit][D] CTA partials, gathered in rank 0
+    float* part = raw + 2 * D;            // [VG][D] value partial sums of this CTA
+    float* fin = part + VG * D;           // [kSplit][D] CTA partials, gathered in rank 0
     float* sc = fin + kSplit * D;         // [local keys] scores / probabilities
     __shared__ __align__(16) float cl_max[kSplit], cl_sum[kSplit];
     __shared__ __align__(16) float red[16];
@@ -565,19 +572,31 @@ __global__ void __launch_bounds__(kAttnThreads, MINB) attention_split_kernel(con
     {
         const uint32_t u = __reduce_max_sync(0xffffffffu, float_to_ordered(mx));
         if (lane == 0) red[warp] = ordered_to_float(u);
+        if (NT < kAttnThreads && tid < 8 - NT / 32) red[NT / 32 + tid] = -INFINITY;      // the warps this CTA does not have
         __syncthreads();
         const float4 a = *reinterpret_cast<const float4*>(red), b = *reinterpret_cast<const float4*>(red + 4);
         mx = fmaxf(fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)), fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
     }
-    float sum = 0.0f;
+    float sum = 0.0f, sum_hi = 0.0f;              // defined thread tid, and (half-size CTAs) defined thread tid + NT
     for (int j = tid; j < n_local; j += kAttnThreads) {
         const float e = expf(sc[j] - mx);
         sc[j] = e;
         sum += e;
     }
+    if (NT < kAttnThreads) {
+        for (int j = tid + NT; j < n_local; j += kAttnThreads) {
+            const float e = expf(sc[j] - mx);
+            sc[j] = e;
+            sum_hi += e;
+        }
+    }
     {
         sum = warp_sum(sum);
         if (lane == 0) red[8 + warp] = sum;
+        if (NT < kAttnThreads) {
+            sum_hi = warp_sum(sum_hi);
+            if (lane == 0) red[8 + NT / 32 + warp] = sum_hi;
+        }
         __syncthreads();                          // also publishes sc[] to the value phase
         const float4 a = *reinterpret_cast<const float4*>(red + 8), b = *reinterpret_cast<const float4*>(red + 12);
         sum = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
@@ -585,11 +604,13 @@ __global__ void __launch_bounds__(kAttnThreads, MINB) attention_split_kernel(con
     tr.mark();                                   // 4: local softmax terms done
 
     // ---- unnormalised weighted sum of this CTA's values ------------------------------------------------------
-    float o[CPT][VEC];
+    float o[ACC][CPT][VEC];
 #pragma unroll
-    for (int u = 0; u < CPT; ++u)
+    for (int a = 0; a < ACC; ++a)
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) o[u][e] = 0.0f;
+        for (int u = 0; u < CPT; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) o[a][u][e] = 0.0f;
     for (int base = 0; base < n_local; base += KPB) {
         if (base > 0) {
 #pragma unroll
@@ -618,23 +639,25 @@ __global__ void __launch_bounds__(kAttnThreads, MINB) attention_split_kernel(con
                         KvVec<KVT>::unpack(vbuf[j][u], f);
                     }
 #pragma unroll
-                    for (int e = 0; e < VEC; ++e) o[u][e] = fmaf(pi, f[e], o[u][e]);
+                    for (int e = 0; e < VEC; ++e) o[j % ACC][u][e] = fmaf(pi, f[e], o[j % ACC][u][e]);
                 }
             }
         }
     }
     tr.mark();                                   // 5: values accumulated
 #pragma unroll
-    for (int u = 0; u < CPT; ++u)
+    for (int a = 0; a < ACC; ++a)
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) part[g * D + (c + u * TPK) * VEC + e] = o[u][e];
+        for (int u = 0; u < CPT; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) part[(g + a * NG) * D + (c + u * TPK) * VEC + e] = o[a][u][e];
     __syncthreads();
     // ---- hand (maximum, sum, partial output) to rank 0, which merges the kSplit softmax pieces --------------
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");      // every CTA of the cluster is running
     if (tid < D) {
         float acc = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NG; ++w) acc += part[w * D + tid];
+        for (int w = 0; w < VG; ++w) acc += part[w * D + tid];
         cluster.map_shared_rank(fin, 0)[r * D + tid] = acc;
     }
     if (tid == 0) {
@@ -908,7 +931,7 @@ static int attention_launch_t(const AttnParams& p) {
         if (!split_attr_set) {
             LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 128, kAttnThreads / 2, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             LSPK_CUDA(cudaFuncSetAttribute(attention_split_kernel<KVT, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             split_attr_set = true;
         }
@@ -916,7 +939,7 @@ static int attention_launch_t(const AttnParams& p) {
         const dim3 sgrid(p.Q, p.T, kSplit), cl(1, 1, kSplit);
         cudaError_t se;
         if (D == 64) se = launch_cluster(attention_split_kernel<KVT, 64>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
-        else if (D == 128 && p.T >= 4) se = launch_cluster(attention_split_kernel<KVT, 128, 4>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
+        else if (D == 128 && p.T >= 4) se = launch_cluster(attention_split_kernel<KVT, 128, kAttnThreads / 2, 6>, sgrid, dim3(kAttnThreads / 2), sm, true, cl, p);
         else if (D == 128) se = launch_cluster(attention_split_kernel<KVT, 128>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
         else se = launch_cluster(attention_split_kernel<KVT, 256>, sgrid, dim3(kAttnThreads), sm, true, cl, p);
         if (se != cudaSuccess) return fail(LSPK_ERR_CUDA, "attention (split) launch failed: %s", cudaGetErrorString(se));

@@ -223,7 +223,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 // mode 0: stream `stages_per_cta` stages of 16 KB per CTA through the ring, no exchange
 // mode 1: `rounds` exchanges of a 2560-float vector (slices by rank), no streaming
 // mode 2: both: an exchange after every `stages_per_round` stages
-// + 4: every stage is requested as four 4 KB copies by lane 0 of four warps instead of one 16 KB copy by one thread
+// + 4: four warps request the stages (stage k by lane 0 of warp k % 4) instead of one thread requesting all of them
 __global__ void __launch_bounds__(256, 1)
 cluster_probe_kernel(const unsigned char* __restrict__ src, size_t src_bytes, int stages_per_cta, int rounds,
                      int stages_per_round, int mode, int* error_word, float* sink) {
@@ -239,22 +239,21 @@ cluster_probe_kernel(const unsigned char* __restrict__ src, size_t src_bytes, in
     mode &= 3;
     if (tid == 0) {
         s_fail = 0;
-        for (int s = 0; s < kCpStages; ++s) mbar_init(&bars[s], issuers);
+        for (int s = 0; s < kCpStages; ++s) mbar_init(&bars[s], 1);
         fence_mbar_init();
     }
     __syncthreads();
     cluster_sync_all();                                              // every CTA of the cluster has started
     const int n_stages = mode == 1 ? 0 : stages_per_cta;
     const size_t base = (cta_lin * (size_t)stages_per_cta * kCpStage) % (src_bytes - (size_t)stages_per_cta * kCpStage);
-    auto issue = [&](int k, int part) {                                // part: which of `issuers` equal pieces
+    auto issue = [&](int k) {
         const int s = k % kCpStages;
-        const uint32_t bytes = kCpStage / issuers;
-        mbar_expect_tx(&bars[s], bytes);
-        bulk_load_stream(ring + (size_t)s * kCpStage + (size_t)part * bytes,
-                         src + ((base + (size_t)k * kCpStage) & ~(size_t)15) + (size_t)part * bytes, bytes, &bars[s]);
+        mbar_expect_tx(&bars[s], kCpStage);
+        bulk_load_stream(ring + (size_t)s * kCpStage, src + ((base + (size_t)k * kCpStage) & ~(size_t)15), kCpStage, &bars[s]);
     };
-    if ((tid & 31) == 0 && (tid >> 5) < issuers)
-        for (int k = 0; k < kCpStages && k < n_stages; ++k) issue(k, tid >> 5);
+    const bool issuer = (tid & 31) == 0 && (tid >> 5) < issuers;      // stage k is requested by warp k % issuers
+    if (issuer)
+        for (int k = tid >> 5; k < kCpStages && k < n_stages; k += issuers) issue(k);
     float acc = 0.0f;
     int done_rounds = 0;
     const int slice = 2560 / (int)nrank;                              // floats of the vector this CTA produces
@@ -288,7 +287,7 @@ cluster_probe_kernel(const unsigned char* __restrict__ src, size_t src_bytes, in
         }
         __syncthreads();
         if (s_fail) break;
-        if ((tid & 31) == 0 && (tid >> 5) < issuers && k + kCpStages < n_stages) issue(k + kCpStages, tid >> 5);
+        if (issuer && (k + kCpStages) % issuers == (tid >> 5) && k + kCpStages < n_stages) issue(k + kCpStages);
         if (mode == 2 && (k + 1) % stages_per_round == 0) exchange();
     }
     if (mode == 1)

@@ -122,4 +122,39 @@ struct AttnParams {
 };
 int attention_launch(const AttnParams& p, int kv_is_fp16);
 
+// One product of a streamed batch (linear_stream.cu).  The caller fills everything above the line; stream_launch
+// fills the rest.  With `sel` set the product's matrices are chosen on the device: expert e = *sel (written by an
+// earlier kernel of the stream), matrices w[m] + e * sel_stride, scales sel_scales[3 * e + scale_idx[m]].
+struct StreamItem {
+    const uint4* w[2];
+    float* out;
+    int32_t* acc[2];
+    const int8_t* x;
+    const float* xs;
+    float ws[2];
+    int N, K, chunks, groups;
+    int nm;            // matrices per unit: 1, or 2 for the gated pairing
+    int epilogue;
+    const int* sel;
+    size_t sel_stride; // uint4 units
+    const float* sel_scales;
+    int scale_idx[2];
+    // ---- filled by stream_launch ----
+    int unit0;         // flat index of this product's first unit
+    int q0;            // flat index of this product's first stage
+    int cps;           // chunks per stage and matrix
+    int sub;           // stages per unit
+};
+constexpr int kStreamMaxItems = 96;
+constexpr int kStreamMaxKp = 8192;               // longest row (K rounded up to 64)
+struct StreamParams {
+    StreamItem it[kStreamMaxItems];
+    int n;
+    int total_units;
+    int* error_flag;
+    int wait_for_predecessor;   // the requesting warps may not start before the previous kernel has finished (sel)
+};
+// Launch the streamed batch described by p->it[0 .. p->n) on the library stream.
+int stream_launch(StreamParams* p);
+
 }  // namespace lspk

@@ -34,31 +34,9 @@ constexpr int kSThreads = 32 * (kSConsumers + kSProducers);
 constexpr int kSSlots = 18;                      // stages of the CTA's ring (shared by all consumer warps)
 constexpr int kSStageChunks = 40;                // 16-row x 16-byte chunks per stage (all matrices of a unit)
 constexpr int kSStageBytes = kSStageChunks * kRowsPerGroup * 16;   // 10240: 180 KB of ring per SM
-constexpr int kSMaxItems = 96;
-constexpr int kSMaxKp = 8192;                    // longest row (K rounded up to 64)
+constexpr int kSMaxItems = kStreamMaxItems;
+constexpr int kSMaxKp = kStreamMaxKp;
 constexpr long long kSBudgetCycles = 1ll << 31;  // SM cycles (about a second) after which every wait of a CTA gives up
-
-struct StreamItem {
-    const uint4* w[2];
-    float* out;
-    int32_t* acc[2];
-    const int8_t* x;
-    const float* xs;
-    float ws[2];
-    int N, K, chunks, groups;
-    int nm;            // matrices per unit: 1, or 2 for the gated pairing
-    int epilogue;
-    int unit0;         // flat index of this product's first unit
-    int q0;            // flat index of this product's first stage
-    int cps;           // chunks per stage and matrix
-    int sub;           // stages per unit
-};
-struct StreamParams {
-    StreamItem it[kSMaxItems];
-    int n;
-    int total_units;
-    int* error_flag;
-};
 
 __device__ __forceinline__ void consumer_barrier() {      // the consumer warps only (the requesting warps never join)
     asm volatile("bar.sync 1, %0;" ::"n"(32 * kSConsumers) : "memory");
@@ -103,9 +81,11 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
     }
     __syncthreads();
     grid_dependency_launch();
+    auto expert_of = [&](const StreamItem& it) -> size_t { return it.sel ? (size_t)*(volatile const int*)it.sel : 0; };
 
     if (warp >= kSConsumers) {
         const int pw = warp - kSConsumers;
+        if (p.wait_for_predecessor) grid_dependency_wait();      // which matrices to stream is the previous kernel's output
         // ---------------- producers: lane 0 of warp pw requests stages pw, pw + kSProducers, ... as slots come free --
         // (the weights do not depend on whatever ran before, so this starts at once)
         if (lane == 0 && i_hi >= i_lo) {
@@ -117,8 +97,9 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
                 const StreamItem& it = p.it[i];
                 const int g_first = max(u_lo, it.unit0) - it.unit0, g_end = min(u_hi, it.unit0 + it.groups) - it.unit0;
                 const int nm = it.nm, chunks = it.chunks, cps = it.cps, sub = it.sub;
-                const uint4* ua = it.w[0] + (size_t)g_first * chunks * kRowsPerGroup;
-                const uint4* ub = nm == 2 ? it.w[1] + (size_t)g_first * chunks * kRowsPerGroup : nullptr;
+                const size_t w_off = expert_of(it) * it.sel_stride;
+                const uint4* ua = it.w[0] + w_off + (size_t)g_first * chunks * kRowsPerGroup;
+                const uint4* ub = nm == 2 ? it.w[1] + w_off + (size_t)g_first * chunks * kRowsPerGroup : nullptr;
                 for (int g = g_first; g < g_end && ok; ++g) {
                     for (int s = 0; s < sub; ++s, ++q) {
                         if (q % kSProducers != pw) continue;
@@ -217,6 +198,12 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 #pragma unroll
         for (int w = 0; w < kSConsumers; ++w) sx += s_sumx[i & 1][w];
         const float xscale = s_scale[i & 1];
+        float ws0 = it.ws[0], ws1 = it.ws[1];
+        if (it.sel) {
+            const size_t e = expert_of(it);
+            ws0 = it.sel_scales[3 * e + it.scale_idx[0]];
+            ws1 = it.sel_scales[3 * e + it.scale_idx[1]];
+        }
         const int unit_end = min(u_hi, it.unit0 + it.groups);
         for (; !dead && unit < unit_end; unit += kSConsumers) {
             const int g = unit - it.unit0;
@@ -275,11 +262,11 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
             if (h == 0 && n < it.N) {
                 va -= sx;
                 if (it.acc[0]) it.acc[0][n] = va;
-                const float ya = __fmul_rn((float)va, __fmul_rn(xscale, it.ws[0]));
+                const float ya = __fmul_rn((float)va, __fmul_rn(xscale, ws0));
                 if (it.nm == 2) {
                     vb -= sx;
                     if (it.acc[1]) it.acc[1][n] = vb;
-                    const float yb = __fmul_rn((float)vb, __fmul_rn(xscale, it.ws[1]));
+                    const float yb = __fmul_rn((float)vb, __fmul_rn(xscale, ws1));
                     if (it.epilogue == LSPK_EPI_SILU_MUL) {
                         it.out[n] = __fmul_rn(__fdiv_rn(ya, __fadd_rn(expf(-ya), 1.0f)), yb);
                     } else {
@@ -303,6 +290,38 @@ ternary_gemv_stream_kernel(const __grid_constant__ StreamParams p) {
 
 static size_t stream_smem_bytes() { return (size_t)kSSlots * kSStageBytes + 2 * (size_t)kSMaxKp; }
 
+int stream_launch(StreamParams* p) {
+    LSPK_REQUIRE(p && p->n >= 1 && p->n <= kSMaxItems, "streamed batch: 1..%d products per launch", kSMaxItems);
+    p->error_flag = device_wait_flag();
+    p->wait_for_predecessor = 0;
+    int unit0 = 0, q0 = 0;
+    for (int i = 0; i < p->n; ++i) {
+        StreamItem& it = p->it[i];
+        LSPK_REQUIRE(it.chunks * kWeightsPerChunk <= kSMaxKp, "streamed batch: product %d: K=%d too long (limit %d)", i, it.K, kSMaxKp);
+        it.unit0 = unit0;
+        it.q0 = q0;
+        it.cps = kSStageChunks / it.nm;
+        it.sub = (it.chunks + it.cps - 1) / it.cps;
+        unit0 += it.groups;
+        q0 += it.groups * it.sub;
+        if (it.sel) p->wait_for_predecessor = 1;
+    }
+    p->total_units = unit0;
+    static bool attr_set = false;
+    const size_t smem = stream_smem_bytes();
+    if (!attr_set) {
+        LSPK_CUDA(cudaFuncSetAttribute(ternary_gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    // one CTA per SM as soon as there are two units for each: a short batch is bound by how many SMs pull on it
+    // (an SM takes in about 76 GB/s through the copy engine), not by idle consumer warps
+    int ctas = (unit0 + 1) / 2;
+    if (ctas > sm_count()) ctas = sm_count();
+    if (ctas < 1) ctas = 1;
+    LSPK_CUDA(launch(ternary_gemv_stream_kernel, dim3(ctas), dim3(kSThreads), smem, true, *p));
+    return LSPK_OK;
+}
+
 }  // namespace lspk
 
 using namespace lspk;
@@ -312,8 +331,6 @@ extern "C" int lspk_linear_batch(const lspk_linear_args* args, int n) {
     LSPK_REQUIRE(args && n >= 1 && n <= kSMaxItems, "lspk_linear_batch: 1..%d products per call (got %d)", kSMaxItems, n);
     static StreamParams p;                        // 10 KB: kept off the stack; calls are serialised by the caller
     p.n = n;
-    p.error_flag = device_wait_flag();
-    int unit0 = 0, q0 = 0;
     for (int i = 0; i < n; ++i) {
         const lspk_linear_args& a = args[i];
         const bool pair = a.epilogue == LSPK_EPI_RELU2_MUL || a.epilogue == LSPK_EPI_SILU_MUL;
@@ -348,22 +365,6 @@ extern "C" int lspk_linear_batch(const lspk_linear_args* args, int n) {
         it.chunks = w0->chunks;
         it.groups = w0->groups;
         it.epilogue = a.epilogue;
-        it.unit0 = unit0;
-        it.q0 = q0;
-        it.cps = kSStageChunks / it.nm;
-        it.sub = (it.chunks + it.cps - 1) / it.cps;
-        unit0 += it.groups;
-        q0 += it.groups * it.sub;
     }
-    p.total_units = unit0;
-    static bool attr_set = false;
-    const size_t smem = stream_smem_bytes();
-    if (!attr_set) {
-        LSPK_CUDA(cudaFuncSetAttribute(ternary_gemv_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
-    }
-    int ctas = (unit0 + kSConsumers - 1) / kSConsumers;
-    if (ctas > sm_count()) ctas = sm_count();
-    LSPK_CUDA(launch(ternary_gemv_stream_kernel, dim3(ctas), dim3(kSThreads), smem, true, p));
-    return LSPK_OK;
+    return stream_launch(&p);
 }

@@ -236,6 +236,63 @@ int moe_forward(Moe* m, float* x, int B, int32_t* sel_out, float* selw_out, int3
     if (B > 1)      // a single token's two rows are listed by the router kernel itself
         LSPK_CUDA(launch(moe_group_kernel, dim3(1), dim3(32), 0, true, (const int*)m->sel, R, E, m->counts, m->rows, R));
 
+    if (B == 1) {
+        // A single token: its two experts' products are one-row products whose matrices the router has just chosen.
+        // Both experts of a stage go through ONE launch of the streamed batch (linear_stream.cu), which reads the
+        // expert indices on the device; same integer arithmetic as the eight-row kernel, so the same bits.
+        static StreamParams sp;
+        sp.n = 2;
+        for (int slot = 0; slot < 2; ++slot) {
+            StreamItem& it = sp.it[slot];
+            it = StreamItem{};
+            it.w[0] = m->w;
+            it.w[1] = m->w + m->mat_stride;
+            it.sel = m->sel + slot;
+            it.sel_stride = 3 * m->mat_stride;
+            it.sel_scales = m->scales;
+            it.scale_idx[0] = 0;
+            it.scale_idx[1] = 1;
+            it.out = m->inter + (size_t)slot * I;
+            it.acc[0] = acc_gate ? acc_gate + (size_t)slot * I : nullptr;
+            it.acc[1] = acc_up ? acc_up + (size_t)slot * I : nullptr;
+            it.x = m->xq;
+            it.xs = m->xs;
+            it.N = I;
+            it.K = H;
+            it.chunks = m->chunks_gu;
+            it.groups = m->groups_gu;
+            it.nm = 2;
+            it.epilogue = LSPK_EPI_RELU2_MUL;
+        }
+        if (int rc = stream_launch(&sp)) return rc;
+        if (int rc = norm_quant_rows_selected(m->inter, m->sub_norm, m->sel, m->xq2, m->xs2, R, I, m->eps)) return rc;
+        for (int slot = 0; slot < 2; ++slot) {
+            StreamItem& it = sp.it[slot];
+            it = StreamItem{};
+            it.w[0] = m->w + 2 * m->mat_stride;
+            it.sel = m->sel + slot;
+            it.sel_stride = 3 * m->mat_stride;
+            it.sel_scales = m->scales;
+            it.scale_idx[0] = 2;
+            it.scale_idx[1] = 2;
+            it.out = m->ydown + (size_t)slot * H;
+            it.acc[0] = acc_down ? acc_down + (size_t)slot * H : nullptr;
+            it.x = m->xq2 + (size_t)slot * I;
+            it.xs = m->xs2 + slot;
+            it.N = H;
+            it.K = I;
+            it.chunks = m->chunks_d;
+            it.groups = m->groups_d;
+            it.nm = 1;
+            it.epilogue = LSPK_EPI_STORE;
+        }
+        if (int rc = stream_launch(&sp)) return rc;
+        LSPK_CUDA(launch(moe_combine_kernel, dim3(B), dim3(256), 0, true, x, (const float*)m->ydown, (const float*)m->selw, H));
+        if (sel_out) LSPK_CUDA(cudaMemcpyAsync(sel_out, m->sel, (size_t)R * 4, cudaMemcpyDeviceToDevice, stream()));
+        if (selw_out) LSPK_CUDA(cudaMemcpyAsync(selw_out, m->selw, (size_t)R * 4, cudaMemcpyDeviceToDevice, stream()));
+        return LSPK_OK;
+    }
+
     // At most min(E, R) experts have rows; CTAs of the others leave at once.  Two resident CTAs per SM
     // over the experts that can be active keeps enough weight bytes in flight.
     const int active = E < R ? E : R;

@@ -21,7 +21,8 @@ namespace lspk {
 __global__ void embed_kernel(const int* __restrict__ tokens, int kind, const void* __restrict__ emb,
                              const float* __restrict__ scale, float* __restrict__ x, int H, int V,
                              const int* __restrict__ pos, const float* __restrict__ rope_cos,
-                             const float* __restrict__ rope_sin, float* __restrict__ rope_cur, int half) {
+                             const float* __restrict__ rope_sin, float* __restrict__ rope_cur, int half,
+                             int tokens_in_host_memory) {
     grid_dependency_launch();
     grid_dependency_wait();
     const int r = blockIdx.x;
@@ -32,7 +33,9 @@ __global__ void embed_kernel(const int* __restrict__ tokens, int kind, const voi
             rope_cur[(size_t)r * 2 * half + half + i] = rope_sin[(size_t)ps * half + i];
         }
     }
-    int tok = tokens[r];
+    int tok;
+    if (tokens_in_host_memory) asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(tok) : "l"(tokens + r) : "memory");
+    else tok = tokens[r];
     tok = min(max(tok, 0), V - 1);
     float* dst = x + (size_t)r * H;
     if (kind == 0) {
@@ -82,8 +85,11 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int V, unsi
 
 // End of a decode step: turn the argmax keys into token ids, make them the next step's input,
 // append them to the output list, advance every position, clear the keys.
+// host_pkt (optional, one sequence): mapped host word that receives (count of host-fed steps << 32 | token) in one
+// 8-byte store, so that a host that sees the count has the token.
 __global__ void finish_step_kernel(int* __restrict__ ctl, unsigned long long* __restrict__ best,
-                                   int* __restrict__ tokens_out, int batch, int out_cap) {
+                                   int* __restrict__ tokens_out, int batch, int out_cap,
+                                   unsigned long long* host_pkt, unsigned* host_seq) {
     grid_dependency_launch();
     grid_dependency_wait();
     const int b = threadIdx.x;
@@ -94,6 +100,12 @@ __global__ void finish_step_kernel(int* __restrict__ ctl, unsigned long long* __
         ctl[batch + b] = tok;
         if (step < out_cap) tokens_out[(size_t)step * batch + b] = tok;
         ctl[b] += 1;
+        if (host_pkt && b == 0) {
+            const unsigned seq = *host_seq + 1u;
+            *host_seq = seq;
+            const unsigned long long pkt = ((unsigned long long)seq << 32) | (unsigned long long)(uint32_t)tok;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(host_pkt), "l"(pkt) : "memory");
+        }
     }
     __syncthreads();
     if (b == 0) ctl[2 * batch] += 1;
@@ -108,7 +120,7 @@ __global__ void advance_pos_kernel(int* __restrict__ ctl, int seq, int by) {
 // ---- launch wrappers shared with the hybrid runtime (kernels must be launched from this file) ----
 int launch_embed(const int* tokens, int rows, int kind, const void* emb, const float* scale, float* x, int H, int V) {
     LSPK_CUDA(launch(embed_kernel, dim3(rows), dim3(256), 0, true, tokens, kind, emb, scale, x, H, V, (const int*)nullptr,
-                     (const float*)nullptr, (const float*)nullptr, (float*)nullptr, 0));
+                     (const float*)nullptr, (const float*)nullptr, (float*)nullptr, 0, 0));
     return LSPK_OK;
 }
 int launch_argmax_rows(const float* logits, int rows, int V, unsigned long long* best) {
@@ -117,7 +129,7 @@ int launch_argmax_rows(const float* logits, int rows, int V, unsigned long long*
 }
 int launch_finish_step(int* ctl, unsigned long long* best, int* tokens_out, int batch, int out_cap) {
     LSPK_CUDA(launch(finish_step_kernel, dim3(1), dim3(((batch + 31) / 32) * 32), 0, true, ctl, best, tokens_out,
-                     batch, out_cap));
+                     batch, out_cap, (unsigned long long*)nullptr, (unsigned*)nullptr));
     return LSPK_OK;
 }
 
@@ -250,13 +262,13 @@ int run_layer(State* s, int li, int rows, bool per_row_seq, int seq, bool skip_a
 
 // The kernels of one decode step for every sequence of the state (enqueued on the stream;
 // captured into a graph by the caller).
-static int enqueue_step(State* s, bool store_logits) {
+static int enqueue_step(State* s, bool store_logits, bool host_io = false) {
     Model* m = s->m;
     const lspk_model_config& c = m->cfg;
     const int B = s->batch, H = c.hidden_size, V = c.vocab_size;
-    LSPK_CUDA(launch(embed_kernel, dim3(B), dim3(256), 0, true, (const int*)(s->ctl + B), m->emb.kind,
-                     (const void*)m->emb.data, (const float*)m->emb.scale, s->x, H, V, (const int*)s->ctl,
-                     (const float*)s->rope_cos, (const float*)s->rope_sin, s->rope_cur, m->D() / 2));
+    LSPK_CUDA(launch(embed_kernel, dim3(B), dim3(256), 0, true, host_io ? (const int*)s->io_tok_dev : (const int*)(s->ctl + B),
+                     m->emb.kind, (const void*)m->emb.data, (const float*)m->emb.scale, s->x, H, V, (const int*)s->ctl,
+                     (const float*)s->rope_cos, (const float*)s->rope_sin, s->rope_cur, m->D() / 2, host_io ? 1 : 0));
     s->rope_cur_valid = true;
     for (int li = 0; li < c.num_layers; ++li)
         if (int rc = run_layer(s, li, B, B > 1, 0)) {
@@ -276,7 +288,8 @@ static int enqueue_step(State* s, bool store_logits) {
                                     m->final_norm.g, m->final_norm.is_bf16, c.rms_norm_eps, s->best)) return rc;
     }
     LSPK_CUDA(launch(finish_step_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, true, s->ctl, s->best,
-                     s->tokens_out, B, s->t_max));
+                     s->tokens_out, B, s->t_max, host_io ? s->io_pkt_dev : (unsigned long long*)nullptr,
+                     host_io ? s->io_seq_dev : (unsigned*)nullptr));
     return LSPK_OK;
 }
 
@@ -296,14 +309,15 @@ static int build_graph(State* s, int variant) {
     std::vector<int> saved(nctl);
     LSPK_CUDA(cudaMemcpyAsync(saved.data(), s->ctl, nctl * sizeof(int), cudaMemcpyDeviceToHost, stream()));
     LSPK_CUDA(cudaStreamSynchronize(stream()));
-    if (int rc = enqueue_step(s, variant == 1)) return rc;
+    if (int rc = enqueue_step(s, variant == 1, variant == 2)) return rc;
     LSPK_CUDA(cudaStreamSynchronize(stream()));
     LSPK_CUDA(cudaMemcpyAsync(s->ctl, saved.data(), nctl * sizeof(int), cudaMemcpyHostToDevice, stream()));
     LSPK_CUDA(cudaStreamSynchronize(stream()));
+    if (variant == 2) s->io_seq += 1;          // the warm-up step counted itself on the device
 
     cudaGraph_t g = nullptr;
     LSPK_CUDA(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_step(s, variant == 1);
+    int rc = enqueue_step(s, variant == 1, variant == 2);
     cudaError_t e = cudaStreamEndCapture(stream(), &g);
     if (rc) {
         if (g) cudaGraphDestroy(g);
@@ -507,6 +521,23 @@ lspk_state_t lspk_state_create(lspk_model_t h, int t_max, int batch, int kv_fp16
     rc |= dev_alloc((void**)&s->tok_rows, R * 4, &s->bytes);
     if (!rc && cudaMallocHost((void**)&s->h_int, (size_t)(t_max * batch + R + 16) * 4) != cudaSuccess) rc = 1;
     if (!rc && cudaMallocHost((void**)&s->h_logits, (size_t)s->logits_rows * V * 4) != cudaSuccess) rc = 1;
+    if (!rc && batch == 1) {
+        // the two words of the host-fed step (see State): mapped pinned memory and its device alias
+        void *io = nullptr, *io_dev = nullptr;
+        if (cudaHostAlloc(&io, 64, cudaHostAllocMapped) != cudaSuccess) rc = 1;
+        if (!rc && cudaHostGetDevicePointer(&io_dev, io, 0) != cudaSuccess) rc = 1;
+        if (io) {
+            memset(io, 0, 64);
+            s->io_pkt = static_cast<unsigned long long*>(io);
+            s->io_tok = reinterpret_cast<int*>(static_cast<char*>(io) + 16);
+        }
+        if (!rc) {
+            s->io_pkt_dev = static_cast<unsigned long long*>(io_dev);
+            s->io_tok_dev = reinterpret_cast<int*>(static_cast<char*>(io_dev) + 16);
+            rc |= dev_alloc((void**)&s->io_seq_dev, 4, &s->bytes);
+            if (!rc && cudaMemset(s->io_seq_dev, 0, 4) != cudaSuccess) rc = 1;
+        }
+    }
     if (!rc) {
         cudaError_t e = cudaMemset(s->cache_k, 0, cache_bytes);
         if (e == cudaSuccess) e = cudaMemset(s->cache_v, 0, cache_bytes);
@@ -536,6 +567,8 @@ int lspk_state_free(lspk_state_t h) {
     for (void* p : dev) cudaFree(p);
     if (s->h_int) cudaFreeHost(s->h_int);
     if (s->h_logits) cudaFreeHost(s->h_logits);
+    if (s->io_pkt) cudaFreeHost(s->io_pkt);
+    cudaFree(s->io_seq_dev);
     delete s;
     return LSPK_OK;
 }
@@ -588,6 +621,33 @@ int lspk_forward_step(lspk_state_t h, const int* tokens_host, float* logits_host
     for (int b = 0; b < B; ++b)
         if (s->host_pos[b] >= s->t_max)
             return fail(LSPK_ERR_STATE, "inference state exhausted: pos=%d >= t_max=%d", s->host_pos[b], s->t_max);
+    if (B == 1 && !logits_host && next_tokens_host && s->io_seq_dev) {
+        // One sequence, token id in, token id out: no copy operations and no stream wait.  The step's first kernel
+        // reads the token from mapped pinned memory; its last kernel stores (count << 32 | next token) there.
+        *(volatile int*)s->io_tok = tokens_host[0];
+        if (int rc = build_graph(s, 2)) return rc;
+        const unsigned want = ++s->io_seq;
+        LSPK_CUDA(cudaGraphLaunch(s->graph[2], stream()));
+        unsigned long long pkt = 0;
+        for (unsigned spins = 1;; ++spins) {
+            pkt = *(volatile unsigned long long*)s->io_pkt;
+            if ((unsigned)(pkt >> 32) == want) break;
+            if ((spins & 0x3fffu) == 0) {
+                // every so often ask the driver: an error ends the wait, and so does a stream that has finished
+                // without the packet showing the expected count (host and device counts out of step)
+                const cudaError_t q = cudaStreamQuery(stream());
+                if (q == cudaErrorNotReady) continue;
+                pkt = *(volatile unsigned long long*)s->io_pkt;
+                if (q == cudaSuccess && (unsigned)(pkt >> 32) == want) break;
+                s->io_seq = (unsigned)(pkt >> 32);
+                if (q != cudaSuccess) return fail(LSPK_ERR_CUDA, "lspk_forward_step: %s", cudaGetErrorString(q));
+                return fail(LSPK_ERR_STATE, "lspk_forward_step: step %u finished without its result packet", want);
+            }
+        }
+        next_tokens_host[0] = (int)(uint32_t)pkt;
+        s->host_pos[0] += 1;
+        return LSPK_OK;
+    }
     const int variant = (logits_host || B > 1) ? 1 : 0;
     if (int rc = build_graph(s, variant)) return rc;
     memcpy(s->h_int, tokens_host, (size_t)B * 4);

@@ -56,8 +56,17 @@ struct State {
     int* h_int = nullptr;             // pinned staging for ints
     float* h_logits = nullptr;        // pinned staging for logits
     std::vector<int> host_pos;
-    cudaGraphExec_t graph[2] = {nullptr, nullptr};   // [0] no logits store, [1] with logits
-    unsigned graph_gen[2] = {0, 0};   // scratch_generation() at capture: a later move of library scratch voids the graph
+    // Host-fed single step without copy operations (one sequence, no logits): the step's first kernel reads the token
+    // from mapped pinned memory, its last kernel stores (step number << 32 | next token) there with one 8-byte store
+    // and the host polls that word instead of waiting for the stream.
+    int* io_tok = nullptr;                 // mapped pinned: token in (host pointer)
+    unsigned long long* io_pkt = nullptr;  // mapped pinned: packet out (host pointer)
+    int* io_tok_dev = nullptr;             // the same two words as the device sees them
+    unsigned long long* io_pkt_dev = nullptr;
+    unsigned* io_seq_dev = nullptr;        // device: steps of this kind finished so far
+    unsigned io_seq = 0;                   // host: the same count
+    cudaGraphExec_t graph[3] = {nullptr, nullptr, nullptr};   // [0] no logits store, [1] with logits, [2] host-fed step
+    unsigned graph_gen[3] = {0, 0, 0};   // scratch_generation() at capture: a later move of library scratch voids the graph
     int graph_nodes = 0;
     size_t bytes = 0;
     size_t kv_elem() const { return kv_fp16 ? 2 : 4; }

@@ -110,3 +110,44 @@ def test_long_context_at_head_dim_128(shaped, oracle, port):
     for t in prompt[n:]:
         e = _rel_l2(rt.forward_one(dm, st, t), oracle.forward_one(port, m, ost, t))
         assert e <= max(2.0 * e0, 0.1) + 0.05, f"decode step error {e:.3e} vs prefill error {e0:.3e}"
+
+
+@pytest.mark.parametrize("kv", ["fp16", "fp32"])
+def test_batched_decode_is_bit_identical_to_single_sequences(shaped, kv):
+    """A sequence's activations do not depend on what it is batched with: eight sequences of different lengths
+    decoded in lock step (eight-row products, row-quantiser kernel, 128-thread attention CTAs) against each sequence
+    decoded alone (one-row products with the fused quantiser, 256-thread attention CTAs), along the same tokens, at
+    head size 128 and across the key counts where an attention rank goes from one key batch to two.  Compared bit
+    for bit: the K and V rows every layer writes for the decoded positions (those of layer l + 1 are functions of
+    layer l's attention output).  The logits come from two LM-head kernels that sum in different orders (one row:
+    CUDA cores; several rows: tensor cores on a three-term bf16 split), so they are compared to 1e-5 of their
+    spread and through the greedy choice."""
+    cfg, m, dm = shaped
+    rng = np.random.default_rng(21)
+    lens = (3, 40, 17, 64, 9, 130, 33, 255)
+    steps = 6
+    prompts = [[int(t) for t in rng.integers(0, cfg.vocab_size, n)] for n in lens]
+    forced = rng.integers(0, cfg.vocab_size, (steps, len(lens))).astype(np.int32)
+    t_max = max(lens) + steps + 1
+    B = len(lens)
+    st = rt.init_state(dm, t_max, batch=B, kv_dtype=kv)
+    for b, p in enumerate(prompts):
+        ids = np.ascontiguousarray(p, dtype=np.int32)
+        assert st.lib.lspk_forward_prefill(st.handle, b, ids.ctypes.data, int(ids.size), None, None, None) == 0
+    together = [rt.forward_step(st, forced[i], want_logits=True)[1].copy() for i in range(steps)]
+    kv_together = [[st.read_kv(li, lens[b] + steps, seq=b) for li in range(cfg.num_layers)] for b in range(B)]
+    st.close()
+    for b, p in enumerate(prompts):
+        s1 = rt.init_state(dm, t_max, kv_dtype=kv)
+        rt.forward_prefill(dm, s1, p)
+        for i in range(steps):
+            alone = rt.forward_one(dm, s1, int(forced[i, b]))
+            spread = float(alone.max() - alone.min())
+            assert np.abs(alone - together[i][b]).max() <= 1e-5 * spread, (b, i)
+            assert int(np.argmax(alone)) == int(np.argmax(together[i][b])), (b, i)
+        for li in range(cfg.num_layers):
+            k1, v1 = s1.read_kv(li, lens[b] + steps)
+            k8, v8 = kv_together[b][li]
+            assert np.array_equal(k1.view(np.uint32), k8.view(np.uint32)), (b, li)
+            assert np.array_equal(v1.view(np.uint32), v8.view(np.uint32)), (b, li)
+        s1.close()
