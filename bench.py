@@ -406,6 +406,43 @@ def measure_shape(lib, dev, K, synthetic, rng, peak, name, Ms, copies_mb=300.0):
     return rows
 
 
+def cpu_shape_medians(synthetic, rng, shapes, ms):
+    """The reference's own CPU kernels at the same shapes: median microseconds of matmul_lut_{tier}_m1 (one row) and
+    of the batched kernel (more rows), int8 rows in, for each compiled build, with all host threads and with one."""
+    orc = entry.load_oracle()
+    best = orc.ref_tier()
+    tiers = [t for t in ("avx512", "avx2") if best is not None and (t != "avx512" or best == "avx512")]
+    out = []
+    for tier in tiers:
+        kern = orc.Kernels("ref", tier)
+        all_threads = kern.max_threads()
+        for name in shapes:
+            N, Kd = synthetic.BITNET_2B_SHAPES[name]
+            proj = synthetic.random_projection_fast(rng, N, Kd)
+            for M in ms:
+                x = rng.standard_normal((M, Kd)).astype(np.float32)
+                xq, xs = np.empty((M, Kd), np.int8), np.empty(M, np.float32)
+                kern.quantize_activation_batched(x, xq, xs)
+                y = np.empty((M, N), np.float32)
+                row = {"build": tier, "threads": all_threads, "shape": name, "N": N, "K": Kd, "M": M}
+                for threads in (all_threads, 1):
+                    if not _set_omp_threads(threads):
+                        continue
+                    reps = 40 if M <= 8 else (8 if M <= 128 else 3)
+                    times = []
+                    for _ in range(reps):
+                        t0 = time.perf_counter()
+                        if M == 1:
+                            kern.matmul_packed_m1(xq[0], proj.w_packed, proj.scale, float(xs[0]), y[0])
+                        else:
+                            kern.matmul_packed_mT(xq, xs, proj.w_packed, proj.scale, y)
+                        times.append(time.perf_counter() - t0)
+                    row["us_all_threads" if threads > 1 else "us_1_thread"] = 1e6 * statistics.median(times)
+                _set_omp_threads(all_threads)
+                out.append(row)
+    return out
+
+
 def run_sweep(args):
     """The BitNet-2B projection shapes x token counts (M = 1, 8, 32, 128, 512)."""
     entry.load_package()
@@ -420,7 +457,9 @@ def run_sweep(args):
     ms = tuple(int(t) for t in args.sweep_m.split(",") if t)
     for name in shapes:
         rows += measure_shape(lib, dev, K, synthetic, rng, peak, name, ms, args.sweep_mb)
-    print(json.dumps({"workload": "sweep", "peak_GBps": peak, "peak_kind": peak_kind, "rows": rows}))
+    cpu = None if args.no_cpu_baseline else cpu_shape_medians(synthetic, np.random.default_rng(1), shapes, ms)
+    print(json.dumps({"workload": "sweep", "peak_GBps": peak, "peak_kind": peak_kind, "rows": rows,
+                      "cpu_reference_kernels": cpu}))
 
 
 def run_gemv(args):
