@@ -203,12 +203,15 @@ __device__ __forceinline__ uint32_t bf16_rn_bits(float v) {          // round to
     return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
 }
 
-// NT: tiles of eight rows of x (1 or 2).  Shared memory: [3 terms][8 * NT rows][H + 32] bf16.
+// NT: tiles of eight rows of x (1 or 2) a CTA holds.  Shared memory: [3 terms][8 * NT rows][H + 32] bf16.
+// passes: more rows than a CTA holds are served side by side in ONE launch: CTA b takes the row block b % passes
+// and the table tiles of position b / passes, so the CTAs that need the same table rows run next to each other
+// and the table comes from HBM once (the second reader finds it in L2).
 template <int NT>
 __global__ void __launch_bounds__(kLmThreads)
-lm_head_mma_kernel(const uint4* __restrict__ emb, const float* __restrict__ x, float* __restrict__ logits, int T, int V,
+lm_head_mma_kernel(const uint4* __restrict__ emb, const float* __restrict__ x, float* __restrict__ logits, int T_all, int V,
                    int H, const void* __restrict__ norm_gamma, int gamma_is_bf16, float eps,
-                   unsigned long long* __restrict__ best_keys) {
+                   unsigned long long* __restrict__ best_keys, int passes) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint16_t* xs = reinterpret_cast<uint16_t*>(smem_raw);
     __shared__ float red[32];
@@ -219,12 +222,17 @@ lm_head_mma_kernel(const uint4* __restrict__ emb, const float* __restrict__ x, f
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     constexpr int R = 8 * NT;
+    const int pass = (int)blockIdx.x % passes, cta = (int)blockIdx.x / passes, ncta = (int)gridDim.x / passes;
+    const int T = min(R, T_all - pass * R);                // rows of this CTA's block
+    x += (size_t)pass * R * H;
+    if (logits) logits += (size_t)pass * R * V;
+    if (best_keys) best_keys += pass * R;
     const int ld = H + 32;                                 // row stride in bf16: 64 bytes of padding make the quarter-warp 16-byte loads conflict-free
     const int steps = H / 32;                              // host guarantees H % 32 == 0
     const size_t row_chunks = (size_t)H / 8;
 
     // table rows of this warp's first tile can be requested before the activations exist
-    auto tile_of = [&](int i) { return (blockIdx.x * kLmWarps + warp) + i * gridDim.x * kLmWarps; };
+    auto tile_of = [&](int i) { return (cta * kLmWarps + warp) + i * ncta * kLmWarps; };
     uint4 buf[kLmmStepsInFlight][2];
     auto request = [&](int v0, int s0) {
 #pragma unroll
@@ -379,36 +387,34 @@ int lm_head_launch(int kind, const void* emb, const float* emb_scale, const floa
     if (grid > cap) grid = cap;
     const uint4* e4 = reinterpret_cast<const uint4*>(emb);
     if (kind == 0 && T > 1 && H % 32 == 0 && (logits || best_key)) {
-        // several rows against the bf16 table: tensor-core kernel, up to sixteen rows per pass
-        // sixteen rows per pass where their three bf16 terms fit the shared memory (H <= 2100), else eight
-        const int per_pass = ((size_t)3 * 16 * (H + 32) * 2 <= 200 * 1024 && T > 8) ? 16 : 8;
-        for (int t0 = 0; t0 < T; t0 += per_pass) {
-            const int tt = (T - t0) < per_pass ? (T - t0) : per_pass;
-            const int nt = tt > 8 ? 2 : 1;
-            const size_t smem = (size_t)3 * 8 * nt * (H + 32) * 2;
-            LSPK_REQUIRE(smem <= 200 * 1024, "lm_head: H=%d too large for %d rows", H, tt);
-            int mgrid = (V + 16 * kLmWarps - 1) / (16 * kLmWarps);
-            const int mcap = sm_count();
-            if (mgrid > mcap) mgrid = mcap;
-            static bool attr1 = false, attr2 = false;
-            cudaError_t e = cudaSuccess;
-            if (nt == 1) {
-                if (!attr1) e = cudaFuncSetAttribute(lm_head_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-                attr1 = attr1 || e == cudaSuccess;
-                if (e == cudaSuccess)
-                    e = launch(lm_head_mma_kernel<1>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x + (size_t)t0 * H,
-                               logits ? logits + (size_t)t0 * V : (float*)nullptr, tt, V, H, norm_gamma, gamma_is_bf16, eps,
-                               best_key ? best_key + t0 : (unsigned long long*)nullptr);
-            } else {
-                if (!attr2) e = cudaFuncSetAttribute(lm_head_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-                attr2 = attr2 || e == cudaSuccess;
-                if (e == cudaSuccess)
-                    e = launch(lm_head_mma_kernel<2>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x + (size_t)t0 * H,
-                               logits ? logits + (size_t)t0 * V : (float*)nullptr, tt, V, H, norm_gamma, gamma_is_bf16, eps,
-                               best_key ? best_key + t0 : (unsigned long long*)nullptr);
-            }
-            if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head (mma) launch failed: %s", cudaGetErrorString(e));
+        // several rows against the bf16 table: tensor-core kernel.  A CTA holds sixteen rows where their three bf16
+        // terms fit the shared memory (H <= 2100), else eight; more rows than that are row blocks served side by
+        // side in one launch (the kernel's `passes`), so the table is read from HBM once
+        const int nt = ((size_t)3 * 16 * (H + 32) * 2 <= 200 * 1024 && T > 8) ? 2 : 1;
+        const int rows_per_cta = 8 * nt;
+        const int passes = (T + rows_per_cta - 1) / rows_per_cta;
+        const size_t smem = (size_t)3 * rows_per_cta * (H + 32) * 2;
+        LSPK_REQUIRE(smem <= 200 * 1024, "lm_head: H=%d too large for %d rows", H, rows_per_cta);
+        LSPK_REQUIRE(passes <= sm_count(), "lm_head: too many rows (%d) for one launch", T);
+        int per_pass = (V + 16 * kLmWarps - 1) / (16 * kLmWarps);
+        if (per_pass > sm_count() / passes) per_pass = sm_count() / passes;
+        const int mgrid = per_pass * passes;
+        static bool attr1 = false, attr2 = false;
+        cudaError_t e = cudaSuccess;
+        if (nt == 1) {
+            if (!attr1) e = cudaFuncSetAttribute(lm_head_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            attr1 = attr1 || e == cudaSuccess;
+            if (e == cudaSuccess)
+                e = launch(lm_head_mma_kernel<1>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x, logits, T, V, H, norm_gamma,
+                           gamma_is_bf16, eps, best_key, passes);
+        } else {
+            if (!attr2) e = cudaFuncSetAttribute(lm_head_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            attr2 = attr2 || e == cudaSuccess;
+            if (e == cudaSuccess)
+                e = launch(lm_head_mma_kernel<2>, dim3(mgrid), dim3(kLmThreads), smem, true, e4, x, logits, T, V, H, norm_gamma,
+                           gamma_is_bf16, eps, best_key, passes);
         }
+        if (e != cudaSuccess) return fail(LSPK_ERR_CUDA, "lm_head (mma) launch failed: %s", cudaGetErrorString(e));
         return LSPK_OK;
     }
     // several rows with a greedy choice wanted, on the CUDA-core kernels: logits are stored and a row argmax follows
