@@ -7,8 +7,8 @@
 //   state[h,p,n] = state * dA + (dt * x[h,p]) * B[n];  y[h,p] = sum_n state * C[n] + D_h * x[h,p]
 //   out = out_proj(quant(RMSNorm(y * SiLU(z))));  x += out      ternary linear, residual epilogue
 // The state update is the HBM-bound part: the fp32 state [heads, head_dim, d_state] (2.6 MB per
-// sequence and layer at 80 x 64 x 128) is read and written once per step.  One CTA owns half a head
-// (32 rows of 128 states, 16 KB in and out); grid = 2 * heads x sequences.
+// sequence and layer at 80 x 64 x 128) is read and written once per step.  One CTA owns half a head (32 rows of
+// 128 states, 16 KB in and out; grid = 2 * heads x sequences) or, for four and more sequences, a whole head.
 #include "internal.cuh"
 #include "../../include/lspk_hybrid.h"
 
@@ -28,31 +28,42 @@ struct Mamba {
 
 __device__ __forceinline__ float silu_f(float v) { return __fdiv_rn(v, __fadd_rn(expf(-v), 1.0f)); }
 
-// P = head_dim = 64, N = d_state = 128: a CTA of 256 threads owns 32 rows; 8 threads share a row.
-__global__ void __launch_bounds__(256)
+// P = head_dim = 64, N = d_state = 128.  A CTA of 256 threads owns ROWS rows of one head (32: half a head, grid
+// 2 * heads x sequences; 64: a whole head, grid heads x sequences); 8 threads share a row, a thread holds 16 state
+// values of each of its ROWS / 32 rows.  Whole-head CTAs keep twice the state bytes in flight per thread and run
+// the B / C convolution once per head instead of twice: the form for several sequences, where the launch is bound
+// by HBM; with one sequence the half-head form covers more SMs.  Same arithmetic per element in both.
+template <int ROWS>
+__global__ void __launch_bounds__(256, ROWS == 64 ? 4 : 1)
 mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const int* __restrict__ pos_ptr,
                   const float* __restrict__ conv_w, const float* __restrict__ conv_b, const float* __restrict__ A,
                   const float* __restrict__ dt_bias, const float* __restrict__ Dskip, float* __restrict__ vout,
                   int d_inner, int conv_dim, int in_out, size_t state_floats) {
-    constexpr int P = 64, N = 128, ROWS = 32;
+    constexpr int P = 64, N = 128, RS = ROWS / 32;       // RS: rows per thread
+    static_assert(ROWS == 32 || ROWS == 64, "a CTA owns half a head or a whole one");
     __shared__ float xs_s[ROWS];
     __shared__ __align__(16) float B_s[N];
     __shared__ __align__(16) float C_s[N];
-    const int b = blockIdx.y, hh = blockIdx.x, head = hh >> 1, p0 = (hh & 1) * ROWS;
+    const int b = blockIdx.y, hh = blockIdx.x, head = ROWS == 64 ? hh : hh >> 1, p0 = ROWS == 64 ? 0 : (hh & 1) * ROWS;
     const int tid = threadIdx.x;
-    // This thread's 16 state values are requested before the dependency wait: the state was last written by
-    // this kernel one decode step ago, not by the projection that runs in front of it, and it is the bulk
-    // of the bytes (16 KB per CTA each way against 1.3 KB of projection output).
-    float4 st[4];
-    float4* srow;
-    {
-        float* ssm0 = state + (size_t)b * state_floats + (size_t)conv_dim * 4;
-        srow = reinterpret_cast<float4*>(ssm0 + ((size_t)(head * P + p0 + (tid >> 3)) * N + (tid & 7) * 16));
-#pragma unroll
-        for (int q = 0; q < 4; ++q) st[q] = srow[q];
-    }
     grid_dependency_launch();
     grid_dependency_wait();
+    // This thread's state values are requested first thing after the dependency wait, ahead of the convolution's
+    // loads, so that their trip to HBM (16 KB per 32 rows each way, the bulk of the bytes) runs under the
+    // convolution.  Not before the wait: the state was written by this kernel one decode step ago, and with
+    // programmatic launch nothing orders code in front of the wait after a kernel that is not the direct
+    // predecessor (in a short chain -- a single layer stepped in a loop -- that kernel may still be running).
+    float4 st[RS][4];
+    float4* srow[RS];
+    {
+        float* ssm0 = state + (size_t)b * state_floats + (size_t)conv_dim * 4;
+#pragma unroll
+        for (int rr = 0; rr < RS; ++rr) {
+            srow[rr] = reinterpret_cast<float4*>(ssm0 + ((size_t)(head * P + p0 + 32 * rr + (tid >> 3)) * N + (tid & 7) * 16));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) st[rr][q] = srow[rr][q];
+        }
+    }
     const float* zrow = zx + (size_t)b * in_out;
     const float* xbc_raw = zrow + d_inner;
     const float* dt_raw = zrow + d_inner + conv_dim;
@@ -60,12 +71,14 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     // behind the ring: the state matrices [heads][P][N] (srow above)
     const int pos = pos_ptr[b];
     const int slot = pos & 3;
-    // per-head scalars and this thread's gate input: requested here so that their round trip overlaps the
+    // per-head scalars and this thread's gate inputs: requested here so that their round trip overlaps the
     // convolution's (they are used after the barrier below)
     const float dt_in = dt_raw[head], dt_b = dt_bias[head], a_head = A[head], d_head = Dskip[head];
-    const float z_gate = (tid & 7) == 0 ? zrow[head * P + p0 + (tid >> 3)] : 0.0f;
+    float z_gate[RS];
+#pragma unroll
+    for (int rr = 0; rr < RS; ++rr) z_gate[rr] = (tid & 7) == 0 ? zrow[head * P + p0 + 32 * rr + (tid >> 3)] : 0.0f;
 
-    // depthwise conv step + SiLU for the channels this CTA needs: its 32 x-channels, all of B and C
+    // depthwise conv step + SiLU for the channels this CTA needs: its ROWS x-channels, all of B and C
     for (int idx = tid; idx < ROWS + 2 * N; idx += 256) {
         int c;
         if (idx < ROWS) c = head * P + p0 + idx;
@@ -88,31 +101,36 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     const float dv = __fadd_rn(dt_in, dt_b);
     const float dt = dv > 20.0f ? dv : log1pf(expf(dv));
     const float dA = expf(__fmul_rn(dt, a_head));
-    const int p = tid >> 3, seg = tid & 7;
-    const float xv = xs_s[p];
-    const float dtx = __fmul_rn(dt, xv);
-    float ysum = 0.0f;
+    const int seg = tid & 7;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float4 Bv = *reinterpret_cast<const float4*>(B_s + seg * 16 + q * 4);
-        const float4 Cv = *reinterpret_cast<const float4*>(C_s + seg * 16 + q * 4);
-        st[q].x = __fadd_rn(__fmul_rn(st[q].x, dA), __fmul_rn(dtx, Bv.x));
-        st[q].y = __fadd_rn(__fmul_rn(st[q].y, dA), __fmul_rn(dtx, Bv.y));
-        st[q].z = __fadd_rn(__fmul_rn(st[q].z, dA), __fmul_rn(dtx, Bv.z));
-        st[q].w = __fadd_rn(__fmul_rn(st[q].w, dA), __fmul_rn(dtx, Bv.w));
-        ysum = fmaf(st[q].x, Cv.x, ysum);
-        ysum = fmaf(st[q].y, Cv.y, ysum);
-        ysum = fmaf(st[q].z, Cv.z, ysum);
-        ysum = fmaf(st[q].w, Cv.w, ysum);
-        srow[q] = st[q];
-    }
-    ysum += __shfl_xor_sync(0xffffffffu, ysum, 4);
-    ysum += __shfl_xor_sync(0xffffffffu, ysum, 2);
-    ysum += __shfl_xor_sync(0xffffffffu, ysum, 1);
-    if (seg == 0) {
-        const int ch = head * P + p0 + p;
-        const float y = __fadd_rn(ysum, __fmul_rn(d_head, xv));
-        vout[(size_t)b * d_inner + ch] = __fmul_rn(y, silu_f(z_gate));
+    for (int rr = 0; rr < RS; ++rr) {
+        const int p = 32 * rr + (tid >> 3);
+        const float xv = xs_s[p];
+        const float dtx = __fmul_rn(dt, xv);
+        float ysum = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 Bv = *reinterpret_cast<const float4*>(B_s + seg * 16 + q * 4);
+            const float4 Cv = *reinterpret_cast<const float4*>(C_s + seg * 16 + q * 4);
+            float4 s4 = st[rr][q];
+            s4.x = __fadd_rn(__fmul_rn(s4.x, dA), __fmul_rn(dtx, Bv.x));
+            s4.y = __fadd_rn(__fmul_rn(s4.y, dA), __fmul_rn(dtx, Bv.y));
+            s4.z = __fadd_rn(__fmul_rn(s4.z, dA), __fmul_rn(dtx, Bv.z));
+            s4.w = __fadd_rn(__fmul_rn(s4.w, dA), __fmul_rn(dtx, Bv.w));
+            ysum = fmaf(s4.x, Cv.x, ysum);
+            ysum = fmaf(s4.y, Cv.y, ysum);
+            ysum = fmaf(s4.z, Cv.z, ysum);
+            ysum = fmaf(s4.w, Cv.w, ysum);
+            srow[rr][q] = s4;
+        }
+        ysum += __shfl_xor_sync(0xffffffffu, ysum, 4);
+        ysum += __shfl_xor_sync(0xffffffffu, ysum, 2);
+        ysum += __shfl_xor_sync(0xffffffffu, ysum, 1);
+        if (seg == 0) {
+            const int ch = head * P + p0 + p;
+            const float y = __fadd_rn(ysum, __fmul_rn(d_head, xv));
+            vout[(size_t)b * d_inner + ch] = __fmul_rn(y, silu_f(z_gate[rr]));
+        }
     }
 }
 
@@ -148,9 +166,14 @@ int mamba_step(Mamba* m, float* x, float* state, const int* pos, int B) {
     a.eps = m->cfg.eps;
     // several rows: linear_cuda_core quantises them once, straight into the eight-row kernel's tile layout
     if (int rc = linear_cuda_core(&a)) return rc;
-    LSPK_CUDA(launch(mamba2_ssu_kernel, dim3(m->cfg.nheads * 2, B), dim3(256), 0, true, (const float*)m->zx, state, pos,
-                     (const float*)m->conv_w, (const float*)m->conv_b, (const float*)m->A, (const float*)m->dt_bias,
-                     (const float*)m->D, m->v, m->d_inner, m->conv_dim, m->in_out, m->state_floats()));
+    if (B >= 4)
+        LSPK_CUDA(launch(mamba2_ssu_kernel<64>, dim3(m->cfg.nheads, B), dim3(256), 0, true, (const float*)m->zx, state, pos,
+                         (const float*)m->conv_w, (const float*)m->conv_b, (const float*)m->A, (const float*)m->dt_bias,
+                         (const float*)m->D, m->v, m->d_inner, m->conv_dim, m->in_out, m->state_floats()));
+    else
+        LSPK_CUDA(launch(mamba2_ssu_kernel<32>, dim3(m->cfg.nheads * 2, B), dim3(256), 0, true, (const float*)m->zx, state, pos,
+                         (const float*)m->conv_w, (const float*)m->conv_b, (const float*)m->A, (const float*)m->dt_bias,
+                         (const float*)m->D, m->v, m->d_inner, m->conv_dim, m->in_out, m->state_floats()));
     lspk_linear_args o = {};
     o.w[0] = m->out_proj;
     o.out[0] = x;
