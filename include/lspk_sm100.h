@@ -134,7 +134,9 @@ typedef struct {
  * rows: the TMA + tcgen05 GEMM (all four epilogues; the gated prologue stays on the tile kernel).
  * With more than one row of fp32 input the rows are normalised + quantised once, by a separate kernel,
  * into library scratch that grows with cudaMalloc: make the first call of a new size outside stream
- * capture. */
+ * capture.  The kernels request the packed weights and gamma before they wait for the work queued ahead of them
+ * on the library stream: both must be complete in memory when the call is made (the upload functions of this
+ * header synchronise); activations, residuals and outputs are ordered after everything queued before. */
 int lspk_linear(const lspk_linear_args* a);
 int lspk_linear_force_path(int path);   /* 0 auto, 1 CUDA-core kernel only, 2 tcgen05 only */
 /* n independent one-row products in ONE launch: product i is args[i], which must have M == 1 and the int8
