@@ -666,10 +666,10 @@ def main():
     # ---- end to end through the public API: host feeds each token, reads each greedy token ----
     def tg128_host():
         state.pos = PROMPT_LEN
-        tok = np.array([int(first[0])], dtype=np.int32)
+        tok = int(first[0])
         t0 = time.perf_counter()
         for _ in range(GEN_LEN):
-            tok = rt.forward_step(state, tok)
+            tok = rt.forward_token(state, tok)
         return time.perf_counter() - t0
 
     if args.skip_extras:
@@ -847,7 +847,7 @@ def main():
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4 * GEN_LEN,
                 "d2h_bytes_per_step": 4 * GEN_LEN,
-                "how": "host loop over lspk_forward_step: token id up from pinned memory, greedy token id back, every step"},
+                "how": "host loop over runtime.forward_token (lspk_forward_step): token id up from pinned memory, greedy token id back, every step"},
         "e2e_logits_to_host": {"value": e2e_logits_value, "unit": "tok/s", "d2h_bytes_per_step": 4 * cfg.vocab_size * GEN_LEN,
                                "how": "forward_one returning fp32 logits [V] to the host + np.argmax, the reference API's loop"},
         "prefill": {"tokens": PROMPT_LEN, "ms": pp_ms, "tok_s": PROMPT_LEN / (pp_ms / 1000.0),

@@ -142,6 +142,9 @@ class InferState:
         if not self.handle:
             raise _k.KernelError(_k.last_error())
         self.vocab = c.vocab_size
+        # argument words of forward_token, made once (a ctypes conversion per call costs more than the call)
+        self._tok_in = (ctypes.c_int * 1)()
+        self._tok_out = (ctypes.c_int * 1)()
 
     @property
     def pos(self) -> int:
@@ -204,6 +207,17 @@ def forward_one(model, state: InferState, token_id: int) -> np.ndarray:
     if rc:
         _raise_state(state.lib, rc)
     return logits
+
+
+def forward_token(state: InferState, token_id: int) -> int:
+    """One decode step of a single sequence, token id in, greedy next token id out: the step of a host loop that
+    chooses its own tokens (sampling, constraints, stop strings) and needs no logits.  No copy operation and no
+    stream synchronisation on this path (lspk_forward_step, one sequence, no logits)."""
+    state._tok_in[0] = token_id
+    rc = state.lib.lspk_forward_step(state.handle, state._tok_in, None, state._tok_out)
+    if rc:
+        _raise_state(state.lib, rc)
+    return state._tok_out[0]
 
 
 def forward_step(state: InferState, tokens, want_logits: bool = False):

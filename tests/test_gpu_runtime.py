@@ -69,6 +69,17 @@ def test_greedy_tokens_match_reference(toy, gold):
         toks.append(int(np.argmax(lg)))
         lg = rt.forward_one(dm, st, toks[-1])
     assert toks == [int(t) for t in gold["greedy24"]]
+    # host-driven loop on token ids only (the step without copy operations), interleaved with a rollback
+    st = rt.init_state(dm, len(prompt) + 24, kv_dtype="fp32")
+    tok = int(np.argmax(rt.forward_prefill(dm, st, prompt)))
+    toks = [tok]
+    for i in range(23):
+        tok = rt.forward_token(st, tok)
+        toks.append(tok)
+        if i == 10:                       # take the last step back and repeat it: same token again
+            st.pos = st.pos - 1
+            assert rt.forward_token(st, toks[-2]) == tok
+    assert toks == [int(t) for t in gold["greedy24"]]
 
 
 def test_speculative_decode_matches_reference_and_greedy(toy, gold):
