@@ -42,8 +42,11 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
     constexpr int P = 64, N = 128, RS = ROWS / 32;       // RS: rows per thread
     static_assert(ROWS == 32 || ROWS == 64, "a CTA owns half a head or a whole one");
     __shared__ float xs_s[ROWS];
-    __shared__ __align__(16) float B_s[N];
-    __shared__ __align__(16) float C_s[N];
+    // B and C with four floats of padding after every 16: the eight threads of a row read 16-byte pieces 80 bytes
+    // apart, which fall into eight different bank groups (64 bytes apart they collide four ways)
+    constexpr int NPAD = N + N / 16 * 4;
+    __shared__ __align__(16) float B_s[NPAD];
+    __shared__ __align__(16) float C_s[NPAD];
     const int b = blockIdx.y, hh = blockIdx.x, head = ROWS == 64 ? hh : hh >> 1, p0 = ROWS == 64 ? 0 : (hh & 1) * ROWS;
     const int tid = threadIdx.x;
     grid_dependency_launch();
@@ -78,23 +81,48 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
 #pragma unroll
     for (int rr = 0; rr < RS; ++rr) z_gate[rr] = (tid & 7) == 0 ? zrow[head * P + p0 + 32 * rr + (tid >> 3)] : 0.0f;
 
-    // depthwise conv step + SiLU for the channels this CTA needs: its ROWS x-channels, all of B and C
-    for (int idx = tid; idx < ROWS + 2 * N; idx += 256) {
-        int c;
-        if (idx < ROWS) c = head * P + p0 + idx;
-        else c = d_inner + (idx - ROWS);
-        const float newv = xbc_raw[c];
-        float acc = conv_b[c];
+    // depthwise conv step + SiLU for the channels this CTA needs: its ROWS x-channels, all of B and C.  A thread
+    // takes channel index tid and, the first ROWS + 2 N - 256 threads, a second one; everything both need (the
+    // newest input, the bias, the four taps as one 16-byte load, the four ring slots as another) is requested
+    // before either is computed, so the two cost one trip to memory, not two.
+    constexpr int NCH2 = ROWS + 2 * N - 256;     // channels beyond one per thread
+    static_assert(NCH2 > 0 && NCH2 <= 256, "one or two channels per thread");
+    const bool second = tid < NCH2;
+    int cch[2];
+    float newv[2], bias[2];
+    float4 taps[2], hist[2];
 #pragma unroll
-        for (int j = 0; j < 3; ++j)
-            acc = __fadd_rn(acc, __fmul_rn(conv_w[c * 4 + j], ring[(size_t)c * 4 + ((pos - 3 + j) & 3)]));
-        acc = __fadd_rn(acc, __fmul_rn(conv_w[c * 4 + 3], newv));
-        const float act = silu_f(acc);
-        if (idx < ROWS) xs_s[idx] = act;
-        else if (idx < ROWS + N) B_s[idx - ROWS] = act;
-        else C_s[idx - ROWS - N] = act;
-        // the newest input replaces the oldest slot; nobody reads that slot during this step
-        if (idx < ROWS || hh == 0) ring[(size_t)c * 4 + slot] = newv;
+    for (int k = 0; k < 2; ++k) {
+        const int idx = tid + 256 * k;
+        cch[k] = idx < ROWS ? head * P + p0 + idx : d_inner + (idx - ROWS);
+        if (k == 0 || second) {
+            newv[k] = xbc_raw[cch[k]];
+            bias[k] = conv_b[cch[k]];
+            taps[k] = *reinterpret_cast<const float4*>(conv_w + (size_t)cch[k] * 4);
+            hist[k] = *reinterpret_cast<const float4*>(ring + (size_t)cch[k] * 4);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        if (k == 0 || second) {
+            const int idx = tid + 256 * k;
+            const float h4[4] = {hist[k].x, hist[k].y, hist[k].z, hist[k].w};
+            const float w4[4] = {taps[k].x, taps[k].y, taps[k].z, taps[k].w};
+            float acc = bias[k];
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const int sl = (pos - 3 + j) & 3;
+                const float hv = sl == 0 ? h4[0] : sl == 1 ? h4[1] : sl == 2 ? h4[2] : h4[3];
+                acc = __fadd_rn(acc, __fmul_rn(w4[j], hv));
+            }
+            acc = __fadd_rn(acc, __fmul_rn(w4[3], newv[k]));
+            const float act = silu_f(acc);
+            if (idx < ROWS) xs_s[idx] = act;
+            else if (idx < ROWS + N) B_s[(idx - ROWS) + ((idx - ROWS) >> 4) * 4] = act;
+            else C_s[(idx - ROWS - N) + ((idx - ROWS - N) >> 4) * 4] = act;
+            // the newest input replaces the oldest slot; nobody reads that slot during this step
+            if (idx < ROWS || hh == 0) ring[(size_t)cch[k] * 4 + slot] = newv[k];
+        }
     }
     __syncthreads();
 
@@ -110,8 +138,8 @@ mamba2_ssu_kernel(const float* __restrict__ zx, float* __restrict__ state, const
         float ysum = 0.0f;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const float4 Bv = *reinterpret_cast<const float4*>(B_s + seg * 16 + q * 4);
-            const float4 Cv = *reinterpret_cast<const float4*>(C_s + seg * 16 + q * 4);
+            const float4 Bv = *reinterpret_cast<const float4*>(B_s + seg * 20 + q * 4);
+            const float4 Cv = *reinterpret_cast<const float4*>(C_s + seg * 20 + q * 4);
             float4 s4 = st[rr][q];
             s4.x = __fadd_rn(__fmul_rn(s4.x, dA), __fmul_rn(dtx, Bv.x));
             s4.y = __fadd_rn(__fmul_rn(s4.y, dA), __fmul_rn(dtx, Bv.y));
@@ -152,6 +180,7 @@ int mamba_reserve(Mamba* m, int B) {
 
 int mamba_step(Mamba* m, float* x, float* state, const int* pos, int B) {
     LSPK_REQUIRE(m && x && state && pos && B >= 1, "mamba_step: bad arguments");
+    LSPK_REQUIRE((reinterpret_cast<uintptr_t>(state) & 15) == 0, "mamba_step: the state buffer must be 16-byte aligned");
     if (int rc = mamba_reserve(m, B)) return rc;
     lspk_linear_args a = {};
     a.w[0] = m->in_proj;
