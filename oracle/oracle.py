@@ -388,7 +388,7 @@ def forward_hidden(kern: Kernels, model, state: State, token_ids, trace: Optiona
     """Layer loop for T >= 1 tokens starting at state.pos; returns the post-final-norm hidden
     rows [T, H] and advances state.pos.  Row by row this is the reference's decode step
     (torchless/runtime.py:171-282); for T > 1 it is its batched prefill (:285-436), which the
-    reference documents (and the survey confirmed) to be identical per row.  Layers without sub-norms are the
+    reference documents to be identical per row (its fixtures agree).  Layers without sub-norms are the
     Falcon-E family (falcon_forward_one, runtime.py:735-817): the attention output and the gated product
     are quantised as they are, and the gate is SiLU."""
     c = model.config
